@@ -1,0 +1,615 @@
+// fp32 GEMM for B200 (sm_100a): TMA-staged 128-byte-swizzled tiles, tcgen05.mma kind::tf32
+// accumulating in tensor memory, persistent CTAs with warp-specialised roles.
+//
+//   warp 0 (one thread)  : TMA producer, fills a ring of STAGES shared-memory stages
+//   warp 1 (one thread)  : MMA issuer; owns the TMEM allocation (two accumulators, ping-pong)
+//   warps 2..5           : epilogue, TMEM -> registers -> global (bias / accumulate / split-K sum)
+//
+// Replaces the per-batch cublasSgemm loops of the reference (src/matmul_kernel.cu:111-143 forward,
+// :347-402 the two backward products) and, through the `red` batch dim, the unreduced
+// weight-gradient product plus sum_axis passes of src/bindings.cpp:1750-1758, 1467-1503.
+//
+// Operand layouts: each operand may be K-major or M/N-major in global memory; the tile is staged
+// the way it lies and the UMMA descriptors carry the major-ness, so transposed views need no copy.
+// TF32 mode issues one MMA per 8-deep k-slice; 3xTF32 mode issues three (lo*hi, hi*lo, hi*hi) on
+// pre-split operands, giving fp32-level accuracy.
+#include "gemm_sm100.h"
+#include "sm100_ptx.cuh"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace akr {
+
+namespace {
+
+constexpr int BM = 128;        // rows of D per CTA tile (UMMA M, one TMEM lane per row)
+constexpr int BK = 32;         // fp32 per k-block: 128 bytes, one swizzle row
+constexpr int UMMA_K = 8;      // k per tcgen05.mma kind::tf32
+constexpr int CHUNK = 32;      // M/N elements per 128-byte row of an MN-major tile
+constexpr int GROUP_M = 16;    // tile rasterisation: m-tiles per group (L2 reuse of B panels)
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
+
+struct KernelParams {
+    CUtensorMap tmA, tmB, tmAlo, tmBlo;
+    float* C;
+    const float* bias;
+    float* partials;
+    int* counters;
+    int* status;
+    long long ldc, c_bs0, c_bs1;
+    int M, N, K;
+    int o0, o1, red, splits;
+    int a_mul[3], b_mul[3];  // 1 when the operand varies along (o0, o1, r), 0 when broadcast
+    int accumulate, vec_ok;
+    int mt, nt, nkb, total_tiles;
+};
+
+struct Tile {
+    int split, batch, i0, i1, m0, n0;
+};
+
+__device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn) {
+    Tile c;
+    c.split = t % p.splits;
+    t /= p.splits;
+    const int per_batch = p.mt * p.nt;
+    c.batch = t / per_batch;
+    const int r = t - c.batch * per_batch;
+    c.i0 = c.batch / p.o1;
+    c.i1 = c.batch - c.i0 * p.o1;
+    const int group_sz = GROUP_M * p.nt;
+    const int g = r / group_sz;
+    const int first_m = g * GROUP_M;
+    const int gm = min(p.mt - first_m, GROUP_M);
+    const int in = r - g * group_sz;
+    const int n_t = in / gm;
+    const int m_t = first_m + (in - n_t * gm);
+    c.m0 = m_t * BM;
+    c.n0 = n_t * bn;
+    return c;
+}
+
+template <int BN, int TERMS>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = (TERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
+};
+
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
+    using L = SmemLayout<BN, TERMS>;
+    constexpr int TMEM_COLS = 2 * BN;  // two accumulators
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+    const uint32_t bar_base = smem_base + STAGES * L::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), 4);
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+        if (TERMS == 3) {
+            ptx::prefetch_tensormap(&p.tmAlo);
+            ptx::prefetch_tensormap(&p.tmBlo);
+        }
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<TMEM_COLS>(ptx::smem_u32(tmem_slot));
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_iters = p.red * p.nkb;  // contraction steps of one output tile
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                const Tile c = decode_tile(t, p, BN);
+                const int it0 = (int)((long long)total_iters * c.split / p.splits);
+                const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
+                for (int it = it0; it < it1; ++it) {
+                    const int r = it / p.nkb;
+                    const int k0 = (it - r * p.nkb) * BK;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = full_bar(stage);
+                    ptx::mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
+                    const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+                    const uint32_t sb = sa + L::A_BYTES;
+                    const int a1 = c.i1 * p.a_mul[1], a0 = c.i0 * p.a_mul[0], ar = r * p.a_mul[2];
+                    const int b1 = c.i1 * p.b_mul[1], b0 = c.i0 * p.b_mul[0], br = r * p.b_mul[2];
+#pragma unroll
+                    for (int term = 0; term < (TERMS == 3 ? 2 : 1); ++term) {
+                        const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
+                        const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
+                        const uint32_t da = sa + term * (L::A_BYTES + L::B_BYTES);
+                        const uint32_t db = sb + term * (L::A_BYTES + L::B_BYTES);
+                        if (MAJA == 0) {
+                            ptx::tma_load_5d(da, ma, fb, k0, c.m0, a1, a0, ar);
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < BM / CHUNK; ++ch)
+                                ptx::tma_load_5d(da + ch * (BK * 128), ma, fb, c.m0 + ch * CHUNK, k0,
+                                                 a1, a0, ar);
+                        }
+                        if (MAJB == 0) {
+                            ptx::tma_load_5d(db, mb, fb, k0, c.n0, b1, b0, br);
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < BN / CHUNK; ++ch)
+                                ptx::tma_load_5d(db + ch * (BK * 128), mb, fb, c.n0 + ch * CHUNK, k0,
+                                                 b1, b0, br);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // Gave up: let the copies still in flight land before the CTA tears down.
+                int s = stage;
+                uint32_t ph = phase;
+                const int n = issued < STAGES ? (int)issued : STAGES;
+                for (int i = 0; i < n; ++i) {
+                    if (--s < 0) {
+                        s = STAGES - 1;
+                        ph ^= 1u;
+                    }
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (!ptx::mbar_try_wait(full_bar(s), ph)) {
+                        if (ptx::globaltimer_ns() - t0 > 200000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BN, MAJA, MAJB);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+                const Tile c = decode_tile(t, p, BN);
+                const int it0 = (int)((long long)total_iters * c.split / p.splits);
+                const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int it = it0; it < it1; ++it) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+                    const uint32_t sb = sa + L::A_BYTES;
+                    const uint32_t sa_lo = sa + L::A_BYTES + L::B_BYTES;
+                    const uint32_t sb_lo = sb + L::A_BYTES + L::B_BYTES;
+#pragma unroll
+                    for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                        // K-major: step 32 bytes inside the 128-byte swizzle row.
+                        // MN-major: step 8 k-rows (two 4-row swizzle groups, 8 * 128 bytes).
+                        const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                        const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                        const uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128;
+                        const uint32_t b_lbo = MAJB == 0 ? 16 : BK * 128;
+                        const uint32_t a_sbo = MAJA == 0 ? 1024 : 512;
+                        const uint32_t b_sbo = MAJB == 0 ? 1024 : 512;
+                        constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+                        constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+                        const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
+                        const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                        const uint32_t first = (it == it0 && k8 == 0) ? 0u : 1u;
+                        if (TERMS == 3) {
+                            const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32_ss(d_tmem, da_lo, db, IDESC, first);
+                            ptx::mma_tf32_ss(d_tmem, da, db_lo, IDESC, 1u);
+                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 1u);
+                        } else {
+                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, first);
+                        }
+                    }
+                    ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs finish
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit(tfull_bar(buf));  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        const int nbatch = p.o0 * p.o1;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+            const Tile c = decode_tile(t, p, BN);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1u;
+            if (!ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const int row = c.m0 + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const bool split_mode = p.splits > 1;
+            float* out_row;
+            bool vec;
+            if (split_mode) {
+                out_row = p.partials +
+                          (((size_t)c.split * nbatch + c.batch) * p.M + (size_t)(row_ok ? row : 0)) *
+                              (size_t)p.N;
+                vec = (p.N & 3) == 0;
+            } else {
+                out_row = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)(row_ok ? row : 0) * p.ldc;
+                vec = p.vec_ok != 0;
+            }
+            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int col0 = c.n0 + ch * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                __syncwarp();            // tcgen05.ld needs the whole warp converged
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                ptx::tmem_ld_wait();
+                if (!row_ok) continue;
+                float* dst = out_row + col0;
+                const bool full = col0 + 32 <= p.N;
+                if (!split_mode) {
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (full || col0 + j < p.N)
+                                v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col0 + j));
+                    }
+                    if (p.accumulate) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (full || col0 + j < p.N)
+                                v[j] = __float_as_uint(__uint_as_float(v[j]) + dst[j]);
+                    }
+                }
+                if (full && vec) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                               __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        *reinterpret_cast<float4*>(dst + j) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) dst[j] = __uint_as_float(v[j]);
+                }
+            }
+            // Accumulator drained: hand the TMEM buffer back to the MMA warp.
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+
+            if (split_mode) {
+                // Last CTA to finish this tile adds the partials in split order (deterministic).
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int tile_id = (t / p.splits);
+                if (threadIdx.x == 64) {
+                    const int prev = atomicAdd(p.counters + tile_id, 1);
+                    const int last = (prev == p.splits - 1) ? 1 : 0;
+                    if (last) p.counters[tile_id] = 0;  // self-cleaning for the next launch
+                    *last_flag = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int is_last = *last_flag;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (is_last && row_ok) {
+                    __threadfence();
+                    float* crow = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)row * p.ldc;
+                    const size_t split_stride = (size_t)nbatch * p.M * p.N;
+                    const float* prow = p.partials + ((size_t)c.batch * p.M + row) * (size_t)p.N;
+                    const int ncols = min(BN, p.N - c.n0);
+                    for (int j = 0; j < ncols; ++j) {
+                        const int col = c.n0 + j;
+                        float acc = 0.f;
+                        for (int s = 0; s < p.splits; ++s)
+                            acc += __ldcg(prow + (size_t)s * split_stride + col);
+                        if (p.bias != nullptr) acc += __ldg(p.bias + col);
+                        if (p.accumulate) acc += crow[col];
+                        crow[col] = acc;
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown (all paths)
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+// ---------------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+void seterr(char* err, int errlen, const char* msg) {
+    if (err && errlen > 0) {
+        std::strncpy(err, msg, errlen - 1);
+        err[errlen - 1] = 0;
+    }
+}
+
+// Rank-5 map over (unit-stride matrix dim, other matrix dim, o1, o0, r).
+bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, int mn, int k,
+              const int batch[3], int tile_mn) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return false;
+    const int e_o0 = op.bs[0] != 0 ? batch[0] : 1;
+    const int e_o1 = op.bs[1] != 0 ? batch[1] : 1;
+    const int e_r = op.bs[2] != 0 ? batch[2] : 1;
+    const uint64_t d0 = op.mn_major ? mn : k;
+    const uint64_t d1 = op.mn_major ? k : mn;
+    // Stride of a dim of extent 1 is never used for addressing; it only has to be well-formed.
+    const uint64_t ld_b = (uint64_t)(d1 > 1 ? op.ld : ((d0 + 3) / 4) * 4) * 4;
+    auto bstride = [&](int e, int64_t s) { return (uint64_t)(e > 1 ? s * 4 : (int64_t)ld_b); };
+    cuuint64_t dims[5] = {d0, d1, (cuuint64_t)e_o1, (cuuint64_t)e_o0, (cuuint64_t)e_r};
+    cuuint64_t strides[4] = {ld_b, bstride(e_o1, op.bs[1]), bstride(e_o0, op.bs[0]),
+                             bstride(e_r, op.bs[2])};
+    cuuint32_t box[5] = {32u, (cuuint32_t)(op.mn_major ? BK : tile_mn), 1u, 1u, 1u};
+    cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES>
+int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
+    using L = SmemLayout<BN, TERMS>;
+    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256;
+    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES>;
+    static bool attr_done = false;  // per instantiation
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            seterr(err, errlen, cudaGetErrorString(e));
+            return -3;
+        }
+        attr_done = true;
+    }
+    kern<<<grid, NUM_THREADS, smem, stream>>>(kp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        seterr(err, errlen, cudaGetErrorString(e));
+        return -3;
+    }
+    return 0;
+}
+
+template <int BN, int TERMS, int STAGES>
+int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream_t s, char* err,
+                 int errlen) {
+    const int key = g.A.mn_major * 2 + g.B.mn_major;
+    switch (key) {
+        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES>(kp, grid, s, err, errlen);
+        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES>(kp, grid, s, err, errlen);
+        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES>(kp, grid, s, err, errlen);
+        default: return launch_variant<BN, 1, 1, TERMS, STAGES>(kp, grid, s, err, errlen);
+    }
+}
+
+int pick_bn(const GemmDesc& g) {
+    // Wide tiles when there is enough work to fill the machine with them, else narrow ones.
+    if (g.N <= 128) return 128;
+    const long long tiles256 = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + 255) / 256);
+    return tiles256 >= gemm_sm100_num_ctas() ? 256 : 128;
+}
+
+}  // namespace
+
+int gemm_sm100_num_ctas() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        n = sms;
+    }
+    return n;
+}
+
+bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch[3]) {
+    if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0) return false;
+    if (op.lo && (reinterpret_cast<uintptr_t>(op.lo) & 15u) != 0) return false;
+    const int other = op.mn_major ? k : mn;
+    if (other > 1 && (op.ld <= 0 || (op.ld & 3) != 0)) return false;
+    for (int i = 0; i < 3; ++i) {
+        if (batch[i] > 1 && op.bs[i] != 0 && ((op.bs[i] & 3) != 0 || op.bs[i] < 0)) return false;
+    }
+    return true;
+}
+
+int gemm_sm100_pick_splits(const GemmDesc& g) {
+    const int bn = g.N <= 128 ? 128 : 256;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
+    const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
+    const int ctas = gemm_sm100_num_ctas();
+    if (tiles * 2 > ctas || iters < 64) return 1;
+    long long s = ctas / tiles;
+    const long long max_by_work = iters / 16;  // keep at least 16 k-blocks per split
+    if (s > max_by_work) s = max_by_work;
+    if (s > 64) s = 64;
+    return s < 1 ? 1 : (int)s;
+}
+
+void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* counter_count) {
+    const int bn = pick_bn(g);
+    const size_t tiles = (size_t)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
+    *partial_bytes = g.splits > 1 ? (size_t)g.splits * g.o0 * g.o1 * g.M * g.N * sizeof(float) : 0;
+    *counter_count = g.splits > 1 ? tiles : 0;
+}
+
+int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, char* err,
+                      int errlen) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0 || g.o0 <= 0 || g.o1 <= 0 || g.red <= 0) {
+        seterr(err, errlen, "gemm_sm100: empty problem");
+        return -1;
+    }
+    const int batch[3] = {g.o0, g.o1, g.red};
+    if (!gemm_sm100_operand_ok(g.A, g.M, g.K, batch) || !gemm_sm100_operand_ok(g.B, g.N, g.K, batch)) {
+        seterr(err, errlen, "gemm_sm100: operand not readable by TMA (alignment / stride)");
+        return -1;
+    }
+    if (g.terms == 3 && (!g.A.lo || !g.B.lo)) {
+        seterr(err, errlen, "gemm_sm100: 3xTF32 needs split operands");
+        return -1;
+    }
+    if (g.splits > 1 && (!g.partials || !g.counters)) {
+        seterr(err, errlen, "gemm_sm100: split launch without scratch");
+        return -1;
+    }
+    const int bn = pick_bn(g);
+
+    KernelParams kp;
+    std::memset(&kp, 0, sizeof(kp));
+    if (!make_map(&kp.tmA, g.A.ptr, g.A, g.M, g.K, batch, BM) ||
+        !make_map(&kp.tmB, g.B.ptr, g.B, g.N, g.K, batch, bn)) {
+        seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
+        return -2;
+    }
+    if (g.terms == 3) {
+        if (!make_map(&kp.tmAlo, g.A.lo, g.A, g.M, g.K, batch, BM) ||
+            !make_map(&kp.tmBlo, g.B.lo, g.B, g.N, g.K, batch, bn)) {
+            seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed (lo)");
+            return -2;
+        }
+    }
+    kp.C = g.C;
+    kp.bias = g.bias;
+    kp.partials = g.partials;
+    kp.counters = g.counters;
+    kp.status = status_dev;
+    kp.ldc = g.ldc;
+    kp.c_bs0 = g.c_bs0;
+    kp.c_bs1 = g.c_bs1;
+    kp.M = g.M;
+    kp.N = g.N;
+    kp.K = g.K;
+    kp.o0 = g.o0;
+    kp.o1 = g.o1;
+    kp.red = g.red;
+    kp.splits = g.splits < 1 ? 1 : g.splits;
+    for (int i = 0; i < 3; ++i) {
+        kp.a_mul[i] = (g.A.bs[i] != 0 && batch[i] > 1) ? 1 : 0;
+        kp.b_mul[i] = (g.B.bs[i] != 0 && batch[i] > 1) ? 1 : 0;
+    }
+    kp.accumulate = g.accumulate;
+    kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 &&
+                 (g.o0 == 1 || (g.c_bs0 & 3) == 0) && (g.o1 == 1 || (g.c_bs1 & 3) == 0))
+                    ? 1
+                    : 0;
+    kp.mt = (g.M + BM - 1) / BM;
+    kp.nt = (g.N + bn - 1) / bn;
+    kp.nkb = (g.K + BK - 1) / BK;
+    const long long total = (long long)g.o0 * g.o1 * kp.mt * kp.nt * kp.splits;
+    if (total > 0x7fffffffLL) {
+        seterr(err, errlen, "gemm_sm100: too many tiles");
+        return -1;
+    }
+    if ((long long)kp.red * kp.nkb < kp.splits) {
+        seterr(err, errlen, "gemm_sm100: more splits than contraction steps");
+        return -1;
+    }
+    kp.total_tiles = (int)total;
+    const int ctas = gemm_sm100_num_ctas();
+    const int grid = (int)(total < ctas ? total : ctas);
+
+    if (g.terms == 3) {
+        if (bn == 256) return launch_major<256, 3, 2>(g, kp, grid, stream, err, errlen);
+        return launch_major<128, 3, 3>(g, kp, grid, stream, err, errlen);
+    }
+    if (bn == 256) return launch_major<256, 1, 4>(g, kp, grid, stream, err, errlen);
+    return launch_major<128, 1, 6>(g, kp, grid, stream, err, errlen);
+}
+
+}  // namespace akr

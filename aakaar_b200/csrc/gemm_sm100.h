@@ -1,0 +1,58 @@
+// Host-side description of one batched fp32 GEMM for the sm_100a tcgen05 kernels.
+//
+//   D[o0, o1, m, n] (+)= sum_r sum_k A[o0, o1, r, m, k] * B[o0, o1, r, k, n]  (+ bias[n])
+//
+// o0/o1 are output batch dims, r is a batch dim that is summed away (the broadcast-batch
+// reduction of a weight gradient). An operand that does not vary along a batch dim has
+// stride 0 there. Either matrix dim of an operand may be the unit-stride one: the kernels read
+// transposed views in place.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace akr {
+
+struct GemmOperand {
+    const float* ptr = nullptr;  // first element of the view
+    const float* lo = nullptr;   // 3xTF32 only: low parts, same geometry as ptr
+    int mn_major = 0;            // 1: the M (for A) / N (for B) index is unit stride; 0: K is
+    int64_t ld = 0;              // element stride of the other matrix dim
+    int64_t bs[3] = {0, 0, 0};   // element strides along o0, o1, r (0 = broadcast)
+};
+
+struct GemmDesc {
+    int M = 0, N = 0, K = 0;
+    int o0 = 1, o1 = 1, red = 1;  // batch extents
+    GemmOperand A, B;
+    float* C = nullptr;
+    int64_t ldc = 0, c_bs0 = 0, c_bs1 = 0;
+    const float* bias = nullptr;  // optional row vector of N values added to every row
+    int accumulate = 0;           // 1: C += result
+    int terms = 1;                // 1 = TF32, 3 = 3xTF32 (needs A.lo and B.lo)
+    // Split of the contraction across CTAs (weight gradients with few output tiles):
+    // splits > 1 writes fp32 partials to `partials` ([splits][o0*o1][M][N]) and the last CTA
+    // to finish a tile adds them up in split order. `counters` holds one int per output tile.
+    int splits = 1;
+    float* partials = nullptr;
+    int* counters = nullptr;
+};
+
+// True when the operand can be read by TMA as it lies (16-byte aligned base, unit stride on one
+// matrix dim, every other stride a multiple of 4 elements).
+bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch[3]);
+
+// Enqueue on `stream`. `status_dev` points at one device int that the kernel sets non-zero when a
+// bounded wait ran out. Returns 0, or a negative akr status with the message in `err`.
+int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, char* err,
+                      int errlen);
+
+// Number of CTAs the persistent kernels are launched with on the current device.
+int gemm_sm100_num_ctas();
+
+// Bytes of `partials` and number of `counters` entries a split launch needs.
+void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* counter_count);
+
+// Picks a split factor for `g` (1 when the output already fills the GPU).
+int gemm_sm100_pick_splits(const GemmDesc& g);
+
+}  // namespace akr

@@ -1,0 +1,226 @@
+"""CPU restatement of the reference's fp32 matmul path (forward + autograd backward).
+
+TEST INFRASTRUCTURE ONLY. Nothing in the product package imports this module; it is the checker
+used by tests/, by ``__graft_entry__.smoke()`` and by the ``cpu_baseline`` / ``--impl reference``
+legs of bench.py. The product path is CUDA-only and fails loudly without its extension.
+
+Every function follows one piece of the reference (paths relative to the reference checkout):
+
+* ``plan_nd_matmul`` / ``batch_offset``  - src/matmul_kernel.cu:55-109 (CUDA planner, the one with the
+  explicit rank check) and the equivalent lambdas in src/cpu_kernel.cpp:102-138.
+* ``matmul_forward``                     - src/cpu_kernel.cpp:98-153 (one row-major sgemm per
+  broadcast batch index, contiguous operands only).
+* ``matmul_a_bt`` / ``matmul_at_b``      - src/cpu_kernel.cpp:1674-1691 (2-D backward products).
+* ``matmul_backward``                    - the backward lambda of dispatch_matmul,
+  src/bindings.cpp:1726-1759 (2-D fast path, otherwise transposed copies + forward + reduction).
+* ``reduce_grad_to_shape``               - src/bindings.cpp:1467-1503.
+* ``linear_forward``                     - aakaar/nn.py:5-18 (y = x @ W + b, W stored (in, out)).
+* ``tanh`` / ``mse_loss`` / ``sgd_step`` - src/cpu_kernel.cpp:484-514, aakaar/__init__.py:222-224,
+  src/optim_kernels_cpu.cpp:7-28 (support ops of the Linear training step).
+
+The arithmetic of the reference lives in OpenBLAS ``cblas_sgemm`` (third party, version not pinned
+by the reference; the build in oracle/_ref links OpenBLAS 0.3.15). Here the same products are
+numpy float32 ``@`` (also an sgemm) or float64 for a stricter check; both differ from the
+reference only in summation order, so parity is stated as relative Frobenius error, not bitwise.
+
+Pinning: tests/test_oracle.py checks this module against (a) the documentation examples the
+reference ships (docs/concepts/math-operations/matmul.md:36-57, docs/getting-started/
+quick-start.md:57-73) and (b) vectors produced by the reference's own CPU build
+(oracle/build_ref.sh -> oracle/_ref), committed under tests/golden/.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+__all__ = [
+    "plan_nd_matmul",
+    "batch_offset",
+    "matmul_forward",
+    "matmul_a_bt",
+    "matmul_at_b",
+    "matmul_backward",
+    "reduce_grad_to_shape",
+    "linear_forward",
+    "tanh",
+    "tanh_backward",
+    "mse_loss",
+    "sgd_step",
+    "mlp_step",
+    "rel_frobenius",
+]
+
+
+def rel_frobenius(x, ref) -> float:
+    """||x - ref||_F / ||ref||_F in float64."""
+    x = np.asarray(x, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    den = np.linalg.norm(ref.ravel())
+    num = np.linalg.norm((x - ref).ravel())
+    return float(num / den) if den > 0 else float(num)
+
+
+def plan_nd_matmul(shape_a, shape_b):
+    """Right-aligned broadcast of the batch dims; returns (batch_shape, M, K, N).
+
+    Raises ValueError with the reference's messages (src/matmul_kernel.cu:56-70).
+    """
+    shape_a = tuple(int(d) for d in shape_a)
+    shape_b = tuple(int(d) for d in shape_b)
+    if len(shape_a) < 2 or len(shape_b) < 2:
+        raise ValueError("matmul requires tensors with at least 2 dimensions")
+    M, K = shape_a[-2], shape_a[-1]
+    K2, N = shape_b[-2], shape_b[-1]
+    if K != K2:
+        raise ValueError("Shape mismatch: inner dimensions must match for matmul")
+    ba, bb = shape_a[:-2], shape_b[:-2]
+    ndb = max(len(ba), len(bb))
+    out = [0] * ndb
+    for i in range(ndb):
+        da = ba[len(ba) - 1 - i] if i < len(ba) else 1
+        db = bb[len(bb) - 1 - i] if i < len(bb) else 1
+        if da != db and da != 1 and db != 1:
+            raise ValueError("Batch dimensions are not broadcastable for matmul")
+        out[ndb - 1 - i] = max(da, db)
+    return tuple(out), M, K, N
+
+
+def batch_offset(flat_idx, out_batch, in_shape, mat_size):
+    """Element offset of batch `flat_idx` inside a contiguous operand; size-1 dims map to 0."""
+    in_batch = tuple(in_shape[:-2])
+    ndb, nd_in = len(out_batch), len(in_batch)
+    idx = [0] * ndb
+    rem = flat_idx
+    for i in range(ndb - 1, -1, -1):
+        idx[i] = rem % out_batch[i]
+        rem //= out_batch[i]
+    off, stride = 0, mat_size
+    for i in range(ndb - 1, -1, -1):
+        in_i = i - (ndb - nd_in)
+        in_dim = in_batch[in_i] if in_i >= 0 else 1
+        use = 0 if in_dim == 1 else idx[i]
+        if in_i >= 0:
+            off += use * stride
+            stride *= in_dim
+    return off
+
+
+def _require_contiguous(x, what):
+    if not x.flags["C_CONTIGUOUS"]:
+        raise ValueError(what)
+
+
+def matmul_forward(a, b, acc=np.float32):
+    """C[bi] = A[offA(bi)] @ B[offB(bi)] for every broadcast batch index bi."""
+    a = np.asarray(a)
+    b = np.asarray(b)
+    _require_contiguous(a, "matmul requires contiguous tensors. Call .contiguous() first.")
+    _require_contiguous(b, "matmul requires contiguous tensors. Call .contiguous() first.")
+    batch, M, K, N = plan_nd_matmul(a.shape, b.shape)
+    total = int(np.prod(batch)) if batch else 1
+    out = np.empty(tuple(batch) + (M, N), dtype=np.float32)
+    af, bf, of = a.reshape(-1), b.reshape(-1), out.reshape(-1)
+    for bi in range(total):
+        oa = batch_offset(bi, batch, a.shape, M * K)
+        ob = batch_offset(bi, batch, b.shape, K * N)
+        am = af[oa:oa + M * K].reshape(M, K).astype(acc, copy=False)
+        bm = bf[ob:ob + K * N].reshape(K, N).astype(acc, copy=False)
+        of[bi * M * N:(bi + 1) * M * N] = (am @ bm).astype(np.float32).reshape(-1)
+    return out
+
+
+def matmul_a_bt(a, b, acc=np.float32):
+    """C(m,n) = A(m,k) @ B(n,k)^T, B in its original (n,k) layout."""
+    _require_contiguous(a, "matmul_a_bt requires contiguous tensors.")
+    _require_contiguous(b, "matmul_a_bt requires contiguous tensors.")
+    return (a.astype(acc, copy=False) @ b.astype(acc, copy=False).T).astype(np.float32)
+
+
+def matmul_at_b(a, b, acc=np.float32):
+    """C(m,n) = A(k,m)^T @ B(k,n), A in its original (k,m) layout."""
+    _require_contiguous(a, "matmul_at_b requires contiguous tensors.")
+    _require_contiguous(b, "matmul_at_b requires contiguous tensors.")
+    return (a.astype(acc, copy=False).T @ b.astype(acc, copy=False)).astype(np.float32)
+
+
+def reduce_grad_to_shape(grad, target_shape, skip_trailing=0, acc=np.float32):
+    """Sum a broadcast gradient back to `target_shape`.
+
+    Leading extra dims are summed away (axis 0, repeatedly, keepdim=False); then every aligned dim
+    where the target is 1 and the gradient is not is summed with keepdim=True. The last
+    `skip_trailing` dims are never touched.
+    """
+    g = np.asarray(grad)
+    target_shape = tuple(target_shape)
+    if g.ndim < len(target_shape):
+        raise RuntimeError("reduce_grad_to_shape: gradient has fewer dims than its target shape")
+    for _ in range(g.ndim - len(target_shape)):
+        g = g.astype(acc, copy=False).sum(axis=0).astype(np.float32)
+    for i in range(len(target_shape) - skip_trailing):
+        if i >= g.ndim:
+            break
+        if target_shape[i] == 1 and g.shape[i] != 1:
+            g = g.astype(acc, copy=False).sum(axis=i, keepdims=True).astype(np.float32)
+    if skip_trailing == 0 and g.shape != target_shape:
+        raise RuntimeError("reduce_grad_to_shape: reduced gradient shape does not match target shape")
+    return g
+
+
+def matmul_backward(a, b, grad_out, acc=np.float32):
+    """(dA, dB) for C = A @ B given dC. Both are always computed, as the reference does."""
+    a, b, grad_out = np.asarray(a), np.asarray(b), np.asarray(grad_out)
+    if a.ndim == 2 and b.ndim == 2 and grad_out.ndim == 2:
+        return matmul_a_bt(grad_out, b, acc), matmul_at_b(a, grad_out, acc)
+    bT = np.ascontiguousarray(np.swapaxes(b, -1, -2))
+    aT = np.ascontiguousarray(np.swapaxes(a, -1, -2))
+    da_full = matmul_forward(grad_out, bT, acc)
+    db_full = matmul_forward(aT, grad_out, acc)
+    return (reduce_grad_to_shape(da_full, a.shape, 2, acc),
+            reduce_grad_to_shape(db_full, b.shape, 2, acc))
+
+
+# ---------------------------------------------------------------- Linear training step support
+
+def linear_forward(x, w, bias, acc=np.float32):
+    """y = x @ W + b with W (in, out) and b (1, out)."""
+    y = matmul_forward(np.ascontiguousarray(x), np.ascontiguousarray(w), acc)
+    return (y + bias).astype(np.float32) if bias is not None else y
+
+
+def tanh(x):
+    return np.tanh(x.astype(np.float32))
+
+
+def tanh_backward(grad, out):
+    return (grad * (1.0 - out * out)).astype(np.float32)
+
+
+def mse_loss(pred, target):
+    """sum((p - t)^2) / n, composed as sub, mul, sum_all, div like aakaar.mse_loss."""
+    d = (pred - target).astype(np.float32)
+    return np.float32((d * d).astype(np.float32).sum(dtype=np.float32) / np.float32(d.size))
+
+
+def sgd_step(param, grad, lr):
+    """Plain SGD (no momentum / weight decay): p -= lr * g."""
+    return (param - np.float32(lr) * grad).astype(np.float32)
+
+
+def mlp_step(x, target, w1, b1, w2, b2, lr, acc=np.float32):
+    """One Linear -> tanh -> Linear -> MSE -> backward -> SGD step.
+
+    Returns (loss, (w1', b1', w2', b2'), grads dict). Gradient flow follows the reference's
+    autograd: matmul node backward, bias gradient = sum over rows (keepdim), tanh' = 1 - t^2.
+    """
+    z1 = linear_forward(x, w1, b1, acc)
+    h = tanh(z1)
+    y = linear_forward(h, w2, b2, acc)
+    loss = mse_loss(y, target)
+    n = np.float32(y.size)
+    dy = (np.float32(2.0) * (y - target) / n).astype(np.float32)
+    dh, dw2 = matmul_backward(h, w2, dy, acc)
+    db2 = reduce_grad_to_shape(dy, b2.shape, 0, acc)
+    dz1 = tanh_backward(dh, h)
+    _, dw1 = matmul_backward(x, w1, dz1, acc)
+    db1 = reduce_grad_to_shape(dz1, b1.shape, 0, acc)
+    new = (sgd_step(w1, dw1, lr), sgd_step(b1, db1, lr), sgd_step(w2, dw2, lr), sgd_step(b2, db2, lr))
+    return loss, new, {"w1": dw1, "b1": db1, "w2": dw2, "b2": db2, "y": y}
