@@ -1,0 +1,212 @@
+"""ctypes binding of the C ABI (``include/akr_b200.h``) - the same entry points the pybind11
+module calls, reachable without it. Used by the parity tests and the benchmark to drive the
+library exactly as a foreign-language host would: raw device pointers, shapes and strides.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libakr_b200.so")
+
+AKR_MAX_DIMS = 8
+MODE_GLOBAL, MODE_FP32, MODE_TF32 = -1, 0, 1
+OK, ERR_INVALID, ERR_RUNTIME, ERR_CUDA, ERR_NOGPU, ERR_ABORTED = 0, -1, -2, -3, -4, -5
+
+
+class View(C.Structure):
+    _fields_ = [
+        ("data", C.c_void_p),
+        ("ndim", C.c_int32),
+        ("dtype", C.c_int32),
+        ("shape", C.c_int64 * AKR_MAX_DIMS),
+        ("stride", C.c_int64 * AKR_MAX_DIMS),
+    ]
+
+
+class AkrError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"[akr {code}] {msg}")
+        self.code = code
+        self.msg = msg
+
+
+def load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(f"{_LIB_PATH} is not built: run `python -m aakaar_b200._build`")
+    lib = C.CDLL(_LIB_PATH)
+    lib.akr_last_error.restype = C.c_char_p
+    lib.akr_launch_count.restype = C.c_int64
+    vp, sz, fp = C.c_void_p, C.c_size_t, C.POINTER(C.c_float)
+    V = C.POINTER(View)
+    sigs = {
+        "akr_alloc": [sz, C.POINTER(fp)],
+        "akr_free": [fp, sz],
+        "akr_host_alloc": [sz, C.POINTER(vp)],
+        "akr_host_free": [vp],
+        "akr_memcpy_h2d": [vp, vp, sz, vp],
+        "akr_memcpy_d2h": [vp, vp, sz, vp],
+        "akr_memcpy_d2d": [vp, vp, sz, vp],
+        "akr_memset_zero": [vp, sz, vp],
+        "akr_stream_synchronize": [vp],
+        "akr_matmul_plan": [V, V, C.POINTER(C.c_int64), C.POINTER(C.c_int32)],
+        "akr_matmul_fwd": [V, V, V, V, C.c_int, vp],
+        "akr_matmul_bwd": [V, V, V, V, V, C.c_int, vp],
+        "akr_matmul_a_bt": [V, V, V, C.c_int, vp],
+        "akr_matmul_at_b": [V, V, V, C.c_int, vp],
+        "akr_matmul_fwd_simt": [V, V, V, vp],
+        "akr_workspace_bytes": [C.POINTER(sz)],
+        "akr_launch_count": [C.c_int],
+        "akr_allocator_stats": [C.POINTER(C.c_int64), C.POINTER(C.c_int64)],
+        "akr_contiguous": [V, fp, vp],
+        "akr_add": [V, V, V, vp],
+        "akr_sum_to": [V, V, vp],
+        "akr_scale": [fp, C.c_float, fp, sz, vp],
+        "akr_fill": [fp, C.c_float, sz, vp],
+        "akr_tanh_fwd": [fp, fp, sz, vp],
+        "akr_tanh_bwd": [fp, fp, fp, sz, vp],
+        "akr_mse_fwd": [fp, fp, fp, sz, vp],
+        "akr_mse_bwd": [fp, fp, fp, fp, sz, vp],
+        "akr_sgd_step": [fp, fp, fp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, sz, vp],
+        "akr_set_tf32": [C.c_int],
+        "akr_set_cudnn_tf32": [C.c_int],
+        "akr_set_device": [C.c_int],
+    }
+    for name, args in sigs.items():
+        getattr(lib, name).argtypes = args
+    lib.akr_set_tf32.restype = None
+    lib.akr_set_cudnn_tf32.restype = None
+    return lib
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = load()
+    return _lib
+
+
+def check(rc):
+    if rc != OK:
+        raise AkrError(rc, lib().akr_last_error().decode())
+
+
+class DeviceArray:
+    """A device buffer from the library's caching allocator plus view metadata (element strides)."""
+
+    def __init__(self, shape, strides=None, ptr=None, offset=0, base=None):
+        self.shape = tuple(int(s) for s in shape)
+        n = int(np.prod(self.shape)) if self.shape else 1
+        if ptr is None:
+            p = C.POINTER(C.c_float)()
+            check(lib().akr_alloc(n, C.byref(p)))
+            self._owned = (p, n)
+            self.ptr = C.cast(p, C.c_void_p).value
+        else:
+            self._owned = None
+            self.ptr = ptr + 4 * offset
+        self.base = base
+        if strides is None:
+            strides, acc = [], 1
+            for d in reversed(self.shape):
+                strides.append(acc)
+                acc *= d
+            strides = tuple(reversed(strides))
+        self.strides = tuple(int(s) for s in strides)
+        self.size = n
+
+    def __del__(self):
+        if getattr(self, "_owned", None) is not None and _lib is not None:
+            p, n = self._owned
+            _lib.akr_free(p, n)
+            self._owned = None
+
+    @classmethod
+    def from_numpy(cls, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.float32)
+        d = cls(arr.shape)
+        check(lib().akr_memcpy_h2d(d.ptr, arr.ctypes.data, arr.nbytes, None))
+        check(lib().akr_stream_synchronize(None))
+        return d
+
+    def view(self):
+        v = View()
+        v.data = self.ptr
+        v.ndim = len(self.shape)
+        v.dtype = 0
+        for i in range(AKR_MAX_DIMS):
+            v.shape[i] = self.shape[i] if i < len(self.shape) else 1
+            v.stride[i] = self.strides[i] if i < len(self.shape) else 0
+        return v
+
+    def transpose(self, d0, d1):
+        sh, st = list(self.shape), list(self.strides)
+        sh[d0], sh[d1] = sh[d1], sh[d0]
+        st[d0], st[d1] = st[d1], st[d0]
+        return DeviceArray(sh, st, ptr=self.ptr, base=self)
+
+    def as_strided(self, shape, strides, offset=0):
+        return DeviceArray(shape, strides, ptr=self.ptr, offset=offset, base=self)
+
+    def to_numpy(self):
+        """Downloads the underlying elements of a CONTIGUOUS array."""
+        assert self._is_contiguous(), "to_numpy needs a contiguous array"
+        out = np.empty(self.shape, dtype=np.float32)
+        check(lib().akr_memcpy_d2h(out.ctypes.data, self.ptr, out.nbytes, None))
+        check(lib().akr_synchronize())
+        return out
+
+    def _is_contiguous(self):
+        acc = 1
+        for d, s in zip(reversed(self.shape), reversed(self.strides)):
+            if d != 1 and s != acc:
+                return False
+            acc *= d
+        return True
+
+
+def plan(a: DeviceArray, b: DeviceArray):
+    shape = (C.c_int64 * (AKR_MAX_DIMS + 2))()
+    nd = C.c_int32(0)
+    va, vb = a.view(), b.view()
+    check(lib().akr_matmul_plan(C.byref(va), C.byref(vb), shape, C.byref(nd)))
+    return tuple(shape[i] for i in range(nd.value))
+
+
+def matmul_fwd(a, b, bias=None, mode=MODE_GLOBAL, out=None):
+    c = out if out is not None else DeviceArray(plan(a, b))
+    va, vb, vc = a.view(), b.view(), c.view()
+    vbias = bias.view() if bias is not None else None
+    check(lib().akr_matmul_fwd(C.byref(va), C.byref(vb), C.byref(vbias) if bias is not None else None,
+                               C.byref(vc), mode, None))
+    return c
+
+
+def matmul_bwd(a, b, dc, mode=MODE_GLOBAL, need_da=True, need_db=True, da=None, db=None):
+    if need_da and da is None:
+        da = DeviceArray(a.shape)
+    if need_db and db is None:
+        db = DeviceArray(b.shape)
+    va, vb, vg = a.view(), b.view(), dc.view()
+    vda = da.view() if need_da else None
+    vdb = db.view() if need_db else None
+    check(lib().akr_matmul_bwd(C.byref(va), C.byref(vb), C.byref(vg),
+                               C.byref(vda) if need_da else None, C.byref(vdb) if need_db else None,
+                               mode, None))
+    return (da if need_da else None), (db if need_db else None)
+
+
+def matmul_simt(a, b):
+    c = DeviceArray(plan(a, b))
+    va, vb, vc = a.view(), b.view(), c.view()
+    check(lib().akr_matmul_fwd_simt(C.byref(va), C.byref(vb), C.byref(vc), None))
+    return c
+
+
+def synchronize():
+    check(lib().akr_synchronize())

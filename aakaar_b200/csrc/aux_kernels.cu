@@ -1,0 +1,472 @@
+// Helper kernels around the GEMM (see aux_kernels.h). All are HBM-bound: grid-stride loops,
+// coalesced along the unit-stride dim, grids sized in multiples of the SM count.
+#include "aux_kernels.h"
+
+#include <cstdint>
+
+namespace akr {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+int grid_for(size_t n, int per_thread = 4) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    size_t blocks = (n + (size_t)kThreads * per_thread - 1) / ((size_t)kThreads * per_thread);
+    const size_t cap = (size_t)sms * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+// Round-to-nearest (ties away from zero) to 10 explicit mantissa bits; the value stays an fp32.
+__device__ __forceinline__ float to_tf32_rna(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+
+struct PackArgs {
+    const float* src;
+    float* hi;
+    float* lo;
+    int nb;
+    int64_t bshape[kMaxDims];
+    int64_t bstride[kMaxDims];
+    int64_t rows, cols, ld;
+    int64_t row_stride, col_stride;
+    int64_t total;  // batch * rows * ld
+};
+
+__global__ void pack_split_kernel(const PackArgs a) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
+        const int64_t c = i % a.ld;
+        int64_t t = i / a.ld;
+        const int64_t r = t % a.rows;
+        t /= a.rows;
+        float v = 0.f;
+        if (c < a.cols) {
+            int64_t off = r * a.row_stride + c * a.col_stride;
+            for (int d = a.nb - 1; d >= 0; --d) {
+                const int64_t idx = t % a.bshape[d];
+                t /= a.bshape[d];
+                off += idx * a.bstride[d];
+            }
+            v = __ldg(a.src + off);
+        }
+        if (a.lo != nullptr) {
+            const float h = to_tf32_rna(v);
+            a.hi[i] = h;
+            a.lo[i] = v - h;
+        } else {
+            a.hi[i] = v;
+        }
+    }
+}
+
+// Contiguous-source fast path of the split: 4 elements per thread, no index decode.
+__global__ void split_vec4_kernel(const float4* __restrict__ src, float4* __restrict__ hi,
+                                  float4* __restrict__ lo, int64_t n4) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = __ldg(src + i);
+        float4 h, l;
+        h.x = to_tf32_rna(v.x); l.x = v.x - h.x;
+        h.y = to_tf32_rna(v.y); l.y = v.y - h.y;
+        h.z = to_tf32_rna(v.z); l.z = v.z - h.z;
+        h.w = to_tf32_rna(v.w); l.w = v.w - h.w;
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+constexpr int ST = 16;  // SIMT reference GEMM tile
+
+__global__ void simt_gemm_kernel(const SimtGemm g) {
+    __shared__ float As[ST][ST + 1];
+    __shared__ float Bs[ST][ST + 1];
+    int64_t t = blockIdx.z;
+    int64_t ao = 0, bo = 0, co = 0;
+    for (int d = g.nb - 1; d >= 0; --d) {
+        const int64_t idx = t % g.bshape[d];
+        t /= g.bshape[d];
+        ao += idx * g.a_bs[d];
+        bo += idx * g.b_bs[d];
+        co += idx * g.c_bs[d];
+    }
+    const int row = blockIdx.y * ST + threadIdx.y;
+    const int col = blockIdx.x * ST + threadIdx.x;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < g.K; k0 += ST) {
+        const int ka = k0 + threadIdx.x;
+        const int kb = k0 + threadIdx.y;
+        As[threadIdx.y][threadIdx.x] =
+            (row < g.M && ka < g.K) ? g.A[ao + (int64_t)row * g.a_rs + (int64_t)ka * g.a_cs] : 0.f;
+        Bs[threadIdx.y][threadIdx.x] =
+            (kb < g.K && col < g.N) ? g.B[bo + (int64_t)kb * g.b_rs + (int64_t)col * g.b_cs] : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < ST; ++k) acc = fmaf(As[threadIdx.y][k], Bs[k][threadIdx.x], acc);
+        __syncthreads();
+    }
+    if (row < g.M && col < g.N) g.C[co + (int64_t)row * g.c_rs + (int64_t)col * g.c_cs] = acc;
+}
+
+struct GatherArgs {
+    const float* src;
+    float* dst;
+    int nd;
+    int64_t shape[kMaxDims];
+    int64_t stride[kMaxDims];
+    int64_t total;
+};
+
+__global__ void gather_kernel(const GatherArgs a) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
+        int64_t t = i, off = 0;
+        for (int d = a.nd - 1; d >= 0; --d) {
+            const int64_t idx = t % a.shape[d];
+            t /= a.shape[d];
+            off += idx * a.stride[d];
+        }
+        a.dst[i] = __ldg(a.src + off);
+    }
+}
+
+struct AddArgs {
+    const float *a, *b;
+    float* out;
+    int nd;
+    int64_t shape[kMaxDims];
+    int64_t as[kMaxDims], bs[kMaxDims];
+    int64_t total;
+};
+
+__global__ void add_kernel(const AddArgs p) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
+        int64_t t = i, ao = 0, bo = 0;
+        for (int d = p.nd - 1; d >= 0; --d) {
+            const int64_t idx = t % p.shape[d];
+            t /= p.shape[d];
+            ao += idx * p.as[d];
+            bo += idx * p.bs[d];
+        }
+        p.out[i] = __ldg(p.a + ao) + __ldg(p.b + bo);
+    }
+}
+
+__global__ void add_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
+                                float4* __restrict__ o, int64_t n4) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 x = __ldg(a + i), y = __ldg(b + i);
+        o[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+}
+
+// Sum over reduced dims. One block per 32 kept-output elements x 8 reduction lanes.
+struct SumArgs {
+    const float* g;
+    float* out;
+    int nk;  // kept dims
+    int nr;  // reduced dims
+    int64_t kshape[kMaxDims], kstride[kMaxDims];
+    int64_t rshape[kMaxDims], rstride[kMaxDims];
+    int64_t nkept, nred;
+};
+
+__global__ void sum_to_kernel(const SumArgs a) {
+    __shared__ float part[8][33];
+    const int64_t o = (int64_t)blockIdx.x * 32 + threadIdx.x;
+    float acc = 0.f;
+    if (o < a.nkept) {
+        int64_t t = o, base = 0;
+        for (int d = a.nk - 1; d >= 0; --d) {
+            const int64_t idx = t % a.kshape[d];
+            t /= a.kshape[d];
+            base += idx * a.kstride[d];
+        }
+        for (int64_t r = threadIdx.y; r < a.nred; r += 8) {
+            int64_t tr = r, off = base;
+            for (int d = a.nr - 1; d >= 0; --d) {
+                const int64_t idx = tr % a.rshape[d];
+                tr /= a.rshape[d];
+                off += idx * a.rstride[d];
+            }
+            acc += __ldg(a.g + off);
+        }
+    }
+    part[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && o < a.nkept) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += part[j][threadIdx.x];
+        a.out[o] = s;
+    }
+}
+
+__global__ void scale_kernel(const float* __restrict__ x, float alpha, float* __restrict__ y, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = x[i] * alpha;
+}
+__global__ void fill_kernel(float* __restrict__ x, float v, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = v;
+}
+__global__ void tanh_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = tanhf(x[i]);
+}
+__global__ void tanh_bwd_kernel(const float* __restrict__ g, const float* __restrict__ y,
+                                float* __restrict__ dx, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float t = y[i];
+        dx[i] = g[i] * (1.0f - t * t);
+    }
+}
+
+__device__ __forceinline__ float block_sum(float v) {
+    __shared__ float warp_part[kThreads / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+    if (threadIdx.x < kThreads / 32) s = warp_part[threadIdx.x];
+    if (threadIdx.x < 32) {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    }
+    return s;  // valid in thread 0
+}
+
+__global__ void mse_partial_kernel(const float* __restrict__ p, const float* __restrict__ t,
+                                   float* __restrict__ partials, size_t n) {
+    float acc = 0.f;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float d = p[i] - t[i];
+        acc = fmaf(d, d, acc);
+    }
+    const float s = block_sum(acc);
+    if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+__global__ void mse_final_kernel(const float* __restrict__ partials, int count, float n,
+                                 float* __restrict__ out) {
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) acc += partials[i];
+    const float s = block_sum(acc);
+    if (threadIdx.x == 0) out[0] = s / n;
+}
+__global__ void mse_bwd_kernel(const float* __restrict__ p, const float* __restrict__ t,
+                               const float* __restrict__ gscalar, float inv_n, float* __restrict__ dp,
+                               size_t n) {
+    const float scale = 2.0f * inv_n * (gscalar ? gscalar[0] : 1.0f);
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dp[i] = (p[i] - t[i]) * scale;
+}
+
+__global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ grad, float* __restrict__ vel,
+                           float lr, float momentum, float wd, float dampening, int nesterov,
+                           int has_momentum, int vel_init, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float g = grad[i];
+        if (wd != 0.0f) g += p[i] * wd;
+        float update;
+        if (has_momentum) {
+            const float v = vel_init ? (vel[i] * momentum + g * (1.0f - dampening)) : g;
+            vel[i] = v;
+            update = nesterov ? (g + v * momentum) : v;
+        } else {
+            update = g;
+        }
+        p[i] = p[i] - update * lr;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t ld, cudaStream_t s) {
+    int64_t batch = 1;
+    for (int d = 0; d < src.nb; ++d) batch *= src.bshape[d];
+    const int64_t total = batch * src.rows * ld;
+    if (total == 0) return cudaSuccess;
+    // Dense source with the same leading dimension: plain vectorised split.
+    bool dense = lo != nullptr && src.col_stride == 1 && src.row_stride == ld && ld == src.cols &&
+                 (ld & 3) == 0 && ((uintptr_t)src.ptr & 15u) == 0;
+    if (dense) {
+        int64_t expect = src.rows * ld;
+        for (int d = src.nb - 1; d >= 0 && dense; --d) {
+            if (src.bshape[d] != 1 && src.bstride[d] != expect) dense = false;
+            expect *= src.bshape[d];
+        }
+    }
+    if (dense) {
+        const int64_t n4 = total / 4;
+        split_vec4_kernel<<<grid_for((size_t)n4, 2), kThreads, 0, s>>>(
+            reinterpret_cast<const float4*>(src.ptr), reinterpret_cast<float4*>(hi),
+            reinterpret_cast<float4*>(lo), n4);
+        return cudaGetLastError();
+    }
+    PackArgs a;
+    a.src = src.ptr;
+    a.hi = hi;
+    a.lo = lo;
+    a.nb = src.nb;
+    for (int d = 0; d < kMaxDims; ++d) {
+        a.bshape[d] = d < src.nb ? src.bshape[d] : 1;
+        a.bstride[d] = d < src.nb ? src.bstride[d] : 0;
+    }
+    a.rows = src.rows;
+    a.cols = src.cols;
+    a.ld = ld;
+    a.row_stride = src.row_stride;
+    a.col_stride = src.col_stride;
+    a.total = total;
+    pack_split_kernel<<<grid_for((size_t)total, 2), kThreads, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_simt_gemm(const SimtGemm& g, cudaStream_t s) {
+    int64_t batch = 1;
+    for (int d = 0; d < g.nb; ++d) batch *= g.bshape[d];
+    if (batch > 65535) return cudaErrorInvalidValue;
+    dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, (unsigned)batch);
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    simt_gemm_kernel<<<grid, dim3(ST, ST), 0, s>>>(g);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s) {
+    GatherArgs a;
+    a.src = v.ptr;
+    a.dst = dst;
+    a.nd = v.nd;
+    a.total = 1;
+    for (int d = 0; d < kMaxDims; ++d) {
+        a.shape[d] = d < v.nd ? v.shape[d] : 1;
+        a.stride[d] = d < v.nd ? v.stride[d] : 0;
+        a.total *= a.shape[d];
+    }
+    if (a.total == 0) return cudaSuccess;
+    gather_kernel<<<grid_for((size_t)a.total, 2), kThreads, 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
+                       const int64_t* shape, cudaStream_t s) {
+    AddArgs p;
+    p.a = a.ptr;
+    p.b = b.ptr;
+    p.out = out;
+    p.nd = nd;
+    p.total = 1;
+    bool flat = true;
+    int64_t expect = 1;
+    for (int d = kMaxDims - 1; d >= 0; --d) {
+        if (d < nd) {
+            p.shape[d] = shape[d];
+            p.as[d] = a.stride[d];
+            p.bs[d] = b.stride[d];
+            if (shape[d] != 1 && (a.stride[d] != expect || b.stride[d] != expect)) flat = false;
+            expect *= shape[d];
+            p.total *= shape[d];
+        } else {
+            p.shape[d] = 1;
+            p.as[d] = p.bs[d] = 0;
+        }
+    }
+    if (p.total == 0) return cudaSuccess;
+    if (flat && (p.total & 3) == 0 && (((uintptr_t)a.ptr | (uintptr_t)b.ptr | (uintptr_t)out) & 15u) == 0) {
+        add_flat_kernel<<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(
+            reinterpret_cast<const float4*>(a.ptr), reinterpret_cast<const float4*>(b.ptr),
+            reinterpret_cast<float4*>(out), p.total / 4);
+        return cudaGetLastError();
+    }
+    add_kernel<<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float* out, cudaStream_t s) {
+    SumArgs a;
+    a.g = g.ptr;
+    a.out = out;
+    a.nk = a.nr = 0;
+    a.nkept = a.nred = 1;
+    for (int d = 0; d < g.nd; ++d) {
+        if (out_shape[d] == g.shape[d]) {
+            if (g.shape[d] == 1) continue;
+            a.kshape[a.nk] = g.shape[d];
+            a.kstride[a.nk] = g.stride[d];
+            a.nkept *= g.shape[d];
+            ++a.nk;
+        } else {
+            a.rshape[a.nr] = g.shape[d];
+            a.rstride[a.nr] = g.stride[d];
+            a.nred *= g.shape[d];
+            ++a.nr;
+        }
+    }
+    if (a.nkept == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((a.nkept + 31) / 32);
+    sum_to_kernel<<<blocks, dim3(32, 8), 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    scale_kernel<<<grid_for(n), kThreads, 0, s>>>(x, alpha, y, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    fill_kernel<<<grid_for(n), kThreads, 0, s>>>(x, v, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    tanh_fwd_kernel<<<grid_for(n), kThreads, 0, s>>>(x, y, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    tanh_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(g, y, dx, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
+                           cudaStream_t s) {
+    int blocks = grid_for(n);
+    if (blocks > 1024) blocks = 1024;
+    mse_partial_kernel<<<blocks, kThreads, 0, s>>>(p, t, partials, n);
+    mse_final_kernel<<<1, kThreads, 0, s>>>(partials, blocks, (float)n, loss_out);
+    return cudaGetLastError();
+}
+cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
+                           cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    mse_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(p, t, gscalar, 1.0f / (float)n, dp, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float momentum, float wd,
+                       float dampening, int nesterov, int has_momentum, int vel_init, size_t n,
+                       cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    sgd_kernel<<<grid_for(n), kThreads, 0, s>>>(p, g, vel, lr, momentum, wd, dampening, nesterov,
+                                                 has_momentum, vel_init, n);
+    return cudaGetLastError();
+}
+
+}  // namespace akr

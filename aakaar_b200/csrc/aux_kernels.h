@@ -1,0 +1,65 @@
+// Bandwidth-bound helper kernels around the GEMM: operand packing / TF32 splitting, a plain-FMA
+// reference matmul, and the elementwise / reduction ops of the Linear training step.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace akr {
+
+constexpr int kMaxDims = 8;
+
+// Source view of a pack: `nb` batch dims followed by a (rows, cols) matrix.
+struct PackSrc {
+    const float* ptr;
+    int nb;
+    int64_t bshape[kMaxDims];
+    int64_t bstride[kMaxDims];
+    int64_t rows, cols;
+    int64_t row_stride, col_stride;
+};
+
+// Gathers `src` into dense [batch][rows][ld] arrays. hi receives the value rounded to TF32
+// (round-to-nearest, ties away) when `lo` is given, else the value itself; lo receives value - hi.
+// Padding columns [cols, ld) are zeroed.
+cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t ld, cudaStream_t s);
+
+struct SimtGemm {
+    const float *A, *B;
+    float* C;
+    int M, N, K;
+    int nb;
+    int64_t bshape[kMaxDims];
+    int64_t a_bs[kMaxDims], b_bs[kMaxDims], c_bs[kMaxDims];
+    int64_t a_rs, a_cs, b_rs, b_cs, c_rs, c_cs;
+};
+cudaError_t launch_simt_gemm(const SimtGemm& g, cudaStream_t s);
+
+struct StridedView {
+    const float* ptr;
+    int nd;
+    int64_t shape[kMaxDims];
+    int64_t stride[kMaxDims];
+};
+// dst (contiguous, shape = v.shape) = gather(v)
+cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s);
+// out[i] = a[bcast(i)] + b[bcast(i)], out contiguous with shape `shape`
+cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
+                       const int64_t* shape, cudaStream_t s);
+// out (contiguous `out_shape`, same rank as g, dims of size 1 where reduced) = sum of g over reduced dims
+cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float* out, cudaStream_t s);
+
+cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s);
+cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s);
+cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s);
+cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n, cudaStream_t s);
+// loss_out[0] = sum((p-t)^2)/n ; uses `partials` (>= 1024 floats) as scratch
+cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
+                           cudaStream_t s);
+cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
+                           cudaStream_t s);
+cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float momentum, float wd,
+                       float dampening, int nesterov, int has_momentum, int vel_init, size_t n,
+                       cudaStream_t s);
+
+}  // namespace akr

@@ -3,7 +3,8 @@
 //
 //   warp 0 (one thread)  : TMA producer, fills a ring of STAGES shared-memory stages
 //   warp 1 (one thread)  : MMA issuer; owns the TMEM allocation (two accumulators, ping-pong)
-//   warps 2..5           : epilogue, TMEM -> registers -> global (bias / accumulate / split-K sum)
+//   warps 2..5 (2..9 for 256-wide tiles): epilogue, TMEM -> registers -> global
+//                          (bias / accumulate / split-K sum / fp32 promotion of partial chains)
 //
 // Replaces the per-batch cublasSgemm loops of the reference (src/matmul_kernel.cu:111-143 forward,
 // :347-402 the two backward products) and, through the `red` batch dim, the unreduced
@@ -29,7 +30,6 @@ constexpr int BK = 32;         // fp32 per k-block: 128 bytes, one swizzle row
 constexpr int UMMA_K = 8;      // k per tcgen05.mma kind::tf32
 constexpr int CHUNK = 32;      // M/N elements per 128-byte row of an MN-major tile
 constexpr int GROUP_M = 16;    // tile rasterisation: m-tiles per group (L2 reuse of B panels)
-constexpr int NUM_THREADS = 192;
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
 
 struct KernelParams {
@@ -79,10 +79,46 @@ struct SmemLayout {
     static constexpr int STAGE_BYTES = (TERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
 };
 
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// Threads of one CTA: producer warp, MMA warp and one epilogue warp per (TMEM lane quarter,
+// 128-column slab of the tile).
+template <int BN>
+constexpr int num_threads() { return 64 + (BN / 128) * 128; }
+
+// Stores (or accumulates / adds bias to) 32 consecutive columns of one output row.
+__device__ __forceinline__ void store_chunk(float (&v)[32], float* dst, int col0, int N, bool vec,
+                                            const float* bias, bool accumulate) {
+    const bool full = col0 + 32 <= N;
+    if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (full || col0 + j < N) v[j] += __ldg(bias + col0 + j);
+    }
+    if (accumulate) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (full || col0 + j < N) v[j] += dst[j];
+    }
+    if (full && vec) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) dst[j] = v[j];
+    }
+}
+
+// KC > 0: the tensor core only accumulates KC k-blocks at a time; the epilogue warps add those
+// partial tiles into fp32 registers with round-to-nearest. The accumulator inside the tensor core
+// truncates on every add, which over a long contraction costs more accuracy than the fp32-accurate
+// mode may lose, so that mode keeps the in-core chains short. KC == 0: one chain per output tile.
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC>
+__global__ void __launch_bounds__(num_threads<BN>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     using L = SmemLayout<BN, TERMS>;
+    constexpr int EPI_WARPS = (BN / 128) * 4;
+    constexpr int CHUNK_ITERS = KC > 0 ? KC : 0x7fffffff;
     constexpr int TMEM_COLS = 2 * BN;  // two accumulators
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
 
@@ -112,7 +148,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
-            ptx::mbar_init(tempty_bar(b), 4);
+            ptx::mbar_init(tempty_bar(b), EPI_WARPS);
         }
         *abort_flag = 0;
         *last_flag = 0;
@@ -212,82 +248,82 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BN, MAJA, MAJB);
             int stage = 0;
             uint32_t phase = 0;
-            int local = 0;
+            int handoff = 0;  // accumulator hand-offs so far (one per chunk of the contraction)
             bool ok = true;
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
                 const Tile c = decode_tile(t, p, BN);
                 const int it0 = (int)((long long)total_iters * c.split / p.splits);
                 const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
-                const int buf = local & 1;
-                const uint32_t acc_phase = (local >> 1) & 1u;
-                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int it = it0; it < it1; ++it) {
-                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                for (int cs = it0, ce = it0; cs < it1 && ok; cs = ce) {
+                    ce = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1;
+                    const int buf = handoff & 1;
+                    const uint32_t acc_phase = (handoff >> 1) & 1u;
+                    if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
-                    const uint32_t sb = sa + L::A_BYTES;
-                    const uint32_t sa_lo = sa + L::A_BYTES + L::B_BYTES;
-                    const uint32_t sb_lo = sb + L::A_BYTES + L::B_BYTES;
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+                    for (int it = cs; it < ce; ++it) {
+                        if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
+                        const uint32_t sb = sa + L::A_BYTES;
+                        const uint32_t sa_lo = sa + L::A_BYTES + L::B_BYTES;
+                        const uint32_t sb_lo = sb + L::A_BYTES + L::B_BYTES;
 #pragma unroll
-                    for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
-                        // K-major: step 32 bytes inside the 128-byte swizzle row.
-                        // MN-major: step 8 k-rows (two 4-row swizzle groups, 8 * 128 bytes).
-                        const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
-                        const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
-                        const uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128;
-                        const uint32_t b_lbo = MAJB == 0 ? 16 : BK * 128;
-                        const uint32_t a_sbo = MAJA == 0 ? 1024 : 512;
-                        const uint32_t b_sbo = MAJB == 0 ? 1024 : 512;
-                        constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
-                        constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
-                        const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
-                        const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
-                        const uint32_t first = (it == it0 && k8 == 0) ? 0u : 1u;
-                        if (TERMS == 3) {
-                            const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
-                            const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
-                            ptx::mma_tf32_ss(d_tmem, da_lo, db, IDESC, first);
-                            ptx::mma_tf32_ss(d_tmem, da, db_lo, IDESC, 1u);
-                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 1u);
-                        } else {
-                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, first);
+                        for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                            // K-major: step 32 bytes inside the 128-byte swizzle row.
+                            // MN-major: step 8 k-rows (two 4-row swizzle groups, 8 * 128 bytes).
+                            const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                            const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                            const uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128;
+                            const uint32_t b_lbo = MAJB == 0 ? 16 : BK * 128;
+                            const uint32_t a_sbo = MAJA == 0 ? 1024 : 512;
+                            const uint32_t b_sbo = MAJB == 0 ? 1024 : 512;
+                            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+                            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+                            const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                            const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
+                            if (TERMS == 3) {
+                                const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
+                                const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
+                                ptx::mma_tf32_ss(d_tmem, da_lo, db, IDESC, first);
+                                ptx::mma_tf32_ss(d_tmem, da, db_lo, IDESC, 1u);
+                                ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 1u);
+                            } else {
+                                ptx::mma_tf32_ss(d_tmem, da, db, IDESC, first);
+                            }
+                        }
+                        ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs finish
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
                         }
                     }
-                    ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs finish
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                    if (ok) ptx::mma_commit(tfull_bar(buf));  // this chunk's accumulator is complete
+                    ++handoff;
                 }
-                if (ok) ptx::mma_commit(tfull_bar(buf));  // accumulator complete
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        // ------------------------------------------------------------ epilogue (warps 2 ..)
+        const int q = warp & 3;             // TMEM lane quarter this warp may read
+        const int slab = (warp - 2) >> 2;   // which 128-column slab of the tile
         const int nbatch = p.o0 * p.o1;
-        int local = 0;
+        const bool split_mode = p.splits > 1;
+        int handoff = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
             const Tile c = decode_tile(t, p, BN);
-            const int buf = local & 1;
-            const uint32_t acc_phase = (local >> 1) & 1u;
-            if (!ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
-                ok = false;
-                break;
-            }
-            ptx::tc_fence_after();
+            const int it0 = (int)((long long)total_iters * c.split / p.splits);
+            const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             const int row = c.m0 + q * 32 + lane;
             const bool row_ok = row < p.M;
-            const bool split_mode = p.splits > 1;
             float* out_row;
             bool vec;
             if (split_mode) {
@@ -299,54 +335,66 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 out_row = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)(row_ok ? row : 0) * p.ldc;
                 vec = p.vec_ok != 0;
             }
-            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                const int col0 = c.n0 + ch * 32;
-                if (col0 >= p.N) break;  // warp-uniform
-                __syncwarp();            // tcgen05.ld needs the whole warp converged
-                uint32_t v[32];
-                ptx::tmem_ld_32x32(t_row + ch * 32, v);
-                ptx::tmem_ld_wait();
-                if (!row_ok) continue;
-                float* dst = out_row + col0;
-                const bool full = col0 + 32 <= p.N;
-                if (!split_mode) {
-                    if (p.bias != nullptr) {
+            const float* bias = split_mode ? nullptr : p.bias;
+            const bool accumulate = !split_mode && p.accumulate != 0;
+            const int slab_col0 = c.n0 + slab * 128;
+
+            float acc[KC > 0 ? 128 : 1];
+            if (KC > 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (full || col0 + j < p.N)
-                                v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(p.bias + col0 + j));
-                    }
-                    if (p.accumulate) {
+                for (int j = 0; j < (KC > 0 ? 128 : 1); ++j) acc[j] = 0.f;
+            }
+            for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
+                const int buf = handoff & 1;
+                const uint32_t acc_phase = (handoff >> 1) & 1u;
+                if (!ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * BN + slab * 128;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (full || col0 + j < p.N)
-                                v[j] = __float_as_uint(__uint_as_float(v[j]) + dst[j]);
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int col0 = slab_col0 + ch * 32;
+                    if (col0 < p.N) {  // warp-uniform
+                        __syncwarp();  // tcgen05.ld needs the whole warp converged
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                        ptx::tmem_ld_wait();
+                        if (KC > 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)] += __uint_as_float(v[j]);
+                        } else if (row_ok) {
+                            float f[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                            store_chunk(f, out_row + col0, col0, p.N, vec, bias, accumulate);
+                        }
                     }
                 }
-                if (full && vec) {
+                // Accumulator drained: hand the TMEM buffer back to the MMA warp.
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+                ++handoff;
+            }
+            if (KC > 0 && ok && row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
-                                               __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        *reinterpret_cast<float4*>(dst + j) = o;
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int col0 = slab_col0 + ch * 32;
+                    if (col0 < p.N) {
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)];
+                        store_chunk(f, out_row + col0, col0, p.N, vec, bias, accumulate);
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) dst[j] = __uint_as_float(v[j]);
                 }
             }
-            // Accumulator drained: hand the TMEM buffer back to the MMA warp.
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
 
-            if (split_mode) {
+            if (split_mode && ok) {
                 // Last CTA to finish this tile adds the partials in split order (deterministic).
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 const int tile_id = (t / p.splits);
                 if (threadIdx.x == 64) {
                     const int prev = atomicAdd(p.counters + tile_id, 1);
@@ -354,23 +402,23 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     if (last) p.counters[tile_id] = 0;  // self-cleaning for the next launch
                     *last_flag = last;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 const int is_last = *last_flag;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 if (is_last && row_ok) {
                     __threadfence();
                     float* crow = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)row * p.ldc;
                     const size_t split_stride = (size_t)nbatch * p.M * p.N;
                     const float* prow = p.partials + ((size_t)c.batch * p.M + row) * (size_t)p.N;
-                    const int ncols = min(BN, p.N - c.n0);
+                    const int ncols = min(128, p.N - slab_col0);
                     for (int j = 0; j < ncols; ++j) {
-                        const int col = c.n0 + j;
-                        float acc = 0.f;
-                        for (int s = 0; s < p.splits; ++s)
-                            acc += __ldcg(prow + (size_t)s * split_stride + col);
-                        if (p.bias != nullptr) acc += __ldg(p.bias + col);
-                        if (p.accumulate) acc += crow[col];
-                        crow[col] = acc;
+                        const int col = slab_col0 + j;
+                        float sum = 0.f;
+                        for (int sp = 0; sp < p.splits; ++sp)
+                            sum += __ldcg(prow + (size_t)sp * split_stride + col);
+                        if (p.bias != nullptr) sum += __ldg(p.bias + col);
+                        if (p.accumulate) sum += crow[col];
+                        crow[col] = sum;
                     }
                 }
             }
@@ -441,11 +489,11 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, int mn
     return r == CUDA_SUCCESS;
 }
 
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES>
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS>;
     constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256;
-    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES>;
+    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -455,7 +503,7 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
         }
         attr_done = true;
     }
-    kern<<<grid, NUM_THREADS, smem, stream>>>(kp);
+    kern<<<grid, num_threads<BN>(), smem, stream>>>(kp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -464,15 +512,15 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
     return 0;
 }
 
-template <int BN, int TERMS, int STAGES>
+template <int BN, int TERMS, int STAGES, int KC>
 int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream_t s, char* err,
                  int errlen) {
     const int key = g.A.mn_major * 2 + g.B.mn_major;
     switch (key) {
-        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES>(kp, grid, s, err, errlen);
-        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES>(kp, grid, s, err, errlen);
-        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES>(kp, grid, s, err, errlen);
-        default: return launch_variant<BN, 1, 1, TERMS, STAGES>(kp, grid, s, err, errlen);
+        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
+        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
+        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
+        default: return launch_variant<BN, 1, 1, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
     }
 }
 
@@ -604,12 +652,13 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     const int ctas = gemm_sm100_num_ctas();
     const int grid = (int)(total < ctas ? total : ctas);
 
+    // fp32-accurate mode: chains of 2 k-blocks (64 deep) inside the tensor core, see the kernel.
     if (g.terms == 3) {
-        if (bn == 256) return launch_major<256, 3, 2>(g, kp, grid, stream, err, errlen);
-        return launch_major<128, 3, 3>(g, kp, grid, stream, err, errlen);
+        if (bn == 256) return launch_major<256, 3, 2, 2>(g, kp, grid, stream, err, errlen);
+        return launch_major<128, 3, 3, 2>(g, kp, grid, stream, err, errlen);
     }
-    if (bn == 256) return launch_major<256, 1, 4>(g, kp, grid, stream, err, errlen);
-    return launch_major<128, 1, 6>(g, kp, grid, stream, err, errlen);
+    if (bn == 256) return launch_major<256, 1, 4, 0>(g, kp, grid, stream, err, errlen);
+    return launch_major<128, 1, 6, 0>(g, kp, grid, stream, err, errlen);
 }
 
 }  // namespace akr

@@ -1,0 +1,646 @@
+// pybind11 module `_C` of aakaar_b200: the Python-facing surface of the matmul path, with the
+// names and behaviour of the reference's module (src/bindings.cpp:2472-2874) for this path:
+// Tensor (views, autograd, backward), cuda_matmul / __matmul__, from_numpy, set_tf32 switches,
+// synchronize, the caching-allocator hooks, plus the few support ops the Linear training step
+// needs. Every computation is a call into the C ABI of include/akr_b200.h; nothing here touches
+// CUDA or PyTorch directly.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+#include <unordered_map>
+#include <unordered_set>
+
+#include "tensor.h"
+
+namespace py = pybind11;
+using namespace akrhost;
+
+namespace {
+
+bool g_grad_enabled = true;
+
+TensorPtr make_cuda(const std::vector<int64_t>& shape) { return std::make_shared<Tensor>(shape, "cuda"); }
+
+bool needs_graph(const TensorPtr& a) { return g_grad_enabled && a->requires_grad; }
+bool needs_graph(const TensorPtr& a, const TensorPtr& b) {
+    return g_grad_enabled && (a->requires_grad || b->requires_grad);
+}
+
+void attach(const TensorPtr& out, const char* name, std::vector<TensorPtr> inputs,
+            std::function<std::vector<TensorPtr>(TensorPtr)> fn) {
+    out->requires_grad = true;
+    auto node = std::make_shared<Node>();
+    node->inputs = std::move(inputs);
+    node->op_name = name;
+    node->backward_fn = std::move(fn);
+    out->grad_fn = node;
+}
+
+// ------------------------------------------------------------------ basic ops
+
+TensorPtr op_contiguous(const TensorPtr& t);
+
+TensorPtr op_add_raw(const TensorPtr& a, const TensorPtr& b) {
+    require_cuda(a, "add");
+    require_cuda(b, "add");
+    const size_t nd = std::max(a->shape.size(), b->shape.size());
+    std::vector<int64_t> shape(nd);
+    for (size_t i = 0; i < nd; ++i) {
+        const int ia = (int)i - (int)(nd - a->shape.size()), ib = (int)i - (int)(nd - b->shape.size());
+        const int64_t da = ia >= 0 ? a->shape[ia] : 1, db = ib >= 0 ? b->shape[ib] : 1;
+        if (da != db && da != 1 && db != 1) throw std::invalid_argument("Shapes are not broadcastable");
+        shape[i] = std::max(da, db);
+    }
+    auto out = make_cuda(shape);
+    akr_view va = a->view(), vb = b->view(), vo = out->view();
+    check(akr_add(&va, &vb, &vo, nullptr));
+    return out;
+}
+
+// reduce_grad_to_shape of the reference (src/bindings.cpp:1467-1503) in one reduction launch.
+TensorPtr op_sum_to(const TensorPtr& g, const std::vector<int64_t>& target) {
+    if (g->shape == target) return g;
+    auto out = make_cuda(target);
+    akr_view vg = g->view(), vo = out->view();
+    check(akr_sum_to(&vg, &vo, nullptr));
+    return out;
+}
+
+TensorPtr op_scale(const TensorPtr& a, float s);
+
+TensorPtr op_add(const TensorPtr& a, const TensorPtr& b) {
+    auto out = op_add_raw(a, b);
+    if (needs_graph(a, b)) {
+        const auto sa = a->shape, sb = b->shape;
+        attach(out, "add", {a, b}, [sa, sb](TensorPtr g) {
+            return std::vector<TensorPtr>{op_sum_to(g, sa), op_sum_to(g, sb)};
+        });
+    }
+    return out;
+}
+
+TensorPtr op_scale(const TensorPtr& a, float s) {
+    require_cuda(a, "mul");
+    auto src = a->is_contiguous() ? a : op_contiguous(a);
+    auto out = make_cuda(a->shape);
+    check(akr_scale(src->data, s, out->data, (size_t)a->size, nullptr));
+    if (needs_graph(a)) {
+        attach(out, "mul_scalar", {a}, [s](TensorPtr g) {
+            bool prev = g_grad_enabled;
+            g_grad_enabled = false;
+            auto r = op_scale(g, s);
+            g_grad_enabled = prev;
+            return std::vector<TensorPtr>{r};
+        });
+    }
+    return out;
+}
+
+TensorPtr op_sub(const TensorPtr& a, const TensorPtr& b) { return op_add(a, op_scale(b, -1.0f)); }
+
+TensorPtr scalar_tensor(float v) {
+    auto t = make_cuda({1});
+    check(akr_fill(t->data, v, 1, nullptr));
+    return t;
+}
+
+TensorPtr op_contiguous(const TensorPtr& t) {
+    if (t->is_contiguous()) return t;
+    require_cuda(t, "contiguous");
+    auto out = make_cuda(t->shape);
+    akr_view v = t->view();
+    check(akr_contiguous(&v, out->data, nullptr));
+    if (needs_graph(t)) {
+        attach(out, "contiguous", {t}, [](TensorPtr g) { return std::vector<TensorPtr>{g}; });
+    }
+    return out;
+}
+
+TensorPtr op_transpose(const TensorPtr& t, int d0, int d1) {
+    const int nd = (int)t->shape.size();
+    if (d0 < 0) d0 += nd;
+    if (d1 < 0) d1 += nd;
+    if (d0 < 0 || d1 < 0 || d0 >= nd || d1 >= nd) throw std::out_of_range("transpose: dimension out of range");
+    auto shape = t->shape;
+    auto strides = t->strides;
+    std::swap(shape[d0], shape[d1]);
+    std::swap(strides[d0], strides[d1]);
+    auto out = std::make_shared<Tensor>(t, 0, shape, strides);
+    if (needs_graph(t)) {
+        attach(out, "transpose", {t}, [d0, d1](TensorPtr g) {
+            bool prev = g_grad_enabled;
+            g_grad_enabled = false;
+            auto r = op_transpose(g, d0, d1);
+            g_grad_enabled = prev;
+            return std::vector<TensorPtr>{r};
+        });
+    }
+    return out;
+}
+
+TensorPtr op_view(const TensorPtr& t, std::vector<int64_t> new_shape, bool allow_copy) {
+    int64_t known = 1;
+    int infer = -1;
+    for (size_t i = 0; i < new_shape.size(); ++i) {
+        if (new_shape[i] == -1) {
+            if (infer >= 0) throw std::invalid_argument("view: only one dimension can be inferred");
+            infer = (int)i;
+        } else {
+            known *= new_shape[i];
+        }
+    }
+    if (infer >= 0) {
+        if (known == 0 || t->size % known != 0) throw std::invalid_argument("view: shape is invalid for input size");
+        new_shape[infer] = t->size / known;
+        known *= new_shape[infer];
+    }
+    if (known != t->size) throw std::invalid_argument("view: shape is invalid for input size");
+    TensorPtr src = t;
+    if (!t->is_contiguous()) {
+        if (!allow_copy) throw std::invalid_argument("view requires a contiguous tensor. Call .contiguous() first.");
+        src = op_contiguous(t);
+    }
+    auto out = std::make_shared<Tensor>(src, 0, new_shape, contiguous_strides(new_shape));
+    if (needs_graph(src)) {
+        const auto old_shape = src->shape;
+        attach(out, "view", {src}, [old_shape](TensorPtr g) {
+            bool prev = g_grad_enabled;
+            g_grad_enabled = false;
+            auto r = op_view(g, old_shape, true);
+            g_grad_enabled = prev;
+            return std::vector<TensorPtr>{r};
+        });
+    }
+    return out;
+}
+
+TensorPtr op_tanh(const TensorPtr& t) {
+    require_cuda(t, "tanh");
+    auto src = op_contiguous(t);
+    auto out = make_cuda(t->shape);
+    check(akr_tanh_fwd(src->data, out->data, (size_t)t->size, nullptr));
+    if (needs_graph(t)) {
+        // The node is owned by `out`, so it refers to it weakly (no ownership cycle); whoever
+        // runs backward through this node holds `out` alive.
+        std::weak_ptr<Tensor> wout = out;
+        attach(out, "tanh", {t}, [wout](TensorPtr g) {
+            TensorPtr saved = wout.lock();
+            if (!saved) throw std::runtime_error("tanh backward: forward output was released");
+            auto gc = g->is_contiguous() ? g : op_contiguous(g);
+            auto dx = make_cuda(saved->shape);
+            check(akr_tanh_bwd(gc->data, saved->data, dx->data, (size_t)saved->size, nullptr));
+            return std::vector<TensorPtr>{dx};
+        });
+    }
+    return out;
+}
+
+TensorPtr op_sum_all(const TensorPtr& t) {
+    require_cuda(t, "sum");
+    auto out = make_cuda({1});
+    akr_view vg = t->view(), vo = out->view();
+    check(akr_sum_to(&vg, &vo, nullptr));
+    if (needs_graph(t)) {
+        const auto shape = t->shape;
+        attach(out, "sum", {t}, [shape](TensorPtr g) {
+            // broadcast the scalar gradient: zeros(shape) + g
+            auto z = make_cuda(shape);
+            int64_t n = 1;
+            for (auto d : shape) n *= d;
+            check(akr_fill(z->data, 0.0f, (size_t)n, nullptr));
+            return std::vector<TensorPtr>{op_add_raw(z, g)};
+        });
+    }
+    return out;
+}
+
+// ------------------------------------------------------------------ matmul
+
+int g_matmul_mode_override = AKR_MODE_GLOBAL;
+
+// dispatch_matmul of the reference (src/bindings.cpp:1686-1764): forward product plus the autograd
+// node. The backward closure calls the fused backward on the original strided operands: no
+// transposed copies, no unreduced [batch..., K, N] intermediate, and only the gradients needed.
+TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr& bias) {
+    if (a->device != b->device) throw std::runtime_error("Both tensors must be on the same device!");
+    require_cuda(a, "matmul");
+    akr_view va = a->view(), vb = b->view();
+    int64_t oshape[AKR_MAX_DIMS + 2];
+    int32_t ond = 0;
+    check(akr_matmul_plan(&va, &vb, oshape, &ond));
+    auto out = make_cuda(std::vector<int64_t>(oshape, oshape + ond));
+    akr_view vo = out->view();
+    akr_view vbias;
+    if (bias) {
+        require_cuda(bias, "matmul bias");
+        vbias = bias->view();
+    }
+    const int mode = g_matmul_mode_override;
+    check(akr_matmul_fwd(&va, &vb, bias ? &vbias : nullptr, &vo, mode, nullptr));
+
+    const bool bias_grad = bias && bias->requires_grad;
+    if (g_grad_enabled && (a->requires_grad || b->requires_grad || bias_grad)) {
+        std::vector<TensorPtr> inputs{a, b};
+        if (bias) inputs.push_back(bias);
+        attach(out, bias ? "linear" : "matmul", inputs, [a, b, bias, mode](TensorPtr g) {
+            require_cuda(g, "matmul backward");
+            TensorPtr da, db, dbias;
+            if (a->requires_grad) da = make_cuda(a->shape);
+            if (b->requires_grad) db = make_cuda(b->shape);
+            akr_view va = a->view(), vb = b->view(), vg = g->view();
+            akr_view vda, vdb;
+            if (da) vda = da->view();
+            if (db) vdb = db->view();
+            if (da || db)
+                check(akr_matmul_bwd(&va, &vb, &vg, da ? &vda : nullptr, db ? &vdb : nullptr, mode, nullptr));
+            std::vector<TensorPtr> grads{da, db};
+            if (bias) {
+                if (bias->requires_grad) dbias = op_sum_to(g, bias->shape);
+                grads.push_back(dbias);
+            }
+            return grads;
+        });
+    }
+    return out;
+}
+
+TensorPtr op_matmul(const TensorPtr& a, const TensorPtr& b) { return op_matmul_bias(a, b, nullptr); }
+
+TensorPtr cpu_matmul_refused(const TensorPtr&, const TensorPtr&) {
+    throw std::runtime_error(
+        "cpu_matmul: this build computes on CUDA (sm_100a) only; there is no CPU matmul. "
+        "Create the tensors with device='cuda'.");
+}
+
+// ------------------------------------------------------------------ losses / optimiser
+
+// _mse_fused of the reference (src/bindings.cpp:2821, src/elementwise_kernel.cu:2253-2300).
+TensorPtr op_mse(const TensorPtr& pred, const TensorPtr& target) {
+    require_cuda(pred, "mse");
+    require_cuda(target, "mse");
+    if (pred->shape != target->shape) throw std::invalid_argument("MSELoss: pred and target shapes differ");
+    if (!pred->is_contiguous() || !target->is_contiguous())
+        throw std::invalid_argument("MSELoss requires contiguous tensors. Call .contiguous() first.");
+    auto out = make_cuda({1});
+    check(akr_mse_fwd(pred->data, target->data, out->data, (size_t)pred->size, nullptr));
+    if (needs_graph(pred)) {
+        attach(out, "mse", {pred}, [pred, target](TensorPtr g) {
+            auto dp = make_cuda(pred->shape);
+            check(akr_mse_bwd(pred->data, target->data, g->data, dp->data, (size_t)pred->size, nullptr));
+            return std::vector<TensorPtr>{dp};
+        });
+    }
+    return out;
+}
+
+void op_sgd_step(const TensorPtr& p, const TensorPtr& grad, const TensorPtr& velocity, float lr,
+                 float momentum, float weight_decay, float dampening, int nesterov, int has_momentum,
+                 int velocity_initialized) {
+    require_cuda(p, "sgd_step");
+    require_cuda(grad, "sgd_step");
+    if (!p->is_contiguous() || !grad->is_contiguous())
+        throw std::invalid_argument("sgd_step requires contiguous tensors");
+    if (p->size != grad->size) throw std::invalid_argument("sgd_step: parameter and gradient sizes differ");
+    check(akr_sgd_step(p->data, grad->data, velocity ? velocity->data : nullptr, lr, momentum, weight_decay,
+                       dampening, nesterov, has_momentum, velocity_initialized, (size_t)p->size, nullptr));
+}
+
+// ------------------------------------------------------------------ backward driver
+// tensor_backward of the reference (src/bindings.cpp:810-877): reverse topological walk, leaf
+// gradients accumulate with add, a graph can be walked once unless retain_graph is set.
+void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_graph) {
+    if (!grad_output) {
+        if (root->size != 1)
+            throw std::runtime_error("backward() requires an explicit gradient for non-scalar tensors");
+        require_cuda(root, "backward");
+        grad_output = make_cuda(root->shape);
+        check(akr_fill(grad_output->data, 1.0f, 1, nullptr));
+    }
+    std::vector<TensorPtr> topo;
+    std::unordered_set<Tensor*> seen;
+    // Iterative post-order DFS (deep graphs must not overflow the C stack).
+    std::vector<std::pair<TensorPtr, size_t>> stack;
+    stack.emplace_back(root, 0);
+    seen.insert(root.get());
+    while (!stack.empty()) {
+        auto& top = stack.back();
+        TensorPtr t = top.first;
+        if (t->grad_fn && top.second < t->grad_fn->inputs.size()) {
+            TensorPtr nxt = t->grad_fn->inputs[top.second++];
+            if (nxt && !seen.count(nxt.get())) {
+                seen.insert(nxt.get());
+                stack.emplace_back(nxt, 0);
+            }
+        } else {
+            topo.push_back(t);
+            stack.pop_back();
+        }
+    }
+    const bool prev = g_grad_enabled;
+    g_grad_enabled = false;  // gradient arithmetic is not itself recorded
+    try {
+        std::unordered_map<Tensor*, TensorPtr> grads;
+        grads[root.get()] = grad_output;
+        for (auto it = topo.rbegin(); it != topo.rend(); ++it) {
+            const TensorPtr& t = *it;
+            auto found = grads.find(t.get());
+            if (found == grads.end()) continue;
+            TensorPtr g = found->second;
+            if (t->requires_grad && !t->grad_fn) {
+                t->grad = t->grad ? op_add_raw(t->grad, g) : g;
+            }
+            if (t->grad_fn) {
+                if (t->grad_fn->freed)
+                    throw std::runtime_error(
+                        "Trying to backward through the graph a second time (or a part of it), but the "
+                        "intermediate results needed have already been freed. Pass retain_graph=True to "
+                        "backward() the first time if you need to backward through this part of the graph "
+                        "more than once.");
+                auto in_grads = t->grad_fn->backward_fn(g);
+                for (size_t i = 0; i < t->grad_fn->inputs.size(); ++i) {
+                    const TensorPtr& inp = t->grad_fn->inputs[i];
+                    if (!inp || !inp->requires_grad || i >= in_grads.size() || !in_grads[i]) continue;
+                    auto ex = grads.find(inp.get());
+                    if (ex == grads.end()) grads[inp.get()] = in_grads[i];
+                    else ex->second = op_add_raw(ex->second, in_grads[i]);
+                }
+            }
+        }
+    } catch (...) {
+        g_grad_enabled = prev;
+        throw;
+    }
+    g_grad_enabled = prev;
+    if (!retain_graph)
+        for (auto& t : topo)
+            if (t->grad_fn) t->grad_fn->freed = true;
+}
+
+// ------------------------------------------------------------------ host <-> device
+
+TensorPtr from_numpy(py::array array, const std::string& device, bool requires_grad) {
+    if (!py::isinstance<py::array_t<float>>(array))
+        throw std::runtime_error("from_numpy: only float32 arrays are supported on the matmul path (got dtype " +
+                                 std::string(py::str(array.dtype())) + ")");
+    auto arr = py::array_t<float, py::array::c_style | py::array::forcecast>::ensure(array);
+    if (!arr) throw std::runtime_error("from_numpy: could not read the array as contiguous float32");
+    std::vector<int64_t> shape(arr.ndim());
+    for (py::ssize_t i = 0; i < arr.ndim(); ++i) shape[i] = arr.shape(i);
+    if (shape.empty()) shape.push_back(1);
+    auto t = std::make_shared<Tensor>(shape, device);
+    const size_t bytes = (size_t)t->size * sizeof(float);
+    if (device == "cuda") {
+        check(akr_memcpy_h2d(t->data, arr.data(), bytes, nullptr));
+        // the source may be freed by the caller right after this returns
+        check(akr_stream_synchronize(nullptr));
+    } else {
+        std::memcpy(t->data, arr.data(), bytes);
+    }
+    t->requires_grad = requires_grad;
+    return t;
+}
+
+// Asynchronous upload from page-locked memory: returns as soon as the copy is queued. The caller
+// keeps `array` alive and unchanged until the next synchronize().
+TensorPtr from_pinned(py::array_t<float, py::array::c_style> arr, bool requires_grad) {
+    std::vector<int64_t> shape(arr.ndim());
+    for (py::ssize_t i = 0; i < arr.ndim(); ++i) shape[i] = arr.shape(i);
+    if (shape.empty()) shape.push_back(1);
+    auto t = make_cuda(shape);
+    check(akr_memcpy_h2d(t->data, arr.data(), (size_t)t->size * sizeof(float), nullptr));
+    t->requires_grad = requires_grad;
+    return t;
+}
+
+py::array_t<float> to_numpy(const TensorPtr& t) {
+    std::vector<py::ssize_t> shape(t->shape.begin(), t->shape.end());
+    py::array_t<float> out(shape);
+    const size_t bytes = (size_t)t->size * sizeof(float);
+    if (t->device == "cuda") {
+        bool prev = g_grad_enabled;
+        g_grad_enabled = false;
+        TensorPtr src = t->is_contiguous() ? t : op_contiguous(t);
+        g_grad_enabled = prev;
+        check(akr_memcpy_d2h(out.mutable_data(), src->data, bytes, nullptr));
+        check(akr_synchronize());
+    } else {
+        if (!t->is_contiguous()) throw std::runtime_error("to_numpy: non-contiguous CPU tensors are not supported");
+        std::memcpy(out.mutable_data(), t->data, bytes);
+    }
+    return out;
+}
+
+// Download into caller-provided (ideally page-locked) memory without synchronising.
+void copy_to_host(const TensorPtr& t, py::array_t<float, py::array::c_style> out) {
+    require_cuda(t, "copy_to_host");
+    if ((int64_t)out.size() != t->size) throw std::invalid_argument("copy_to_host: size mismatch");
+    bool prev = g_grad_enabled;
+    g_grad_enabled = false;
+    TensorPtr src = t->is_contiguous() ? t : op_contiguous(t);
+    g_grad_enabled = prev;
+    check(akr_memcpy_d2h(out.mutable_data(), src->data, (size_t)t->size * sizeof(float), nullptr));
+}
+
+py::array_t<float> pinned_empty(const std::vector<int64_t>& shape) {
+    size_t n = 1;
+    for (auto d : shape) n *= (size_t)d;
+    void* p = nullptr;
+    check(akr_host_alloc(n * sizeof(float), &p));
+    py::capsule owner(p, [](void* q) { akr_host_free(q); });
+    std::vector<py::ssize_t> shp(shape.begin(), shape.end());
+    return py::array_t<float>(shp, static_cast<float*>(p), owner);
+}
+
+TensorPtr to_device(const TensorPtr& t, const std::string& target) {
+    if (target == t->device) return t;
+    if (target != "cuda" && target != "cpu") throw std::invalid_argument("Unknown device '" + target + "'");
+    auto out = std::make_shared<Tensor>(t->shape, target);
+    const size_t bytes = (size_t)t->size * sizeof(float);
+    if (target == "cuda") {
+        if (!t->is_contiguous()) throw std::runtime_error("to('cuda'): CPU tensor must be contiguous");
+        check(akr_memcpy_h2d(out->data, t->data, bytes, nullptr));
+        check(akr_stream_synchronize(nullptr));
+    } else {
+        bool prev = g_grad_enabled;
+        g_grad_enabled = false;
+        TensorPtr src = t->is_contiguous() ? t : op_contiguous(t);
+        g_grad_enabled = prev;
+        check(akr_memcpy_d2h(out->data, src->data, bytes, nullptr));
+        check(akr_synchronize());
+    }
+    out->requires_grad = t->requires_grad;
+    return out;
+}
+
+void copy_into(const TensorPtr& dst, const TensorPtr& src) {
+    if (dst->size != src->size) throw std::invalid_argument("copy_: size mismatch");
+    if (!dst->is_contiguous()) throw std::invalid_argument("copy_: destination must be contiguous");
+    require_cuda(dst, "copy_");
+    bool prev = g_grad_enabled;
+    g_grad_enabled = false;
+    TensorPtr s = src->is_contiguous() ? src : op_contiguous(src);
+    g_grad_enabled = prev;
+    if (s->device == "cuda") check(akr_memcpy_d2d(dst->data, s->data, (size_t)dst->size * sizeof(float), nullptr));
+    else {
+        check(akr_memcpy_h2d(dst->data, s->data, (size_t)dst->size * sizeof(float), nullptr));
+        check(akr_stream_synchronize(nullptr));
+    }
+}
+
+float item(const TensorPtr& t) {
+    if (t->size != 1) throw std::runtime_error("item() only works on tensors with exactly one element");
+    float v = 0.f;
+    if (t->device == "cuda") {
+        check(akr_memcpy_d2h(&v, t->data, sizeof(float), nullptr));
+        check(akr_synchronize());
+    } else {
+        v = t->data[0];
+    }
+    return v;
+}
+
+// Basic indexing: ints, slices and tuples of them produce a view (offset + scaled strides), as
+// Tensor.__getitem__ of the reference does (src/bindings.cpp:2613-2732). Gradients do not flow
+// through a slice in this build.
+TensorPtr getitem(const TensorPtr& self, py::object key) {
+    if (needs_graph(self))
+        throw std::runtime_error("__getitem__: autograd through slicing is outside the matmul path of this build; "
+                                 "slice a detached tensor or under no_grad()");
+    py::tuple keys = py::isinstance<py::tuple>(key) ? key.cast<py::tuple>() : py::make_tuple(key);
+    if (keys.size() > self->shape.size()) throw std::out_of_range("too many indices for tensor");
+    std::vector<int64_t> shape, strides;
+    int64_t off = 0;
+    size_t dim = 0;
+    for (auto k : keys) {
+        const int64_t extent = self->shape[dim], st = self->strides[dim];
+        if (py::isinstance<py::slice>(k)) {
+            py::ssize_t start, stop, step, len;
+            if (!k.cast<py::slice>().compute(extent, &start, &stop, &step, &len)) throw py::error_already_set();
+            if (step <= 0) throw std::invalid_argument("slice step must be positive");
+            if (len <= 0) throw std::invalid_argument("Tensor dimensions must be positive");
+            off += start * st;
+            shape.push_back(len);
+            strides.push_back(st * step);
+        } else if (py::isinstance<py::int_>(k)) {
+            int64_t i = k.cast<int64_t>();
+            if (i < 0) i += extent;
+            if (i < 0 || i >= extent) throw std::out_of_range("index out of range");
+            off += i * st;
+        } else {
+            throw std::invalid_argument("unsupported index type (ints and slices only)");
+        }
+        ++dim;
+    }
+    for (; dim < self->shape.size(); ++dim) {
+        shape.push_back(self->shape[dim]);
+        strides.push_back(self->strides[dim]);
+    }
+    if (shape.empty()) {
+        shape.push_back(1);
+        strides.push_back(1);
+    }
+    return std::make_shared<Tensor>(self, off, shape, strides);
+}
+
+std::string repr(const TensorPtr& t) {
+    std::ostringstream os;
+    os << "Tensor(shape=[";
+    for (size_t i = 0; i < t->shape.size(); ++i) os << (i ? ", " : "") << t->shape[i];
+    os << "], device='" << t->device << "', dtype=float32" << (t->requires_grad ? ", requires_grad=True" : "") << ")";
+    return os.str();
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_C, m) {
+    m.doc() = "aakaar_b200: B200-native fp32 matmul path behind the Aakaar API";
+
+    py::class_<Tensor, TensorPtr>(m, "Tensor")
+        .def(py::init([](std::vector<int64_t> shape, std::string device) {
+                 return std::make_shared<Tensor>(shape, device);
+             }),
+             py::arg("shape"), py::arg("device") = "cuda")
+        .def_property_readonly("dtype", [](Tensor&) { return std::string("float32"); })
+        .def_readonly("device", &Tensor::device)
+        .def_readonly("size", &Tensor::size)
+        .def_readonly("shape", &Tensor::shape)
+        .def_readonly("strides", &Tensor::strides)
+        .def_readwrite("requires_grad", &Tensor::requires_grad)
+        .def_property(
+            "grad", [](Tensor& t) { return t.grad; }, [](Tensor& t, TensorPtr g) { t.grad = g; })
+        .def_property_readonly("is_leaf", [](Tensor& t) { return !t.grad_fn; })
+        .def_property_readonly("data_ptr", [](Tensor& t) { return (uintptr_t)t.data; })
+        .def("to_numpy", &to_numpy)
+        .def("copy_to_host", &copy_to_host)
+        .def("is_contiguous", &Tensor::is_contiguous)
+        .def("contiguous", &op_contiguous)
+        .def("tanh", &op_tanh)
+        .def("copy_", [](TensorPtr self, TensorPtr src) { copy_into(self, src); return self; })
+        .def("to", &to_device)
+        .def("to_device", &to_device)
+        .def("transpose", &op_transpose)
+        .def("transpose2d", [](TensorPtr self) { return op_transpose(self, -2, -1); })
+        .def_property_readonly("T", [](TensorPtr self) { return op_transpose(self, -2, -1); })
+        .def("backward", &tensor_backward, py::arg("grad_output") = nullptr, py::arg("retain_graph") = false)
+        .def("zero_grad", [](Tensor& t) { t.grad = nullptr; })
+        .def("item", &item)
+        .def("detach",
+             [](TensorPtr self) { return std::make_shared<Tensor>(self, 0, self->shape, self->strides); })
+        .def("__repr__", &repr)
+        .def("__str__", &repr)
+        .def("__len__", [](Tensor& t) { return t.shape.empty() ? (int64_t)0 : t.shape[0]; })
+        .def("view", [](TensorPtr self, std::vector<int64_t> s) { return op_view(self, s, false); })
+        .def("reshape", [](TensorPtr self, std::vector<int64_t> s) { return op_view(self, s, true); })
+        .def("sum", [](TensorPtr self) { return op_sum_all(self); })
+        .def("__getitem__", &getitem)
+        .def("__neg__", [](TensorPtr a) { return op_scale(a, -1.0f); })
+        .def("__add__", [](TensorPtr a, TensorPtr b) { return op_add(a, b); })
+        .def("__add__", [](TensorPtr a, float s) { return op_add(a, scalar_tensor(s)); })
+        .def("__radd__", [](TensorPtr a, float s) { return op_add(a, scalar_tensor(s)); })
+        .def("__sub__", [](TensorPtr a, TensorPtr b) { return op_sub(a, b); })
+        .def("__sub__", [](TensorPtr a, float s) { return op_add(a, scalar_tensor(-s)); })
+        .def("__mul__", [](TensorPtr a, float s) { return op_scale(a, s); })
+        .def("__rmul__", [](TensorPtr a, float s) { return op_scale(a, s); })
+        .def("__truediv__", [](TensorPtr a, float s) { return op_scale(a, 1.0f / s); })
+        .def("__matmul__", &op_matmul);
+
+    m.def("_set_grad_enabled", [](bool e) { g_grad_enabled = e; });
+    m.def("_is_grad_enabled", []() { return g_grad_enabled; });
+    m.def("cuda_matmul", &op_matmul, "tcgen05 GPU matrix multiplication (autograd-aware)");
+    m.def("cpu_matmul", &cpu_matmul_refused, "not available: this build has no CPU matmul");
+    m.def("linear", &op_matmul_bias, py::arg("x"), py::arg("weight"), py::arg("bias") = nullptr,
+          "x @ weight + bias with the bias add fused into the GEMM epilogue");
+    m.def("from_numpy", &from_numpy, py::arg("array"), py::arg("device") = "cuda", py::arg("requires_grad") = false);
+    m.def("from_pinned", &from_pinned, py::arg("array"), py::arg("requires_grad") = false);
+    m.def("pinned_empty", &pinned_empty, py::arg("shape"));
+    m.def("is_available", []() { return akr_device_count() > 0; });
+    m.def("device_count", []() { return akr_device_count(); });
+    m.def("set_device", [](int d) { check(akr_set_device(d)); });
+    m.def("empty_cache", []() { check(akr_empty_cache()); });
+    m.def("_set_tf32_enabled", [](bool e) { akr_set_tf32(e ? 1 : 0); });
+    m.def("_get_tf32_enabled", []() { return akr_get_tf32() != 0; });
+    m.def("_set_cudnn_tf32_enabled", [](bool e) { akr_set_cudnn_tf32(e ? 1 : 0); });
+    m.def("_get_cudnn_tf32_enabled", []() { return akr_get_cudnn_tf32() != 0; });
+    m.def("_synchronize", []() { check(akr_synchronize()); });
+    m.def("_allocator_stats", []() {
+        int64_t h = 0, mi = 0;
+        akr_allocator_stats(&h, &mi);
+        return py::make_tuple(h, mi);
+    });
+    m.def("_workspace_bytes", []() {
+        size_t b = 0;
+        akr_workspace_bytes(&b);
+        return b;
+    });
+    m.def("_launch_count", [](bool reset) { return akr_launch_count(reset ? 1 : 0); }, py::arg("reset") = false);
+    m.def("_mse_fused", &op_mse, py::arg("pred"), py::arg("target"));
+    m.def("_sgd_step_fused", &op_sgd_step);
+    m.def("_set_matmul_mode", [](int mode) { g_matmul_mode_override = mode; },
+          "per-process override of the arithmetic mode: -1 follow set_tf32, 0 fp32-accurate, 1 TF32");
+    m.attr("HAS_CUDA") = true;
+    m.attr("HAS_CUDNN") = false;
+}

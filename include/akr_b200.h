@@ -1,0 +1,169 @@
+/*
+ * akr_b200.h - C ABI of the B200 (sm_100a) fp32 matmul path.
+ *
+ * This is the drop-in boundary for the matmul hot path of the Aakaar tensor library: plain
+ * pointers and sizes, no C++ types, no PyTorch types. A maintainer of the reference binds these
+ * entry points from src/bindings.cpp in place of the functions of src/matmul_kernel.cu; the
+ * reference function each entry point stands in for is cited beside it (paths relative to the
+ * reference checkout).
+ *
+ * Conventions
+ *   - Every function returns AKR_OK (0) or a negative status; nothing throws across this boundary.
+ *     akr_last_error() returns the message of the last failing call on the calling thread.
+ *     AKR_ERR_INVALID corresponds to the reference's std::invalid_argument (Python ValueError),
+ *     AKR_ERR_RUNTIME / AKR_ERR_CUDA to std::runtime_error (Python RuntimeError).
+ *   - Tensors are described by akr_view: base pointer of the view, up to 8 dims, shape and
+ *     strides in ELEMENTS (the reference's Tensor::shape / Tensor::strides, src/tensor.h:46-50).
+ *     Views may be transposed, sliced or broadcast; operands are never required to be contiguous.
+ *   - All device pointers belong to the current CUDA device of the calling thread.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is what
+ *     the reference uses). Work is asynchronous to the host, as in the reference. Calls that need
+ *     scratch memory share one per-device workspace, ordered by the stream: issue the calls of one
+ *     device on one stream, or serialise streams yourself.
+ *   - There is no CPU fallback: without a usable GPU every compute entry point fails with
+ *     AKR_ERR_NOGPU.
+ */
+#ifndef AKR_B200_H
+#define AKR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AKR_MAX_DIMS 8
+
+/* Exported entry points keep default visibility; everything else in the library is hidden. */
+#if defined(__GNUC__)
+#define AKR_API __attribute__((visibility("default")))
+#else
+#define AKR_API
+#endif
+
+enum {
+    AKR_OK = 0,
+    AKR_ERR_INVALID = -1, /* bad shape / argument: the reference's std::invalid_argument */
+    AKR_ERR_RUNTIME = -2, /* the reference's std::runtime_error */
+    AKR_ERR_CUDA = -3,    /* a CUDA runtime / driver call failed */
+    AKR_ERR_NOGPU = -4,   /* no CUDA device: this library has no CPU path */
+    AKR_ERR_ABORTED = -5  /* a kernel gave up on a bounded wait (device status word set) */
+};
+
+enum { AKR_DTYPE_F32 = 0 }; /* src/dtype.h: FLOAT32 = 0; the other dtypes are outside this path */
+
+/* Arithmetic mode of one call. AKR_MODE_GLOBAL follows akr_set_tf32(). */
+enum {
+    AKR_MODE_GLOBAL = -1,
+    AKR_MODE_FP32 = 0, /* 3xTF32 split products: fp32-level accuracy (set_tf32(False)) */
+    AKR_MODE_TF32 = 1  /* single TF32 products (set_tf32(True)) */
+};
+
+typedef struct akr_view {
+    void* data;    /* first element of the view (device memory) */
+    int32_t ndim;  /* 0..AKR_MAX_DIMS */
+    int32_t dtype; /* AKR_DTYPE_F32 */
+    int64_t shape[AKR_MAX_DIMS];
+    int64_t stride[AKR_MAX_DIMS]; /* in elements; may be 0 (broadcast) */
+} akr_view;
+
+/* ------------------------------------------------------------------ errors / info */
+AKR_API const char* akr_last_error(void);
+AKR_API int akr_version(void);
+/* Number of visible CUDA devices (0 without a driver); never fails. Cf. _C.device_count. */
+AKR_API int akr_device_count(void);
+AKR_API int akr_set_device(int ordinal);
+
+/* ------------------------------------------------------------------ global switches
+ * set_tf32_enabled / get_tf32_enabled, src/matmul_kernel.cu:20-37 (default off = fp32-accurate).
+ * The cuDNN flag lives in the same reference file (:24-27) and is read by the conv sources; it is
+ * kept so that a replaced matmul_kernel.cu still exports it, and does nothing here. */
+AKR_API void akr_set_tf32(int enabled);
+AKR_API int akr_get_tf32(void);
+AKR_API void akr_set_cudnn_tf32(int enabled);
+AKR_API int akr_get_cudnn_tf32(void);
+/* cuda_synchronize, src/matmul_kernel.cu:39-41. Also reports a kernel that aborted. */
+AKR_API int akr_synchronize(void);
+
+/* ------------------------------------------------------------------ memory
+ * CachingAllocator, src/allocator.h:12-60: exact-size free lists keyed by element count, blocks
+ * are returned to the driver only by akr_empty_cache(); hit / miss counters as _allocator_stats. */
+AKR_API int akr_alloc(size_t nfloats, float** out);
+AKR_API int akr_free(float* ptr, size_t nfloats);
+AKR_API int akr_empty_cache(void);
+AKR_API int akr_allocator_stats(int64_t* hits, int64_t* misses);
+/* Pinned host staging (src/pinned_allocator.h) and copies (Tensor::to_device, src/tensor.h:418-465;
+ * from_numpy, src/bindings.cpp:2399-2469; to_numpy, src/tensor.h:473-517). */
+AKR_API int akr_host_alloc(size_t bytes, void** out);
+AKR_API int akr_host_free(void* ptr);
+AKR_API int akr_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+AKR_API int akr_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+AKR_API int akr_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+AKR_API int akr_memset_zero(void* dst, size_t bytes, void* stream);
+AKR_API int akr_stream_synchronize(void* stream);
+
+/* ------------------------------------------------------------------ matmul
+ * Shape planning of plan_nd_matmul, src/matmul_kernel.cu:55-83: right-aligned broadcast of the
+ * batch dims, inner-dimension check. Writes the result shape (batch dims + [M, N]).
+ * Pure host code: works without a GPU. */
+AKR_API int akr_matmul_plan(const akr_view* a, const akr_view* b, int64_t* out_shape, int32_t* out_ndim);
+
+/* Forward: run_cublas_matmul, src/matmul_kernel.cu:111-143, for every broadcast batch index in ONE
+ * launch, reading strided views in place. `c` must have the planned shape (any strides with a
+ * unit-stride last dim). `bias` (optional, N values, shape [N] or [1, N]) is added to every row in
+ * the epilogue: the `+ bias` of nn.Linear (aakaar/nn.py:14-15, broadcast add of
+ * src/elementwise_kernel.cu:46-65). */
+AKR_API int akr_matmul_fwd(const akr_view* a, const akr_view* b, const akr_view* bias_or_null, akr_view* c,
+                   int mode, void* stream);
+
+/* Backward of C = A @ B: the lambda of dispatch_matmul, src/bindings.cpp:1726-1759.
+ *   dA = dC . B^T  and  dB = A^T . dC, each summed over the batch dims along which its operand was
+ * broadcast (reduce_grad_to_shape, src/bindings.cpp:1467-1503 + sum_axis_kernel,
+ * src/reduction_kernel.cu:10-26), without transposed copies or the unreduced intermediate.
+ * da / db have the shapes of a / b; either may be NULL to skip that gradient. */
+AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da_or_null,
+                   akr_view* db_or_null, int mode, void* stream);
+
+/* 2-D products the reference exports separately:
+ *   run_cublas_matmul_a_bt, src/matmul_kernel.cu:347-373: C(m,n) = A(m,k) . B(n,k)^T
+ *   run_cublas_matmul_at_b, src/matmul_kernel.cu:378-402: C(m,n) = A(k,m)^T . B(k,n) */
+AKR_API int akr_matmul_a_bt(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream);
+AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream);
+
+/* Plain fp32 FMA matmul on CUDA cores with the same broadcasting (no tensor cores, no TF32).
+ * A slow on-device cross-check for shapes where a host check takes too long; not used by the
+ * product path. */
+AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
+
+/* Bytes of scratch the library currently holds on this device (operand splits, split-K partials). */
+AKR_API int akr_workspace_bytes(size_t* bytes);
+/* Number of kernels launched by this library on this thread's device since the last reset. */
+AKR_API int64_t akr_launch_count(int reset);
+
+/* ------------------------------------------------------------------ support ops of the Linear step
+ * Thin bandwidth-bound kernels so that nn.Linear training (Linear, tanh, MSE, SGD) runs end to end.
+ *   contiguous    : strided gather, src/strided_copy_kernel.cu:13-41 (Tensor::contiguous)
+ *   add           : same-shape or broadcast add, src/elementwise_kernel.cu:46-65
+ *   sum_to        : reduce_grad_to_shape for a generic broadcast add (bias gradient)
+ *   tanh fwd/bwd  : src/elementwise_kernel.cu:494-584
+ *   mse fwd/bwd   : src/elementwise_kernel.cu:2253-2300
+ *   sgd_step      : src/optim_kernels.cu:21-55 (plain / weight decay / momentum) */
+AKR_API int akr_contiguous(const akr_view* src, float* dst, void* stream);
+AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* stream);
+AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream);
+AKR_API int akr_scale(const float* x, float alpha, float* y, size_t n, void* stream);
+AKR_API int akr_tanh_fwd(const float* x, float* y, size_t n, void* stream);
+AKR_API int akr_tanh_bwd(const float* grad, const float* y, float* dx, size_t n, void* stream);
+AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream);
+AKR_API int akr_mse_bwd(const float* pred, const float* target, const float* grad_scalar, float* dpred,
+                size_t n, void* stream);
+AKR_API int akr_sgd_step(float* param, const float* grad, float* velocity_or_null, float lr, float momentum,
+                 float weight_decay, float dampening, int nesterov, int has_momentum,
+                 int velocity_initialized, size_t n, void* stream);
+AKR_API int akr_fill(float* x, float value, size_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKR_B200_H */

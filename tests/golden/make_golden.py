@@ -1,0 +1,135 @@
+"""Generates tests/golden/ref_vectors.npz by running the REFERENCE's own CPU build.
+
+Run in the authoring container only (needs oracle/_ref built by oracle/build_ref.sh from the
+reference checkout):  python tests/golden/make_golden.py
+
+Every case records seeded inputs recipes (regenerated in the tests from the same seeds) and the
+reference's outputs. Large outputs are stored as sampled rows plus norms so the file stays small.
+Inputs come from numpy PCG64 generators, float32, exactly as tests/util.py regenerates them.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import _C as ref  # noqa: E402  (the reference's pybind11 module, CPU build)
+
+from util import uniform, normal  # noqa: E402
+
+
+def T(x, grad=False):
+    return ref.from_numpy(np.ascontiguousarray(x, dtype=np.float32), "cpu", grad)
+
+
+def fwd_bwd(a_np, b_np, dc_np=None, contiguous_a=None):
+    """Reference forward + backward. `contiguous_a`: a callable building A from its base tensor."""
+    a = T(a_np, True)
+    b = T(b_np, True)
+    c = ref.cpu_matmul(a, b)
+    if dc_np is None:
+        dc_np = np.ones(c.shape, dtype=np.float32)
+    c.backward(T(dc_np))
+    return c.to_numpy(), a.grad.to_numpy(), b.grad.to_numpy()
+
+
+out = {}
+meta = {"generator": "reference CPU build (oracle/_ref), OpenBLAS 0.3.15", "cases": {}}
+
+# 1. documentation example, docs/concepts/math-operations/matmul.md:36-57
+a = np.array([[1, 2, 3], [4, 5, 6]], dtype=np.float32)
+b = np.array([[1, 2], [3, 4], [5, 6]], dtype=np.float32)
+A, B = T(a, True), T(b, True)
+C = ref.cpu_matmul(A, B)
+loss = C.sum()
+loss.backward()
+out["doc_c"], out["doc_da"], out["doc_db"] = C.to_numpy(), A.grad.to_numpy(), B.grad.to_numpy()
+meta["cases"]["doc"] = {"a": a.tolist(), "b": b.tolist()}
+
+# 2. config 1: 512^3, uniform[-1,1) seeds 101/102, dC = ones; sampled rows + norms
+a, b = uniform((512, 512), 101), uniform((512, 512), 102)
+c, da, db = fwd_bwd(a, b)
+rows = [0, 7, 255, 511]
+for name, arr in (("c", c), ("da", da), ("db", db)):
+    out[f"cfg1_{name}_rows"] = arr[rows]
+    out[f"cfg1_{name}_norm"] = np.array([np.linalg.norm(arr.astype(np.float64))])
+    out[f"cfg1_{name}_sum"] = np.array([arr.astype(np.float64).sum()])
+meta["cases"]["cfg1"] = {"rows": rows, "seed_a": 101, "seed_b": 102}
+
+# 3. N-D broadcast, both sides broadcast somewhere: A[3,1,5,7] @ B[2,7,4]
+a, b = uniform((3, 1, 5, 7), 11), uniform((2, 7, 4), 12)
+dc = normal((3, 2, 5, 4), 13)
+out["nd_c"], out["nd_da"], out["nd_db"] = fwd_bwd(a, b, dc)
+
+# 4. [B,T,in] @ [in,out]: leading dims of dW summed away
+a, b = uniform((2, 3, 8), 21), uniform((8, 5), 22)
+dc = normal((2, 3, 5), 23)
+out["bt_c"], out["bt_da"], out["bt_db"] = fwd_bwd(a, b, dc)
+
+# 5. config 3 analogue: A = base[4,2,6,16].transpose(-1,-2) (reference needs .contiguous()), B [1,2,6,16]
+base, b = uniform((4, 2, 6, 16), 301), uniform((1, 2, 6, 16), 302)
+base_t = T(base, True)
+a_view = base_t.transpose(2, 3).contiguous()
+bt = T(b, True)
+c = ref.cpu_matmul(a_view, bt)
+c.backward(T(np.ones(c.shape, dtype=np.float32)))
+out["cfg3s_c"], out["cfg3s_dbase"], out["cfg3s_db"] = c.to_numpy(), base_t.grad.to_numpy(), bt.grad.to_numpy()
+
+# 6. ragged 2-D sizes (no multiple of any tile), dC random
+a, b = uniform((77, 45), 31), uniform((45, 19), 32)
+dc = normal((77, 19), 33)
+out["rag_c"], out["rag_da"], out["rag_db"] = fwd_bwd(a, b, dc)
+
+# 7. shared operand: s @ s accumulates both contributions into s.grad
+s_np = uniform((6, 6), 41)
+s = T(s_np, True)
+c = ref.cpu_matmul(s, s)
+c.backward(T(np.ones((6, 6), dtype=np.float32)))
+out["ss_c"], out["ss_ds"] = c.to_numpy(), s.grad.to_numpy()
+
+# 8. MLP training step (config 2 analogue, small): Linear 32->48, tanh, Linear 48->16, MSE, SGD lr 0.01
+x, tgt = normal((64, 32), 201), normal((64, 16), 202)
+rng = np.random.RandomState(203)
+w1 = rng.uniform(-1 / np.sqrt(32), 1 / np.sqrt(32), (32, 48)).astype(np.float32)
+w2 = rng.uniform(-1 / np.sqrt(48), 1 / np.sqrt(48), (48, 16)).astype(np.float32)
+W1, B1 = T(w1, True), T(np.zeros((1, 48), np.float32), True)
+W2, B2 = T(w2, True), T(np.zeros((1, 16), np.float32), True)
+X, TG = T(x), T(tgt)
+h = (ref.cpu_matmul(X, W1) + B1).tanh()
+y = ref.cpu_matmul(h, W2) + B2
+diff = y - TG
+loss = (diff * diff).sum() / y.size
+loss.backward()
+out["mlp_loss"] = loss.to_numpy()
+out["mlp_y"] = y.to_numpy()
+for n, p in (("w1", W1), ("b1", B1), ("w2", W2), ("b2", B2)):
+    out[f"mlp_d{n}"] = p.grad.to_numpy()
+for p in (W1, B1, W2, B2):
+    vel = ref.from_numpy(np.zeros(p.shape, np.float32), "cpu", False)
+    ref._sgd_step_fused(p, p.grad, vel, 0.01, 0.0, 0.0, 0.0, 0, 0, 0)
+for n, p in (("w1", W1), ("b1", B1), ("w2", W2), ("b2", B2)):
+    out[f"mlp_new_{n}"] = p.to_numpy()
+
+# 9. error behaviour of the reference (messages the C ABI reproduces)
+errs = {}
+def err_of(fn):
+    try:
+        fn()
+    except Exception as e:  # noqa: BLE001
+        return [type(e).__name__, str(e)]
+    return None
+errs["k_mismatch"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3))), T(np.ones((4, 2)))))
+errs["batch_mismatch"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 2, 3))), T(np.ones((3, 3, 2)))))
+errs["non_contiguous"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3))).transpose(0, 1), T(np.ones((2, 2)))))
+errs["non_scalar_backward"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3)), True), T(np.ones((3, 2)))).backward())
+meta["errors"] = errs
+
+np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **out)
+with open(os.path.join(HERE, "ref_vectors.json"), "w") as f:
+    json.dump(meta, f, indent=1)
+print("wrote", len(out), "arrays;", os.path.getsize(os.path.join(HERE, "ref_vectors.npz")), "bytes")
+print(json.dumps(errs, indent=1))

@@ -1,0 +1,306 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same
+seeded inputs, against the committed vectors of the reference's own build, and at full benchmark
+sizes through sampled rows and size-independent properties.
+
+Tolerances (relative Frobenius error): 1e-5 in fp32 mode (3xTF32), 2e-3 in TF32 mode.
+"""
+import numpy as np
+import pytest
+
+from util import load_golden, uniform, normal, rel_fro, TOL_FP32, TOL_TF32
+from oracle import matmul_oracle as mo
+from aakaar_b200 import cabi
+from aakaar_b200.cabi import DeviceArray as DA, MODE_FP32, MODE_TF32
+
+pytestmark = pytest.mark.gpu
+
+MODES = [(MODE_FP32, TOL_FP32), (MODE_TF32, TOL_TF32)]
+G, META = None, None
+
+
+def setup_module(module):
+    global G, META
+    G, META = load_golden()
+
+
+def dev(x):
+    return DA.from_numpy(x)
+
+
+def fwd_np(a_np, b_np, mode):
+    return cabi.matmul_fwd(dev(a_np), dev(b_np), mode=mode).to_numpy()
+
+
+# ------------------------------------------------------------------ golden vectors of the reference
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_golden_config1(mode, tol):
+    a, b = uniform((512, 512), 101), uniform((512, 512), 102)
+    da_, db_ = dev(a), dev(b)
+    c = cabi.matmul_fwd(da_, db_, mode=mode)
+    ga, gb = cabi.matmul_bwd(da_, db_, dev(np.ones((512, 512), np.float32)), mode=mode)
+    rows = META["cases"]["cfg1"]["rows"]
+    for name, arr in (("c", c.to_numpy()), ("da", ga.to_numpy()), ("db", gb.to_numpy())):
+        assert rel_fro(arr[rows], G[f"cfg1_{name}_rows"]) < tol, name
+        assert abs(np.linalg.norm(arr.astype(np.float64)) / G[f"cfg1_{name}_norm"][0] - 1) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_golden_small_cases(mode, tol):
+    exact = np.array([[22, 28], [49, 64]], dtype=np.float32)
+    a = np.array(META["cases"]["doc"]["a"], dtype=np.float32)
+    b = np.array(META["cases"]["doc"]["b"], dtype=np.float32)
+    np.testing.assert_array_equal(fwd_np(a, b, mode), exact)  # small integers are exact in TF32 too
+
+    for key, (sa, sb, sc, seeds) in {
+        "nd": ((3, 1, 5, 7), (2, 7, 4), (3, 2, 5, 4), (11, 12, 13)),
+        "bt": ((2, 3, 8), (8, 5), (2, 3, 5), (21, 22, 23)),
+        "rag": ((77, 45), (45, 19), (77, 19), (31, 32, 33)),
+    }.items():
+        a, b, dc = uniform(sa, seeds[0]), uniform(sb, seeds[1]), normal(sc, seeds[2])
+        A, B = dev(a), dev(b)
+        assert rel_fro(cabi.matmul_fwd(A, B, mode=mode).to_numpy(), G[f"{key}_c"]) < tol
+        ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+        assert ga.shape == sa and gb.shape == sb
+        assert rel_fro(ga.to_numpy(), G[f"{key}_da"]) < tol
+        assert rel_fro(gb.to_numpy(), G[f"{key}_db"]) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_golden_transposed_view_no_copy(mode, tol):
+    # The reference needs A.contiguous(); here the transposed view is read in place.
+    base, b = uniform((4, 2, 6, 16), 301), uniform((1, 2, 6, 16), 302)
+    Abase, B = dev(base), dev(b)
+    A = Abase.transpose(2, 3)
+    c = cabi.matmul_fwd(A, B, mode=mode)
+    assert c.shape == (4, 2, 16, 16)
+    assert rel_fro(c.to_numpy(), G["cfg3s_c"]) < tol
+    ga, gb = cabi.matmul_bwd(A, B, dev(np.ones(c.shape, np.float32)), mode=mode)
+    assert gb.shape == (1, 2, 6, 16)
+    assert rel_fro(np.swapaxes(ga.to_numpy(), -1, -2), G["cfg3s_dbase"]) < tol
+    assert rel_fro(gb.to_numpy(), G["cfg3s_db"]) < tol
+
+
+# ------------------------------------------------------------------ shape grid against the oracle
+
+SHAPES = [
+    (1, 1, 1), (1, 7, 3), (5, 1, 9), (16, 16, 16), (33, 65, 17), (128, 128, 32), (128, 256, 64),
+    (129, 257, 33), (200, 300, 100), (256, 512, 1000), (511, 130, 7), (64, 2048, 96), (1000, 24, 513),
+]
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_shape_grid_forward_backward(M, N, K, mode, tol):
+    a, b, dc = uniform((M, K), M * 7 + K), uniform((K, N), N * 3 + K + 1), normal((M, N), M + N)
+    A, B = dev(a), dev(b)
+    ref = mo.matmul_forward(a, b, np.float64)
+    assert rel_fro(cabi.matmul_fwd(A, B, mode=mode).to_numpy(), ref) < tol
+    ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+    rda, rdb = mo.matmul_backward(a, b, dc, np.float64)
+    assert rel_fro(ga.to_numpy(), rda) < tol
+    assert rel_fro(gb.to_numpy(), rdb) < tol
+
+
+BCAST = [
+    ((4, 40, 24), (24, 56)),            # rank mismatch: B has no batch dim
+    ((24, 56), (5, 56, 40)),            # A has no batch dim
+    ((3, 1, 33, 20), (1, 4, 20, 48)),   # both broadcast
+    ((2, 3, 4, 16, 8), (4, 8, 24)),     # three batch dims
+    ((6, 1, 2, 16, 12), (1, 5, 1, 12, 8)),  # interleaved broadcast dims (host-looped)
+    ((1, 1, 9, 5), (1, 5, 3)),          # all-ones batch
+]
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+@pytest.mark.parametrize("sa,sb", BCAST)
+def test_batch_broadcast(sa, sb, mode, tol):
+    a, b = uniform(sa, 5), uniform(sb, 6)
+    batch, M, K, N = mo.plan_nd_matmul(sa, sb)
+    dc = normal(tuple(batch) + (M, N), 7)
+    A, B = dev(a), dev(b)
+    assert cabi.plan(A, B) == tuple(batch) + (M, N)
+    assert rel_fro(cabi.matmul_fwd(A, B, mode=mode).to_numpy(), mo.matmul_forward(a, b, np.float64)) < tol
+    ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+    rda, rdb = mo.matmul_backward(a, b, dc, np.float64)
+    assert ga.shape == sa and gb.shape == sb
+    assert rel_fro(ga.to_numpy(), rda) < tol
+    assert rel_fro(gb.to_numpy(), rdb) < tol
+
+
+# ------------------------------------------------------------------ strided views, no copies
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_transposed_and_sliced_views(mode, tol):
+    base_a, base_b = uniform((3, 72, 136), 81), uniform((3, 200, 72), 82)
+    Abase, Bbase = dev(base_a), dev(base_b)
+    # A = base_a^T  (M-major view), B = base_b^T (K... N-major becomes K-major view)
+    A, B = Abase.transpose(1, 2), Bbase.transpose(1, 2)
+    a, b = np.swapaxes(base_a, 1, 2), np.swapaxes(base_b, 1, 2)
+    ref = mo.matmul_forward(np.ascontiguousarray(a), np.ascontiguousarray(b), np.float64)
+    assert rel_fro(cabi.matmul_fwd(A, B, mode=mode).to_numpy(), ref) < tol
+    dc = normal(ref.shape, 83)
+    ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+    rda, rdb = mo.matmul_backward(np.ascontiguousarray(a), np.ascontiguousarray(b), dc, np.float64)
+    assert rel_fro(ga.to_numpy(), rda) < tol and rel_fro(gb.to_numpy(), rdb) < tol
+
+    # slices: aligned offset (TMA in place), odd offset and stepped inner dim (packed)
+    big = uniform((160, 200), 84)
+    Big = dev(big)
+    other = uniform((64, 40), 85)
+    Other = dev(other)
+    for (r0, r1, c0, c1, cs) in [(32, 96, 64, 128, 1), (3, 67, 5, 69, 1), (0, 64, 1, 129, 2)]:
+        sub = big[r0:r1, c0:c1:cs]
+        V = Big.as_strided(sub.shape, (200, cs), offset=r0 * 200 + c0)
+        ref = mo.matmul_forward(np.ascontiguousarray(sub), other, np.float64)
+        assert rel_fro(cabi.matmul_fwd(V, Other, mode=mode).to_numpy(), ref) < tol
+        dcs = normal(ref.shape, 86)
+        ga, gb = cabi.matmul_bwd(V, Other, dev(dcs), mode=mode)
+        rda, rdb = mo.matmul_backward(np.ascontiguousarray(sub), other, dcs, np.float64)
+        assert rel_fro(ga.to_numpy(), rda) < tol and rel_fro(gb.to_numpy(), rdb) < tol
+    # non-contiguous grad_output (the reference's 2-D backward raises here)
+    a, b = uniform((48, 40), 87), uniform((40, 56), 88)
+    dct = normal((56, 48), 89)
+    DCt = dev(dct).transpose(0, 1)
+    ga, gb = cabi.matmul_bwd(dev(a), dev(b), DCt, mode=mode)
+    rda, rdb = mo.matmul_backward(a, b, np.ascontiguousarray(dct.T), np.float64)
+    assert rel_fro(ga.to_numpy(), rda) < tol and rel_fro(gb.to_numpy(), rdb) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_a_bt_at_b_and_bias(mode, tol):
+    import ctypes as C
+    lib = cabi.lib()
+    a, b = uniform((70, 52), 91), uniform((90, 52), 92)
+    A, B, Cc = dev(a), dev(b), DA((70, 90))
+    va, vb, vc = A.view(), B.view(), Cc.view()
+    cabi.check(lib.akr_matmul_a_bt(C.byref(va), C.byref(vb), C.byref(vc), mode, None))
+    assert rel_fro(Cc.to_numpy(), a.astype(np.float64) @ b.astype(np.float64).T) < tol
+    a2, b2 = uniform((52, 70), 93), uniform((52, 90), 94)
+    A2, B2, C2 = dev(a2), dev(b2), DA((70, 90))
+    va, vb, vc = A2.view(), B2.view(), C2.view()
+    cabi.check(lib.akr_matmul_at_b(C.byref(va), C.byref(vb), C.byref(vc), mode, None))
+    assert rel_fro(C2.to_numpy(), a2.astype(np.float64).T @ b2.astype(np.float64)) < tol
+    # fused Linear bias
+    x, w, bias = normal((130, 64), 95), uniform((64, 200), 96), normal((1, 200), 97)
+    y = cabi.matmul_fwd(dev(x), dev(w), bias=dev(bias), mode=mode).to_numpy()
+    assert rel_fro(y, x.astype(np.float64) @ w.astype(np.float64) + bias) < tol
+
+
+def test_error_paths_through_the_abi():
+    A, B = dev(np.ones((2, 3), np.float32)), dev(np.ones((4, 2), np.float32))
+    with pytest.raises(cabi.AkrError) as e:
+        cabi.matmul_fwd(A, B, out=DA((2, 2)))
+    assert e.value.code == cabi.ERR_INVALID and e.value.msg.startswith(META["errors"]["k_mismatch"][1])
+    with pytest.raises(cabi.AkrError) as e:
+        cabi.plan(dev(np.ones((2, 2, 3), np.float32)), dev(np.ones((3, 3, 2), np.float32)))
+    assert e.value.msg == META["errors"]["batch_mismatch"][1]
+    with pytest.raises(cabi.AkrError):
+        cabi.matmul_fwd(dev(np.ones((2, 3), np.float32)), dev(np.ones((3, 2), np.float32)), out=DA((2, 3)))
+
+
+def test_caching_allocator_semantics():
+    import ctypes as C
+    lib = cabi.lib()
+    h0, m0 = C.c_int64(), C.c_int64()
+    lib.akr_allocator_stats(C.byref(h0), C.byref(m0))
+    p = C.POINTER(C.c_float)()
+    cabi.check(lib.akr_alloc(12345, C.byref(p)))
+    first = C.cast(p, C.c_void_p).value
+    cabi.check(lib.akr_free(p, 12345))
+    q = C.POINTER(C.c_float)()
+    cabi.check(lib.akr_alloc(12345, C.byref(q)))   # exact-size reuse
+    assert C.cast(q, C.c_void_p).value == first
+    r = C.POINTER(C.c_float)()
+    cabi.check(lib.akr_alloc(12346, C.byref(r)))   # different size: a miss
+    assert C.cast(r, C.c_void_p).value != first
+    h1, m1 = C.c_int64(), C.c_int64()
+    lib.akr_allocator_stats(C.byref(h1), C.byref(m1))
+    assert h1.value >= h0.value + 1 and m1.value >= m0.value + 2 - 1
+    cabi.check(lib.akr_free(q, 12345))
+    cabi.check(lib.akr_free(r, 12346))
+
+
+# ------------------------------------------------------------------ benchmark-size checks
+
+def sampled_rows_check(A_np, B_np, C_np, rows, tol):
+    ref = A_np[rows].astype(np.float64) @ B_np.astype(np.float64)
+    assert rel_fro(C_np[rows], ref) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+@pytest.mark.parametrize("n", [2048, 4096])
+def test_square_sweep_sampled(n, mode, tol):
+    s = 1.0 / np.sqrt(n)
+    a, b, dc = normal((n, n), 401, s), normal((n, n), 402, s), normal((n, n), 403)
+    A, B, DC = dev(a), dev(b), dev(dc)
+    rows = [0, 1, n // 3, n // 2 + 5, n - 1]
+    c = cabi.matmul_fwd(A, B, mode=mode).to_numpy()
+    sampled_rows_check(a, b, c, rows, tol)
+    ga, gb = cabi.matmul_bwd(A, B, DC, mode=mode)
+    ga, gb = ga.to_numpy(), gb.to_numpy()
+    assert rel_fro(ga[rows], dc[rows].astype(np.float64) @ b.astype(np.float64).T) < tol
+    assert rel_fro(gb[rows], a[:, rows].astype(np.float64).T @ dc.astype(np.float64)) < tol
+    # on-device cross-check of the whole matrix with the plain-FMA kernel
+    c_simt = cabi.matmul_simt(A, B).to_numpy()
+    assert rel_fro(c, c_simt) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_config3_full_size(mode, tol):
+    # A [64,8,512,64] as a transposed view of [64,8,64,512], B [1,8,64,512]; dB sums over the 64.
+    base, b = uniform((64, 8, 64, 512), 301), uniform((1, 8, 64, 512), 302)
+    Abase, B = dev(base), dev(b)
+    A = Abase.transpose(2, 3)
+    assert A.strides == (262144, 32768, 1, 512)
+    c = cabi.matmul_fwd(A, B, mode=mode)
+    assert c.shape == (64, 8, 512, 512)
+    cn = c.to_numpy()
+    a64 = np.swapaxes(base, -1, -2).astype(np.float64)
+    for (i, j) in [(0, 0), (17, 3), (63, 7)]:
+        assert rel_fro(cn[i, j], a64[i, j] @ b[0, j].astype(np.float64)) < tol
+    dc = np.ones(c.shape, np.float32)
+    ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+    assert ga.shape == (64, 8, 512, 64) and gb.shape == (1, 8, 64, 512)
+    gan, gbn = ga.to_numpy(), gb.to_numpy()
+    # dA[i,j] = ones[512,512] @ B[0,j]^T : every row equals the row sums of B over n
+    for (i, j) in [(0, 0), (40, 5)]:
+        assert rel_fro(gan[i, j], np.ones((512, 512)) @ b[0, j].astype(np.float64).T) < tol
+    # dB[0,j] = sum_i A[i,j]^T @ ones : column sums over (i, m), broadcast along n
+    for j in (0, 6):
+        col = a64[:, j].sum(axis=(0, 1))  # [64] over k
+        assert rel_fro(gbn[0, j], np.repeat(col[:, None], 512, axis=1)) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_config5a_batched_slice(mode, tol):
+    # 1024 of the 8192 independent [256x256]@[256x256] pairs (one GPU's share at 8 GPUs)
+    nb = 1024
+    a, b = uniform((nb, 256, 256), 501), uniform((nb, 256, 256), 502)
+    A, B = dev(a), dev(b)
+    c = cabi.matmul_fwd(A, B, mode=mode).to_numpy()
+    for i in (0, 511, 1023):
+        assert rel_fro(c[i], a[i].astype(np.float64) @ b[i].astype(np.float64)) < tol
+    ga, gb = cabi.matmul_bwd(A, B, dev(np.ones((nb, 256, 256), np.float32)), mode=mode)
+    ga, gb = ga.to_numpy(), gb.to_numpy()
+    ones = np.ones((256, 256))
+    for i in (3, 1000):
+        assert rel_fro(ga[i], ones @ b[i].astype(np.float64).T) < tol
+        assert rel_fro(gb[i], a[i].astype(np.float64).T @ ones) < tol
+
+
+def test_linearity_and_transpose_identity_8192():
+    # Size-independent properties at the headline size, TF32 mode:
+    #   (A @ B)^T == B^T @ A^T evaluated through transposed VIEWS (exercises the other operand majors)
+    n = 8192
+    s = 1.0 / np.sqrt(n)
+    A, B = dev(normal((n, n), 401, s)), dev(normal((n, n), 402, s))
+    c1 = cabi.matmul_fwd(A, B, mode=MODE_TF32)
+    c2 = cabi.matmul_fwd(B.transpose(0, 1), A.transpose(0, 1), mode=MODE_TF32)
+    x, y = c1.to_numpy(), c2.to_numpy()
+    assert rel_fro(y.T, x) < 2 * TOL_TF32
+    # fp32 mode agrees with TF32 mode to TF32 accuracy and is itself far tighter on sampled rows
+    c3 = cabi.matmul_fwd(A, B, mode=MODE_FP32).to_numpy()
+    assert rel_fro(x, c3) < TOL_TF32
+    a_np, b_np = A.to_numpy(), B.to_numpy()
+    sampled_rows_check(a_np, b_np, c3, [0, 4097, 8191], TOL_FP32)

@@ -1,0 +1,144 @@
+"""GPU: the Python package (reference-facing API) end to end - autograd, Linear training step."""
+import numpy as np
+import pytest
+
+from util import load_golden, uniform, normal, rel_fro, TOL_FP32, TOL_TF32
+from oracle import matmul_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ak():
+    import aakaar_b200
+    return aakaar_b200
+
+
+@pytest.mark.parametrize("tf32,tol", [(False, TOL_FP32), (True, TOL_TF32)])
+def test_config1_autograd(ak, tf32, tol):
+    G, META = load_golden()
+    ak.set_tf32(tf32)
+    try:
+        a = ak.from_numpy(uniform((512, 512), 101), "cuda", requires_grad=True)
+        b = ak.from_numpy(uniform((512, 512), 102), "cuda", requires_grad=True)
+        c = ak.matmul(a, b)
+        assert c.requires_grad and c.shape == [512, 512] and c.device == "cuda"
+        c.backward(ak.from_numpy(np.ones((512, 512), np.float32), "cuda"))
+        rows = META["cases"]["cfg1"]["rows"]
+        assert rel_fro(c.to_numpy()[rows], G["cfg1_c_rows"]) < tol
+        assert rel_fro(a.grad.to_numpy()[rows], G["cfg1_da_rows"]) < tol
+        assert rel_fro(b.grad.to_numpy()[rows], G["cfg1_db_rows"]) < tol
+    finally:
+        ak.set_tf32(False)
+
+
+def test_doc_example_and_shared_operand(ak):
+    G, META = load_golden()
+    a = ak.from_numpy(np.array(META["cases"]["doc"]["a"], np.float32), "cuda", requires_grad=True)
+    b = ak.from_numpy(np.array(META["cases"]["doc"]["b"], np.float32), "cuda", requires_grad=True)
+    r = ak.matmul(a, b)
+    assert r.shape == [2, 2]
+    r.sum().backward()
+    np.testing.assert_allclose(r.to_numpy(), G["doc_c"], rtol=1e-6)
+    np.testing.assert_allclose(a.grad.to_numpy(), G["doc_da"], rtol=1e-6)
+    np.testing.assert_allclose(b.grad.to_numpy(), G["doc_db"], rtol=1e-6)
+    s = ak.from_numpy(uniform((6, 6), 41), "cuda", requires_grad=True)
+    c = s @ s
+    c.backward(ak.from_numpy(np.ones((6, 6), np.float32), "cuda"))
+    assert rel_fro(c.to_numpy(), G["ss_c"]) < TOL_FP32
+    assert rel_fro(s.grad.to_numpy(), G["ss_ds"]) < TOL_FP32
+
+
+def test_strided_view_autograd_and_only_needed_grads(ak):
+    G, _ = load_golden()
+    base = ak.from_numpy(uniform((4, 2, 6, 16), 301), "cuda", requires_grad=True)
+    b = ak.from_numpy(uniform((1, 2, 6, 16), 302), "cuda", requires_grad=True)
+    a = base.transpose(-1, -2)
+    assert not a.is_contiguous()
+    c = ak.matmul(a, b)               # the reference raises ValueError here
+    c.backward(ak.from_numpy(np.ones(c.shape, np.float32), "cuda"))
+    assert rel_fro(c.to_numpy(), G["cfg3s_c"]) < TOL_FP32
+    assert base.grad.shape == [4, 2, 6, 16] and b.grad.shape == [1, 2, 6, 16]
+    assert rel_fro(base.grad.to_numpy(), G["cfg3s_dbase"]) < TOL_FP32
+    assert rel_fro(b.grad.to_numpy(), G["cfg3s_db"]) < TOL_FP32
+    x = ak.from_numpy(uniform((8, 4), 1), "cuda")
+    w = ak.from_numpy(uniform((4, 3), 2), "cuda", requires_grad=True)
+    y = x @ w
+    assert y.requires_grad
+    y.backward(ak.from_numpy(np.ones((8, 3), np.float32), "cuda"))
+    assert x.grad is None and w.grad is not None
+
+
+def test_backward_rules(ak):
+    a = ak.from_numpy(uniform((4, 4), 1), "cuda", requires_grad=True)
+    b = ak.from_numpy(uniform((4, 4), 2), "cuda")
+    c = a @ b
+    with pytest.raises(RuntimeError, match="explicit gradient"):
+        c.backward()
+    g = ak.from_numpy(np.ones((4, 4), np.float32), "cuda")
+    c.backward(g)
+    with pytest.raises(RuntimeError, match="second time"):
+        c.backward(g)
+    c2 = a @ b
+    c2.backward(g, retain_graph=True)
+    c2.backward(g)
+    with ak.no_grad():
+        assert not (a @ b).requires_grad
+    with pytest.raises(ValueError, match="inner dimensions must match"):
+        ak.matmul(a, ak.from_numpy(np.ones((3, 2), np.float32), "cuda"))
+    with pytest.raises(ValueError, match="at least 2 dimensions"):
+        ak.matmul(a, ak.from_numpy(np.ones((4,), np.float32), "cuda"))
+
+
+@pytest.mark.parametrize("tf32,tol", [(False, 2e-5), (True, 4e-3)])
+def test_mlp_training_step_small(ak, tf32, tol):
+    G, _ = load_golden()
+    ak.set_tf32(tf32)
+    try:
+        np.random.seed(203)
+        l1, l2 = ak.nn.Linear(32, 48), ak.nn.Linear(48, 16)
+        x = ak.from_numpy(normal((64, 32), 201), "cuda")
+        t = ak.from_numpy(normal((64, 16), 202), "cuda")
+        opt = ak.optim.SGD(l1.parameters() + l2.parameters(), lr=0.01)
+        y = l2(l1(x).tanh())
+        loss = ak.mse_loss(y, t)
+        loss.backward()
+        assert abs(loss.item() / float(G["mlp_loss"].ravel()[0]) - 1) < tol
+        assert rel_fro(y.to_numpy(), G["mlp_y"]) < tol
+        for n, p in (("w1", l1.weight), ("b1", l1.bias), ("w2", l2.weight), ("b2", l2.bias)):
+            assert p.grad.shape == p.shape
+            assert rel_fro(p.grad.to_numpy(), G[f"mlp_d{n}"]) < tol, n
+        opt.step()
+        for n, p in (("w1", l1.weight), ("b1", l1.bias), ("w2", l2.weight), ("b2", l2.bias)):
+            assert rel_fro(p.to_numpy(), G[f"mlp_new_{n}"]) < tol, n
+        opt.zero_grad()
+        assert l1.weight.grad is None
+    finally:
+        ak.set_tf32(False)
+
+
+@pytest.mark.parametrize("tf32,tol", [(False, 2e-5), (True, 4e-3)])
+def test_mlp_config2_full_size(ak, tf32, tol):
+    # input [4096,1024], Linear 1024->4096, tanh, Linear 4096->1024, MSE, SGD lr 0.01; vs the oracle
+    ak.set_tf32(tf32)
+    try:
+        np.random.seed(203)
+        l1, l2 = ak.nn.Linear(1024, 4096), ak.nn.Linear(4096, 1024)
+        w1, w2 = l1.weight.to_numpy(), l2.weight.to_numpy()
+        xn, tn = normal((4096, 1024), 201), normal((4096, 1024), 202)
+        x, t = ak.from_numpy(xn, "cuda"), ak.from_numpy(tn, "cuda")
+        opt = ak.optim.SGD(l1.parameters() + l2.parameters(), lr=0.01)
+        loss = ak.mse_loss(l2(l1(x).tanh()), t)
+        loss.backward()
+        opt.step()
+        ak.synchronize()
+        rloss, new, grads = mo.mlp_step(xn, tn, w1, np.zeros((1, 4096), np.float32), w2,
+                                        np.zeros((1, 1024), np.float32), 0.01)
+        assert abs(loss.item() / float(rloss) - 1) < tol
+        assert rel_fro(l1.weight.grad.to_numpy(), grads["w1"]) < tol
+        assert rel_fro(l2.weight.grad.to_numpy(), grads["w2"]) < tol
+        assert rel_fro(l1.bias.grad.to_numpy(), grads["b1"]) < tol
+        assert rel_fro(l2.bias.grad.to_numpy(), grads["b2"]) < tol
+        assert rel_fro(l1.weight.to_numpy(), new[0]) < tol
+    finally:
+        ak.set_tf32(False)

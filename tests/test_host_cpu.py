@@ -1,0 +1,81 @@
+"""CPU: host-side logic of the Python module (view metadata, errors, refusal to compute on CPU)."""
+import numpy as np
+import pytest
+
+import aakaar_b200 as ak
+from aakaar_b200 import _C
+
+
+def cpu(shape):
+    return ak.from_numpy(np.arange(int(np.prod(shape)), dtype=np.float32).reshape(shape), "cpu")
+
+
+def test_api_surface_matches_reference_names():
+    for name in ("matmul", "from_numpy", "set_tf32", "is_tf32_enabled", "synchronize", "no_grad", "mse_loss",
+                 "add", "sub", "zero_grad_all", "is_grad_enabled"):
+        assert hasattr(ak, name)
+    for name in ("Tensor", "cuda_matmul", "cpu_matmul", "from_numpy", "_set_tf32_enabled", "_get_tf32_enabled",
+                 "_synchronize", "empty_cache", "_allocator_stats", "_set_grad_enabled", "_is_grad_enabled",
+                 "HAS_CUDA", "_sgd_step_fused", "_mse_fused", "is_available", "device_count",
+                 "_set_cudnn_tf32_enabled", "_get_cudnn_tf32_enabled"):
+        assert hasattr(_C, name), name
+    assert hasattr(ak.nn, "Linear") and hasattr(ak.optim, "SGD") and hasattr(ak.losses, "MSELoss")
+
+
+def test_view_metadata_follows_reference_semantics():
+    t = cpu((2, 3, 4))
+    assert t.shape == [2, 3, 4] and t.strides == [12, 4, 1] and t.size == 24 and t.is_contiguous()
+    tt = t.transpose(1, 2)
+    assert tt.shape == [2, 4, 3] and tt.strides == [12, 1, 4] and not tt.is_contiguous()
+    assert t.T.shape == [2, 4, 3]
+    assert t.transpose(-1, -2).strides == tt.strides
+    s = t[1, 0:3:2, 1:]
+    assert s.shape == [2, 3] and s.strides == [8, 1]
+    np.testing.assert_array_equal(t.view([6, 4]).to_numpy(), t.to_numpy().reshape(6, 4))
+    assert t.view([-1, 8]).shape == [3, 8]
+    with pytest.raises(ValueError):
+        tt.view([24])
+    with pytest.raises(ValueError):
+        t.view([5, 5])
+    with pytest.raises(IndexError):
+        t[5]
+
+
+def test_tf32_flag_roundtrip_and_default():
+    assert ak.is_tf32_enabled() is False
+    ak.set_tf32(True)
+    assert ak.is_tf32_enabled() is True
+    ak.set_tf32(False)
+    assert ak.is_tf32_enabled() is False
+
+
+def test_no_grad_context():
+    assert ak.is_grad_enabled()
+    with ak.no_grad():
+        assert not ak.is_grad_enabled()
+    assert ak.is_grad_enabled()
+
+
+def test_cpu_tensors_never_compute():
+    a, b = cpu((2, 3)), cpu((3, 2))
+    with pytest.raises(RuntimeError, match="no CPU"):
+        ak.matmul(a, b)
+    with pytest.raises(RuntimeError, match="no CPU matmul"):
+        _C.cpu_matmul(a, b)
+    with pytest.raises(RuntimeError):
+        a + a
+    with pytest.raises(RuntimeError):
+        a.tanh()
+
+
+def test_from_numpy_rejects_other_dtypes_and_missing_gpu():
+    with pytest.raises(RuntimeError, match="float32"):
+        ak.from_numpy(np.ones((2, 2), dtype=np.float64), "cpu")
+    if not ak.is_available():
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cuda")
+
+
+def test_sgd_argument_check():
+    with pytest.raises(ValueError):
+        ak.optim.SGD([], nesterov=True)
