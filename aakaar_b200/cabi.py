@@ -73,6 +73,12 @@ def load():
         "akr_set_tf32": [C.c_int],
         "akr_set_cudnn_tf32": [C.c_int],
         "akr_set_device": [C.c_int],
+        "akr_set_gemm_cta_limit": [C.c_int],
+        "akr_event_create": [C.POINTER(vp)],
+        "akr_event_record": [vp, vp],
+        "akr_event_synchronize": [vp],
+        "akr_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
+        "akr_event_destroy": [vp],
     }
     for name, args in sigs.items():
         getattr(lib, name).argtypes = args
@@ -134,6 +140,12 @@ class DeviceArray:
         check(lib().akr_stream_synchronize(None))
         return d
 
+    @property
+    def __cuda_array_interface__(self):
+        """Zero-copy export (e.g. ``torch.as_tensor(x, device="cuda")`` for a NCCL collective)."""
+        return {"shape": self.shape, "typestr": "<f4", "data": (self.ptr, False), "version": 3,
+                "strides": tuple(4 * s for s in self.strides)}
+
     def view(self):
         v = View()
         v.data = self.ptr
@@ -168,6 +180,31 @@ class DeviceArray:
                 return False
             acc *= d
         return True
+
+
+class Event:
+    """CUDA event on the library's stream (NULL = legacy default stream)."""
+
+    def __init__(self):
+        self.h = C.c_void_p()
+        check(lib().akr_event_create(C.byref(self.h)))
+
+    def record(self):
+        check(lib().akr_event_record(self.h, None))
+        return self
+
+    def synchronize(self):
+        check(lib().akr_event_synchronize(self.h))
+
+    def elapsed_ms(self, end: "Event") -> float:
+        ms = C.c_float()
+        check(lib().akr_event_elapsed_ms(self.h, end.h, C.byref(ms)))
+        return float(ms.value)
+
+    def __del__(self):
+        if _lib is not None and self.h:
+            _lib.akr_event_destroy(self.h)
+            self.h = None
 
 
 def plan(a: DeviceArray, b: DeviceArray):

@@ -811,6 +811,42 @@ AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* 
     return AKR_OK;
 }
 
+AKR_API int akr_set_gemm_cta_limit(int ctas) {
+    gemm_sm100_set_cta_limit(ctas);
+    return AKR_OK;
+}
+
+AKR_API int akr_event_create(void** event) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    cudaEvent_t ev;
+    cudaError_t e = cudaEventCreate(&ev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+    *event = (void*)ev;
+    return AKR_OK;
+}
+AKR_API int akr_event_record(void* event, void* stream) {
+    cudaError_t e = cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord");
+    return AKR_OK;
+}
+AKR_API int akr_event_synchronize(void* event) {
+    cudaError_t e = cudaEventSynchronize((cudaEvent_t)event);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventSynchronize");
+    return AKR_OK;
+}
+AKR_API int akr_event_elapsed_ms(void* start, void* end, float* ms) {
+    cudaError_t e = cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)end);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventElapsedTime");
+    return AKR_OK;
+}
+AKR_API int akr_event_destroy(void* event) {
+    cudaError_t e = cudaEventDestroy((cudaEvent_t)event);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventDestroy");
+    return AKR_OK;
+}
+
 AKR_API int akr_workspace_bytes(size_t* bytes) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {

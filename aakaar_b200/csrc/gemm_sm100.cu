@@ -533,17 +533,20 @@ int pick_bn(const GemmDesc& g) {
 
 }  // namespace
 
+static int g_cta_limit = 0;
+
+void gemm_sm100_set_cta_limit(int ctas) { g_cta_limit = ctas > 0 ? ctas : 0; }
+
 int gemm_sm100_num_ctas() {
-    static int n = 0;
-    if (n == 0) {
+    static int sms = 0;
+    if (sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
-        int sms = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-        n = sms;
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        sms = v;
     }
-    return n;
+    return (g_cta_limit > 0 && g_cta_limit < sms) ? g_cta_limit : sms;
 }
 
 bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch[3]) {

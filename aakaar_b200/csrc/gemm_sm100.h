@@ -46,8 +46,11 @@ bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch
 int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, char* err,
                       int errlen);
 
-// Number of CTAs the persistent kernels are launched with on the current device.
+// Number of CTAs the persistent kernels are launched with on the current device
+// (the SM count, or the lower limit set below).
 int gemm_sm100_num_ctas();
+// Caps the persistent grid (0 = one CTA per SM).
+void gemm_sm100_set_cta_limit(int ctas);
 
 // Bytes of `partials` and number of `counters` entries a split launch needs.
 void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* counter_count);

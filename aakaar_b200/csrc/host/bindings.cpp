@@ -574,6 +574,19 @@ PYBIND11_MODULE(_C, m) {
             "grad", [](Tensor& t) { return t.grad; }, [](Tensor& t, TensorPtr g) { t.grad = g; })
         .def_property_readonly("is_leaf", [](Tensor& t) { return !t.grad_fn; })
         .def_property_readonly("data_ptr", [](Tensor& t) { return (uintptr_t)t.data; })
+        .def_property_readonly("__cuda_array_interface__",
+                               [](Tensor& t) {
+                                   if (t.device != "cuda") throw std::runtime_error("not a CUDA tensor");
+                                   py::dict d;
+                                   d["shape"] = py::tuple(py::cast(t.shape));
+                                   d["typestr"] = "<f4";
+                                   d["data"] = py::make_tuple((uintptr_t)t.data, false);
+                                   d["version"] = 3;
+                                   std::vector<int64_t> bs(t.strides.size());
+                                   for (size_t i = 0; i < bs.size(); ++i) bs[i] = t.strides[i] * 4;
+                                   d["strides"] = py::tuple(py::cast(bs));
+                                   return d;
+                               })
         .def("to_numpy", &to_numpy)
         .def("copy_to_host", &copy_to_host)
         .def("is_contiguous", &Tensor::is_contiguous)

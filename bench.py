@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the fp32 matmul hot path: forward + backward GEMMs at 8192^3 per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is C = A @ B, dA = dC . B^T, dB = A^T . dC on fp32 operands of 8192 x 8192 per GPU
+(3 * 2 * 8192^3 = 3.30 TFLOP). At N > 1 (launched by torch.distributed.run, one process per GPU) the
+product is the row-sharded large GEMM: M = 8192 * N split along M, B replicated, dB all-reduced
+over NCCL - weak scaling, at N = 8 exactly the M=65536, N=K=8192 workload.
+
+The JSON line reports: `value` = whole-job TFLOP/s in TF32 mode with inputs resident in HBM;
+`e2e` = the same metric through the Python API with pinned HOST buffers (H2D of A, B, dC and D2H of
+C, dA, dB inside the timed region); `modes` = the fp32-accurate (3xTF32) mode beside TF32;
+`roofline` = the dominant GEMM launch against the measured tensor peak; `cpu_baseline` = the
+reference's own CPU path (OpenBLAS build under oracle/_ref) timed on this box's host cores.
+
+`--impl reference` times only that CPU path (the reference has no sm_100 GPU build).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_SQ = 8192
+FLOP_PER_STEP = 3 * 2 * N_SQ ** 3           # per GPU
+WORKLOAD = "square GEMM fwd+dA+dB, M=N=K=8192 per GPU, fp32 operands N(0, 1/sqrt(K)), seeds 401/402/403"
+
+
+def set_size(n):
+    """--size: a smaller square problem for profiler captures (the benchmark itself is 8192)."""
+    global N_SQ, FLOP_PER_STEP, WORKLOAD
+    N_SQ = n
+    FLOP_PER_STEP = 3 * 2 * n ** 3
+    WORKLOAD = WORKLOAD.replace("8192", str(n))
+
+# DRAM bytes moved by one launch of the dominant kernel (dB = A^T.dC at 8192^3, TF32 mode), from
+# an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/. None = not captured.
+NCU_TRAFFIC_BYTES = None
+
+
+def normal(shape, seed, sigma):
+    g = np.random.Generator(np.random.PCG64(seed))
+    return (g.standard_normal(shape, dtype=np.float32) * np.float32(sigma))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        sm, mx, pw, reasons = [], [], [], set()
+        for ts, r in self.rows:
+            if ts < t0 or ts > t1 or len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------- reference (CPU) arm
+
+def load_reference_module():
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not any(f.startswith("_C") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
+        return None
+    sys.path.insert(0, ref_dir)
+    import _C as ref  # the reference's own pybind11 module, CPU build
+    return ref
+
+
+def cpu_step(ref, a_np, b_np, dc_np):
+    """One fwd+bwd of the reference's CPU path (or of the numpy oracle when the build is absent)."""
+    t0 = time.perf_counter()
+    if ref is not None:
+        a = ref.from_numpy(a_np, "cpu", True)
+        b = ref.from_numpy(b_np, "cpu", True)
+        c = ref.cpu_matmul(a, b)
+        c.backward(ref.from_numpy(dc_np, "cpu", False))
+        _ = (a.grad.shape, b.grad.shape)
+    else:
+        from oracle import matmul_oracle as mo
+        mo.matmul_forward(a_np, b_np)
+        mo.matmul_backward(a_np, b_np, dc_np)
+    return time.perf_counter() - t0
+
+
+def cpu_inputs(m_rows):
+    s = 1.0 / np.sqrt(N_SQ)
+    return normal((m_rows, N_SQ), 401, s), normal((N_SQ, N_SQ), 402, s), normal((m_rows, N_SQ), 403, 1.0)
+
+
+def pick_cpu_rows(ref, budget_s):
+    """Rows of the 8192-row problem one CPU step covers so that a step costs about `budget_s`."""
+    a, b, dc = cpu_inputs(128)
+    cpu_step(ref, a, b, dc)
+    t = cpu_step(ref, a, b, dc)
+    rate = 3 * 2 * 128 * N_SQ * N_SQ / max(t, 1e-6)   # flop/s
+    rows = int(budget_s * rate / (3 * 2 * N_SQ * N_SQ))
+    rows = max(128, min(N_SQ, (rows // 128) * 128))
+    return rows
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    ref = load_reference_module()
+    kind = "reference" if ref is not None else "port"
+    cores = os.cpu_count()
+    total_steps = args.steps + args.warmup
+    rows = pick_cpu_rows(ref, budget_s=max(0.5, 150.0 / max(total_steps, 1)))
+    a, b, dc = cpu_inputs(rows)
+    for _ in range(args.warmup):
+        cpu_step(ref, a, b, dc)
+    times = [cpu_step(ref, a, b, dc) for _ in range(args.steps)]
+    flop = 3 * 2 * rows * N_SQ * N_SQ
+    t = sum(times) / len(times)
+    val = flop / t / 1e12
+    sample = f"{rows} of 8192 rows of A and dC against the full 8192x8192 B (fwd+dA+dB), every step"
+    line = {
+        "impl": "reference", "metric": "matmul fwd+bwd TFLOP/s at 8192^3", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "device": "host CPU", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def cpu_baseline_child():
+    """Bounded CPU sample, run in a child process so that OpenBLAS threads do not linger."""
+    ref = load_reference_module()
+    rows = pick_cpu_rows(ref, budget_s=12.0)
+    a, b, dc = cpu_inputs(rows)
+    t = cpu_step(ref, a, b, dc)
+    flop = 3 * 2 * rows * N_SQ * N_SQ
+    print(json.dumps({"value": flop / t / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                      "kind": "reference" if ref is not None else "port",
+                      "sample": f"one fwd+dA+dB step on {rows} of 8192 rows of A and dC against the full B ({t:.1f} s)"}))
+
+
+# ---------------------------------------------------------------------------------- GPU arm
+
+def run_gpu_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world > 1:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}; using WORLD_SIZE", file=sys.stderr)
+    n_gpus = world
+
+    from aakaar_b200 import cabi
+    import aakaar_b200 as ak
+    from aakaar_b200 import _C
+    from aakaar_b200.distributed import RowShardedMatmul, CudaBackend
+
+    lib = cabi.lib()
+    if lib.akr_device_count() <= 0:
+        raise RuntimeError("bench.py: no CUDA device; the product path has no CPU fallback")
+    cabi.check(lib.akr_set_device(local_rank))
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        cabi.synchronize()
+        if dist is not None:
+            dist.barrier()
+            cabi.synchronize()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs: generated on the host into PINNED buffers (also the source of the e2e copies)
+    s = 1.0 / np.sqrt(N_SQ)
+    hA, hB, hDC = _C.pinned_empty([N_SQ, N_SQ]), _C.pinned_empty([N_SQ, N_SQ]), _C.pinned_empty([N_SQ, N_SQ])
+    hA[...] = normal((N_SQ, N_SQ), 401 + 1000 * rank, s)
+    hB[...] = normal((N_SQ, N_SQ), 402, s)
+    hDC[...] = normal((N_SQ, N_SQ), 403 + 1000 * rank, 1.0)
+    hC, hDA, hDB = _C.pinned_empty([N_SQ, N_SQ]), _C.pinned_empty([N_SQ, N_SQ]), _C.pinned_empty([N_SQ, N_SQ])
+
+    A, B, DC = cabi.DeviceArray.from_numpy(hA), cabi.DeviceArray.from_numpy(hB), cabi.DeviceArray.from_numpy(hDC)
+    Cd, DAd, DBd = cabi.DeviceArray((N_SQ, N_SQ)), cabi.DeviceArray((N_SQ, N_SQ)), cabi.DeviceArray((N_SQ, N_SQ))
+
+    results = {}
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    if rank == 0:
+        sampler.start()
+
+    def device_phase(mode, steps, warmup):
+        be = CudaBackend(mode=mode)
+        sh = RowShardedMatmul(total_m=N_SQ * n_gpus, world=n_gpus, rank=rank, backend=be)
+        ev = [[cabi.Event() for _ in range(4)] for _ in range(steps)]
+
+        def step(i=None):
+            if i is not None:
+                ev[i][0].record()
+            sh.forward(A, B, out=Cd)
+            if i is not None:
+                ev[i][1].record()
+            if n_gpus == 1:
+                be.bwd(A, B, DC, need_da=True, need_db=False, da=DAd)
+                if i is not None:
+                    ev[i][2].record()
+                be.bwd(A, B, DC, need_da=False, need_db=True, db=DBd)
+            else:
+                sh.backward(A, B, DC, da=DAd, db=DBd)
+                if i is not None:
+                    ev[i][2].record()
+            if i is not None:
+                ev[i][3].record()
+
+        for _ in range(warmup):
+            step()
+        barrier()
+        lib.akr_launch_count(1)
+        t_wall0 = time.time()
+        e0, e1 = cabi.Event().record(), cabi.Event()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        e1.synchronize()
+        barrier()
+        t_wall1 = time.time()
+        launches = int(lib.akr_launch_count(0))
+        ms = max_over_ranks(e0.elapsed_ms(e1)) / steps
+        per = [[ev[i][j].elapsed_ms(ev[i][j + 1]) for j in range(3)] for i in range(steps)]
+        kern_ms = [sum(p[j] for p in per) / steps for j in range(3)]
+        return ms, kern_ms, launches, (t_wall0, t_wall1)
+
+    ms_tf32, kern_tf32, launches, wall = device_phase(cabi.MODE_TF32, args.steps, args.warmup)
+    if args.profile:
+        # profiler capture: only the TF32 device phase (optionally the fp32-accurate one instead)
+        if args.profile == "fp32":
+            ms_tf32, kern_tf32, launches, wall = device_phase(cabi.MODE_FP32, args.steps, args.warmup)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"profile_run": True, "size": N_SQ, "ms_per_step": ms_tf32, "kernel_ms": kern_tf32,
+                              "gpu_launches": launches}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+    steps32 = max(3, args.steps // 4)
+    ms_fp32, kern_fp32, launches32, _ = device_phase(cabi.MODE_FP32, steps32, max(3, args.warmup))
+
+    # ---- end to end through the Python API, host buffers in, host buffers out
+    def e2e_phase(steps, warmup):
+        ak.set_tf32(True)
+        sh = RowShardedMatmul(total_m=N_SQ * n_gpus, world=n_gpus, rank=rank, backend=CudaBackend(mode=cabi.MODE_TF32))
+
+        def step():
+            a = _C.from_pinned(hA, True)
+            b = _C.from_pinned(hB, True)
+            dc = _C.from_pinned(hDC, False)
+            c = ak.matmul(a, b)
+            c.backward(dc)
+            if n_gpus > 1:
+                h = sh.backend.allreduce_start(b.grad)
+                sh.backend.allreduce_wait(h)
+            c.copy_to_host(hC)
+            a.grad.copy_to_host(hDA)
+            b.grad.copy_to_host(hDB)
+            ak.synchronize()
+
+        for _ in range(warmup):
+            step()
+        barrier()
+        e0, e1 = cabi.Event().record(), cabi.Event()
+        for _ in range(steps):
+            step()
+        e1.record()
+        e1.synchronize()
+        barrier()
+        ak.set_tf32(False)
+        return max_over_ranks(e0.elapsed_ms(e1)) / steps
+
+    ms_e2e = e2e_phase(max(3, min(args.steps, 5)), 3)
+    if rank == 0:
+        sampler.stop()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    clocks = sampler.summary(*wall)
+    if clocks["samples"] < 3:   # very short timed region: fall back to every sample of the run
+        clocks = sampler.summary(0, float("inf"))
+        clocks["note"] = "timed region shorter than the sampling period; samples cover the whole run"
+    peaks, peak_src = measured_peaks()
+    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0   # no TF32 figure is measured: dense TF32 = bf16 / 2
+    value = n_gpus * FLOP_PER_STEP / (ms_tf32 * 1e-3) / 1e12
+    names = ["fwd C=A.B (K-major A, N-major B)", "dA=dC.B^T (K-major, K-major)", "dB=A^T.dC (M-major, N-major)"]
+    if n_gpus > 1:
+        names = names[:1] + ["dB + all-reduce + dA", "-"]
+    dom = max(range(3), key=lambda j: kern_tf32[j]) if n_gpus == 1 else 0
+    per_launch_flop = 2 * N_SQ ** 3
+    achieved = per_launch_flop / (kern_tf32[dom] * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": names[dom], "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                "frac": achieved / tf32_peak,
+                "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained/2 ({peak_src}); nominal dense TF32 1125",
+                "traffic": NCU_TRAFFIC_BYTES,
+                "by_kernel": [{"kernel": names[j], "ms": kern_tf32[j],
+                               "tflops": per_launch_flop / (kern_tf32[j] * 1e-3) / 1e12 if n_gpus == 1 else None}
+                              for j in range(3)]}
+
+    cpu = None
+    if n_gpus == 1 and not args.no_cpu_baseline:
+        try:
+            out = subprocess.run([sys.executable, os.path.abspath(__file__), "--_cpu-child"], capture_output=True,
+                                 text=True, timeout=600)
+            cpu = json.loads(out.stdout.strip().splitlines()[-1])
+        except Exception as exc:  # noqa: BLE001
+            cpu = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "reference",
+                   "sample": f"failed: {exc}"}
+
+    bytes_each_way = 3 * N_SQ * N_SQ * 4
+    line = {
+        "metric": "matmul fwd+bwd TFLOP/s at 8192^3", "value": value, "unit": "TFLOP/s", "n_gpus": n_gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_tf32, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "tf32 products, f32 accumulate (f32 storage)",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "mode": "set_tf32(True)", "l2": "inputs (768 MB) larger than L2 (126 MB)",
+                   "sharding": "none" if n_gpus == 1 else f"M = {N_SQ * n_gpus} split along M over {n_gpus} ranks, "
+                                                          "B replicated, dB all-reduced (NCCL)"},
+        "clocks": clocks,
+        "e2e": {"value": n_gpus * FLOP_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_each_way, "d2h_bytes_per_step": bytes_each_way},
+        "gpu_launches": launches,
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "modes": {
+            "tf32": {"ms_per_step": ms_tf32, "tflops": value, "frac_of_peak": value / n_gpus / tf32_peak,
+                     "frac_of_nominal_1125": value / n_gpus / 1125.0},
+            "fp32_3xtf32": {"ms_per_step": ms_fp32, "steps": steps32,
+                            "tflops": n_gpus * FLOP_PER_STEP / (ms_fp32 * 1e-3) / 1e12,
+                            "frac_of_peak_div3": n_gpus * FLOP_PER_STEP / (ms_fp32 * 1e-3) / 1e12 / n_gpus / (tf32_peak / 3),
+                            "kernel_ms": kern_fp32, "gpu_launches": launches32},
+        },
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--size", type=int, default=8192, help="square size (profiling only; the benchmark is 8192)")
+    ap.add_argument("--profile", default="", choices=["", "tf32", "fp32"],
+                    help="profiler capture run: one device phase only, warm-up not forced to 3")
+    ap.add_argument("--_cpu-child", dest="cpu_child", action="store_true", help=argparse.SUPPRESS)
+    args = ap.parse_args()
+    if not args.profile:
+        args.warmup = max(args.warmup, 3)
+    if args.size != 8192:
+        set_size(args.size)
+    if args.cpu_child:
+        cpu_baseline_child()
+        return 0
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

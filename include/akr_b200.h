@@ -136,6 +136,19 @@ AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, i
  * product path. */
 AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
 
+/* Number of CTAs the persistent GEMM kernels may occupy (default and maximum: one per SM). A host
+ * that overlaps a collective with a GEMM lowers it so that the collective's kernels find free SMs;
+ * 0 restores the default. No counterpart in the reference (it has no multi-GPU path). */
+AKR_API int akr_set_gemm_cta_limit(int ctas);
+
+/* CUDA events for timing on the stream the work was issued on (the reference times with
+ * synchronize() + host clocks, docs/concepts/hardware-and-cuda/performance.md:52-75). */
+AKR_API int akr_event_create(void** event);
+AKR_API int akr_event_record(void* event, void* stream);
+AKR_API int akr_event_synchronize(void* event);
+AKR_API int akr_event_elapsed_ms(void* start, void* end, float* ms);
+AKR_API int akr_event_destroy(void* event);
+
 /* Bytes of scratch the library currently holds on this device (operand splits, split-K partials). */
 AKR_API int akr_workspace_bytes(size_t* bytes);
 /* Number of kernels launched by this library on this thread's device since the last reset. */
