@@ -42,9 +42,14 @@ struct KernelParams {
     long long ldc, c_bs0, c_bs1;
     int M, N, K;
     int o0, o1, red, splits;
-    int a_mul[3], b_mul[3];  // 1 when the operand varies along (o0, o1, r), 0 when broadcast
+    // Batch coordinates of the tensor maps: slot j of an operand's map takes (i1, i0, r, 0)[sel[j]].
+    int a_sel[3], b_sel[3];
+    // 1: the M/N-major operand's map is folded to (32, K, MN/32, ...) so that ONE box fetches the
+    // whole tile (a box per 32-column chunk costs the TMA unit a fixed overhead per box).
+    int a_fold, b_fold;
     int accumulate, vec_ok;
     int mt, nt, nkb, total_tiles;
+    int debug;  // diagnostics: bit 0 = skip TMA loads, bit 1 = skip MMAs (timing experiments only)
 };
 
 struct Tile {
@@ -190,11 +195,21 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         break;
                     }
                     const uint32_t fb = full_bar(stage);
+                    if (p.debug & 1) {
+                        ptx::mbar_arrive(fb);
+                        ++issued;
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     ptx::mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
                     const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                     const uint32_t sb = sa + L::A_BYTES;
-                    const int a1 = c.i1 * p.a_mul[1], a0 = c.i0 * p.a_mul[0], ar = r * p.a_mul[2];
-                    const int b1 = c.i1 * p.b_mul[1], b0 = c.i0 * p.b_mul[0], br = r * p.b_mul[2];
+                    const int bcv[4] = {c.i1, c.i0, r, 0};
+                    const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                    const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
 #pragma unroll
                     for (int term = 0; term < (TERMS == 3 ? 2 : 1); ++term) {
                         const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
@@ -202,20 +217,24 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         const uint32_t da = sa + term * (L::A_BYTES + L::B_BYTES);
                         const uint32_t db = sb + term * (L::A_BYTES + L::B_BYTES);
                         if (MAJA == 0) {
-                            ptx::tma_load_5d(da, ma, fb, k0, c.m0, a1, a0, ar);
+                            ptx::tma_load_5d(da, ma, fb, k0, c.m0, a0, a1, a2);
+                        } else if (p.a_fold) {
+                            ptx::tma_load_5d(da, ma, fb, 0, k0, c.m0 / CHUNK, a0, a1);
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BM / CHUNK; ++ch)
                                 ptx::tma_load_5d(da + ch * (BK * 128), ma, fb, c.m0 + ch * CHUNK, k0,
-                                                 a1, a0, ar);
+                                                 a0, a1, a2);
                         }
                         if (MAJB == 0) {
-                            ptx::tma_load_5d(db, mb, fb, k0, c.n0, b1, b0, br);
+                            ptx::tma_load_5d(db, mb, fb, k0, c.n0, b0, b1, b2);
+                        } else if (p.b_fold) {
+                            ptx::tma_load_5d(db, mb, fb, 0, k0, c.n0 / CHUNK, b0, b1);
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BN / CHUNK; ++ch)
                                 ptx::tma_load_5d(db + ch * (BK * 128), mb, fb, c.n0 + ch * CHUNK, k0,
-                                                 b1, b0, br);
+                                                 b0, b1, b2);
                         }
                     }
                     ++issued;
@@ -289,7 +308,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
-                            if (TERMS == 3) {
+                            if (p.debug & 2) {
+                                if (k8 == 0 && it == cs) ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 0u);
+                            } else if (TERMS == 3) {
                                 const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
                                 const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
                                 ptx::mma_tf32_ss(d_tmem, da_lo, db, IDESC, first);
@@ -464,23 +485,56 @@ void seterr(char* err, int errlen, const char* msg) {
     }
 }
 
-// Rank-5 map over (unit-stride matrix dim, other matrix dim, o1, o0, r).
-bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, int mn, int k,
-              const int batch[3], int tile_mn) {
+// How one operand is addressed by its tensor map.
+struct MapPlan {
+    bool fold = false;          // M/N-major operand fetched with one box per tile
+    int sel[3] = {3, 3, 3};     // batch slot -> index into (i1, i0, r, 0)
+    uint64_t ext[3] = {1, 1, 1};
+    int64_t str[3] = {0, 0, 0};  // element strides of the batch slots
+};
+
+// Batch slots hold only the dims the operand really varies along; a folded map has two slots.
+MapPlan plan_map(const GemmOperand& op, int mn, const int batch[3], bool allow_fold) {
+    MapPlan mp;
+    // kernel-side order of the candidates: i1 (o1), i0 (o0), r
+    const int cand_idx[3] = {1, 0, 2};
+    int n = 0;
+    for (int j = 0; j < 3; ++j) {
+        const int b = cand_idx[j];
+        if (batch[b] > 1 && op.bs[b] != 0) {
+            mp.sel[n] = j;
+            mp.ext[n] = (uint64_t)batch[b];
+            mp.str[n] = op.bs[b];
+            ++n;
+        }
+    }
+    mp.fold = allow_fold && op.mn_major && (mn % CHUNK == 0) && n <= 2;
+    return mp;
+}
+
+bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const MapPlan& mp, int mn,
+              int k, int tile_mn) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
-    const int e_o0 = op.bs[0] != 0 ? batch[0] : 1;
-    const int e_o1 = op.bs[1] != 0 ? batch[1] : 1;
-    const int e_r = op.bs[2] != 0 ? batch[2] : 1;
     const uint64_t d0 = op.mn_major ? mn : k;
     const uint64_t d1 = op.mn_major ? k : mn;
     // Stride of a dim of extent 1 is never used for addressing; it only has to be well-formed.
     const uint64_t ld_b = (uint64_t)(d1 > 1 ? op.ld : ((d0 + 3) / 4) * 4) * 4;
-    auto bstride = [&](int e, int64_t s) { return (uint64_t)(e > 1 ? s * 4 : (int64_t)ld_b); };
-    cuuint64_t dims[5] = {d0, d1, (cuuint64_t)e_o1, (cuuint64_t)e_o0, (cuuint64_t)e_r};
-    cuuint64_t strides[4] = {ld_b, bstride(e_o1, op.bs[1]), bstride(e_o0, op.bs[0]),
-                             bstride(e_r, op.bs[2])};
-    cuuint32_t box[5] = {32u, (cuuint32_t)(op.mn_major ? BK : tile_mn), 1u, 1u, 1u};
+    auto bstride = [&](int j) { return (uint64_t)(mp.ext[j] > 1 ? mp.str[j] * 4 : (int64_t)ld_b); };
+    cuuint64_t dims[5], strides[4];
+    cuuint32_t box[5];
+    if (mp.fold) {
+        // (32 contiguous, k rows, 32-column chunks, batch, batch)
+        dims[0] = CHUNK; dims[1] = (cuuint64_t)k; dims[2] = (cuuint64_t)(mn / CHUNK);
+        dims[3] = mp.ext[0]; dims[4] = mp.ext[1];
+        strides[0] = ld_b; strides[1] = CHUNK * 4; strides[2] = bstride(0); strides[3] = bstride(1);
+        box[0] = CHUNK; box[1] = BK; box[2] = (cuuint32_t)(tile_mn / CHUNK); box[3] = 1; box[4] = 1;
+    } else {
+        // (unit-stride matrix dim, other matrix dim, batch, batch, batch)
+        dims[0] = d0; dims[1] = d1; dims[2] = mp.ext[0]; dims[3] = mp.ext[1]; dims[4] = mp.ext[2];
+        strides[0] = ld_b; strides[1] = bstride(0); strides[2] = bstride(1); strides[3] = bstride(2);
+        box[0] = 32; box[1] = (cuuint32_t)(op.mn_major ? BK : tile_mn); box[2] = box[3] = box[4] = 1;
+    }
     cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
     CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides,
                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -603,17 +657,26 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
-    if (!make_map(&kp.tmA, g.A.ptr, g.A, g.M, g.K, batch, BM) ||
-        !make_map(&kp.tmB, g.B.ptr, g.B, g.N, g.K, batch, bn)) {
+    MapPlan pa = plan_map(g.A, g.M, batch, g.debug & 4 ? false : true);
+    MapPlan pb = plan_map(g.B, g.N, batch, g.debug & 4 ? false : true);
+    auto build = [&](CUtensorMap* hi, CUtensorMap* lo, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
+        bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile);
+        if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
+            mp.fold = false;
+            ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile);
+        }
+        if (ok && g.terms == 3) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile);
+        return ok;
+    };
+    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, BM) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
-    if (g.terms == 3) {
-        if (!make_map(&kp.tmAlo, g.A.lo, g.A, g.M, g.K, batch, BM) ||
-            !make_map(&kp.tmBlo, g.B.lo, g.B, g.N, g.K, batch, bn)) {
-            seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed (lo)");
-            return -2;
-        }
+    kp.a_fold = pa.fold ? 1 : 0;
+    kp.b_fold = pb.fold ? 1 : 0;
+    for (int i = 0; i < 3; ++i) {
+        kp.a_sel[i] = pa.sel[i];
+        kp.b_sel[i] = pb.sel[i];
     }
     kp.C = g.C;
     kp.bias = g.bias;
@@ -630,10 +693,6 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     kp.o1 = g.o1;
     kp.red = g.red;
     kp.splits = g.splits < 1 ? 1 : g.splits;
-    for (int i = 0; i < 3; ++i) {
-        kp.a_mul[i] = (g.A.bs[i] != 0 && batch[i] > 1) ? 1 : 0;
-        kp.b_mul[i] = (g.B.bs[i] != 0 && batch[i] > 1) ? 1 : 0;
-    }
     kp.accumulate = g.accumulate;
     kp.vec_ok = ((reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 &&
                  (g.o0 == 1 || (g.c_bs0 & 3) == 0) && (g.o1 == 1 || (g.c_bs1 & 3) == 0))
@@ -652,6 +711,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         return -1;
     }
     kp.total_tiles = (int)total;
+    kp.debug = g.debug;
     const int ctas = gemm_sm100_num_ctas();
     const int grid = (int)(total < ctas ? total : ctas);
 
