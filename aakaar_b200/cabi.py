@@ -57,6 +57,7 @@ def load():
         "akr_matmul_a_bt": [V, V, V, C.c_int, vp],
         "akr_matmul_at_b": [V, V, V, C.c_int, vp],
         "akr_matmul_fwd_simt": [V, V, V, vp],
+        "akr_matmul_at_b_noalloc": [V, V, V, vp],
         "akr_workspace_bytes": [C.POINTER(sz)],
         "akr_launch_count": [C.c_int],
         "akr_allocator_stats": [C.POINTER(C.c_int64), C.POINTER(C.c_int64)],

@@ -437,6 +437,11 @@ int need_gpu(DeviceState** st) { return get_state(st); }
 
 }  // namespace
 
+namespace akr {
+// Lets the library's other translation units record the message akr_last_error() returns.
+void set_last_error(const std::string& msg) { g_err = msg; }
+}  // namespace akr
+
 extern "C" {
 
 AKR_API const char* akr_last_error(void) { return g_err.c_str(); }

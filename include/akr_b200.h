@@ -131,6 +131,26 @@ AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view*
 AKR_API int akr_matmul_a_bt(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream);
 AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream);
 
+/* The weight-gradient product of akr_matmul_at_b, C(m,n) = A(k,m)^T . B(k,n), for callers that must
+ * not allocate device memory when they call: a host whose own pool already owns all of HBM (a later
+ * cudaMalloc would fail or eat into the pool), or a latency-critical loop that cannot absorb the
+ * device-wide synchronisation cudaMalloc / cudaFree bring. It has no counterpart in the reference.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine. The scratch of the split
+ *     contraction (partial tiles, tile counters, status word) is a fixed array inside the library:
+ *     8 MiB of partial tiles and 4096 tile counters per GPU, held from library load until exit.
+ *   - TF32 products only (AKR_MODE_TF32); both operands must be readable in place (16-byte aligned
+ *     base, unit stride on one dim, the other stride a multiple of 4 elements). A product whose
+ *     partial tiles would not fit, or an operand that would need a packed copy, is rejected with
+ *     AKR_ERR_INVALID and a message naming the limit; use akr_matmul_at_b for those.
+ *   - The first call on a device looks up the array's device address; make that call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous call's contents (what must
+ *     start at zero is cleared on every call): two calls that overlap on the GPU, on different
+ *     streams, race. Keep them on one stream or order them yourself.
+ *   - A kernel that gave up on a bounded wait is reported by the next call on that device that finds
+ *     the stream idle (AKR_ERR_ABORTED). */
+AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
+
 /* Plain fp32 FMA matmul on CUDA cores with the same broadcasting (no tensor cores, no TF32).
  * A slow on-device cross-check for shapes where a host check takes too long; not used by the
  * product path. */
