@@ -56,7 +56,7 @@ struct Tile {
     int split, batch, i0, i1, m0, n0;
 };
 
-__device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn) {
+__device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn, int bm = BM) {
     Tile c;
     c.split = t % p.splits;
     t /= p.splits;
@@ -72,7 +72,7 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     const int in = r - g * group_sz;
     const int n_t = in / gm;
     const int m_t = first_m + (in - n_t * gm);
-    c.m0 = m_t * BM;
+    c.m0 = m_t * bm;
     c.n0 = n_t * bn;
     return c;
 }
@@ -457,6 +457,237 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
+
+// ---------------------------------------------------------------------------------- 256 x 256 tiles
+// TF32 kernel for large products: one CTA computes a 256 x 256 tile as two 128 x 256 accumulators
+// that share the B tile in shared memory. Per flop it pulls one third fewer bytes from L2 than the
+// 128 x 256 kernel above, whose speed is set by the L2 -> SM load rate rather than by the MMA pipe.
+// Both accumulators fill all 512 TMEM columns, so a tile's MMAs may only start on an accumulator
+// once the epilogue has drained it: one short stall per tile, amortised over a long contraction.
+// No split-K and no fp32 promotion here; those stay with the general kernel.
+constexpr int BIG_BM = 256, BIG_BN = 256, BIG_STAGES = 3;
+constexpr int BIG_A_BYTES = BIG_BM * BK * 4, BIG_B_BYTES = BIG_BN * BK * 4;
+constexpr int BIG_STAGE_BYTES = BIG_A_BYTES + BIG_B_BYTES;
+constexpr int BIG_THREADS = 64 + 256;
+
+template <int MAJA, int MAJB>
+__global__ void __launch_bounds__(BIG_THREADS, 1)
+gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BIG_STAGES * BIG_STAGE_BYTES);
+    const uint32_t bar_base = smem_base + BIG_STAGES * BIG_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (BIG_STAGES + s); };
+    const uint32_t tfull_bar = bar_base + 8u * (2 * BIG_STAGES);
+    auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * BIG_STAGES + 1 + h); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * BIG_STAGES + 3);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < BIG_STAGES; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(tfull_bar, 1);
+        ptx::mbar_init(tempty_bar(0), 8);
+        ptx::mbar_init(tempty_bar(1), 8);
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<512>(ptx::smem_u32(tmem_slot));
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_iters = p.red * p.nkb;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
+                for (int it = 0; it < total_iters; ++it) {
+                    const int r = it / p.nkb;
+                    const int k0 = (it - r * p.nkb) * BK;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = full_bar(stage);
+                    ptx::mbar_arrive_expect_tx(fb, BIG_STAGE_BYTES);
+                    const uint32_t da = smem_base + stage * BIG_STAGE_BYTES;
+                    const uint32_t db = da + BIG_A_BYTES;
+                    const int bcv[4] = {c.i1, c.i0, r, 0};
+                    const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                    const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
+                    if (MAJA == 0) {
+                        ptx::tma_load_5d(da, &p.tmA, fb, k0, c.m0, a0, a1, a2);
+                    } else if (p.a_fold) {
+                        ptx::tma_load_5d(da, &p.tmA, fb, 0, k0, c.m0 / CHUNK, a0, a1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < BIG_BM / CHUNK; ++ch)
+                            ptx::tma_load_5d(da + ch * (BK * 128), &p.tmA, fb, c.m0 + ch * CHUNK, k0, a0, a1, a2);
+                    }
+                    if (MAJB == 0) {
+                        ptx::tma_load_5d(db, &p.tmB, fb, k0, c.n0, b0, b1, b2);
+                    } else if (p.b_fold) {
+                        ptx::tma_load_5d(db, &p.tmB, fb, 0, k0, c.n0 / CHUNK, b0, b1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < BIG_BN / CHUNK; ++ch)
+                            ptx::tma_load_5d(db + ch * (BK * 128), &p.tmB, fb, c.n0 + ch * CHUNK, k0, b0, b1, b2);
+                    }
+                    ++issued;
+                    if (++stage == BIG_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // Gave up: let the copies still in flight land before the CTA tears down.
+                int s = stage;
+                uint32_t ph = phase;
+                const int n = issued < BIG_STAGES ? (int)issued : BIG_STAGES;
+                for (int i = 0; i < n; ++i) {
+                    if (--s < 0) {
+                        s = BIG_STAGES - 1;
+                        ph ^= 1u;
+                    }
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (!ptx::mbar_try_wait(full_bar(s), ph)) {
+                        if (ptx::globaltimer_ns() - t0 > 200000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BIG_BN, MAJA, MAJB);
+            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128, b_lbo = MAJB == 0 ? 16 : BK * 128;
+            constexpr uint32_t a_sbo = MAJA == 0 ? 1024 : 512, b_sbo = MAJB == 0 ? 1024 : 512;
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+                const uint32_t tile_par = local & 1u;
+                for (int it = 0; it < total_iters && ok; ++it) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_base + stage * BIG_STAGE_BYTES;
+                    const uint32_t sb = sa + BIG_A_BYTES;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (it == 0) {
+                            // accumulator h must have been drained by the epilogue of the previous tile
+                            if (!ptx::mbar_wait(tempty_bar(h), tile_par ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                                ok = false;
+                                break;
+                            }
+                            ptx::tc_fence_after();
+                        }
+                        // rows h*128.. of the A tile: 128 rows x 128 B (K-major) or 4 chunks x 4 KB
+                        const uint32_t sa_h = sa + h * (BM * BK * 4);
+                        const uint32_t d_tmem = tmem_base + h * BIG_BN;
+#pragma unroll
+                        for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                            const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                            const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                            const uint64_t da = ptx::smem_desc(sa_h + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::mma_commit(empty_bar(stage));
+                    if (++stage == BIG_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit(tfull_bar);  // both accumulators complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int slab = (warp - 2) >> 2;  // 128-column slab of the tile
+        const bool vec = p.vec_ok != 0;
+        const bool accumulate = p.accumulate != 0;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
+            const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
+            if (!ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, WAIT_LIMIT_NS)) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const int slab_col0 = c.n0 + slab * 128;
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const int row = c.m0 + h * 128 + q * 32 + lane;
+                const bool row_ok = row < p.M;
+                float* out_row = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)(row_ok ? row : 0) * p.ldc;
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + h * BIG_BN + slab * 128;
+                if (c.m0 + h * 128 < p.M) {  // warp-uniform: skip a half that lies below the matrix
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const int col0 = slab_col0 + ch * 32;
+                        if (col0 < p.N) {
+                            __syncwarp();
+                            uint32_t v[32];
+                            ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                            ptx::tmem_ld_wait();
+                            if (row_ok) {
+                                float f[32];
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                                store_chunk(f, out_row + col0, col0, p.N, vec, p.bias, accumulate);
+                            }
+                        }
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tempty_bar(h));
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<512>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
+}
+
 // ---------------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -578,6 +809,37 @@ int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream
     }
 }
 
+template <int MAJA, int MAJB>
+int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
+    constexpr int smem = BIG_STAGES * BIG_STAGE_BYTES + 1024 + 256;
+    auto kern = gemm_tf32_big_kernel<MAJA, MAJB>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            seterr(err, errlen, cudaGetErrorString(e));
+            return -3;
+        }
+        attr_done = true;
+    }
+    kern<<<grid, BIG_THREADS, smem, stream>>>(kp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        seterr(err, errlen, cudaGetErrorString(e));
+        return -3;
+    }
+    return 0;
+}
+
+// 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
+// amortise the accumulator hand-over between tiles.
+bool use_big_tiles(const GemmDesc& g) {
+    if (g.terms != 1 || g.splits > 1 || (g.debug & 8)) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + BIG_BM - 1) / BIG_BM) * ((g.N + BIG_BN - 1) / BIG_BN);
+    const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
+    return tiles >= gemm_sm100_num_ctas() && iters >= 32;
+}
+
 int pick_bn(const GemmDesc& g) {
     // Wide tiles when there is enough work to fill the machine with them, else narrow ones.
     if (g.N <= 128) return 128;
@@ -653,7 +915,9 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: split launch without scratch");
         return -1;
     }
-    const int bn = pick_bn(g);
+    const bool big = use_big_tiles(g);
+    const int bn = big ? BIG_BN : pick_bn(g);
+    const int bm = big ? BIG_BM : BM;
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
@@ -668,7 +932,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         if (ok && g.terms == 3) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile);
         return ok;
     };
-    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, BM) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
+    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, bm) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
@@ -698,7 +962,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                  (g.o0 == 1 || (g.c_bs0 & 3) == 0) && (g.o1 == 1 || (g.c_bs1 & 3) == 0))
                     ? 1
                     : 0;
-    kp.mt = (g.M + BM - 1) / BM;
+    kp.mt = (g.M + bm - 1) / bm;
     kp.nt = (g.N + bn - 1) / bn;
     kp.nkb = (g.K + BK - 1) / BK;
     const long long total = (long long)g.o0 * g.o1 * kp.mt * kp.nt * kp.splits;
@@ -715,6 +979,14 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     const int ctas = gemm_sm100_num_ctas();
     const int grid = (int)(total < ctas ? total : ctas);
 
+    if (big) {
+        switch (g.A.mn_major * 2 + g.B.mn_major) {
+            case 0: return launch_big_variant<0, 0>(kp, grid, stream, err, errlen);
+            case 1: return launch_big_variant<0, 1>(kp, grid, stream, err, errlen);
+            case 2: return launch_big_variant<1, 0>(kp, grid, stream, err, errlen);
+            default: return launch_big_variant<1, 1>(kp, grid, stream, err, errlen);
+        }
+    }
     // fp32-accurate mode: chains of 2 k-blocks (64 deep) inside the tensor core, see the kernel.
     if (g.terms == 3) {
         if (bn == 256) return launch_major<256, 3, 2, 2>(g, kp, grid, stream, err, errlen);

@@ -304,3 +304,25 @@ def test_linearity_and_transpose_identity_8192():
     assert rel_fro(x, c3) < TOL_TF32
     a_np, b_np = A.to_numpy(), B.to_numpy()
     sampled_rows_check(a_np, b_np, c3, [0, 4097, 8191], TOL_FP32)
+
+
+def test_big_tile_kernel_ragged_all_layouts():
+    # Large enough for the 256 x 256-tile TF32 kernel (>= 148 such tiles), ragged in M, N and K,
+    # every operand layout through transposed views, plus the fused bias. Sampled rows vs fp64.
+    M, N, K = 3000, 3300, 1028
+    a, b = normal((M, K), 601, 0.05), normal((K, N), 602, 0.05)
+    at, bt = np.ascontiguousarray(a.T), np.ascontiguousarray(b.T)
+    bias = normal((1, N), 603)
+    A, B, AT, BT = dev(a), dev(b), dev(at), dev(bt)
+    rows = [0, 127, 128, 255, 256, 1500, 2943, 2999]
+    ref = a[rows].astype(np.float64) @ b.astype(np.float64)
+    for Aop, Bop in ((A, B), (A, BT.transpose(0, 1)), (AT.transpose(0, 1), B), (AT.transpose(0, 1), BT.transpose(0, 1))):
+        c = cabi.matmul_fwd(Aop, Bop, mode=MODE_TF32).to_numpy()
+        assert rel_fro(c[rows], ref) < TOL_TF32
+    c = cabi.matmul_fwd(A, B, bias=dev(bias), mode=MODE_TF32).to_numpy()
+    assert rel_fro(c[rows], ref + bias) < TOL_TF32
+    # batched: 2 x (1536 x 2560 x 1024) -> 2*6*10 = 120 tiles < 148: general kernel; 3 batches -> big kernel
+    ab, bb = normal((3, 1536, 1024), 604, 0.05), normal((1, 1024, 2560), 605, 0.05)
+    cb = cabi.matmul_fwd(dev(ab), dev(bb), mode=MODE_TF32).to_numpy()
+    for i in range(3):
+        assert rel_fro(cb[i][[0, 700, 1535]], ab[i][[0, 700, 1535]].astype(np.float64) @ bb[0].astype(np.float64)) < TOL_TF32
