@@ -71,17 +71,33 @@ __global__ void pack_split_kernel(const PackArgs a) {
     }
 }
 
-// Contiguous-source fast path of the split: 4 elements per thread, no index decode.
+// Contiguous-source fast path of the split: no index decode, four independent 16-byte loads in
+// flight per thread before the first use (the pass is HBM-bound; memory-level parallelism decides).
+__device__ __forceinline__ void split4(const float4 v, float4& h, float4& l) {
+    h.x = to_tf32_rna(v.x); l.x = v.x - h.x;
+    h.y = to_tf32_rna(v.y); l.y = v.y - h.y;
+    h.z = to_tf32_rna(v.z); l.z = v.z - h.z;
+    h.w = to_tf32_rna(v.w); l.w = v.w - h.w;
+}
+
 __global__ void split_vec4_kernel(const float4* __restrict__ src, float4* __restrict__ hi,
                                   float4* __restrict__ lo, int64_t n4) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        const float4 v = __ldg(src + i);
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n4; i += 4 * stride) {
+        float4 v[4], h, l;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcs(src + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            split4(v[u], h, l);
+            hi[i + u * stride] = h;
+            lo[i + u * stride] = l;
+        }
+    }
+    for (; i < n4; i += stride) {
         float4 h, l;
-        h.x = to_tf32_rna(v.x); l.x = v.x - h.x;
-        h.y = to_tf32_rna(v.y); l.y = v.y - h.y;
-        h.z = to_tf32_rna(v.z); l.z = v.z - h.z;
-        h.w = to_tf32_rna(v.w); l.w = v.w - h.w;
+        split4(__ldcs(src + i), h, l);
         hi[i] = h;
         lo[i] = l;
     }

@@ -45,7 +45,7 @@ def set_size(n):
 
 # DRAM bytes moved by one launch of the dominant kernel (dB = A^T.dC at 8192^3, TF32 mode), from
 # an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/. None = not captured.
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 1887909632  # dA launch at 8192^3: 1 653 852 160 read + 234 057 472 written
 
 
 def normal(shape, seed, sigma):
@@ -65,53 +65,71 @@ def measured_peaks():
 # ---------------------------------------------------------------------------------- clocks
 
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and clock-event reasons of one GPU in a background thread (NVML, read-only;
+    falls back to polling nvidia-smi when the NVML binding is missing)."""
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
+               ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, gpu_index):
-        self.rows = []
-        self.proc = None
+        self.rows = []          # (timestamp, sm_mhz, max_sm_mhz, power_w, reasons bitmask)
         self.gpu_index = gpu_index
+        self._stop = threading.Event()
+        self.thread = None
+        self.source = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.rows.append((time.time(), float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
+                                          float(mx), pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0, int(get_reasons(h))))
+                    except Exception:  # noqa: BLE001
+                        pass
+                    time.sleep(0.002)
+            self.source = "nvml"
+        except Exception:  # noqa: BLE001
+            fields = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                      "clocks_event_reasons.sw_power_cap,clocks_event_reasons.sw_thermal_slowdown,"
+                      "clocks_event_reasons.hw_thermal_slowdown")
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        out = subprocess.run(["nvidia-smi", f"--query-gpu={fields}", "--format=csv,noheader,nounits",
+                                              "-i", str(self.gpu_index)], capture_output=True, text=True, timeout=5).stdout
+                        r = [x.strip() for x in out.strip().split(",")]
+                        mask = sum(bit for (name, bit), v in zip(self.REASONS, r[3:7]) if v.lower().startswith("active"))
+                        self.rows.append((time.time(), float(r[0]), float(r[1]), float(r[2]), mask))
+                    except Exception:  # noqa: BLE001
+                        time.sleep(0.05)
+            self.source = "nvidia-smi"
+        self.thread = threading.Thread(target=loop, daemon=True)
+        self.thread.start()
 
     def stop(self):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except Exception:  # noqa: BLE001
-                self.proc.kill()
+        self._stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=5)
 
     def summary(self, t0, t1):
-        sm, mx, pw, reasons = [], [], [], set()
-        for ts, r in self.rows:
-            if ts < t0 or ts > t1 or len(r) < 9:
-                continue
-            try:
-                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
-                "reasons": sorted(reasons), "samples": len(sm)}
+        rows = [r for r in self.rows if t0 <= r[0] <= t1]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": self.source}
+        mask = 0
+        for r in rows:
+            mask |= r[4]
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_min_mhz": min(r[1] for r in rows),
+                "sm_max_mhz": max(r[2] for r in rows), "power_w_max": max(r[3] for r in rows),
+                "reasons": sorted(name for name, bit in self.REASONS if mask & bit), "samples": len(rows),
+                "source": self.source}
 
 
 # ---------------------------------------------------------------------------------- reference (CPU) arm
@@ -252,8 +270,12 @@ def run_gpu_arm(args):
     Cd, DAd, DBd = cabi.DeviceArray((N_SQ, N_SQ)), cabi.DeviceArray((N_SQ, N_SQ)), cabi.DeviceArray((N_SQ, N_SQ))
 
     results = {}
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
+    gpu_index = local_rank
+    try:   # NVML / nvidia-smi count physical GPUs; CUDA_VISIBLE_DEVICES may remap them
+        gpu_index = int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local_rank])
+    except (ValueError, IndexError):
+        pass
+    sampler = ClockSampler(gpu_index)
     if rank == 0:
         sampler.start()
 
@@ -417,7 +439,7 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
