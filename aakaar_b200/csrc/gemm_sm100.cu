@@ -77,10 +77,10 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     return c;
 }
 
-template <int BN, int TERMS>
+template <int BN, int TERMS, int BKT>
 struct SmemLayout {
-    static constexpr int A_BYTES = BM * BK * 4;
-    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int A_BYTES = BM * BKT * 4;
+    static constexpr int B_BYTES = BN * BKT * 4;
     static constexpr int STAGE_BYTES = (TERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
 };
 
@@ -118,10 +118,13 @@ __device__ __forceinline__ void store_chunk(float (&v)[32], float* dst, int col0
 // partial tiles into fp32 registers with round-to-nearest. The accumulator inside the tensor core
 // truncates on every add, which over a long contraction costs more accuracy than the fp32-accurate
 // mode may lose, so that mode keeps the in-core chains short. KC == 0: one chain per output tile.
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC>
+// BKT: fp32 per k-block. 32 = one 128-byte swizzle row per K-major tile row; 16 = 64-byte rows
+// (64-byte swizzle), used by the fp32-accurate mode to have four finer stages in flight instead of
+// two coarse ones (its stages carry hi and lo parts and are twice as large per k).
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 __global__ void __launch_bounds__(num_threads<BN>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
-    using L = SmemLayout<BN, TERMS>;
+    using L = SmemLayout<BN, TERMS, BKT>;
     constexpr int EPI_WARPS = (BN / 128) * 4;
     constexpr int CHUNK_ITERS = KC > 0 ? KC : 0x7fffffff;
     constexpr int TMEM_COLS = 2 * BN;  // two accumulators
@@ -189,7 +192,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
                 for (int it = it0; it < it1; ++it) {
                     const int r = it / p.nkb;
-                    const int k0 = (it - r * p.nkb) * BK;
+                    const int k0 = (it - r * p.nkb) * BKT;
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
                         ok = false;
                         break;
@@ -223,7 +226,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BM / CHUNK; ++ch)
-                                ptx::tma_load_5d(da + ch * (BK * 128), ma, fb, c.m0 + ch * CHUNK, k0,
+                                ptx::tma_load_5d(da + ch * (BKT * 128), ma, fb, c.m0 + ch * CHUNK, k0,
                                                  a0, a1, a2);
                         }
                         if (MAJB == 0) {
@@ -233,7 +236,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BN / CHUNK; ++ch)
-                                ptx::tma_load_5d(db + ch * (BK * 128), mb, fb, c.n0 + ch * CHUNK, k0,
+                                ptx::tma_load_5d(db + ch * (BKT * 128), mb, fb, c.n0 + ch * CHUNK, k0,
                                                  b0, b1, b2);
                         }
                     }
@@ -294,17 +297,20 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         const uint32_t sa_lo = sa + L::A_BYTES + L::B_BYTES;
                         const uint32_t sb_lo = sb + L::A_BYTES + L::B_BYTES;
 #pragma unroll
-                        for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                        for (int k8 = 0; k8 < BKT / UMMA_K; ++k8) {
                             // K-major: step 32 bytes inside the 128-byte swizzle row.
                             // MN-major: step 8 k-rows (two 4-row swizzle groups, 8 * 128 bytes).
                             const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
                             const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
-                            const uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128;
-                            const uint32_t b_lbo = MAJB == 0 ? 16 : BK * 128;
-                            const uint32_t a_sbo = MAJA == 0 ? 1024 : 512;
-                            const uint32_t b_sbo = MAJB == 0 ? 1024 : 512;
-                            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
-                            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+                            // K-major rows are BKT * 4 bytes (128- or 64-byte swizzle), 8 rows per group.
+                            constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
+                            constexpr uint32_t K_SBO = 8 * BKT * 4;
+                            const uint32_t a_lbo = MAJA == 0 ? 16 : BKT * 128;
+                            const uint32_t b_lbo = MAJB == 0 ? 16 : BKT * 128;
+                            const uint32_t a_sbo = MAJA == 0 ? K_SBO : 512;
+                            const uint32_t b_sbo = MAJB == 0 ? K_SBO : 512;
+                            constexpr uint32_t a_lay = MAJA == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+                            constexpr uint32_t b_lay = MAJB == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
                             const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
@@ -744,7 +750,7 @@ MapPlan plan_map(const GemmOperand& op, int mn, const int batch[3], bool allow_f
 }
 
 bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const MapPlan& mp, int mn,
-              int k, int tile_mn) {
+              int k, int tile_mn, int bk) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return false;
     const uint64_t d0 = op.mn_major ? mn : k;
@@ -759,26 +765,28 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const 
         dims[0] = CHUNK; dims[1] = (cuuint64_t)k; dims[2] = (cuuint64_t)(mn / CHUNK);
         dims[3] = mp.ext[0]; dims[4] = mp.ext[1];
         strides[0] = ld_b; strides[1] = CHUNK * 4; strides[2] = bstride(0); strides[3] = bstride(1);
-        box[0] = CHUNK; box[1] = BK; box[2] = (cuuint32_t)(tile_mn / CHUNK); box[3] = 1; box[4] = 1;
+        box[0] = CHUNK; box[1] = (cuuint32_t)bk; box[2] = (cuuint32_t)(tile_mn / CHUNK); box[3] = 1; box[4] = 1;
     } else {
         // (unit-stride matrix dim, other matrix dim, batch, batch, batch)
         dims[0] = d0; dims[1] = d1; dims[2] = mp.ext[0]; dims[3] = mp.ext[1]; dims[4] = mp.ext[2];
         strides[0] = ld_b; strides[1] = bstride(0); strides[2] = bstride(1); strides[3] = bstride(2);
-        box[0] = 32; box[1] = (cuuint32_t)(op.mn_major ? BK : tile_mn); box[2] = box[3] = box[4] = 1;
+        box[0] = (cuuint32_t)(op.mn_major ? 32 : bk); box[1] = (cuuint32_t)(op.mn_major ? bk : tile_mn);
+        box[2] = box[3] = box[4] = 1;
     }
     cuuint32_t estr[5] = {1u, 1u, 1u, 1u, 1u};
     CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides,
                      box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                  : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC>
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
-    using L = SmemLayout<BN, TERMS>;
+    using L = SmemLayout<BN, TERMS, BKT>;
     constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256;
-    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC>;
+    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -797,15 +805,15 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
     return 0;
 }
 
-template <int BN, int TERMS, int STAGES, int KC>
+template <int BN, int TERMS, int STAGES, int KC, int BKT>
 int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream_t s, char* err,
                  int errlen) {
     const int key = g.A.mn_major * 2 + g.B.mn_major;
     switch (key) {
-        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
-        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
-        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
-        default: return launch_variant<BN, 1, 1, TERMS, STAGES, KC>(kp, grid, s, err, errlen);
+        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
+        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
+        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
+        default: return launch_variant<BN, 1, 1, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
     }
 }
 
@@ -918,18 +926,19 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     const bool big = use_big_tiles(g);
     const int bn = big ? BIG_BN : pick_bn(g);
     const int bm = big ? BIG_BM : BM;
+    const int bk = g.terms == 3 ? 16 : BK;  // finer stages for the hi+lo mode
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
     MapPlan pa = plan_map(g.A, g.M, batch, g.debug & 4 ? false : true);
     MapPlan pb = plan_map(g.B, g.N, batch, g.debug & 4 ? false : true);
     auto build = [&](CUtensorMap* hi, CUtensorMap* lo, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
-        bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile);
+        bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
         if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
             mp.fold = false;
-            ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile);
+            ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
         }
-        if (ok && g.terms == 3) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile);
+        if (ok && g.terms == 3) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile, bk);
         return ok;
     };
     if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, bm) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
@@ -964,7 +973,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                     : 0;
     kp.mt = (g.M + bm - 1) / bm;
     kp.nt = (g.N + bn - 1) / bn;
-    kp.nkb = (g.K + BK - 1) / BK;
+    kp.nkb = (g.K + bk - 1) / bk;
     const long long total = (long long)g.o0 * g.o1 * kp.mt * kp.nt * kp.splits;
     if (total > 0x7fffffffLL) {
         seterr(err, errlen, "gemm_sm100: too many tiles");
@@ -987,13 +996,13 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
             default: return launch_big_variant<1, 1>(kp, grid, stream, err, errlen);
         }
     }
-    // fp32-accurate mode: chains of 2 k-blocks (64 deep) inside the tensor core, see the kernel.
+    // fp32-accurate mode: 16-deep k-blocks, chains of 4 of them (64 deep) inside the tensor core.
     if (g.terms == 3) {
-        if (bn == 256) return launch_major<256, 3, 2, 2>(g, kp, grid, stream, err, errlen);
-        return launch_major<128, 3, 3, 2>(g, kp, grid, stream, err, errlen);
+        if (bn == 256) return launch_major<256, 3, 4, 4, 16>(g, kp, grid, stream, err, errlen);
+        return launch_major<128, 3, 6, 4, 16>(g, kp, grid, stream, err, errlen);
     }
-    if (bn == 256) return launch_major<256, 1, 4, 0>(g, kp, grid, stream, err, errlen);
-    return launch_major<128, 1, 6, 0>(g, kp, grid, stream, err, errlen);
+    if (bn == 256) return launch_major<256, 1, 4, 0, 32>(g, kp, grid, stream, err, errlen);
+    return launch_major<128, 1, 6, 0, 32>(g, kp, grid, stream, err, errlen);
 }
 
 }  // namespace akr

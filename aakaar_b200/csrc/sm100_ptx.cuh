@@ -167,6 +167,7 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //                     pattern repeating every 4 k-rows); lbo = byte stride between 32-element
 //                     (128 B) chunks along M/N, sbo = byte stride between groups of 4 k-rows.
 constexpr uint32_t LAYOUT_SW128 = 2;
+constexpr uint32_t LAYOUT_SW64 = 4;  // 64-byte swizzle span (K-major tiles with 64-byte rows)
 constexpr uint32_t LAYOUT_SW128_ATOM32B = 1;
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
                                               uint32_t layout) {
