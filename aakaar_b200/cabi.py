@@ -75,6 +75,9 @@ def load():
         "akr_set_cudnn_tf32": [C.c_int],
         "akr_set_device": [C.c_int],
         "akr_set_gemm_cta_limit": [C.c_int],
+        "akr_stream_create": [C.POINTER(vp)],
+        "akr_stream_destroy": [vp],
+        "akr_stream_wait_event": [vp, vp],
         "akr_event_create": [C.POINTER(vp)],
         "akr_event_record": [vp, vp],
         "akr_event_synchronize": [vp],
@@ -183,6 +186,25 @@ class DeviceArray:
         return True
 
 
+class Stream:
+    """A non-blocking CUDA stream owned by the library."""
+
+    def __init__(self):
+        self.h = C.c_void_p()
+        check(lib().akr_stream_create(C.byref(self.h)))
+
+    def wait_event(self, ev: "Event"):
+        check(lib().akr_stream_wait_event(self.h, ev.h))
+
+    def synchronize(self):
+        check(lib().akr_stream_synchronize(self.h))
+
+    def __del__(self):
+        if _lib is not None and self.h:
+            _lib.akr_stream_destroy(self.h)
+            self.h = None
+
+
 class Event:
     """CUDA event on the library's stream (NULL = legacy default stream)."""
 
@@ -190,8 +212,8 @@ class Event:
         self.h = C.c_void_p()
         check(lib().akr_event_create(C.byref(self.h)))
 
-    def record(self):
-        check(lib().akr_event_record(self.h, None))
+    def record(self, stream=None):
+        check(lib().akr_event_record(self.h, stream.h if stream is not None else None))
         return self
 
     def synchronize(self):
@@ -216,16 +238,20 @@ def plan(a: DeviceArray, b: DeviceArray):
     return tuple(shape[i] for i in range(nd.value))
 
 
-def matmul_fwd(a, b, bias=None, mode=MODE_GLOBAL, out=None):
+def _sh(stream):
+    return stream.h if stream is not None else None
+
+
+def matmul_fwd(a, b, bias=None, mode=MODE_GLOBAL, out=None, stream=None):
     c = out if out is not None else DeviceArray(plan(a, b))
     va, vb, vc = a.view(), b.view(), c.view()
     vbias = bias.view() if bias is not None else None
     check(lib().akr_matmul_fwd(C.byref(va), C.byref(vb), C.byref(vbias) if bias is not None else None,
-                               C.byref(vc), mode, None))
+                               C.byref(vc), mode, _sh(stream)))
     return c
 
 
-def matmul_bwd(a, b, dc, mode=MODE_GLOBAL, need_da=True, need_db=True, da=None, db=None):
+def matmul_bwd(a, b, dc, mode=MODE_GLOBAL, need_da=True, need_db=True, da=None, db=None, stream=None):
     if need_da and da is None:
         da = DeviceArray(a.shape)
     if need_db and db is None:
@@ -235,7 +261,7 @@ def matmul_bwd(a, b, dc, mode=MODE_GLOBAL, need_da=True, need_db=True, da=None, 
     vdb = db.view() if need_db else None
     check(lib().akr_matmul_bwd(C.byref(va), C.byref(vb), C.byref(vg),
                                C.byref(vda) if need_da else None, C.byref(vdb) if need_db else None,
-                               mode, None))
+                               mode, _sh(stream)))
     return (da if need_da else None), (db if need_db else None)
 
 
@@ -244,6 +270,15 @@ def matmul_simt(a, b):
     va, vb, vc = a.view(), b.view(), c.view()
     check(lib().akr_matmul_fwd_simt(C.byref(va), C.byref(vb), C.byref(vc), None))
     return c
+
+
+def h2d(dst: DeviceArray, src_np, stream=None, dst_offset_elems=0):
+    """Asynchronous copy of a C-contiguous float32 numpy array (ideally page-locked) into `dst`."""
+    check(lib().akr_memcpy_h2d(dst.ptr + 4 * dst_offset_elems, src_np.ctypes.data, src_np.nbytes, _sh(stream)))
+
+
+def d2h(dst_np, src: DeviceArray, stream=None, src_offset_elems=0):
+    check(lib().akr_memcpy_d2h(dst_np.ctypes.data, src.ptr + 4 * src_offset_elems, dst_np.nbytes, _sh(stream)))
 
 
 def synchronize():

@@ -821,6 +821,27 @@ AKR_API int akr_set_gemm_cta_limit(int ctas) {
     return AKR_OK;
 }
 
+AKR_API int akr_stream_create(void** stream) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    cudaStream_t s;
+    cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreateWithFlags");
+    *stream = (void*)s;
+    return AKR_OK;
+}
+AKR_API int akr_stream_destroy(void* stream) {
+    cudaError_t e = cudaStreamDestroy((cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamDestroy");
+    return AKR_OK;
+}
+AKR_API int akr_stream_wait_event(void* stream, void* event) {
+    cudaError_t e = cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+    return AKR_OK;
+}
+
 AKR_API int akr_event_create(void** event) {
     DeviceState* st = nullptr;
     int rc = need_gpu(&st);

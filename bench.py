@@ -366,7 +366,83 @@ def run_gpu_arm(args):
         ak.set_tf32(False)
         return max_over_ranks(e0.elapsed_ms(e1)) / steps
 
-    ms_e2e = e2e_phase(max(3, min(args.steps, 5)), 3)
+    # ---- end to end through the C ABI with three streams: H2D, compute and D2H overlap.
+    # Row chunks of A / dC feed the forward and dA GEMMs as they arrive; dB is computed in row
+    # panels once dC is complete, each panel's download overlapping the next panel's GEMM.
+    def e2e_pipelined_phase(steps, warmup, nch=4):
+        s_in, s_c, s_out = cabi.Stream(), cabi.Stream(), cabi.Stream()
+        rows = N_SQ // nch
+        mode = cabi.MODE_TF32
+
+        def rowv(x, i):
+            return x.as_strided((rows, N_SQ), (N_SQ, 1), offset=i * rows * N_SQ)
+
+        def colv(x, j):
+            return x.as_strided((N_SQ, rows), (N_SQ, 1), offset=j * rows)
+
+        def step():
+            ev = lambda: cabi.Event()   # noqa: E731
+            e_b = ev()
+            cabi.h2d(B, hB, s_in); e_b.record(s_in)
+            e_a, e_dc = [], []
+            for i in range(nch):
+                cabi.h2d(A, hA[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
+                e_a.append(ev().record(s_in))
+            for i in range(nch):
+                cabi.h2d(DC, hDC[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
+                e_dc.append(ev().record(s_in))
+            s_c.wait_event(e_b)
+            for i in range(nch):                                   # forward, chunk by chunk
+                s_c.wait_event(e_a[i])
+                cabi.matmul_fwd(rowv(A, i), B, mode=mode, out=rowv(Cd, i), stream=s_c)
+                e = ev().record(s_c)
+                s_out.wait_event(e)
+                cabi.d2h(hC[i * rows:(i + 1) * rows], Cd, s_out, i * rows * N_SQ)
+            for i in range(nch):                                   # dA, chunk by chunk
+                s_c.wait_event(e_dc[i])
+                cabi.matmul_bwd(rowv(A, i), B, rowv(DC, i), mode=mode, need_da=True, need_db=False,
+                                da=rowv(DAd, i), stream=s_c)
+                e = ev().record(s_c)
+                s_out.wait_event(e)
+                cabi.d2h(hDA[i * rows:(i + 1) * rows], DAd, s_out, i * rows * N_SQ)
+            if n_gpus == 1:
+                for j in range(nch):                               # dB in row panels (k range j of A)
+                    cabi.matmul_bwd(colv(A, j), rowv(B, j), DC, mode=mode, need_da=False, need_db=True,
+                                    db=rowv(DBd, j), stream=s_c)
+                    e = ev().record(s_c)
+                    s_out.wait_event(e)
+                    cabi.d2h(hDB[j * rows:(j + 1) * rows], DBd, s_out, j * rows * N_SQ)
+            else:
+                cabi.matmul_bwd(A, B, DC, mode=mode, need_da=False, need_db=True, db=DBd, stream=s_c)
+                s_c.synchronize()
+                h = CudaBackend(mode=mode).allreduce_start(DBd)
+                h[0].wait()
+                cabi.d2h(hDB, DBd, None)
+                cabi.synchronize()
+            s_out.synchronize()
+
+        for _ in range(warmup):
+            step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        cabi.synchronize()
+        t1 = time.perf_counter()
+        barrier()
+        return max_over_ranks((t1 - t0) * 1e3) / steps
+
+    ms_e2e_api = e2e_phase(max(3, min(args.steps, 5)), 3)
+    probe_rows = (5, N_SQ // 2 + 4, N_SQ - 1)
+    snap = [np.array(h[r]) for h, r in zip((hC, hDA, hDB), probe_rows)]
+    for h, r in zip((hC, hDA, hDB), probe_rows):
+        h[r] = 0.0
+    ms_e2e = e2e_pipelined_phase(max(3, min(args.steps, 10)), 3)
+    # the overlapped path must deliver the same results as the sequential one
+    e2e_dev = max(float(np.abs(np.array(h[r]) - s0).max() / (np.abs(s0).max() + 1e-30))
+                  for h, r, s0 in zip((hC, hDA, hDB), probe_rows, snap))
+    if n_gpus == 1 and not e2e_dev < 1e-5:
+        raise RuntimeError(f"bench.py: overlapped end-to-end path disagrees with the sequential one ({e2e_dev})")
     if rank == 0:
         sampler.stop()
 
@@ -417,7 +493,10 @@ def run_gpu_arm(args):
                                                           "B replicated, dB all-reduced (NCCL)"},
         "clocks": clocks,
         "e2e": {"value": n_gpus * FLOP_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_each_way, "d2h_bytes_per_step": bytes_each_way},
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_each_way, "d2h_bytes_per_step": bytes_each_way,
+                "path": "C ABI, pinned host buffers, copies and GEMMs overlapped on three streams",
+                "python_api_sequential": {"ms_per_step": ms_e2e_api,
+                                          "value": n_gpus * FLOP_PER_STEP / (ms_e2e_api * 1e-3) / 1e12}},
         "gpu_launches": launches,
         "roofline": roofline,
         "cpu_baseline": cpu,

@@ -161,6 +161,13 @@ AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* 
  * 0 restores the default. No counterpart in the reference (it has no multi-GPU path). */
 AKR_API int akr_set_gemm_cta_limit(int ctas);
 
+/* Extra streams for hosts that overlap host<->device copies with the GEMMs (the reference issues
+ * everything on the default stream; no counterpart there). Streams are non-blocking with respect to
+ * the default stream; order them with events. */
+AKR_API int akr_stream_create(void** stream);
+AKR_API int akr_stream_destroy(void* stream);
+AKR_API int akr_stream_wait_event(void* stream, void* event);
+
 /* CUDA events for timing on the stream the work was issued on (the reference times with
  * synchronize() + host clocks, docs/concepts/hardware-and-cuda/performance.md:52-75). */
 AKR_API int akr_event_create(void** event);
