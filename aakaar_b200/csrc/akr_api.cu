@@ -208,8 +208,8 @@ struct Prepared {
     std::vector<int64_t> bs;
 };
 
-// Decides how the GEMM kernel reads one operand: in place through TMA when its layout allows it
-// (TF32 mode), else from a packed copy; in fp32 mode always from freshly split hi / lo arrays.
+// Decides how the GEMM kernel reads one operand: in place through TMA when its layout allows it,
+// else from a packed copy; with `split` from freshly split hi / lo arrays (large fp32-accurate products).
 int prepare_operand(DeviceState* st, const Operand& src, int64_t mn, int64_t k,
                     const std::vector<Dim>& dims, bool is_a, bool split, cudaStream_t stream,
                     Prepared* out) {
@@ -302,7 +302,15 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     for (const Dim& d : all)
         if (d.e > 0x7fffffff) return fail(AKR_ERR_INVALID, "matmul: batch extent exceeds 2^31-1");
 
-    const bool split = p.mode == AKR_MODE_FP32;
+    // fp32-accurate mode: the kernel derives the low parts of its operands in shared memory, which
+    // costs shared-memory bandwidth. Large compute-bound products are faster when hi / lo are split
+    // once up front (an extra HBM pass over the operands) and both fetched by TMA.
+    bool split = false;
+    if (p.mode == AKR_MODE_FP32) {
+        const double flop = 2.0 * (double)p.M * (double)p.N * (double)p.K;
+        const double bytes = 4.0 * ((double)p.M * p.K + (double)p.K * p.N + (double)p.M * p.N);
+        split = flop / bytes >= 512.0;
+    }
     Prepared A, B;
     rc = prepare_operand(st, p.A, p.M, p.K, all, true, split, stream, &A);
     if (rc != AKR_OK) return rc;
@@ -325,7 +333,7 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     g.B = B.op;
     g.ldc = p.c_rs;
     g.bias = p.bias;
-    g.terms = split ? 3 : 1;
+    g.terms = p.mode == AKR_MODE_FP32 ? 3 : 1;
     g.o0 = g.o1 = g.red = 1;
     for (int i = 0; i < 3; ++i) g.A.bs[i] = g.B.bs[i] = 0;
     if (ko == 2) {

@@ -12,8 +12,9 @@
 //
 // Operand layouts: each operand may be K-major or M/N-major in global memory; the tile is staged
 // the way it lies and the UMMA descriptors carry the major-ness, so transposed views need no copy.
-// TF32 mode issues one MMA per 8-deep k-slice; 3xTF32 mode issues three (lo*hi, hi*lo, hi*hi) on
-// pre-split operands, giving fp32-level accuracy.
+// TF32 mode issues one MMA per 8-deep k-slice; 3xTF32 mode issues three (lo*hi, hi*lo, hi*hi), the
+// low parts either derived in shared memory by two converter warps or, for large compute-bound
+// products, split once up front and fetched by TMA; both give fp32-level accuracy.
 #include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
 
@@ -33,7 +34,9 @@ constexpr int GROUP_M = 16;    // tile rasterisation: m-tiles per group (L2 reus
 constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
 
 struct KernelParams {
-    CUtensorMap tmA, tmB, tmAlo, tmBlo;
+    CUtensorMap tmA, tmB;
+    CUtensorMap tmAlo, tmBlo;  // pre-split low parts (fp32-accurate mode of large products)
+    int presplit;              // 1: low parts come from tmAlo / tmBlo, 0: derived in shared memory
     float* C;
     const float* bias;
     float* partials;
@@ -86,32 +89,65 @@ struct SmemLayout {
 
 // Threads of one CTA: producer warp, MMA warp and one epilogue warp per (TMEM lane quarter,
 // 128-column slab of the tile).
-template <int BN>
-constexpr int num_threads() { return 64 + (BN / 128) * 128; }
+// plus, in the fp32-accurate mode, two converter warps that derive the low parts in shared memory.
+template <int BN, int TERMS = 1>
+constexpr int num_threads() { return 64 + (BN / 128) * 128 + (TERMS == 3 ? 64 : 0); }
 
-// Stores (or accumulates / adds bias to) 32 consecutive columns of one output row.
-__device__ __forceinline__ void store_chunk(float (&v)[32], float* dst, int col0, int N, bool vec,
-                                            const float* bias, bool accumulate) {
-    const bool full = col0 + 32 <= N;
+// Bytes of shared memory each epilogue warp uses to turn "one row per lane" into coalesced stores.
+constexpr int EPI_STAGE_BYTES = 32 * 128;
+
+// Stores a 32 x 32 block of the output held one row per lane (lane l: row row0 + l, columns
+// col0 .. col0+31). The block goes through a swizzled shared-memory tile so that every store
+// instruction writes 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes: with one row per
+// lane the LSU touches 32 cache lines per instruction, which capped the output rate of the
+// write-heavy (short-K, batched) products well below what HBM takes.
+// Must be called by all 32 lanes. Optionally adds a bias row vector and / or the previous contents.
+__device__ __forceinline__ void store_block_warp(float (&v)[32], uint32_t stage, float* out_base,
+                                                 long long ld, int row0, int M, int col0, int N, bool vec,
+                                                 const float* bias, bool accumulate, int lane) {
     if (bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            if (full || col0 + j < N) v[j] += __ldg(bias + col0 + j);
+            if (col0 + j < N) v[j] += __ldg(bias + col0 + j);
     }
-    if (accumulate) {
+    // lane's row -> 8 chunks of 16 bytes, chunk index XOR (row & 7): conflict-free both ways
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (full || col0 + j < N) v[j] += dst[j];
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t addr = stage + lane * 128 + ((j ^ (lane & 7)) << 4);
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                     : "memory");
     }
-    if (full && vec) {
+    __syncwarp();
+    const int c4 = lane & 7;
+    const int col = col0 + 4 * c4;
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-    } else {
+    for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3);
+        float4 x;
+        const uint32_t addr = stage + r * 128 + ((c4 ^ (r & 7)) << 4);
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                     : "r"(addr)
+                     : "memory");
+        const int grow = row0 + r;
+        if (grow < M && col < N) {
+            float* dst = out_base + (long long)grow * ld + col;
+            if (vec && col + 3 < N) {
+                if (accumulate) {
+                    const float4 o = *reinterpret_cast<const float4*>(dst);
+                    x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                }
+                *reinterpret_cast<float4*>(dst) = x;
+            } else {
+                const float e[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            if (col0 + j < N) dst[j] = v[j];
+                for (int t = 0; t < 4; ++t)
+                    if (col + t < N) dst[t] = accumulate ? dst[t] + e[t] : e[t];
+            }
+        }
     }
+    __syncwarp();  // the tile is reused by the next block
 }
 
 // KC > 0: the tensor core only accumulates KC k-blocks at a time; the epilogue warps add those
@@ -122,10 +158,11 @@ __device__ __forceinline__ void store_chunk(float (&v)[32], float* dst, int col0
 // (64-byte swizzle), used by the fp32-accurate mode to have four finer stages in flight instead of
 // two coarse ones (its stages carry hi and lo parts and are twice as large per k).
 template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
-__global__ void __launch_bounds__(num_threads<BN>(), 1)
+__global__ void __launch_bounds__(num_threads<BN, TERMS>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     using L = SmemLayout<BN, TERMS, BKT>;
     constexpr int EPI_WARPS = (BN / 128) * 4;
+    constexpr int CONV_WARPS = TERMS == 3 ? 2 : 0;
     constexpr int CHUNK_ITERS = KC > 0 ? KC : 0x7fffffff;
     constexpr int TMEM_COLS = 2 * BN;  // two accumulators
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
@@ -142,9 +179,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    auto conv_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 4 + s); };  // low parts written
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+    const uint32_t epi_stage_base = bar_base + 256;  // EPI_WARPS tiles of EPI_STAGE_BYTES
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -153,6 +192,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
+            ptx::mbar_init(conv_bar(s), CONV_WARPS > 0 ? CONV_WARPS : 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
@@ -163,10 +203,6 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&p.tmA);
         ptx::prefetch_tensormap(&p.tmB);
-        if (TERMS == 3) {
-            ptx::prefetch_tensormap(&p.tmAlo);
-            ptx::prefetch_tensormap(&p.tmBlo);
-        }
     }
     if (warp == 1) {
         ptx::tmem_alloc<TMEM_COLS>(ptx::smem_u32(tmem_slot));
@@ -207,14 +243,14 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         }
                         continue;
                     }
-                    ptx::mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
+                    ptx::mbar_arrive_expect_tx(fb, (TERMS == 3 && p.presplit) ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES);
                     const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                     const uint32_t sb = sa + L::A_BYTES;
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
                     const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-#pragma unroll
-                    for (int term = 0; term < (TERMS == 3 ? 2 : 1); ++term) {
+                    const int nterm = (TERMS == 3 && p.presplit) ? 2 : 1;
+                    for (int term = 0; term < nterm; ++term) {
                         const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
                         const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
                         const uint32_t da = sa + term * (L::A_BYTES + L::B_BYTES);
@@ -287,7 +323,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     ptx::tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     for (int it = cs; it < ce; ++it) {
-                        if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                        // fp32-accurate mode: the stage is ready once the converter warps wrote the low parts
+                        if (!ptx::mbar_wait((TERMS == 3 && !p.presplit) ? conv_bar(stage) : full_bar(stage), phase, abort_flag,
+                                            WAIT_LIMIT_NS)) {
                             ok = false;
                             break;
                         }
@@ -337,6 +375,51 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 }
             }
         }
+    } else if (CONV_WARPS > 0 && warp >= 2 + EPI_WARPS) {
+        // ------------------------------------------------------------ low-part converter (fp32 mode)
+        // The tensor core truncates an fp32 operand to TF32, so the raw tile already acts as the high
+        // part trunc(x). These warps write lo = x - trunc(x) (exact in fp32) beside it, at the same
+        // offset, so the swizzled tile layout is preserved without knowing it.
+        const int ct = (warp - 2 - EPI_WARPS) * 32 + lane;
+        constexpr int RAW_BYTES = L::A_BYTES + L::B_BYTES;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        // with pre-split operands the low parts arrive by TMA and these warps have nothing to do
+        for (int t = blockIdx.x; t < p.total_tiles && ok && !p.presplit; t += gridDim.x) {
+            const Tile c = decode_tile(t, p, BN);
+            const int it0 = (int)((long long)total_iters * c.split / p.splits);
+            const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
+            for (int it = it0; it < it1; ++it) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS))) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t src = smem_base + stage * L::STAGE_BYTES;
+#pragma unroll 4
+                for (int o = ct * 16; o < RAW_BYTES; o += CONV_WARPS * 32 * 16) {
+                    float4 x;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                                 : "r"(src + o)
+                                 : "memory");
+                    x.x -= __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
+                    x.y -= __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+                    x.z -= __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
+                    x.w -= __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(src + RAW_BYTES + o), "f"(x.x),
+                                 "f"(x.y), "f"(x.z), "f"(x.w)
+                                 : "memory");
+                }
+                ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(conv_bar(stage));
+                if (++stage == STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2 ..)
         const int q = warp & 3;             // TMEM lane quarter this warp may read
@@ -349,19 +432,22 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const Tile c = decode_tile(t, p, BN);
             const int it0 = (int)((long long)total_iters * c.split / p.splits);
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
-            const int row = c.m0 + q * 32 + lane;
+            const int row0 = c.m0 + q * 32;   // first row of this warp's 32-row band
+            const int row = row0 + lane;
             const bool row_ok = row < p.M;
-            float* out_row;
+            float* out_base;
+            long long out_ld;
             bool vec;
             if (split_mode) {
-                out_row = p.partials +
-                          (((size_t)c.split * nbatch + c.batch) * p.M + (size_t)(row_ok ? row : 0)) *
-                              (size_t)p.N;
+                out_base = p.partials + ((size_t)c.split * nbatch + c.batch) * (size_t)p.M * (size_t)p.N;
+                out_ld = p.N;
                 vec = (p.N & 3) == 0;
             } else {
-                out_row = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)(row_ok ? row : 0) * p.ldc;
+                out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+                out_ld = p.ldc;
                 vec = p.vec_ok != 0;
             }
+            const uint32_t my_stage = epi_stage_base + (warp - 2) * EPI_STAGE_BYTES;
             const float* bias = split_mode ? nullptr : p.bias;
             const bool accumulate = !split_mode && p.accumulate != 0;
             const int slab_col0 = c.n0 + slab * 128;
@@ -374,8 +460,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
-                if (!ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS)) {
-                    ok = false;
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS))) {
+                    ok = false;  // warp-uniform: every lane leaves together
                     break;
                 }
                 ptx::tc_fence_after();
@@ -391,11 +477,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         if (KC > 0) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)] += __uint_as_float(v[j]);
-                        } else if (row_ok) {
+                        } else {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            store_chunk(f, out_row + col0, col0, p.N, vec, bias, accumulate);
+                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
+                                             accumulate, lane);
                         }
                     }
                 }
@@ -405,7 +492,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
                 ++handoff;
             }
-            if (KC > 0 && ok && row_ok) {
+            if (KC > 0 && ok) {
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     const int col0 = slab_col0 + ch * 32;
@@ -413,7 +500,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)];
-                        store_chunk(f, out_row + col0, col0, p.N, vec, bias, accumulate);
+                        store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias, accumulate,
+                                         lane);
                     }
                 }
             }
@@ -492,6 +580,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * BIG_STAGES + 1 + h); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * BIG_STAGES + 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t epi_stage_base = bar_base + 256;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -647,7 +736,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
-            if (!ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, WAIT_LIMIT_NS)) {
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, WAIT_LIMIT_NS))) {
                 ok = false;
                 break;
             }
@@ -655,9 +744,9 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
             const int slab_col0 = c.n0 + slab * 128;
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                const int row = c.m0 + h * 128 + q * 32 + lane;
-                const bool row_ok = row < p.M;
-                float* out_row = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)(row_ok ? row : 0) * p.ldc;
+                const int row0 = c.m0 + h * 128 + q * 32;
+                float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+                const uint32_t my_stage = epi_stage_base + (warp - 2) * EPI_STAGE_BYTES;
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + h * BIG_BN + slab * 128;
                 if (c.m0 + h * 128 < p.M) {  // warp-uniform: skip a half that lies below the matrix
 #pragma unroll 1
@@ -668,12 +757,11 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                             uint32_t v[32];
                             ptx::tmem_ld_32x32(t_row + ch * 32, v);
                             ptx::tmem_ld_wait();
-                            if (row_ok) {
-                                float f[32];
+                            float f[32];
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                                store_chunk(f, out_row + col0, col0, p.N, vec, p.bias, accumulate);
-                            }
+                            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias,
+                                             accumulate, lane);
                         }
                     }
                 }
@@ -785,7 +873,7 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const 
 template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS, BKT>;
-    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256;
+    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256 + (BN / 128) * 4 * EPI_STAGE_BYTES;
     auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
@@ -796,7 +884,7 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
         }
         attr_done = true;
     }
-    kern<<<grid, num_threads<BN>(), smem, stream>>>(kp);
+    kern<<<grid, num_threads<BN, TERMS>(), smem, stream>>>(kp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -819,7 +907,7 @@ int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream
 
 template <int MAJA, int MAJB>
 int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
-    constexpr int smem = BIG_STAGES * BIG_STAGE_BYTES + 1024 + 256;
+    constexpr int smem = BIG_STAGES * BIG_STAGE_BYTES + 1024 + 256 + 8 * EPI_STAGE_BYTES;
     auto kern = gemm_tf32_big_kernel<MAJA, MAJB>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -915,10 +1003,6 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: operand not readable by TMA (alignment / stride)");
         return -1;
     }
-    if (g.terms == 3 && (!g.A.lo || !g.B.lo)) {
-        seterr(err, errlen, "gemm_sm100: 3xTF32 needs split operands");
-        return -1;
-    }
     if (g.splits > 1 && (!g.partials || !g.counters)) {
         seterr(err, errlen, "gemm_sm100: split launch without scratch");
         return -1;
@@ -932,19 +1016,21 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     std::memset(&kp, 0, sizeof(kp));
     MapPlan pa = plan_map(g.A, g.M, batch, g.debug & 4 ? false : true);
     MapPlan pb = plan_map(g.B, g.N, batch, g.debug & 4 ? false : true);
+    const bool presplit = g.terms == 3 && g.A.lo != nullptr && g.B.lo != nullptr;
     auto build = [&](CUtensorMap* hi, CUtensorMap* lo, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
         bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
         if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
             mp.fold = false;
             ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
         }
-        if (ok && g.terms == 3) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile, bk);
+        if (ok && presplit) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile, bk);
         return ok;
     };
     if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, bm) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
+    kp.presplit = presplit ? 1 : 0;
     kp.a_fold = pa.fold ? 1 : 0;
     kp.b_fold = pb.fold ? 1 : 0;
     for (int i = 0; i < 3; ++i) {

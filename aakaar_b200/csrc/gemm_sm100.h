@@ -14,7 +14,7 @@ namespace akr {
 
 struct GemmOperand {
     const float* ptr = nullptr;  // first element of the view
-    const float* lo = nullptr;   // 3xTF32 only: low parts, same geometry as ptr
+    const float* lo = nullptr;   // optional pre-split low parts (same geometry); then ptr holds the high parts
     int mn_major = 0;            // 1: the M (for A) / N (for B) index is unit stride; 0: K is
     int64_t ld = 0;              // element stride of the other matrix dim
     int64_t bs[3] = {0, 0, 0};   // element strides along o0, o1, r (0 = broadcast)
@@ -28,7 +28,8 @@ struct GemmDesc {
     int64_t ldc = 0, c_bs0 = 0, c_bs1 = 0;
     const float* bias = nullptr;  // optional row vector of N values added to every row
     int accumulate = 0;           // 1: C += result
-    int terms = 1;                // 1 = TF32, 3 = 3xTF32 (needs A.lo and B.lo)
+    int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate). With terms == 3 the low parts are
+                                  // derived in the kernel unless BOTH operands carry pre-split `lo` arrays
     // Split of the contraction across CTAs (weight gradients with few output tiles):
     // splits > 1 writes fp32 partials to `partials` ([splits][o0*o1][M][N]) and the last CTA
     // to finish a tile adds them up in split order. `counters` holds one int per output tile.

@@ -515,6 +515,126 @@ def run_gpu_arm(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------- other configurations
+
+def run_config(args):
+    """Secondary workloads (parity-test configurations, not the headline line): `c3` the broadcast
+    batched product with a transposed-view operand, `c5a` 8192 independent 256^3 products split
+    along batch over the ranks, `c2` the Linear-tanh-Linear-MSE-SGD training step."""
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from aakaar_b200 import cabi
+    import aakaar_b200 as ak
+    from aakaar_b200.distributed import shard_range
+    lib = cabi.lib()
+    cabi.check(lib.akr_set_device(local_rank))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks, peak_src = measured_peaks()
+
+    def uniform(shape, seed):
+        g = np.random.Generator(np.random.PCG64(seed))
+        return (g.random(shape, dtype=np.float32) * np.float32(2.0) - np.float32(1.0))
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        cabi.synchronize()
+        if dist is not None:
+            dist.barrier()
+            cabi.synchronize()
+        lib.akr_launch_count(1)
+        e0, e1 = cabi.Event().record(), cabi.Event()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        ms = e0.elapsed_ms(e1) / steps
+        launches = int(lib.akr_launch_count(0))
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    out = {"config": args.config, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
+    results = {}
+    if args.config == "c3":
+        base = cabi.DeviceArray.from_numpy(uniform((64, 8, 64, 512), 301))
+        B = cabi.DeviceArray.from_numpy(uniform((1, 8, 64, 512), 302))
+        A = base.transpose(2, 3)
+        DC = cabi.DeviceArray.from_numpy(np.ones((64, 8, 512, 512), np.float32))
+        Cd, DAd, DBd = cabi.DeviceArray((64, 8, 512, 512)), cabi.DeviceArray((64, 8, 512, 64)), cabi.DeviceArray((1, 8, 64, 512))
+        bytes_step = 1731 * 2 ** 20           # each operand read once, each result written once (fwd + dA + dB)
+        flop_step = 3 * 2 * 64 * 8 * 512 * 64 * 512
+        for name, mode in (("tf32", cabi.MODE_TF32), ("fp32_3xtf32", cabi.MODE_FP32)):
+            def step(mode=mode):
+                cabi.matmul_fwd(A, B, mode=mode, out=Cd)
+                cabi.matmul_bwd(A, B, DC, mode=mode, da=DAd, db=DBd)
+            ms, launches = timed(step, args.steps, args.warmup)
+            results[name] = {"ms_per_step": ms, "gbs": bytes_step / ms / 1e6, "tflops": flop_step / ms / 1e9,
+                             "frac_of_hbm": bytes_step / ms / 1e6 / peaks["hbm_gbs"], "gpu_launches_per_step": launches / args.steps}
+        out.update({"workload": "A [64,8,512,64] (transposed view) @ B [1,8,64,512], dC ones; fwd + dA + dB (dB summed over 64)",
+                    "bound": "hbm", "algorithmic_bytes_per_step": bytes_step, "hbm_peak_gbs": peaks["hbm_gbs"],
+                    "peak_source": peak_src, "scaling": "n/a"})
+    elif args.config == "c5a":
+        total = 8192
+        lo, hi = shard_range(total, world, rank)
+        nb = hi - lo
+        g = np.random.Generator(np.random.PCG64(501 + rank))
+        A = cabi.DeviceArray.from_numpy(g.random((nb, 256, 256), dtype=np.float32) * 2 - 1)
+        B = cabi.DeviceArray.from_numpy(g.random((nb, 256, 256), dtype=np.float32) * 2 - 1)
+        DC = cabi.DeviceArray.from_numpy(np.ones((nb, 256, 256), np.float32))
+        Cd, DAd, DBd = cabi.DeviceArray((nb, 256, 256)), cabi.DeviceArray((nb, 256, 256)), cabi.DeviceArray((nb, 256, 256))
+        bytes_step = 9 * total * 256 * 256 * 4     # whole job: 3 GEMMs x (2 operands + 1 result)
+        flop_step = 3 * 2 * total * 256 ** 3
+        for name, mode in (("tf32", cabi.MODE_TF32), ("fp32_3xtf32", cabi.MODE_FP32)):
+            def step(mode=mode):
+                cabi.matmul_fwd(A, B, mode=mode, out=Cd)
+                cabi.matmul_bwd(A, B, DC, mode=mode, da=DAd, db=DBd)
+            ms, launches = timed(step, args.steps, args.warmup)
+            results[name] = {"ms_per_step": ms, "gbs": bytes_step / ms / 1e6, "tflops": flop_step / ms / 1e9,
+                             "frac_of_hbm": bytes_step / ms / 1e6 / (peaks["hbm_gbs"] * world),
+                             "gpu_launches_per_step": launches / args.steps}
+        out.update({"workload": f"8192 independent [256x256]@[256x256] products, batch split over {world} rank(s), fwd + dA + dB",
+                    "bound": "hbm", "algorithmic_bytes_per_step": bytes_step, "hbm_peak_gbs": peaks["hbm_gbs"],
+                    "peak_source": peak_src, "scaling": "strong"})
+    else:  # c2
+        xn = normal((4096, 1024), 201, 1.0)
+        tn = normal((4096, 1024), 202, 1.0)
+        flop_step = 5 * 2 * 4096 * 1024 * 4096
+        for name, tf32 in (("tf32", True), ("fp32_3xtf32", False)):
+            ak.set_tf32(tf32)
+            np.random.seed(203)
+            l1, l2 = ak.nn.Linear(1024, 4096), ak.nn.Linear(4096, 1024)
+            x, t = ak.from_numpy(xn, "cuda"), ak.from_numpy(tn, "cuda")
+            opt = ak.optim.SGD(l1.parameters() + l2.parameters(), lr=0.01)
+
+            def step():
+                opt.zero_grad()
+                loss = ak.mse_loss(l2(l1(x).tanh()), t)
+                loss.backward()
+                opt.step()
+            ms, launches = timed(step, args.steps, args.warmup)
+            results[name] = {"ms_per_step": ms, "tflops": flop_step / ms / 1e9, "gpu_launches_per_step": launches / args.steps}
+        ak.set_tf32(False)
+        out.update({"workload": "MLP step: x[4096,1024] -> Linear 1024->4096 -> tanh -> Linear 4096->1024 -> MSE, backward, SGD",
+                    "bound": "tensor", "flop_per_step": flop_step, "flop_note": "5 needed GEMMs (the reference runs 6)",
+                    "scaling": "n/a"})
+    out["results"] = results
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -522,6 +642,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--config", default="sq8192", choices=["sq8192", "c2", "c3", "c5a"],
+                    help="sq8192 = the benchmark; c2 / c3 / c5a = secondary configurations (own JSON format)")
     ap.add_argument("--size", type=int, default=8192, help="square size (profiling only; the benchmark is 8192)")
     ap.add_argument("--profile", default="", choices=["", "tf32", "fp32"],
                     help="profiler capture run: one device phase only, warm-up not forced to 3")
@@ -536,6 +658,8 @@ def main():
         return 0
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.config != "sq8192":
+        return run_config(args)
     return run_gpu_arm(args)
 
 
