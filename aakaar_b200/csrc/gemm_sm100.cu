@@ -520,20 +520,42 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 const int is_last = *last_flag;
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-                if (is_last && row_ok) {
+                if (is_last) {
+                    // Lanes run along the columns (4 each) so that every load and store of the 32-row
+                    // band is a contiguous 512-byte row segment.
                     __threadfence();
-                    float* crow = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1 + (long long)row * p.ldc;
                     const size_t split_stride = (size_t)nbatch * p.M * p.N;
-                    const float* prow = p.partials + ((size_t)c.batch * p.M + row) * (size_t)p.N;
-                    const int ncols = min(128, p.N - slab_col0);
-                    for (int j = 0; j < ncols; ++j) {
-                        const int col = slab_col0 + j;
-                        float sum = 0.f;
-                        for (int sp = 0; sp < p.splits; ++sp)
-                            sum += __ldcg(prow + (size_t)sp * split_stride + col);
-                        if (p.bias != nullptr) sum += __ldg(p.bias + col);
-                        if (p.accumulate) sum += crow[col];
-                        crow[col] = sum;
+                    const float* pbase = p.partials + (size_t)c.batch * p.M * (size_t)p.N;
+                    float* cbase = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+                    const int col = slab_col0 + lane * 4;
+                    const bool pvec = (p.N & 3) == 0;
+                    const bool cvec = p.vec_ok != 0;
+                    for (int r = 0; r < 32; ++r) {
+                        const int grow = row0 + r;
+                        if (grow >= p.M) break;
+                        if (col >= p.N) continue;
+                        const float* prow = pbase + (size_t)grow * p.N + col;
+                        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+                        const int nv = min(4, p.N - col);
+                        for (int sp = 0; sp < p.splits; ++sp) {
+                            const float* q4 = prow + (size_t)sp * split_stride;
+                            if (pvec) {
+                                const float4 x = __ldcg(reinterpret_cast<const float4*>(q4));
+                                sum[0] += x.x; sum[1] += x.y; sum[2] += x.z; sum[3] += x.w;
+                            } else {
+                                for (int e = 0; e < nv; ++e) sum[e] += __ldcg(q4 + e);
+                            }
+                        }
+                        float* dst = cbase + (long long)grow * p.ldc + col;
+                        for (int e = 0; e < nv; ++e) {
+                            if (p.bias != nullptr) sum[e] += __ldg(p.bias + col + e);
+                            if (p.accumulate) sum[e] += dst[e];
+                        }
+                        if (cvec && nv == 4) {
+                            *reinterpret_cast<float4*>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                        } else {
+                            for (int e = 0; e < nv; ++e) dst[e] = sum[e];
+                        }
                     }
                 }
             }
@@ -939,6 +961,9 @@ bool use_big_tiles(const GemmDesc& g) {
 int pick_bn(const GemmDesc& g) {
     // Wide tiles when there is enough work to fill the machine with them, else narrow ones.
     if (g.N <= 128) return 128;
+    // A split contraction was sized (gemm_sm100_pick_splits) for 256-wide tiles: keep them, so that
+    // tiles x splits stays one balanced wave of CTAs.
+    if (g.splits > 1) return 256;
     const long long tiles256 = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + 255) / 256);
     return tiles256 >= gemm_sm100_num_ctas() ? 256 : 128;
 }

@@ -578,8 +578,14 @@ def run_config(args):
                 cabi.matmul_fwd(A, B, mode=mode, out=Cd)
                 cabi.matmul_bwd(A, B, DC, mode=mode, da=DAd, db=DBd)
             ms, launches = timed(step, args.steps, args.warmup)
+            parts = {}
+            for pname, fn in (("fwd", lambda m=mode: cabi.matmul_fwd(A, B, mode=m, out=Cd)),
+                              ("dA", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_db=False, da=DAd)),
+                              ("dB", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_da=False, db=DBd))):
+                parts[pname] = timed(fn, args.steps, 2)[0]
             results[name] = {"ms_per_step": ms, "gbs": bytes_step / ms / 1e6, "tflops": flop_step / ms / 1e9,
-                             "frac_of_hbm": bytes_step / ms / 1e6 / peaks["hbm_gbs"], "gpu_launches_per_step": launches / args.steps}
+                             "frac_of_hbm": bytes_step / ms / 1e6 / peaks["hbm_gbs"], "gpu_launches_per_step": launches / args.steps,
+                             "kernel_ms": parts}
         out.update({"workload": "A [64,8,512,64] (transposed view) @ B [1,8,64,512], dC ones; fwd + dA + dB (dB summed over 64)",
                     "bound": "hbm", "algorithmic_bytes_per_step": bytes_step, "hbm_peak_gbs": peaks["hbm_gbs"],
                     "peak_source": peak_src, "scaling": "n/a"})
