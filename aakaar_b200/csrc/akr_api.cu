@@ -961,6 +961,37 @@ AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream) {
         if (oshape[i] != grad->shape[i] && oshape[i] != 1)
             return fail(AKR_ERR_RUNTIME, "reduce_grad_to_shape: reduced gradient shape does not match target shape");
     }
+    // Bias-gradient shape: a dense gradient summed over its leading dims only -> column sums.
+    int lead = 0;
+    while (lead < grad->ndim && oshape[lead] == 1) ++lead;
+    bool colsum = lead > 0;
+    int64_t expect = 1, rows = 1, cols = 1;
+    for (int i = grad->ndim - 1; i >= 0 && colsum; --i) {
+        if (grad->shape[i] != 1 && grad->stride[i] != expect) colsum = false;
+        expect *= grad->shape[i];
+        if (i >= lead) {
+            if (oshape[i] != grad->shape[i]) colsum = false;
+            cols *= grad->shape[i];
+        } else {
+            rows *= grad->shape[i];
+        }
+    }
+    if (colsum && rows > 1 && cols >= 32) {
+        DeviceState* st = nullptr;
+        if ((rc = need_gpu(&st)) != AKR_OK) return rc;
+        void* partials = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(st->mu);
+            if ((rc = ws_get(st, WS_MISC, std::max<size_t>(colsum_partial_floats(rows, cols), 4096) * sizeof(float),
+                             &partials)) != AKR_OK)
+                return rc;
+        }
+        cudaError_t e = launch_colsum((const float*)grad->data, rows, cols, (float*)out->data, (float*)partials,
+                                      (cudaStream_t)stream);
+        if (e != cudaSuccess) return cuda_fail(e, "column-sum launch");
+        st->launches += 2;
+        return AKR_OK;
+    }
     AKR_LAUNCH(launch_sum_to(to_strided(grad), oshape, (float*)out->data, (cudaStream_t)stream), "sum_to launch");
 }
 

@@ -2,6 +2,7 @@
 // coalesced along the unit-stride dim, grids sized in multiples of the SM count.
 #include "aux_kernels.h"
 
+#include <algorithm>
 #include <cstdint>
 
 namespace akr {
@@ -231,6 +232,56 @@ __global__ void sum_to_kernel(const SumArgs a) {
     }
 }
 
+// Column sums, stage 1: block (x = 128-column strip, y = row chunk); each warp strides over the rows
+// of its chunk reading 512 contiguous bytes per row, the 8 warps are combined in shared memory.
+__global__ void colsum_partial_kernel(const float* __restrict__ g, int64_t rows, int64_t cols,
+                                      int64_t rows_per_chunk, float* __restrict__ partials) {
+    __shared__ float4 part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col = (int64_t)blockIdx.x * 128 + lane * 4;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+    const int64_t r1 = min(rows, r0 + rows_per_chunk);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col + 3 < cols && (cols & 3) == 0) {
+        for (int64_t r = r0 + warp; r < r1; r += 8) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * cols + col));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    } else {
+        for (int64_t r = r0 + warp; r < r1; r += 8) {
+            const float* p = g + r * cols + col;
+            if (col < cols) acc.x += p[0];
+            if (col + 1 < cols) acc.y += p[1];
+            if (col + 2 < cols) acc.z += p[2];
+            if (col + 3 < cols) acc.w += p[3];
+        }
+    }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        float4 s = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            const float4 v = part[w][lane];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        float* dst = partials + (int64_t)blockIdx.y * cols + col;
+        if (col < cols) dst[0] = s.x;
+        if (col + 1 < cols) dst[1] = s.y;
+        if (col + 2 < cols) dst[2] = s.z;
+        if (col + 3 < cols) dst[3] = s.w;
+    }
+}
+// stage 2: out[c] = sum over chunks, in chunk order
+__global__ void colsum_final_kernel(const float* __restrict__ partials, int chunks, int64_t cols,
+                                    float* __restrict__ out) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int k = 0; k < chunks; ++k) s += partials[(int64_t)k * cols + c];
+    out[c] = s;
+}
+
 __global__ void scale_kernel(const float* __restrict__ x, float alpha, float* __restrict__ y, size_t n) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = x[i] * alpha;
@@ -439,6 +490,24 @@ cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float*
     if (a.nkept == 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((a.nkept + 31) / 32);
     sum_to_kernel<<<blocks, dim3(32, 8), 0, s>>>(a);
+    return cudaGetLastError();
+}
+
+static int colsum_chunks(int64_t rows, int64_t cols) {
+    const int64_t strips = (cols + 127) / 128;
+    int64_t chunks = (148 * 4 + strips - 1) / strips;       // about four blocks per SM in total
+    chunks = std::min<int64_t>(chunks, (rows + 63) / 64);    // at least 64 rows per chunk
+    return (int)std::max<int64_t>(1, std::min<int64_t>(chunks, 256));
+}
+size_t colsum_partial_floats(int64_t rows, int64_t cols) { return (size_t)colsum_chunks(rows, cols) * (size_t)cols; }
+
+cudaError_t launch_colsum(const float* g, int64_t rows, int64_t cols, float* out, float* partials, cudaStream_t s) {
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    const int chunks = colsum_chunks(rows, cols);
+    const int64_t rpc = (rows + chunks - 1) / chunks;
+    dim3 grid((unsigned)((cols + 127) / 128), (unsigned)chunks);
+    colsum_partial_kernel<<<grid, 256, 0, s>>>(g, rows, cols, rpc, partials);
+    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, chunks, cols, out);
     return cudaGetLastError();
 }
 

@@ -48,6 +48,10 @@ cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, i
                        const int64_t* shape, cudaStream_t s);
 // out (contiguous `out_shape`, same rank as g, dims of size 1 where reduced) = sum of g over reduced dims
 cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float* out, cudaStream_t s);
+// Column sums of a dense [rows][cols] matrix (the bias gradient of a Linear layer): out[c] = sum_r g[r][c].
+// `partials` must hold colsum_partial_floats(rows, cols) floats. Deterministic (no atomics).
+size_t colsum_partial_floats(int64_t rows, int64_t cols);
+cudaError_t launch_colsum(const float* g, int64_t rows, int64_t cols, float* out, float* partials, cudaStream_t s);
 
 cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s);
 cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s);

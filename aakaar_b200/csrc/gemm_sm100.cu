@@ -964,8 +964,14 @@ int pick_bn(const GemmDesc& g) {
     // A split contraction was sized (gemm_sm100_pick_splits) for 256-wide tiles: keep them, so that
     // tiles x splits stays one balanced wave of CTAs.
     if (g.splits > 1) return 256;
-    const long long tiles256 = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + 255) / 256);
-    return tiles256 >= gemm_sm100_num_ctas() ? 256 : 128;
+    // Otherwise compare waves of CTAs: a 256-wide tile does twice the work of a 128-wide one, which in
+    // turn moves more operand bytes per flop (modelled as a 15 % penalty).
+    const long long rows = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM);
+    const long long t256 = rows * ((g.N + 255) / 256), t128 = rows * ((g.N + 127) / 128);
+    const long long ctas = gemm_sm100_num_ctas();
+    const double cost256 = 2.0 * (double)((t256 + ctas - 1) / ctas);
+    const double cost128 = 1.15 * (double)((t128 + ctas - 1) / ctas);
+    return cost256 <= cost128 ? 256 : 128;
 }
 
 }  // namespace

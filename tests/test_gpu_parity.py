@@ -326,3 +326,19 @@ def test_big_tile_kernel_ragged_all_layouts():
     cb = cabi.matmul_fwd(dev(ab), dev(bb), mode=MODE_TF32).to_numpy()
     for i in range(3):
         assert rel_fro(cb[i][[0, 700, 1535]], ab[i][[0, 700, 1535]].astype(np.float64) @ bb[0].astype(np.float64)) < TOL_TF32
+
+
+def test_sum_to_bias_gradient_shapes():
+    # reduce_grad_to_shape for a broadcast add: column-sum fast path (dense, leading dims summed) and generic path
+    import ctypes as C
+    lib = cabi.lib()
+    for gshape, oshape in (((1000, 77), (1, 77)), ((4096, 256), (1, 256)), ((3, 5, 40), (1, 1, 40)), ((3, 5, 40), (40,)),
+                           ((64, 16), (1, 16)), ((6, 1, 50), (1, 1, 50)), ((4, 7, 33), (4, 1, 33)), ((9, 9), (1,))):
+        g = normal(gshape, 11)
+        G_, O_ = dev(g), DA(oshape)
+        vg, vo = G_.view(), O_.view()
+        cabi.check(lib.akr_sum_to(C.byref(vg), C.byref(vo), None))
+        pad = (1,) * (len(gshape) - len(oshape)) + tuple(oshape)
+        axes = tuple(i for i, (a, b) in enumerate(zip(gshape, pad)) if a != b)
+        ref = g.astype(np.float64).sum(axis=axes, keepdims=True).reshape(oshape)
+        assert rel_fro(O_.to_numpy(), ref) < 1e-5, (gshape, oshape)
