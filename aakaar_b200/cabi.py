@@ -75,6 +75,7 @@ def load():
         "akr_set_cudnn_tf32": [C.c_int],
         "akr_set_device": [C.c_int],
         "akr_set_gemm_cta_limit": [C.c_int],
+        "akr_debug_configure": [C.c_int, C.c_uint],
         "akr_stream_create": [C.POINTER(vp)],
         "akr_stream_destroy": [vp],
         "akr_stream_wait_event": [vp, vp],

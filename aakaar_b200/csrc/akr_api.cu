@@ -824,6 +824,11 @@ AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* 
     return AKR_OK;
 }
 
+AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms) {
+    gemm_sm100_debug_configure(flags, wait_limit_ms);
+    return AKR_OK;
+}
+
 AKR_API int akr_set_gemm_cta_limit(int ctas) {
     gemm_sm100_set_cta_limit(ctas);
     return AKR_OK;

@@ -31,7 +31,7 @@ constexpr int BK = 32;         // fp32 per k-block: 128 bytes, one swizzle row
 constexpr int UMMA_K = 8;      // k per tcgen05.mma kind::tf32
 constexpr int CHUNK = 32;      // M/N elements per 128-byte row of an MN-major tile
 constexpr int GROUP_M = 16;    // tile rasterisation: m-tiles per group (L2 reuse of B panels)
-constexpr uint64_t WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
+constexpr uint64_t DEFAULT_WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
 
 struct KernelParams {
     CUtensorMap tmA, tmB;
@@ -52,7 +52,9 @@ struct KernelParams {
     int a_fold, b_fold;
     int accumulate, vec_ok;
     int mt, nt, nkb, total_tiles;
-    int debug;  // diagnostics: bit 0 = skip TMA loads, bit 1 = skip MMAs (timing experiments only)
+    int debug;  // diagnostics: bit 0 = skip TMA loads, bit 1 = skip MMAs (timing experiments only),
+                // bit 4 = the producer never signals a stage (exercises the bounded-wait abort path)
+    unsigned long long wait_limit_ns;
 };
 
 struct Tile {
@@ -229,11 +231,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 for (int it = it0; it < it1; ++it) {
                     const int r = it / p.nkb;
                     const int k0 = (it - r * p.nkb) * BKT;
-                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
                     }
                     const uint32_t fb = full_bar(stage);
+                    if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
                     if (p.debug & 1) {
                         ptx::mbar_arrive(fb);
                         ++issued;
@@ -316,7 +319,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     ce = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1;
                     const int buf = handoff & 1;
                     const uint32_t acc_phase = (handoff >> 1) & 1u;
-                    if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
                     }
@@ -325,7 +328,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     for (int it = cs; it < ce; ++it) {
                         // fp32-accurate mode: the stage is ready once the converter warps wrote the low parts
                         if (!ptx::mbar_wait((TERMS == 3 && !p.presplit) ? conv_bar(stage) : full_bar(stage), phase, abort_flag,
-                                            WAIT_LIMIT_NS)) {
+                                            p.wait_limit_ns)) {
                             ok = false;
                             break;
                         }
@@ -391,7 +394,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const int it0 = (int)((long long)total_iters * c.split / p.splits);
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             for (int it = it0; it < it1; ++it) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
@@ -460,7 +463,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, WAIT_LIMIT_NS))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
                     ok = false;  // warp-uniform: every lane leaves together
                     break;
                 }
@@ -641,11 +644,12 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                 for (int it = 0; it < total_iters; ++it) {
                     const int r = it / p.nkb;
                     const int k0 = (it - r * p.nkb) * BK;
-                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
                     }
                     const uint32_t fb = full_bar(stage);
+                    if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
                     ptx::mbar_arrive_expect_tx(fb, BIG_STAGE_BYTES);
                     const uint32_t da = smem_base + stage * BIG_STAGE_BYTES;
                     const uint32_t db = da + BIG_A_BYTES;
@@ -709,7 +713,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
                 const uint32_t tile_par = local & 1u;
                 for (int it = 0; it < total_iters && ok; ++it) {
-                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
                     }
@@ -720,7 +724,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                     for (int h = 0; h < 2; ++h) {
                         if (it == 0) {
                             // accumulator h must have been drained by the epilogue of the previous tile
-                            if (!ptx::mbar_wait(tempty_bar(h), tile_par ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+                            if (!ptx::mbar_wait(tempty_bar(h), tile_par ^ 1u, abort_flag, p.wait_limit_ns)) {
                                 ok = false;
                                 break;
                             }
@@ -758,7 +762,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, WAIT_LIMIT_NS))) {
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns))) {
                 ok = false;
                 break;
             }
@@ -977,6 +981,13 @@ int pick_bn(const GemmDesc& g) {
 }  // namespace
 
 static int g_cta_limit = 0;
+static int g_debug_flags = 0;
+static unsigned long long g_wait_limit_ns = DEFAULT_WAIT_LIMIT_NS;
+
+void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms) {
+    g_debug_flags = flags;
+    g_wait_limit_ns = wait_limit_ms ? (unsigned long long)wait_limit_ms * 1000000ull : DEFAULT_WAIT_LIMIT_NS;
+}
 
 void gemm_sm100_set_cta_limit(int ctas) { g_cta_limit = ctas > 0 ? ctas : 0; }
 
@@ -1101,7 +1112,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         return -1;
     }
     kp.total_tiles = (int)total;
-    kp.debug = g.debug;
+    kp.debug = g.debug | g_debug_flags;
+    kp.wait_limit_ns = g_wait_limit_ns;
     const int ctas = gemm_sm100_num_ctas();
     const int grid = (int)(total < ctas ? total : ctas);
 

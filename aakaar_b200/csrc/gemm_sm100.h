@@ -55,6 +55,9 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
 int gemm_sm100_num_ctas();
 // Caps the persistent grid (0 = one CTA per SM).
 void gemm_sm100_set_cta_limit(int ctas);
+// Test hooks: extra GemmDesc::debug bits for every launch, and the bound of every in-kernel wait
+// (0 = default, 4 s).
+void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms);
 
 // Bytes of `partials` and number of `counters` entries a split launch needs.
 void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* counter_count);

@@ -176,6 +176,14 @@ AKR_API int akr_event_synchronize(void* event);
 AKR_API int akr_event_elapsed_ms(void* start, void* end, float* ms);
 AKR_API int akr_event_destroy(void* event);
 
+/* Test hook for the failure path. Every wait inside the GEMM kernels is bounded; a kernel whose wait
+ * runs out stops, frees its tensor memory and sets a status word that akr_synchronize() reports as
+ * AKR_ERR_ABORTED, leaving the context usable. `wait_limit_ms` sets that bound (0 = default, 4 s);
+ * flag 16 makes the load warp never signal its stages, so that every waiter gives up; flags 1 / 2 / 4 / 8
+ * are timing diagnostics (skip loads, skip MMAs, no folded maps, no 256x256 tiles; results invalid).
+ * akr_debug_configure(0, 0) restores normal operation. */
+AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
+
 /* Bytes of scratch the library currently holds on this device (operand splits, split-K partials). */
 AKR_API int akr_workspace_bytes(size_t* bytes);
 /* Number of kernels launched by this library on this thread's device since the last reset. */

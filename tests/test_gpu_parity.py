@@ -342,3 +342,25 @@ def test_sum_to_bias_gradient_shapes():
         axes = tuple(i for i, (a, b) in enumerate(zip(gshape, pad)) if a != b)
         ref = g.astype(np.float64).sum(axis=axes, keepdims=True).reshape(oshape)
         assert rel_fro(O_.to_numpy(), ref) < 1e-5, (gshape, oshape)
+
+
+def test_bounded_wait_abort_is_reported_and_recoverable():
+    # Failure path without faulting the GPU: the load warp never signals, so every in-kernel wait runs
+    # out (bound lowered to 30 ms), the kernel stops cleanly and the host sees AKR_ERR_ABORTED once.
+    lib = cabi.lib()
+    a, b = uniform((256, 256), 1), uniform((256, 256), 2)
+    A, B = dev(a), dev(b)
+    cabi.synchronize()
+    try:
+        cabi.check(lib.akr_debug_configure(16, 30))
+        for mode in (MODE_TF32, MODE_FP32):
+            cabi.matmul_fwd(A, B, mode=mode)
+            with pytest.raises(cabi.AkrError) as e:
+                cabi.synchronize()
+            assert e.value.code == cabi.ERR_ABORTED
+            cabi.synchronize()   # reported once, then clear
+    finally:
+        cabi.check(lib.akr_debug_configure(0, 0))
+    # the context is still usable and results are right again
+    c = cabi.matmul_fwd(A, B, mode=MODE_FP32).to_numpy()
+    assert rel_fro(c, a.astype(np.float64) @ b.astype(np.float64)) < TOL_FP32
