@@ -48,6 +48,35 @@ def set_size(n):
 NCU_TRAFFIC_BYTES = 1887909632  # dA launch at 8192^3: 1 653 852 160 read + 234 057 472 written
 
 
+
+class _StdoutToStderr:
+    """Libraries (NCCL prints its version banner) must not write into the one-JSON-line stdout:
+    while active, file descriptor 1 points at stderr."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self._saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
+        return False
+
+
+def _init_nccl(local_rank):
+    import torch
+    import torch.distributed as dist
+    with _StdoutToStderr():
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        t = torch.zeros(1, device="cuda")
+        dist.all_reduce(t)          # forces communicator creation (and its banner) now
+        torch.cuda.synchronize()
+    return dist
+
 def normal(shape, seed, sigma):
     g = np.random.Generator(np.random.PCG64(seed))
     return (g.standard_normal(shape, dtype=np.float32) * np.float32(sigma))
@@ -239,10 +268,7 @@ def run_gpu_arm(args):
 
     dist = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = _init_nccl(local_rank)
 
     def barrier():
         cabi.synchronize()
@@ -531,10 +557,7 @@ def run_config(args):
     cabi.check(lib.akr_set_device(local_rank))
     dist = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = _init_nccl(local_rank)
     peaks, peak_src = measured_peaks()
 
     def uniform(shape, seed):
