@@ -18,6 +18,7 @@
 #include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -104,7 +105,7 @@ constexpr int EPI_STAGE_BYTES = 32 * 128;
 // lane the LSU touches 32 cache lines per instruction, which capped the output rate of the
 // write-heavy (short-K, batched) products well below what HBM takes.
 // Must be called by all 32 lanes. Optionally adds a bias row vector and / or the previous contents.
-__device__ __forceinline__ void store_block_warp(float (&v)[32], uint32_t stage, float* out_base,
+__device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, float* out_base,
                                                  long long ld, int row0, int M, int col0, int N, bool vec,
                                                  const float* bias, bool accumulate, int lane) {
     if (bias != nullptr) {
@@ -114,35 +115,30 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], uint32_t stage,
     }
     // lane's row -> 8 chunks of 16 bytes, chunk index XOR (row & 7): conflict-free both ways
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t addr = stage + lane * 128 + ((j ^ (lane & 7)) << 4);
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                     "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
-                     : "memory");
-    }
+    for (int j = 0; j < 8; ++j)
+        stage[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     __syncwarp();
     const int c4 = lane & 7;
     const int col = col0 + 4 * c4;
+    float4 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {  // all eight reads in flight before the first global store
+        const int r = 4 * i + (lane >> 3);
+        x[i] = stage[r * 8 + (c4 ^ (r & 7))];
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int r = 4 * i + (lane >> 3);
-        float4 x;
-        const uint32_t addr = stage + r * 128 + ((c4 ^ (r & 7)) << 4);
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                     : "r"(addr)
-                     : "memory");
-        const int grow = row0 + r;
+        const int grow = row0 + 4 * i + (lane >> 3);
         if (grow < M && col < N) {
             float* dst = out_base + (long long)grow * ld + col;
             if (vec && col + 3 < N) {
                 if (accumulate) {
                     const float4 o = *reinterpret_cast<const float4*>(dst);
-                    x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                    x[i].x += o.x; x[i].y += o.y; x[i].z += o.z; x[i].w += o.w;
                 }
-                *reinterpret_cast<float4*>(dst) = x;
+                *reinterpret_cast<float4*>(dst) = x[i];
             } else {
-                const float e[4] = {x.x, x.y, x.z, x.w};
+                const float e[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                 for (int t = 0; t < 4; ++t)
                     if (col + t < N) dst[t] = accumulate ? dst[t] + e[t] : e[t];
@@ -185,7 +181,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
-    const uint32_t epi_stage_base = bar_base + 256;  // EPI_WARPS tiles of EPI_STAGE_BYTES
+    uint8_t* epi_stage_base = smem + STAGES * L::STAGE_BYTES + 256;  // EPI_WARPS tiles of EPI_STAGE_BYTES
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -398,21 +394,24 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     ok = false;
                     break;
                 }
-                const uint32_t src = smem_base + stage * L::STAGE_BYTES;
-#pragma unroll 4
-                for (int o = ct * 16; o < RAW_BYTES; o += CONV_WARPS * 32 * 16) {
-                    float4 x;
-                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                 : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                                 : "r"(src + o)
-                                 : "memory");
-                    x.x -= __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
-                    x.y -= __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
-                    x.z -= __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
-                    x.w -= __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
-                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(src + RAW_BYTES + o), "f"(x.x),
-                                 "f"(x.y), "f"(x.z), "f"(x.w)
-                                 : "memory");
+                const float4* src = reinterpret_cast<const float4*>(smem + stage * L::STAGE_BYTES);
+                float4* dst = reinterpret_cast<float4*>(smem + stage * L::STAGE_BYTES + RAW_BYTES);
+                constexpr int PER_THREAD = RAW_BYTES / 16 / (CONV_WARPS > 0 ? CONV_WARPS * 32 : 1);
+                constexpr int BATCH = 8;  // loads in flight per thread
+                static_assert(PER_THREAD % BATCH == 0 || CONV_WARPS == 0, "converter work must divide evenly");
+#pragma unroll 1
+                for (int b0 = 0; b0 < PER_THREAD; b0 += BATCH) {
+                    float4 x[BATCH];
+#pragma unroll
+                    for (int u = 0; u < BATCH; ++u) x[u] = src[(b0 + u) * (CONV_WARPS * 32) + ct];
+#pragma unroll
+                    for (int u = 0; u < BATCH; ++u) {
+                        x[u].x -= __uint_as_float(__float_as_uint(x[u].x) & 0xffffe000u);
+                        x[u].y -= __uint_as_float(__float_as_uint(x[u].y) & 0xffffe000u);
+                        x[u].z -= __uint_as_float(__float_as_uint(x[u].z) & 0xffffe000u);
+                        x[u].w -= __uint_as_float(__float_as_uint(x[u].w) & 0xffffe000u);
+                        dst[(b0 + u) * (CONV_WARPS * 32) + ct] = x[u];
+                    }
                 }
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA's reads
                 __syncwarp();
@@ -450,7 +449,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 out_ld = p.ldc;
                 vec = p.vec_ok != 0;
             }
-            const uint32_t my_stage = epi_stage_base + (warp - 2) * EPI_STAGE_BYTES;
+            float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
             const float* bias = split_mode ? nullptr : p.bias;
             const bool accumulate = !split_mode && p.accumulate != 0;
             const int slab_col0 = c.n0 + slab * 128;
@@ -605,7 +604,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * BIG_STAGES + 1 + h); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * BIG_STAGES + 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t epi_stage_base = bar_base + 256;
+    uint8_t* epi_stage_base = smem + BIG_STAGES * BIG_STAGE_BYTES + 256;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -772,7 +771,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
             for (int h = 0; h < 2; ++h) {
                 const int row0 = c.m0 + h * 128 + q * 32;
                 float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
-                const uint32_t my_stage = epi_stage_base + (warp - 2) * EPI_STAGE_BYTES;
+                float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + h * BIG_BN + slab * 128;
                 if (c.m0 + h * 128 < p.M) {  // warp-uniform: skip a half that lies below the matrix
 #pragma unroll 1
@@ -804,6 +803,360 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         __syncwarp();
         ptx::tc_fence_after();
         ptx::tmem_dealloc<512>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+
+// ---------------------------------------------------------------------------------- CTA pairs, fp32-accurate mode
+// The 3xTF32 mode issues three MMAs per k-slice, each re-reading its operands from shared memory;
+// with one CTA per tile that traffic (plus the low-part conversion) exceeds what shared memory
+// delivers and bounds the mode. Here two CTAs of a cluster share one 256 x 256 tile through
+// tcgen05.mma.cta_group::2: each holds 128 rows of A and 128 columns of B, so every MMA reads a
+// third less per CTA, and each CTA loads (and converts) only its own share. No multicast copies.
+//   leader = cluster rank 0: issues the MMAs and owns the barriers the pair synchronises on.
+//   per CTA: warp 0 TMA producer (local barriers), warp 1 MMA (leader) + TMEM, warps 2..9 epilogue
+//   with fp32 promotion of 64-deep chains, warps 10..11 low-part converters that also tell the leader
+//   when this CTA's stage is ready.
+constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 16, PAIR_STAGES = 6, PAIR_KC = 4;
+constexpr int PAIR_A_BYTES = 128 * PAIR_BK * 4, PAIR_B_BYTES = 128 * PAIR_BK * 4;
+constexpr int PAIR_RAW_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_STAGE_BYTES = 2 * PAIR_RAW_BYTES;  // raw (high parts) + low parts
+constexpr int PAIR_THREADS = 64 + 256 + 64;
+constexpr int PAIR_EPI_WARPS = 8, PAIR_CONV_WARPS = 2;
+
+template <int MAJA, int MAJB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    constexpr int S = PAIR_STAGES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * PAIR_STAGE_BYTES);
+    const uint32_t bar_base = smem_base + S * PAIR_STAGE_BYTES;
+    auto landed_bar = [&](int s) { return bar_base + 8u * s; };          // local: this CTA's TMA tiles arrived
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };     // local: stage may be refilled
+    auto ready_bar = [&](int s) { return bar_base + 8u * (2 * S + s); }; // leader: both CTAs' stage complete
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };   // local: accumulator chain done
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };  // leader: both epilogues drained
+    auto done_bar = [&](int s) { return bar_base + 8u * (3 * S + 4 + s); };   // peer: its stage is complete (local)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * S + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* epi_stage_base = smem + S * PAIR_STAGE_BYTES + 256;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(landed_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+            ptx::mbar_init(ready_bar(s), PAIR_CONV_WARPS + 1);  // leader's converter warps + the peer's relay
+            ptx::mbar_init(done_bar(s), PAIR_CONV_WARPS);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), 2 * PAIR_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair<512>(ptx::smem_u32(tmem_slot));
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_iters = p.red * p.nkb;
+    const bool presplit = p.presplit != 0;
+    const int kc = (p.debug & 64) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (own tiles, local barriers)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            long long issued = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+                const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+                const int m_row0 = c.m0 + 128 * (int)rank;  // this CTA's rows of A
+                const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
+                for (int it = 0; it < total_iters; ++it) {
+                    const int r = it / p.nkb;
+                    const int k0 = (it - r * p.nkb) * PAIR_BK;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = landed_bar(stage);
+                    if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
+                    if (p.debug & 1) {           // timing experiment: no loads, stale shared memory
+                        ptx::mbar_arrive(fb);
+                        ++issued;
+                        if (++stage == S) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
+                    ptx::mbar_arrive_expect_tx(fb, presplit ? PAIR_STAGE_BYTES : PAIR_RAW_BYTES);
+                    const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t sb = sa + PAIR_A_BYTES;
+                    const int bcv[4] = {c.i1, c.i0, r, 0};
+                    const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                    const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
+                    const int nterm = presplit ? 2 : 1;
+                    for (int term = 0; term < nterm; ++term) {
+                        const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
+                        const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
+                        const uint32_t da = sa + term * PAIR_RAW_BYTES;
+                        const uint32_t db = sb + term * PAIR_RAW_BYTES;
+                        if (MAJA == 0) {
+                            ptx::tma_load_5d(da, ma, fb, k0, m_row0, a0, a1, a2);
+                        } else if (p.a_fold) {
+                            ptx::tma_load_5d(da, ma, fb, 0, k0, m_row0 / CHUNK, a0, a1);
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                ptx::tma_load_5d(da + ch * (PAIR_BK * 128), ma, fb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
+                        }
+                        if (MAJB == 0) {
+                            ptx::tma_load_5d(db, mb, fb, k0, n_col0, b0, b1, b2);
+                        } else if (p.b_fold) {
+                            ptx::tma_load_5d(db, mb, fb, 0, k0, n_col0 / CHUNK, b0, b1);
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                ptx::tma_load_5d(db + ch * (PAIR_BK * 128), mb, fb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                int s2 = stage;
+                uint32_t ph = phase;
+                const int n = issued < S ? (int)issued : S;
+                for (int i = 0; i < n; ++i) {
+                    if (--s2 < 0) {
+                        s2 = S - 1;
+                        ph ^= 1u;
+                    }
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (!ptx::mbar_try_wait(landed_bar(s2), ph)) {
+                        if (ptx::globaltimer_ns() - t0 > 200000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && !leader) {
+            // Peer CTA: this otherwise idle thread tells the leader when a stage of this CTA is complete.
+            // The cross-CTA arrive is slow; keeping it off the converter warps keeps their loop short.
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+                for (int it = 0; it < total_iters; ++it) {
+                    if (!ptx::mbar_wait(done_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        if (lane == 0 && leader) {
+            constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
+            constexpr uint32_t K_SBO = 8 * PAIR_BK * 4;
+            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : PAIR_BK * 128, b_lbo = MAJB == 0 ? 16 : PAIR_BK * 128;
+            constexpr uint32_t a_sbo = MAJA == 0 ? K_SBO : 512, b_sbo = MAJB == 0 ? K_SBO : 512;
+            int stage = 0;
+            uint32_t phase = 0;
+            int handoff = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+                for (int cs = 0, ce = 0; cs < total_iters && ok; cs = ce) {
+                    ce = (total_iters - cs > kc) ? cs + kc : total_iters;
+                    const int buf = handoff & 1;
+                    const uint32_t acc_phase = (handoff >> 1) & 1u;
+                    if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * PAIR_BN;
+                    for (int it = cs; it < ce; ++it) {
+                        if (!ptx::mbar_wait(ready_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after();
+                        const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                        const uint32_t sb = sa + PAIR_A_BYTES;
+#pragma unroll
+                        for (int k8 = 0; k8 < PAIR_BK / UMMA_K; ++k8) {
+                            const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                            const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                            const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                            const uint64_t da_lo = ptx::smem_desc(sa + PAIR_RAW_BYTES + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db_lo = ptx::smem_desc(sb + PAIR_RAW_BYTES + b_off, b_lbo, b_sbo, b_lay);
+                            const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
+                            if (p.debug & 2) {  // timing experiment: loads and hand-shakes only
+                                if (first == 0u) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                                continue;
+                            }
+                            ptx::mma_tf32_ss_pair(d_tmem, da_lo, db, IDESC, first);
+                            ptx::mma_tf32_ss_pair(d_tmem, da, db_lo, IDESC, 1u);
+                            ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 1u);
+                        }
+                        // both CTAs may refill this stage once these MMAs have read it
+                        ptx::mma_commit_pair(empty_bar(stage));
+                        if (++stage == S) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    if (ok) {  // this chain's accumulator is complete in both CTAs' tensor memory
+                        ptx::mma_commit_pair(tfull_bar(buf));
+                    }
+                    ++handoff;
+                }
+            }
+        }
+    } else if (warp >= 2 + PAIR_EPI_WARPS) {
+        // ------------------------------------------------------------ low-part converter / stage relay
+        const int ct = (warp - 2 - PAIR_EPI_WARPS) * 32 + lane;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+            for (int it = 0; it < total_iters; ++it) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(landed_bar(stage), phase, abort_flag, p.wait_limit_ns))) {
+                    ok = false;
+                    break;
+                }
+                if (!presplit) {
+                    const float4* src = reinterpret_cast<const float4*>(smem + stage * PAIR_STAGE_BYTES);
+                    float4* dst = reinterpret_cast<float4*>(smem + stage * PAIR_STAGE_BYTES + PAIR_RAW_BYTES);
+                    constexpr int PER_THREAD = PAIR_RAW_BYTES / 16 / (PAIR_CONV_WARPS * 32);
+                    constexpr int BATCH = 8;
+                    static_assert(PER_THREAD % BATCH == 0, "converter work must divide evenly");
+#pragma unroll 1
+                    for (int b0 = 0; b0 < PER_THREAD; b0 += BATCH) {
+                        float4 x[BATCH];
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) x[u] = src[(b0 + u) * (PAIR_CONV_WARPS * 32) + ct];
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            x[u].x -= __uint_as_float(__float_as_uint(x[u].x) & 0xffffe000u);
+                            x[u].y -= __uint_as_float(__float_as_uint(x[u].y) & 0xffffe000u);
+                            x[u].z -= __uint_as_float(__float_as_uint(x[u].z) & 0xffffe000u);
+                            x[u].w -= __uint_as_float(__float_as_uint(x[u].w) & 0xffffe000u);
+                            dst[(b0 + u) * (PAIR_CONV_WARPS * 32) + ct] = x[u];
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                }
+                __syncwarp();
+                // cheap local arrive; the peer's stage is announced to the leader by its relay thread
+                if (lane == 0) ptx::mbar_arrive(leader ? ready_bar(stage) : done_bar(stage));
+                if (++stage == S) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..9), fp32 promotion
+        const int q = warp & 3;
+        const int slab = (warp - 2) >> 2;
+        const bool vec = p.vec_ok != 0;
+        const bool accumulate = p.accumulate != 0;
+        float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
+        int handoff = 0;
+        bool ok = true;
+        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+            const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+            const int row0 = c.m0 + 128 * (int)rank + q * 32;
+            const int slab_col0 = c.n0 + slab * 128;
+            float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+            for (int cs = 0; cs < total_iters && ok; cs = (total_iters - cs > kc) ? cs + kc : total_iters) {
+                const int buf = handoff & 1;
+                const uint32_t acc_phase = (handoff >> 1) & 1u;
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * PAIR_BN + slab * 128;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    if (slab_col0 + ch * 32 < p.N) {  // warp-uniform
+                        __syncwarp();
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) acc[ch * 32 + j] += __uint_as_float(v[j]);
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
+                ++handoff;
+            }
+            if (ok) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int col0 = slab_col0 + ch * 32;
+                    if (col0 < p.N) {
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
+                        store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias, accumulate,
+                                         lane);
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown (all paths)
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair<512>(tmem_base);
     }
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
@@ -953,6 +1306,60 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
     return 0;
 }
 
+template <int MAJA, int MAJB>
+int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
+    constexpr int smem = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
+    auto kern = gemm_tf32_pair_kernel<MAJA, MAJB>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            seterr(err, errlen, cudaGetErrorString(e));
+            return -3;
+        }
+        attr_done = true;
+    }
+    // How many 2-CTA clusters can be resident at once (SM counts per GPC need not be even).
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 74);
+        cfg.blockDim = dim3(PAIR_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 64;
+        }
+        max_pairs = n;
+    }
+    if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+    kern<<<grid, PAIR_THREADS, smem, stream>>>(kp);  // cluster of 2 CTAs (compile-time cluster dims)
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        seterr(err, errlen, cudaGetErrorString(e));
+        return -3;
+    }
+    return 0;
+}
+
+// The CTA-pair kernel is correct but not yet faster than one CTA per tile: the cross-CTA hand-shakes
+// (peer stage ready -> leader, MMA done -> peer) put about 5 us into the round trip of a stage while
+// shared memory only holds about 3 us of look-ahead (measured at 8192^3: 5.3 ms against 4.2-4.9 ms;
+// its MMAs alone run at the full rate, 3.5 ms). It is therefore opt-in: debug bit 5.
+bool use_pairs(const GemmDesc& g) {
+    if (!(g.debug & 32) || g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+    return tiles * 4 >= gemm_sm100_num_ctas();
+}
+
 // 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
 // amortise the accumulator hand-over between tiles.
 bool use_big_tiles(const GemmDesc& g) {
@@ -1050,8 +1457,11 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         return -1;
     }
     const bool big = use_big_tiles(g);
-    const int bn = big ? BIG_BN : pick_bn(g);
-    const int bm = big ? BIG_BM : BM;
+    GemmDesc gd = g;
+    gd.debug |= g_debug_flags;
+    const bool pairs = use_pairs(gd);
+    const int bn = big ? BIG_BN : (pairs ? PAIR_BN : pick_bn(g));
+    const int bm = big ? BIG_BM : (pairs ? PAIR_BM : BM);
     const int bk = g.terms == 3 ? 16 : BK;  // finer stages for the hi+lo mode
 
     KernelParams kp;
@@ -1068,7 +1478,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         if (ok && presplit) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile, bk);
         return ok;
     };
-    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, bm) || !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, bn)) {
+    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, pairs ? 128 : bm) ||
+        !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, pairs ? 128 : bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
@@ -1117,6 +1528,15 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     const int ctas = gemm_sm100_num_ctas();
     const int grid = (int)(total < ctas ? total : ctas);
 
+    if (pairs) {
+        const int npairs = (int)std::min<long long>(total, ctas / 2);
+        switch (g.A.mn_major * 2 + g.B.mn_major) {
+            case 0: return launch_pair_variant<0, 0>(kp, 2 * npairs, stream, err, errlen);
+            case 1: return launch_pair_variant<0, 1>(kp, 2 * npairs, stream, err, errlen);
+            case 2: return launch_pair_variant<1, 0>(kp, 2 * npairs, stream, err, errlen);
+            default: return launch_pair_variant<1, 1>(kp, 2 * npairs, stream, err, errlen);
+        }
+    }
     if (big) {
         switch (g.A.mn_major * 2 + g.B.mn_major) {
             case 0: return launch_big_variant<0, 0>(kp, grid, stream, err, errlen);

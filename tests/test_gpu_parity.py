@@ -364,3 +364,21 @@ def test_bounded_wait_abort_is_reported_and_recoverable():
     # the context is still usable and results are right again
     c = cabi.matmul_fwd(A, B, mode=MODE_FP32).to_numpy()
     assert rel_fro(c, a.astype(np.float64) @ b.astype(np.float64)) < TOL_FP32
+
+
+def test_experimental_cta_pair_kernel_parity():
+    # The opt-in cta_group::2 kernel of the fp32-accurate mode (two CTAs share one 256 x 256 tile).
+    lib = cabi.lib()
+    a, b = uniform((1500, 200), 71), uniform((200, 1700), 72)
+    bias = normal((1, 1700), 73)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    try:
+        cabi.check(lib.akr_debug_configure(32, 0))
+        A, B = dev(a), dev(b)
+        assert rel_fro(cabi.matmul_fwd(A, B, mode=MODE_FP32).to_numpy(), ref) < TOL_FP32
+        assert rel_fro(cabi.matmul_fwd(A, B, bias=dev(bias), mode=MODE_FP32).to_numpy(), ref + bias) < TOL_FP32
+        at, bt = dev(np.ascontiguousarray(a.T)), dev(np.ascontiguousarray(b.T))
+        c = cabi.matmul_fwd(at.transpose(0, 1), bt.transpose(0, 1), mode=MODE_FP32).to_numpy()
+        assert rel_fro(c, ref) < TOL_FP32
+    finally:
+        cabi.check(lib.akr_debug_configure(0, 0))
