@@ -2,7 +2,7 @@
 // must not allocate device memory when they call into the library.
 //
 // Who that is: a host runtime that hands the whole of HBM to its own pool at start-up (any later
-// cudaMalloc then fails, or steals from the pool's budget), and latency-critical loops that cannot
+// cudaMalloc then fails, or eats into the pool's share), and latency-critical loops that cannot
 // take the device-wide synchronisation cudaMalloc / cudaFree imply. The regular entry points grow a
 // cached workspace with cudaMalloc the first time a shape needs scratch; this one never does. Its
 // scratch - the fp32 partial tiles and per-tile counters of the split contraction - lives in

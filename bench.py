@@ -193,13 +193,13 @@ def cpu_inputs(m_rows):
     return normal((m_rows, N_SQ), 401, s), normal((N_SQ, N_SQ), 402, s), normal((m_rows, N_SQ), 403, 1.0)
 
 
-def pick_cpu_rows(ref, budget_s):
-    """Rows of the 8192-row problem one CPU step covers so that a step costs about `budget_s`."""
+def pick_cpu_rows(ref, target_s):
+    """Rows of the 8192-row problem one CPU step covers so that a step costs about `target_s`."""
     a, b, dc = cpu_inputs(128)
     cpu_step(ref, a, b, dc)
     t = cpu_step(ref, a, b, dc)
     rate = 3 * 2 * 128 * N_SQ * N_SQ / max(t, 1e-6)   # flop/s
-    rows = int(budget_s * rate / (3 * 2 * N_SQ * N_SQ))
+    rows = int(target_s * rate / (3 * 2 * N_SQ * N_SQ))
     rows = max(128, min(N_SQ, (rows // 128) * 128))
     return rows
 
@@ -212,7 +212,7 @@ def run_reference_arm(args):
     kind = "reference" if ref is not None else "port"
     cores = os.cpu_count()
     total_steps = args.steps + args.warmup
-    rows = pick_cpu_rows(ref, budget_s=max(0.5, 150.0 / max(total_steps, 1)))
+    rows = pick_cpu_rows(ref, target_s=max(0.5, 150.0 / max(total_steps, 1)))
     a, b, dc = cpu_inputs(rows)
     for _ in range(args.warmup):
         cpu_step(ref, a, b, dc)
@@ -237,7 +237,7 @@ def run_reference_arm(args):
 def cpu_baseline_child():
     """Bounded CPU sample, run in a child process so that OpenBLAS threads do not linger."""
     ref = load_reference_module()
-    rows = pick_cpu_rows(ref, budget_s=12.0)
+    rows = pick_cpu_rows(ref, target_s=12.0)
     a, b, dc = cpu_inputs(rows)
     t = cpu_step(ref, a, b, dc)
     flop = 3 * 2 * rows * N_SQ * N_SQ

@@ -69,7 +69,7 @@ def _worker(rank, world, port, out_dir):
         lo, hi = sh.lo, sh.hi
         c_loc = sh.forward(np.ascontiguousarray(a[lo:hi]), b)
         da_loc, db = sh.backward(np.ascontiguousarray(a[lo:hi]), b, np.ascontiguousarray(dc[lo:hi]))
-        assert be.limits == [148 - sh.comm_ctas, 0]      # CTA budget lowered during the overlap, then restored
+        assert be.limits == [148 - sh.comm_ctas, 0]      # CTA limit lowered during the overlap, then restored
         ref_c = mo.matmul_forward(a, b)
         ref_da, ref_db = mo.matmul_backward(a, b, dc)
         assert rel_fro(c_loc, ref_c[lo:hi]) < 1e-6
