@@ -36,6 +36,8 @@ constexpr uint64_t DEFAULT_WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than
 
 struct KernelParams {
     CUtensorMap tmA, tmB;
+    CUtensorMap tmC;           // output map for the TMA-store epilogue (valid when c_tma != 0)
+    int c_tma;                 // 1: epilogue stores through TMA (aligned output, no accumulate, no split)
     CUtensorMap tmAlo, tmBlo;  // pre-split low parts (fp32-accurate mode of large products)
     int presplit;              // 1: low parts come from tmAlo / tmBlo, 0: derived in shared memory
     float* C;
@@ -148,6 +150,32 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
     __syncwarp();  // the tile is reused by the next block
 }
 
+// TMA-store variant: the four warps of one 128-column slab stage their 32-row bands into one
+// [128 rows][128 bytes] tile (the same swizzle the tensor map declares) and one thread sends it as a
+// single 16 KB box. The warps are free again as soon as the box has been read from shared memory;
+// the write itself drains asynchronously, clipped at the matrix edge by the hardware.
+// Must be called by all 128 threads of the slab (named barrier `bar_id`).
+__device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile, uint32_t slab_tile_addr,
+                                                const CUtensorMap* tmC, int col0, int row_base, int i1, int i0,
+                                                int N, const float* bias, int lane, bool issuer, int bar_id) {
+    if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) v[j] += __ldg(bias + col0 + j);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        my_tile[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    ptx::fence_proxy_async_smem();
+    ptx::named_barrier_sync(bar_id, 128);
+    if (issuer) {
+        ptx::tma_store_4d(tmC, slab_tile_addr, col0, row_base, i1, i0);
+        ptx::bulk_commit_group();
+        ptx::bulk_wait_read_all();
+    }
+    ptx::named_barrier_sync(bar_id, 128);  // the tile may be overwritten
+}
+
 // KC > 0: the tensor core only accumulates KC k-blocks at a time; the epilogue warps add those
 // partial tiles into fp32 registers with round-to-nearest. The accumulator inside the tensor core
 // truncates on every add, which over a long contraction costs more accuracy than the fp32-accurate
@@ -171,8 +199,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
 
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
-    const uint32_t bar_base = smem_base + STAGES * L::STAGE_BYTES;
+    // [stages][epilogue staging: one 16 KB tile per 128-column slab, 1024-byte aligned][barriers]
+    constexpr int EPI_BYTES = (BN / 128) * 4 * EPI_STAGE_BYTES;
+    uint8_t* epi_stage_base = smem + STAGES * L::STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES + EPI_BYTES);
+    const uint32_t bar_base = smem_base + STAGES * L::STAGE_BYTES + EPI_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
@@ -181,7 +212,6 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
-    uint8_t* epi_stage_base = smem + STAGES * L::STAGE_BYTES + 256;  // EPI_WARPS tiles of EPI_STAGE_BYTES
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -428,6 +458,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         const int slab = (warp - 2) >> 2;   // which 128-column slab of the tile
         const int nbatch = p.o0 * p.o1;
         const bool split_mode = p.splits > 1;
+        float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
+        const uint32_t slab_tile_addr = smem_base + STAGES * L::STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        const bool use_tma = p.c_tma != 0 && !split_mode;  // kernel-uniform
         int handoff = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
@@ -435,8 +468,6 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const int it0 = (int)((long long)total_iters * c.split / p.splits);
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             const int row0 = c.m0 + q * 32;   // first row of this warp's 32-row band
-            const int row = row0 + lane;
-            const bool row_ok = row < p.M;
             float* out_base;
             long long out_ld;
             bool vec;
@@ -449,7 +480,6 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 out_ld = p.ldc;
                 vec = p.vec_ok != 0;
             }
-            float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
             const float* bias = split_mode ? nullptr : p.bias;
             const bool accumulate = !split_mode && p.accumulate != 0;
             const int slab_col0 = c.n0 + slab * 128;
@@ -462,8 +492,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
-                    ok = false;  // warp-uniform: every lane leaves together
+                bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
+                // the TMA-store path synchronises the four warps of a slab: they must leave together
+                if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);
+                if (!got) {
+                    ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
@@ -483,8 +516,15 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
-                                             accumulate, lane);
+                            if (p.debug & 128) {
+                                // bit 7: timing experiment without the output stores
+                            } else if (use_tma) {
+                                store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias,
+                                                lane, q == 0 && lane == 0, 2 + slab);
+                            } else {
+                                store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
+                                                 accumulate, lane);
+                            }
                         }
                     }
                 }
@@ -502,8 +542,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)];
-                        store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias, accumulate,
-                                         lane);
+                        if (use_tma)
+                            store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
+                                            q == 0 && lane == 0, 2 + slab);
+                        else
+                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
+                                             accumulate, lane);
                     }
                 }
             }
@@ -564,6 +608,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         }
     }
 
+    // the thread that issued bulk stores waits for them before the CTA winds down
+    if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+
     // ------------------------------------------------------------ teardown (all paths)
     ptx::tc_fence_before();
     __syncthreads();
@@ -596,15 +643,16 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BIG_STAGES * BIG_STAGE_BYTES);
-    const uint32_t bar_base = smem_base + BIG_STAGES * BIG_STAGE_BYTES;
+    constexpr int EPI_BYTES = 8 * EPI_STAGE_BYTES;  // staging (1024-byte aligned) before the barriers
+    uint8_t* epi_stage_base = smem + BIG_STAGES * BIG_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BIG_STAGES * BIG_STAGE_BYTES + EPI_BYTES);
+    const uint32_t bar_base = smem_base + BIG_STAGES * BIG_STAGE_BYTES + EPI_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (BIG_STAGES + s); };
     const uint32_t tfull_bar = bar_base + 8u * (2 * BIG_STAGES);
     auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * BIG_STAGES + 1 + h); };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * BIG_STAGES + 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* epi_stage_base = smem + BIG_STAGES * BIG_STAGE_BYTES + 256;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -757,11 +805,16 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         const int slab = (warp - 2) >> 2;  // 128-column slab of the tile
         const bool vec = p.vec_ok != 0;
         const bool accumulate = p.accumulate != 0;
+        const bool use_tma = p.c_tma != 0;
+        float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
+        const uint32_t slab_tile_addr = smem_base + BIG_STAGES * BIG_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
         int local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns))) {
+            bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
+            if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
+            if (!got) {
                 ok = false;
                 break;
             }
@@ -771,7 +824,6 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
             for (int h = 0; h < 2; ++h) {
                 const int row0 = c.m0 + h * 128 + q * 32;
                 float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
-                float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + h * BIG_BN + slab * 128;
                 if (c.m0 + h * 128 < p.M) {  // warp-uniform: skip a half that lies below the matrix
 #pragma unroll 1
@@ -785,8 +837,12 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias,
-                                             accumulate, lane);
+                            if (use_tma)
+                                store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0 + h * 128, c.i1, c.i0, p.N,
+                                                p.bias, lane, q == 0 && lane == 0, 2 + slab);
+                            else
+                                store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias,
+                                                 accumulate, lane);
                         }
                     }
                 }
@@ -797,6 +853,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         }
     }
 
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -1510,6 +1567,21 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                  (g.o0 == 1 || (g.c_bs0 & 3) == 0) && (g.o1 == 1 || (g.c_bs1 & 3) == 0))
                     ? 1
                     : 0;
+    // Output map for the TMA-store epilogue: (N, M, o1, o0), boxes of 32 columns x 128 rows.
+    kp.c_tma = 0;
+    if (kp.vec_ok && !g.accumulate && kp.splits == 1 && !pairs && !((g.debug | g_debug_flags) & 256)) {
+        EncodeTiledFn enc = get_encode_fn();
+        const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
+        cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.o1, (cuuint64_t)g.o0};
+        cuuint64_t strides[3] = {ldc_b, (cuuint64_t)(g.o1 > 1 ? g.c_bs1 * 4 : (long long)ldc_b),
+                                 (cuuint64_t)(g.o0 > 1 ? g.c_bs0 * 4 : (long long)ldc_b)};
+        cuuint32_t box[4] = {32u, 128u, 1u, 1u};
+        cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+        if (enc && enc(&kp.tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            kp.c_tma = 1;
+    }
     kp.mt = (g.M + bm - 1) / bm;
     kp.nt = (g.N + bn - 1) / bn;
     kp.nkb = (g.K + bk - 1) / bk;
