@@ -382,3 +382,52 @@ def test_experimental_cta_pair_kernel_parity():
         assert rel_fro(c, ref) < TOL_FP32
     finally:
         cabi.check(lib.akr_debug_configure(0, 0))
+
+
+def _random_case(rng):
+    """A random product: batch broadcasting, operand layouts (transposed / sliced views), ragged sizes."""
+    nb = int(rng.integers(0, 4))
+    batch = [int(rng.integers(1, 5)) for _ in range(nb)]
+    M, N, K = (int(rng.integers(1, 300)) for _ in range(3))
+    def operand(rows, cols, seed):
+        bshape = [d if rng.random() < 0.7 else 1 for d in batch]
+        drop = int(rng.integers(0, len(bshape) + 1)) if rng.random() < 0.3 else 0   # fewer batch dims than the other
+        bshape = bshape[drop:]
+        transposed = rng.random() < 0.5
+        pad_r, pad_c = int(rng.integers(0, 3)), int(rng.integers(0, 3)) * 4 if rng.random() < 0.5 else int(rng.integers(0, 5))
+        store = (rows, cols) if not transposed else (cols, rows)
+        full = tuple(bshape) + (store[0] + pad_r, store[1] + pad_c)
+        base = uniform(full, seed)
+        r0, c0 = int(rng.integers(0, pad_r + 1)), int(rng.integers(0, pad_c + 1))
+        view_np = base[..., r0:r0 + store[0], c0:c0 + store[1]]
+        Dbase = dev(base)
+        strides = list(Dbase.strides)
+        off = r0 * strides[-2] + c0 * strides[-1]
+        shape = list(bshape) + list(store)
+        V = Dbase.as_strided(shape, strides, offset=off)
+        if transposed:
+            V = V.transpose(len(shape) - 2, len(shape) - 1)
+            view_np = np.swapaxes(view_np, -1, -2)
+        return V, np.ascontiguousarray(view_np), Dbase
+    A, a_np, keep_a = operand(M, K, int(rng.integers(1 << 30)))
+    B, b_np, keep_b = operand(K, N, int(rng.integers(1 << 30)))
+    return A, a_np, B, b_np, (keep_a, keep_b)
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_random_shapes_layouts_and_broadcasts(mode, tol):
+    rng = np.random.Generator(np.random.PCG64(20260 + mode))
+    for case in range(40):
+        A, a_np, B, b_np, keep = _random_case(rng)
+        ref = mo.matmul_forward(a_np, b_np, np.float64)
+        c = cabi.matmul_fwd(A, B, mode=mode)
+        assert c.shape == ref.shape, (case, A.shape, B.shape)
+        scale = max(1e-30, float(np.linalg.norm(ref)))
+        assert np.linalg.norm(c.to_numpy().astype(np.float64) - ref) / scale < tol, (case, A.shape, A.strides, B.shape, B.strides)
+        dc = normal(ref.shape, 77 + case)
+        ga, gb = cabi.matmul_bwd(A, B, dev(dc), mode=mode)
+        rda, rdb = mo.matmul_backward(a_np, b_np, dc, np.float64)
+        assert ga.shape == tuple(a_np.shape) and gb.shape == tuple(b_np.shape)
+        for got, want, what in ((ga, rda, "dA"), (gb, rdb, "dB")):
+            n = max(1e-30, float(np.linalg.norm(want)))
+            assert np.linalg.norm(got.to_numpy().astype(np.float64) - want) / n < tol, (case, what, A.shape, A.strides, B.shape, B.strides)
