@@ -484,11 +484,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const bool accumulate = !split_mode && p.accumulate != 0;
             const int slab_col0 = c.n0 + slab * 128;
 
-            float acc[KC > 0 ? 128 : 1];
-            if (KC > 0) {
+            constexpr int ACC_N = KC > 0 ? 128 : 1;  // fp32 promotion registers (unused without chains)
+            float acc[ACC_N];
 #pragma unroll
-                for (int j = 0; j < (KC > 0 ? 128 : 1); ++j) acc[j] = 0.f;
-            }
+            for (int j = 0; j < ACC_N; ++j) acc[j] = 0.f;
             for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
@@ -511,7 +510,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         ptx::tmem_ld_wait();
                         if (KC > 0) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)] += __uint_as_float(v[j]);
+                            for (int j = 0; j < 32; ++j) acc[ACC_N > 1 ? ch * 32 + j : 0] += __uint_as_float(v[j]);
                         } else {
                             float f[32];
 #pragma unroll
@@ -541,7 +540,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     if (col0 < p.N) {
                         float f[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = acc[(KC > 0 ? ch * 32 : 0) + (KC > 0 ? j : 0)];
+                        for (int j = 0; j < 32; ++j) f[j] = acc[ACC_N > 1 ? ch * 32 + j : 0];
                         if (use_tma)
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
                                             q == 0 && lane == 0, 2 + slab);
@@ -914,7 +913,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         for (int s = 0; s < S; ++s) {
             ptx::mbar_init(landed_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
-            ptx::mbar_init(ready_bar(s), PAIR_CONV_WARPS + 1);  // leader's converter warps + the peer's relay
+            // in-kernel low parts: leader's converter warps + the peer's relay; pre-split operands: the
+            // leader's expect-tx arrive, completed by the TMA bytes of both CTAs
+            ptx::mbar_init(ready_bar(s), p.presplit ? 1 : PAIR_CONV_WARPS + 1);
             ptx::mbar_init(done_bar(s), PAIR_CONV_WARPS);
         }
         for (int b = 0; b < 2; ++b) {
@@ -968,18 +969,55 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         }
                         continue;
                     }
-                    ptx::mbar_arrive_expect_tx(fb, presplit ? PAIR_STAGE_BYTES : PAIR_RAW_BYTES);
                     const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
                     const uint32_t sb = sa + PAIR_A_BYTES;
+                    if (presplit) {
+                        // hi and lo tiles of both CTAs land on the LEADER's ready barrier: no relay hop
+                        const uint32_t lb = ptx::map_to_cta(ready_bar(stage), 0);
+                        if (leader) ptx::mbar_arrive_expect_tx(ready_bar(stage), 2 * PAIR_STAGE_BYTES);
+                        const int bcv[4] = {c.i1, c.i0, r, 0};
+                        const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                        const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
+                        for (int term = 0; term < 2; ++term) {
+                            const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
+                            const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
+                            const uint32_t da = sa + term * PAIR_RAW_BYTES;
+                            const uint32_t db = sb + term * PAIR_RAW_BYTES;
+                            if (MAJA == 0) {
+                                ptx::tma_load_5d_pair(da, ma, lb, k0, m_row0, a0, a1, a2);
+                            } else if (p.a_fold) {
+                                ptx::tma_load_5d_pair(da, ma, lb, 0, k0, m_row0 / CHUNK, a0, a1);
+                            } else {
+#pragma unroll
+                                for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                    ptx::tma_load_5d_pair(da + ch * (PAIR_BK * 128), ma, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
+                            }
+                            if (MAJB == 0) {
+                                ptx::tma_load_5d_pair(db, mb, lb, k0, n_col0, b0, b1, b2);
+                            } else if (p.b_fold) {
+                                ptx::tma_load_5d_pair(db, mb, lb, 0, k0, n_col0 / CHUNK, b0, b1);
+                            } else {
+#pragma unroll
+                                for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                    ptx::tma_load_5d_pair(db + ch * (PAIR_BK * 128), mb, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                            }
+                        }
+                        ++issued;
+                        if (++stage == S) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
+                    ptx::mbar_arrive_expect_tx(fb, PAIR_RAW_BYTES);
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
                     const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-                    const int nterm = presplit ? 2 : 1;
-                    for (int term = 0; term < nterm; ++term) {
-                        const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
-                        const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
-                        const uint32_t da = sa + term * PAIR_RAW_BYTES;
-                        const uint32_t db = sb + term * PAIR_RAW_BYTES;
+                    {
+                        const CUtensorMap* ma = &p.tmA;
+                        const CUtensorMap* mb = &p.tmB;
+                        const uint32_t da = sa;
+                        const uint32_t db = sb;
                         if (MAJA == 0) {
                             ptx::tma_load_5d(da, ma, fb, k0, m_row0, a0, a1, a2);
                         } else if (p.a_fold) {
@@ -1006,7 +1044,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                     }
                 }
             }
-            if (!ok || *abort_flag) {
+            if ((!ok || *abort_flag) && presplit) {
+                const uint64_t t0 = ptx::globaltimer_ns();  // let copies in flight land (they signal the leader)
+                while (ptx::globaltimer_ns() - t0 < 200000ull) {
+                }
+            } else if (!ok || *abort_flag) {
                 int s2 = stage;
                 uint32_t ph = phase;
                 const int n = issued < S ? (int)issued : S;
@@ -1024,7 +1066,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && !leader) {
+        if (lane == 0 && !leader && !presplit) {
             // Peer CTA: this otherwise idle thread tells the leader when a stage of this CTA is complete.
             // The cross-CTA arrive is slow; keeping it off the converter warps keeps their loop short.
             int stage = 0;
@@ -1111,13 +1153,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+        // pre-split operands arrive complete by TMA on the leader's barrier: nothing to do here
+        for (int t = pair_id; t < p.total_tiles && ok && !presplit; t += num_pairs) {
             for (int it = 0; it < total_iters; ++it) {
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(landed_bar(stage), phase, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
-                if (!presplit) {
+                {
                     const float4* src = reinterpret_cast<const float4*>(smem + stage * PAIR_STAGE_BYTES);
                     float4* dst = reinterpret_cast<float4*>(smem + stage * PAIR_STAGE_BYTES + PAIR_RAW_BYTES);
                     constexpr int PER_THREAD = PAIR_RAW_BYTES / 16 / (PAIR_CONV_WARPS * 32);
@@ -1407,12 +1450,16 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
     return 0;
 }
 
-// The CTA-pair kernel is correct but not yet faster than one CTA per tile: the cross-CTA hand-shakes
-// (peer stage ready -> leader, MMA done -> peer) put about 5 us into the round trip of a stage while
-// shared memory only holds about 3 us of look-ahead (measured at 8192^3: 5.3 ms against 4.2-4.9 ms;
-// its MMAs alone run at the full rate, 3.5 ms). It is therefore opt-in: debug bit 5.
+// CTA pairs serve the fp32-accurate mode of large products whose operands were split up front: there
+// both CTAs' tiles land on the leader's barrier by TMA and the pair runs 4.07 ms against 4.34 ms for
+// one CTA per tile at 8192^3. With in-kernel low parts the pair is still slower (5.3 ms against 4.9 ms:
+// the peer's "stage ready" has to be relayed to the leader, which puts about 5 us into the round trip
+// of a stage while shared memory holds about 3 us of look-ahead), so that combination is opt-in
+// (debug bit 5).
 bool use_pairs(const GemmDesc& g) {
-    if (!(g.debug & 32) || g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128) return false;
+    if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || (g.debug & 512)) return false;
+    const bool presplit = g.A.lo != nullptr && g.B.lo != nullptr;
+    if (!presplit && !(g.debug & 32)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     return tiles * 4 >= gemm_sm100_num_ctas();
 }

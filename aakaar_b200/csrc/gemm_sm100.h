@@ -38,7 +38,8 @@ struct GemmDesc {
     int* counters = nullptr;
     int debug = 0;  // timing experiments: bit 0 skips the TMA loads, bit 1 the MMAs (results invalid);
                     // bit 2 disables the folded one-box-per-tile maps of M/N-major operands,
-                    // bit 3 the 256 x 256 tile kernel, bit 5 ENABLES the experimental CTA-pair kernel of the fp32-accurate mode,
+                    // bit 3 the 256 x 256 tile kernel, bit 5 routes fp32-accurate products with in-kernel low parts through the CTA-pair kernel too,
+                    // bit 9 disables the CTA-pair kernel altogether,
                     // bit 7 skips the output stores (timing), bit 8 disables the TMA-store epilogue
 };
 

@@ -181,7 +181,8 @@ AKR_API int akr_event_destroy(void* event);
  * AKR_ERR_ABORTED, leaving the context usable. `wait_limit_ms` sets that bound (0 = default, 4 s);
  * flag 16 makes the load warp never signal its stages, so that every waiter gives up; flags 1 / 2 / 4 / 8
  * are timing diagnostics (skip loads, skip MMAs, no folded maps, no 256x256 tiles; results invalid with 1 / 2);
- * flag 32 routes fp32-accurate products through the experimental CTA-pair (cta_group::2) kernel.
+ * flag 32 routes every fp32-accurate product through the CTA-pair (cta_group::2) kernel (by default only large
+ * pre-split ones use it), flag 512 disables that kernel.
  * akr_debug_configure(0, 0) restores normal operation. */
 AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
 

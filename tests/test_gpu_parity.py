@@ -380,6 +380,13 @@ def test_experimental_cta_pair_kernel_parity():
         at, bt = dev(np.ascontiguousarray(a.T)), dev(np.ascontiguousarray(b.T))
         c = cabi.matmul_fwd(at.transpose(0, 1), bt.transpose(0, 1), mode=MODE_FP32).to_numpy()
         assert rel_fro(c, ref) < TOL_FP32
+        # large compute-bound product: operands are split up front and both CTAs' tiles land on the
+        # leader's barrier directly
+        n = 4096
+        s_ = 1.0 / np.sqrt(n)
+        a2, b2 = normal((n, n), 401, s_), normal((n, n), 402, s_)
+        c2 = cabi.matmul_fwd(dev(a2), dev(b2), mode=MODE_FP32).to_numpy()
+        sampled_rows_check(a2, b2, c2, [0, 129, 2047, 4095], TOL_FP32)
     finally:
         cabi.check(lib.akr_debug_configure(0, 0))
 
