@@ -109,6 +109,7 @@ BCAST = [
     ((2, 3, 4, 16, 8), (4, 8, 24)),     # three batch dims
     ((6, 1, 2, 16, 12), (1, 5, 1, 12, 8)),  # interleaved broadcast dims (host-looped)
     ((1, 1, 9, 5), (1, 5, 3)),          # all-ones batch
+    ((1, 16, 27), (5, 27, 100)),        # the conv-as-matmul caller: [1,Cout,C*K] @ [B,C*K,L] (aakaar/__init__.py:305-307)
 ]
 
 

@@ -142,3 +142,20 @@ def test_mlp_config2_full_size(ak, tf32, tol):
         assert rel_fro(l1.weight.to_numpy(), new[0]) < tol
     finally:
         ak.set_tf32(False)
+
+
+def test_newton_schulz_chain_through_views(ak):
+    # The Muon optimiser's orthogonalisation step (aakaar/optim.py:533-542) is a chain of products on
+    # transposed operands; here the transposes stay views (the reference materialises them).
+    x_np = uniform((64, 160), 9) * np.float32(0.05)
+    a_, b_, c_ = 3.4445, -4.7750, 2.0315
+    X = ak.from_numpy(x_np, "cuda")
+    ref = x_np.astype(np.float64)
+    with ak.no_grad():
+        for _ in range(3):
+            A = X @ X.T                      # [64,64], second operand is a strided view
+            B = A * b_ + (A @ A) * c_
+            X = X * a_ + B @ X
+            Ar = ref @ ref.T
+            ref = a_ * ref + (b_ * Ar + c_ * (Ar @ Ar)) @ ref
+    assert rel_fro(X.to_numpy(), ref) < 1e-5
