@@ -57,6 +57,7 @@ def load():
         "akr_matmul_a_bt": [V, V, V, C.c_int, vp],
         "akr_matmul_at_b": [V, V, V, C.c_int, vp],
         "akr_matmul_fwd_simt": [V, V, V, vp],
+        "akr_matmul_fwd_typed": [V, V, V, vp],
         "akr_matmul_at_b_noalloc": [V, V, V, vp],
         "akr_workspace_bytes": [C.POINTER(sz)],
         "akr_launch_count": [C.c_int],
@@ -271,6 +272,48 @@ def matmul_simt(a, b):
     va, vb, vc = a.view(), b.view(), c.view()
     check(lib().akr_matmul_fwd_simt(C.byref(va), C.byref(vb), C.byref(vc), None))
     return c
+
+
+_TYPED = {"float32": 0, "float64": 1, "int32": 2, "int64": 3}
+
+
+def matmul_typed(a_np, b_np):
+    """Forward-only product of two host arrays of one dtype (float32/float64/int32/int64) through
+    ``akr_matmul_fwd_typed``; the arrays may be strided views (their base storage is uploaded as is)."""
+    a_np, b_np = np.asarray(a_np), np.asarray(b_np)
+    code = _TYPED[a_np.dtype.name]
+    item = a_np.dtype.itemsize
+
+    def upload(x):
+        # the byte range the view touches is uploaded as it lies; the view keeps its own strides
+        lo = sum(min(0, (d - 1) * st) for d, st in zip(x.shape, x.strides))
+        hi = sum(max(0, (d - 1) * st) for d, st in zip(x.shape, x.strides)) + x.dtype.itemsize
+        dev = DeviceArray(((hi - lo + 3) // 4,))
+        check(lib().akr_memcpy_h2d(dev.ptr, x.ctypes.data + lo, hi - lo, None))
+        v = View()
+        v.data = dev.ptr - lo
+        v.ndim, v.dtype = x.ndim, _TYPED[x.dtype.name]
+        for i in range(AKR_MAX_DIMS):
+            v.shape[i] = x.shape[i] if i < x.ndim else 1
+            v.stride[i] = x.strides[i] // x.dtype.itemsize if i < x.ndim else 0
+        return dev, v
+
+    da, va = upload(a_np)
+    db, vb = upload(b_np)
+    shape = (C.c_int64 * (AKR_MAX_DIMS + 2))()
+    nd = C.c_int32(0)
+    check(lib().akr_matmul_plan(C.byref(va), C.byref(vb), shape, C.byref(nd)))
+    out = np.empty(tuple(shape[i] for i in range(nd.value)), dtype=a_np.dtype)
+    dc = DeviceArray(((max(out.nbytes, 4) + 3) // 4,))
+    vc = View()
+    vc.data, vc.ndim, vc.dtype = dc.ptr, out.ndim, code
+    for i in range(AKR_MAX_DIMS):
+        vc.shape[i] = out.shape[i] if i < out.ndim else 1
+        vc.stride[i] = out.strides[i] // item if i < out.ndim else 0
+    check(lib().akr_matmul_fwd_typed(C.byref(va), C.byref(vb), C.byref(vc), None))
+    check(lib().akr_memcpy_d2h(out.ctypes.data, dc.ptr, out.nbytes, None))
+    check(lib().akr_synchronize())
+    return out
 
 
 def h2d(dst: DeviceArray, src_np, stream=None, dst_offset_elems=0):

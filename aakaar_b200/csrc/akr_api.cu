@@ -785,17 +785,34 @@ AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, i
     return run_problem(p, (cudaStream_t)stream);
 }
 
+static int simt_forward(const akr_view* a, const akr_view* b, akr_view* c, int dtype, void* stream);
+
+AKR_API int akr_matmul_fwd_typed(const akr_view* a, const akr_view* b, akr_view* c, void* stream) {
+    if (!a || !b || !c) return fail(AKR_ERR_INVALID, "matmul: null view");
+    const int dt = a->dtype;
+    if (dt != AKR_DTYPE_F64 && dt != AKR_DTYPE_I32 && dt != AKR_DTYPE_I64)
+        return fail(AKR_ERR_RUNTIME, "matmul_fwd_typed handles float64, int32 and int64 (use akr_matmul_fwd for float32)");
+    if (b->dtype != dt || c->dtype != dt) return fail(AKR_ERR_RUNTIME, "matmul: operands must share one dtype");
+    return simt_forward(a, b, c, dt, stream);
+}
+
 AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* c, void* stream) {
+    return simt_forward(a, b, c, AKR_DTYPE_F32, stream);
+}
+
+static int simt_forward(const akr_view* a, const akr_view* b, akr_view* c, int dtype, void* stream) {
     Plan pl;
     int rc = make_plan(a, b, &pl);
     if (rc != AKR_OK) return rc;
-    if ((rc = check_view(a, "matmul input a", 2)) != AKR_OK) return rc;
-    if ((rc = check_view(b, "matmul input b", 2)) != AKR_OK) return rc;
+    akr_view ta = *a, tb = *b, tc = *c;   // the shape checks below are dtype-agnostic
+    ta.dtype = tb.dtype = tc.dtype = AKR_DTYPE_F32;
+    if ((rc = check_view(&ta, "matmul input a", 2)) != AKR_OK) return rc;
+    if ((rc = check_view(&tb, "matmul input b", 2)) != AKR_OK) return rc;
     int64_t oshape[AKR_MAX_DIMS + 2];
     for (int i = 0; i < pl.nb; ++i) oshape[i] = pl.batch[i];
     oshape[pl.nb] = pl.M;
     oshape[pl.nb + 1] = pl.N;
-    if ((rc = check_out(c, pl.nb + 2, oshape, "matmul output")) != AKR_OK) return rc;
+    if ((rc = check_out(&tc, pl.nb + 2, oshape, "matmul output")) != AKR_OK) return rc;
     DeviceState* st = nullptr;
     if ((rc = need_gpu(&st)) != AKR_OK) return rc;
     SimtGemm g;
@@ -818,7 +835,8 @@ AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* 
     g.b_cs = b->stride[b->ndim - 1];
     g.c_rs = c->stride[c->ndim - 2];
     g.c_cs = c->stride[c->ndim - 1];
-    cudaError_t e = launch_simt_gemm(g, (cudaStream_t)stream);
+    cudaError_t e = dtype == AKR_DTYPE_F32 ? launch_simt_gemm(g, (cudaStream_t)stream)
+                                           : launch_simt_gemm_typed(g, dtype, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "simt matmul launch");
     st->launches++;
     return AKR_OK;

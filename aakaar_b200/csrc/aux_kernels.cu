@@ -136,6 +136,43 @@ __global__ void simt_gemm_kernel(const SimtGemm g) {
     if (row < g.M && col < g.N) g.C[co + (int64_t)row * g.c_rs + (int64_t)col * g.c_cs] = acc;
 }
 
+// Typed forward-only matmul (float64, int32, int64) on CUDA cores: same tiling as above. Integer
+// products accumulate in 64 bits and wrap to the output type, as the reference's integer kernel does
+// (src/matmul_kernel.cu:219-341); float64 stands in for its cublasDgemm loop (:151-191).
+template <typename T, typename Acc>
+__global__ void simt_gemm_typed_kernel(const SimtGemm g) {
+    __shared__ T As[ST][ST + 1];
+    __shared__ T Bs[ST][ST + 1];
+    const T* A = reinterpret_cast<const T*>(g.A);
+    const T* B = reinterpret_cast<const T*>(g.B);
+    T* C = reinterpret_cast<T*>(g.C);
+    int64_t t = blockIdx.z;
+    int64_t ao = 0, bo = 0, co = 0;
+    for (int d = g.nb - 1; d >= 0; --d) {
+        const int64_t idx = t % g.bshape[d];
+        t /= g.bshape[d];
+        ao += idx * g.a_bs[d];
+        bo += idx * g.b_bs[d];
+        co += idx * g.c_bs[d];
+    }
+    const int row = blockIdx.y * ST + threadIdx.y;
+    const int col = blockIdx.x * ST + threadIdx.x;
+    Acc acc = 0;
+    for (int k0 = 0; k0 < g.K; k0 += ST) {
+        const int ka = k0 + threadIdx.x;
+        const int kb = k0 + threadIdx.y;
+        As[threadIdx.y][threadIdx.x] =
+            (row < g.M && ka < g.K) ? A[ao + (int64_t)row * g.a_rs + (int64_t)ka * g.a_cs] : T(0);
+        Bs[threadIdx.y][threadIdx.x] =
+            (kb < g.K && col < g.N) ? B[bo + (int64_t)kb * g.b_rs + (int64_t)col * g.b_cs] : T(0);
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < ST; ++k) acc += (Acc)As[threadIdx.y][k] * (Acc)Bs[k][threadIdx.x];
+        __syncthreads();
+    }
+    if (row < g.M && col < g.N) C[co + (int64_t)row * g.c_rs + (int64_t)col * g.c_cs] = (T)acc;
+}
+
 struct GatherArgs {
     const float* src;
     float* dst;
@@ -414,6 +451,21 @@ cudaError_t launch_simt_gemm(const SimtGemm& g, cudaStream_t s) {
     dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, (unsigned)batch);
     if (grid.y > 65535) return cudaErrorInvalidValue;
     simt_gemm_kernel<<<grid, dim3(ST, ST), 0, s>>>(g);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_simt_gemm_typed(const SimtGemm& g, int dtype, cudaStream_t s) {
+    int64_t batch = 1;
+    for (int d = 0; d < g.nb; ++d) batch *= g.bshape[d];
+    if (batch > 65535) return cudaErrorInvalidValue;
+    dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, (unsigned)batch);
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    switch (dtype) {
+        case 1: simt_gemm_typed_kernel<double, double><<<grid, dim3(ST, ST), 0, s>>>(g); break;
+        case 2: simt_gemm_typed_kernel<int, long long><<<grid, dim3(ST, ST), 0, s>>>(g); break;
+        case 3: simt_gemm_typed_kernel<long long, long long><<<grid, dim3(ST, ST), 0, s>>>(g); break;
+        default: return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 

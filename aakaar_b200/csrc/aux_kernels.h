@@ -34,6 +34,8 @@ struct SimtGemm {
     int64_t a_rs, a_cs, b_rs, b_cs, c_rs, c_cs;
 };
 cudaError_t launch_simt_gemm(const SimtGemm& g, cudaStream_t s);
+// Same product for dtype 1 = float64, 2 = int32, 3 = int64 (pointers reinterpreted, strides in elements).
+cudaError_t launch_simt_gemm_typed(const SimtGemm& g, int dtype, cudaStream_t s);
 
 struct StridedView {
     const float* ptr;

@@ -46,7 +46,9 @@ TensorPtr op_contiguous(const TensorPtr& t);
 
 TensorPtr op_add_raw(const TensorPtr& a, const TensorPtr& b) {
     require_cuda(a, "add");
+    require_f32(a, "add");
     require_cuda(b, "add");
+    require_f32(b, "add");
     const size_t nd = std::max(a->shape.size(), b->shape.size());
     std::vector<int64_t> shape(nd);
     for (size_t i = 0; i < nd; ++i) {
@@ -85,6 +87,7 @@ TensorPtr op_add(const TensorPtr& a, const TensorPtr& b) {
 
 TensorPtr op_scale(const TensorPtr& a, float s) {
     require_cuda(a, "mul");
+    require_f32(a, "mul");
     auto src = a->is_contiguous() ? a : op_contiguous(a);
     auto out = make_cuda(a->shape);
     check(akr_scale(src->data, s, out->data, (size_t)a->size, nullptr));
@@ -111,6 +114,7 @@ TensorPtr scalar_tensor(float v) {
 TensorPtr op_contiguous(const TensorPtr& t) {
     if (t->is_contiguous()) return t;
     require_cuda(t, "contiguous");
+    require_f32(t, "contiguous");
     auto out = make_cuda(t->shape);
     akr_view v = t->view();
     check(akr_contiguous(&v, out->data, nullptr));
@@ -180,6 +184,7 @@ TensorPtr op_view(const TensorPtr& t, std::vector<int64_t> new_shape, bool allow
 
 TensorPtr op_tanh(const TensorPtr& t) {
     require_cuda(t, "tanh");
+    require_f32(t, "tanh");
     auto src = op_contiguous(t);
     auto out = make_cuda(t->shape);
     check(akr_tanh_fwd(src->data, out->data, (size_t)t->size, nullptr));
@@ -201,6 +206,7 @@ TensorPtr op_tanh(const TensorPtr& t) {
 
 TensorPtr op_sum_all(const TensorPtr& t) {
     require_cuda(t, "sum");
+    require_f32(t, "sum");
     auto out = make_cuda({1});
     akr_view vg = t->view(), vo = out->view();
     check(akr_sum_to(&vg, &vo, nullptr));
@@ -228,6 +234,22 @@ int g_matmul_mode_override = AKR_MODE_GLOBAL;
 TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr& bias) {
     if (a->device != b->device) throw std::runtime_error("Both tensors must be on the same device!");
     require_cuda(a, "matmul");
+    if (a->dtype != AKR_DTYPE_F32 || b->dtype != AKR_DTYPE_F32) {
+        // float64 / int32 / int64: forward only, as in the reference (src/bindings.cpp:1688-1709)
+        if (a->dtype != b->dtype) throw std::runtime_error("matmul: operands must share one dtype");
+        if (g_grad_enabled && (a->requires_grad || b->requires_grad))
+            throw std::runtime_error(std::string("Autograd is not yet supported for dtype '") + dtype_name(a->dtype) +
+                                     "'. Only float32 currently supports gradients.");
+        if (bias) throw std::runtime_error("linear: only float32 is supported");
+        akr_view ta = a->view(), tb = b->view();
+        int64_t ts[AKR_MAX_DIMS + 2];
+        int32_t tnd = 0;
+        check(akr_matmul_plan(&ta, &tb, ts, &tnd));
+        auto typed = std::make_shared<Tensor>(std::vector<int64_t>(ts, ts + tnd), "cuda", a->dtype);
+        akr_view tc = typed->view();
+        check(akr_matmul_fwd_typed(&ta, &tb, &tc, nullptr));
+        return typed;
+    }
     akr_view va = a->view(), vb = b->view();
     int64_t oshape[AKR_MAX_DIMS + 2];
     int32_t ond = 0;
@@ -281,7 +303,9 @@ TensorPtr cpu_matmul_refused(const TensorPtr&, const TensorPtr&) {
 // _mse_fused of the reference (src/bindings.cpp:2821, src/elementwise_kernel.cu:2253-2300).
 TensorPtr op_mse(const TensorPtr& pred, const TensorPtr& target) {
     require_cuda(pred, "mse");
+    require_f32(pred, "mse");
     require_cuda(target, "mse");
+    require_f32(target, "mse");
     if (pred->shape != target->shape) throw std::invalid_argument("MSELoss: pred and target shapes differ");
     if (!pred->is_contiguous() || !target->is_contiguous())
         throw std::invalid_argument("MSELoss requires contiguous tensors. Call .contiguous() first.");
@@ -301,7 +325,9 @@ void op_sgd_step(const TensorPtr& p, const TensorPtr& grad, const TensorPtr& vel
                  float momentum, float weight_decay, float dampening, int nesterov, int has_momentum,
                  int velocity_initialized) {
     require_cuda(p, "sgd_step");
+    require_f32(p, "sgd_step");
     require_cuda(grad, "sgd_step");
+    require_f32(grad, "sgd_step");
     if (!p->is_contiguous() || !grad->is_contiguous())
         throw std::invalid_argument("sgd_step requires contiguous tensors");
     if (p->size != grad->size) throw std::invalid_argument("sgd_step: parameter and gradient sizes differ");
@@ -383,22 +409,29 @@ void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_g
 // ------------------------------------------------------------------ host <-> device
 
 TensorPtr from_numpy(py::array array, const std::string& device, bool requires_grad) {
-    if (!py::isinstance<py::array_t<float>>(array))
-        throw std::runtime_error("from_numpy: only float32 arrays are supported on the matmul path (got dtype " +
-                                 std::string(py::str(array.dtype())) + ")");
-    auto arr = py::array_t<float, py::array::c_style | py::array::forcecast>::ensure(array);
-    if (!arr) throw std::runtime_error("from_numpy: could not read the array as contiguous float32");
+    int dt;
+    if (py::isinstance<py::array_t<float>>(array)) dt = AKR_DTYPE_F32;
+    else if (py::isinstance<py::array_t<double>>(array)) dt = AKR_DTYPE_F64;
+    else if (py::isinstance<py::array_t<int32_t>>(array)) dt = AKR_DTYPE_I32;
+    else if (py::isinstance<py::array_t<int64_t>>(array)) dt = AKR_DTYPE_I64;
+    else
+        throw std::runtime_error("from_numpy: unsupported dtype " + std::string(py::str(array.dtype())) +
+                                 " (float32, float64, int32 and int64 are accepted)");
+    if (dt != AKR_DTYPE_F32 && requires_grad)
+        throw std::runtime_error(std::string("Autograd is not yet supported for dtype '") + dtype_name(dt) +
+                                 "'. Only float32 currently supports gradients.");
+    py::array arr = py::array::ensure(array, py::array::c_style);
+    if (!arr) throw std::runtime_error("from_numpy: could not read the array as C-contiguous");
     std::vector<int64_t> shape(arr.ndim());
     for (py::ssize_t i = 0; i < arr.ndim(); ++i) shape[i] = arr.shape(i);
     if (shape.empty()) shape.push_back(1);
-    auto t = std::make_shared<Tensor>(shape, device);
-    const size_t bytes = (size_t)t->size * sizeof(float);
+    auto t = std::make_shared<Tensor>(shape, device, dt);
     if (device == "cuda") {
-        check(akr_memcpy_h2d(t->data, arr.data(), bytes, nullptr));
+        check(akr_memcpy_h2d(t->data, arr.data(), t->nbytes(), nullptr));
         // the source may be freed by the caller right after this returns
         check(akr_stream_synchronize(nullptr));
     } else {
-        std::memcpy(t->data, arr.data(), bytes);
+        std::memcpy(t->data, arr.data(), t->nbytes());
     }
     t->requires_grad = requires_grad;
     return t;
@@ -416,20 +449,25 @@ TensorPtr from_pinned(py::array_t<float, py::array::c_style> arr, bool requires_
     return t;
 }
 
-py::array_t<float> to_numpy(const TensorPtr& t) {
+py::array to_numpy(const TensorPtr& t) {
     std::vector<py::ssize_t> shape(t->shape.begin(), t->shape.end());
-    py::array_t<float> out(shape);
-    const size_t bytes = (size_t)t->size * sizeof(float);
+    py::array out;
+    switch (t->dtype) {
+        case AKR_DTYPE_F64: out = py::array_t<double>(shape); break;
+        case AKR_DTYPE_I32: out = py::array_t<int32_t>(shape); break;
+        case AKR_DTYPE_I64: out = py::array_t<int64_t>(shape); break;
+        default: out = py::array_t<float>(shape); break;
+    }
     if (t->device == "cuda") {
         bool prev = g_grad_enabled;
         g_grad_enabled = false;
-        TensorPtr src = t->is_contiguous() ? t : op_contiguous(t);
+        TensorPtr src = t->is_contiguous() ? t : op_contiguous(t);   // gather is float32-only
         g_grad_enabled = prev;
-        check(akr_memcpy_d2h(out.mutable_data(), src->data, bytes, nullptr));
+        check(akr_memcpy_d2h(out.mutable_data(), src->data, t->nbytes(), nullptr));
         check(akr_synchronize());
     } else {
         if (!t->is_contiguous()) throw std::runtime_error("to_numpy: non-contiguous CPU tensors are not supported");
-        std::memcpy(out.mutable_data(), t->data, bytes);
+        std::memcpy(out.mutable_data(), t->data, t->nbytes());
     }
     return out;
 }
@@ -437,6 +475,7 @@ py::array_t<float> to_numpy(const TensorPtr& t) {
 // Download into caller-provided (ideally page-locked) memory without synchronising.
 void copy_to_host(const TensorPtr& t, py::array_t<float, py::array::c_style> out) {
     require_cuda(t, "copy_to_host");
+    require_f32(t, "copy_to_host");
     if ((int64_t)out.size() != t->size) throw std::invalid_argument("copy_to_host: size mismatch");
     bool prev = g_grad_enabled;
     g_grad_enabled = false;
@@ -458,8 +497,8 @@ py::array_t<float> pinned_empty(const std::vector<int64_t>& shape) {
 TensorPtr to_device(const TensorPtr& t, const std::string& target) {
     if (target == t->device) return t;
     if (target != "cuda" && target != "cpu") throw std::invalid_argument("Unknown device '" + target + "'");
-    auto out = std::make_shared<Tensor>(t->shape, target);
-    const size_t bytes = (size_t)t->size * sizeof(float);
+    auto out = std::make_shared<Tensor>(t->shape, target, t->dtype);
+    const size_t bytes = t->nbytes();
     if (target == "cuda") {
         if (!t->is_contiguous()) throw std::runtime_error("to('cuda'): CPU tensor must be contiguous");
         check(akr_memcpy_h2d(out->data, t->data, bytes, nullptr));
@@ -480,6 +519,7 @@ void copy_into(const TensorPtr& dst, const TensorPtr& src) {
     if (dst->size != src->size) throw std::invalid_argument("copy_: size mismatch");
     if (!dst->is_contiguous()) throw std::invalid_argument("copy_: destination must be contiguous");
     require_cuda(dst, "copy_");
+    require_f32(dst, "copy_");
     bool prev = g_grad_enabled;
     g_grad_enabled = false;
     TensorPtr s = src->is_contiguous() ? src : op_contiguous(src);
@@ -492,6 +532,7 @@ void copy_into(const TensorPtr& dst, const TensorPtr& src) {
 }
 
 float item(const TensorPtr& t) {
+    require_f32(t, "item");
     if (t->size != 1) throw std::runtime_error("item() only works on tensors with exactly one element");
     float v = 0.f;
     if (t->device == "cuda") {
@@ -550,7 +591,7 @@ std::string repr(const TensorPtr& t) {
     std::ostringstream os;
     os << "Tensor(shape=[";
     for (size_t i = 0; i < t->shape.size(); ++i) os << (i ? ", " : "") << t->shape[i];
-    os << "], device='" << t->device << "', dtype=float32" << (t->requires_grad ? ", requires_grad=True" : "") << ")";
+    os << "], device='" << t->device << "', dtype=" << dtype_name(t->dtype) << (t->requires_grad ? ", requires_grad=True" : "") << ")";
     return os.str();
 }
 
@@ -564,7 +605,7 @@ PYBIND11_MODULE(_C, m) {
                  return std::make_shared<Tensor>(shape, device);
              }),
              py::arg("shape"), py::arg("device") = "cuda")
-        .def_property_readonly("dtype", [](Tensor&) { return std::string("float32"); })
+        .def_property_readonly("dtype", [](Tensor& t) { return std::string(dtype_name(t.dtype)); })
         .def_readonly("device", &Tensor::device)
         .def_readonly("size", &Tensor::size)
         .def_readonly("shape", &Tensor::shape)

@@ -44,9 +44,20 @@ inline std::vector<int64_t> contiguous_strides(const std::vector<int64_t>& shape
     return st;
 }
 
+inline size_t dtype_size(int dtype) { return (dtype == AKR_DTYPE_F64 || dtype == AKR_DTYPE_I64) ? 8 : 4; }
+inline const char* dtype_name(int dtype) {
+    switch (dtype) {
+        case AKR_DTYPE_F64: return "float64";
+        case AKR_DTYPE_I32: return "int32";
+        case AKR_DTYPE_I64: return "int64";
+        default: return "float32";
+    }
+}
+
 class Tensor : public std::enable_shared_from_this<Tensor> {
 public:
-    float* data = nullptr;
+    float* data = nullptr;         // first element; reinterpret according to `dtype`
+    int dtype = AKR_DTYPE_F32;     // float32 everywhere except forward-only typed matmul
     int64_t size = 0;
     std::vector<int64_t> shape;
     std::vector<int64_t> strides;  // elements
@@ -58,7 +69,8 @@ public:
     TensorPtr base;  // parent of a view
 
     // Fresh contiguous allocation.
-    Tensor(std::vector<int64_t> shp, const std::string& dev) : shape(std::move(shp)), device(dev) {
+    Tensor(std::vector<int64_t> shp, const std::string& dev, int dt = AKR_DTYPE_F32)
+        : dtype(dt), shape(std::move(shp)), device(dev) {
         size = 1;
         for (int64_t d : shape) {
             if (d <= 0) throw std::invalid_argument("Tensor dimensions must be positive");
@@ -67,9 +79,9 @@ public:
         if (shape.size() > AKR_MAX_DIMS) throw std::invalid_argument("Tensors with more than 8 dimensions are not supported");
         strides = contiguous_strides(shape);
         if (device == "cuda") {
-            check(akr_alloc((size_t)size, &owned_));
+            check(akr_alloc(alloc_floats(), &owned_));   // the allocator counts in 4-byte units
         } else if (device == "cpu") {
-            owned_ = static_cast<float*>(::operator new((size_t)size * sizeof(float)));
+            owned_ = static_cast<float*>(::operator new(nbytes()));
         } else {
             throw std::invalid_argument("Unknown device '" + device + "' (expected 'cuda' or 'cpu')");
         }
@@ -78,16 +90,16 @@ public:
 
     // View of `parent` at element offset `off`.
     Tensor(const TensorPtr& parent, int64_t off, std::vector<int64_t> shp, std::vector<int64_t> strd)
-        : shape(std::move(shp)), strides(std::move(strd)), device(parent->device),
+        : dtype(parent->dtype), shape(std::move(shp)), strides(std::move(strd)), device(parent->device),
           base(parent->base ? parent->base : parent) {
         size = 1;
         for (int64_t d : shape) size *= d;
-        data = parent->data + off;
+        data = reinterpret_cast<float*>(reinterpret_cast<char*>(parent->data) + (size_t)off * dtype_size(dtype));
     }
 
     ~Tensor() {
         if (!base && owned_) {
-            if (device == "cuda") akr_free(owned_, (size_t)size);
+            if (device == "cuda") akr_free(owned_, alloc_floats());
             else ::operator delete(owned_);
         }
     }
@@ -95,12 +107,14 @@ public:
     Tensor& operator=(const Tensor&) = delete;
 
     bool is_contiguous() const { return strides == contiguous_strides(shape); }
+    size_t nbytes() const { return (size_t)size * dtype_size(dtype); }
+    size_t alloc_floats() const { return (nbytes() + 3) / 4; }
 
     akr_view view() const {
         akr_view v;
         v.data = data;
         v.ndim = (int32_t)shape.size();
-        v.dtype = AKR_DTYPE_F32;
+        v.dtype = dtype;
         for (int i = 0; i < AKR_MAX_DIMS; ++i) {
             v.shape[i] = i < (int)shape.size() ? shape[i] : 1;
             v.stride[i] = i < (int)shape.size() ? strides[i] : 0;
@@ -111,6 +125,12 @@ public:
 private:
     float* owned_ = nullptr;
 };
+
+inline void require_f32(const TensorPtr& t, const char* op) {
+    if (t->dtype != AKR_DTYPE_F32)
+        throw std::runtime_error(std::string(op) + ": only float32 is supported here (tensor is " +
+                                 dtype_name(t->dtype) + "); the other dtypes support forward matmul only");
+}
 
 inline void require_cuda(const TensorPtr& t, const char* op) {
     if (t->device != "cuda")

@@ -51,7 +51,8 @@ enum {
     AKR_ERR_ABORTED = -5  /* a kernel gave up on a bounded wait (device status word set) */
 };
 
-enum { AKR_DTYPE_F32 = 0 }; /* src/dtype.h: FLOAT32 = 0; the other dtypes are outside this path */
+/* src/dtype.h: FLOAT32, FLOAT64, INT32, INT64. Everything is float32 except akr_matmul_fwd_typed. */
+enum { AKR_DTYPE_F32 = 0, AKR_DTYPE_F64 = 1, AKR_DTYPE_I32 = 2, AKR_DTYPE_I64 = 3 };
 
 /* Arithmetic mode of one call. AKR_MODE_GLOBAL follows akr_set_tf32(). */
 enum {
@@ -150,6 +151,12 @@ AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, i
  *   - A kernel that gave up on a bounded wait is reported by the next call on that device that finds
  *     the stream idle (AKR_ERR_ABORTED). */
 AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
+
+/* Forward-only matmul of the reference's other dtypes, with the same broadcasting:
+ *   run_cuda_matmul_f64, src/matmul_kernel.cu:151-191 (float64) and run_cuda_matmul_int_typed, :300-341
+ *   (int32 / int64, 64-bit accumulation, wrap to the output type). No autograd in the reference either.
+ * All three views must carry the same dtype (AKR_DTYPE_F64 / I32 / I64). Plain CUDA-core kernel. */
+AKR_API int akr_matmul_fwd_typed(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
 
 /* Plain fp32 FMA matmul on CUDA cores with the same broadcasting (no tensor cores, no TF32).
  * A slow on-device cross-check for shapes where a host check takes too long; not used by the

@@ -36,6 +36,7 @@ __all__ = [
     "plan_nd_matmul",
     "batch_offset",
     "matmul_forward",
+    "matmul_forward_typed",
     "matmul_a_bt",
     "matmul_at_b",
     "matmul_backward",
@@ -126,6 +127,21 @@ def matmul_forward(a, b, acc=np.float32):
         bm = bf[ob:ob + K * N].reshape(K, N).astype(acc, copy=False)
         of[bi * M * N:(bi + 1) * M * N] = (am @ bm).astype(np.float32).reshape(-1)
     return out
+
+
+def matmul_forward_typed(a, b):
+    """Forward-only product for float64 / int32 / int64 operands (no autograd in the reference):
+    src/cpu_kernel.cpp:1052-1185. Integers accumulate in 64 bits and wrap to the operand dtype."""
+    a, b = np.asarray(a), np.asarray(b)
+    if a.dtype != b.dtype:
+        raise RuntimeError("matmul: operands must share one dtype")
+    plan_nd_matmul(a.shape, b.shape)
+    if a.dtype == np.float64:
+        return np.matmul(a, b)
+    if a.dtype in (np.int32, np.int64):
+        with np.errstate(over="ignore"):
+            return np.matmul(a.astype(np.int64), b.astype(np.int64)).astype(a.dtype)
+    raise RuntimeError("matmul_forward_typed: unsupported dtype")
 
 
 def matmul_a_bt(a, b, acc=np.float32):

@@ -114,6 +114,17 @@ for p in (W1, B1, W2, B2):
 for n, p in (("w1", W1), ("b1", B1), ("w2", W2), ("b2", B2)):
     out[f"mlp_new_{n}"] = p.to_numpy()
 
+# 8b. forward-only typed matmul of the reference: float64, int32 (64-bit accumulation, wraps), int64 with broadcast
+g = np.random.Generator(np.random.PCG64(77))
+a64, b64 = g.standard_normal((3, 1, 9, 14)), g.standard_normal((2, 14, 11))
+out["f64_c"] = ref.cpu_matmul(ref.from_numpy(a64, "cpu", False), ref.from_numpy(b64, "cpu", False)).to_numpy()
+ai32 = g.integers(-2 ** 20, 2 ** 20, (17, 23)).astype(np.int32)
+bi32 = g.integers(-2 ** 20, 2 ** 20, (23, 13)).astype(np.int32)
+out["i32_c"] = ref.cpu_matmul(ref.from_numpy(ai32, "cpu", False), ref.from_numpy(bi32, "cpu", False)).to_numpy()
+ai64 = g.integers(-2 ** 40, 2 ** 40, (2, 5, 7)).astype(np.int64)
+bi64 = g.integers(-2 ** 20, 2 ** 20, (7, 4)).astype(np.int64)
+out["i64_c"] = ref.cpu_matmul(ref.from_numpy(ai64, "cpu", False), ref.from_numpy(bi64, "cpu", False)).to_numpy()
+
 # 9. error behaviour of the reference (messages the C ABI reproduces)
 errs = {}
 def err_of(fn):
@@ -125,6 +136,7 @@ def err_of(fn):
 errs["k_mismatch"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3))), T(np.ones((4, 2)))))
 errs["batch_mismatch"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 2, 3))), T(np.ones((3, 3, 2)))))
 errs["non_contiguous"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3))).transpose(0, 1), T(np.ones((2, 2)))))
+errs["f64_autograd"] = err_of(lambda: ref.cpu_matmul(ref.from_numpy(np.ones((2, 2)), "cpu", True), ref.from_numpy(np.ones((2, 2)), "cpu", False)))
 errs["non_scalar_backward"] = err_of(lambda: ref.cpu_matmul(T(np.ones((2, 3)), True), T(np.ones((3, 2)))).backward())
 meta["errors"] = errs
 

@@ -439,3 +439,27 @@ def test_random_shapes_layouts_and_broadcasts(mode, tol):
         for got, want, what in ((ga, rda, "dA"), (gb, rdb, "dB")):
             n = max(1e-30, float(np.linalg.norm(want)))
             assert np.linalg.norm(got.to_numpy().astype(np.float64) - want) / n < tol, (case, what, A.shape, A.strides, B.shape, B.strides)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [np.float64, np.int32, np.int64])
+def test_typed_forward_through_abi(dt):
+    # forward-only dtypes of the reference (src/matmul_kernel.cu:151-341): bit-exact for integers
+    # (64-bit accumulation, wrap to the operand width), 1e-14 for float64; strided views read in place
+    g = np.random.Generator(np.random.PCG64(5))
+    if dt == np.float64:
+        a, b = g.standard_normal((2, 3, 33, 70)), g.standard_normal((3, 41, 70))
+    else:
+        hi = 2 ** 30 if dt == np.int32 else 2 ** 45          # int32 products overflow and must wrap
+        a = g.integers(-hi, hi, (2, 3, 33, 70)).astype(dt)
+        b = g.integers(-hi, hi, (3, 41, 70)).astype(dt)
+    bt = np.swapaxes(b, -1, -2)                               # (3, 70, 41) strided view
+    got = cabi.matmul_typed(a, bt)
+    want = mo.matmul_forward_typed(a, bt)
+    assert got.dtype == dt and got.shape == (2, 3, 33, 41)
+    if dt == np.float64:
+        assert rel_fro(got, want) < 1e-14
+    else:
+        np.testing.assert_array_equal(got, want)
+    with pytest.raises(RuntimeError, match="share one dtype"):
+        cabi.matmul_typed(a, bt.astype(np.float32))

@@ -159,3 +159,23 @@ def test_newton_schulz_chain_through_views(ak):
             Ar = ref @ ref.T
             ref = a_ * ref + (b_ * Ar + c_ * (Ar @ Ar)) @ ref
     assert rel_fro(X.to_numpy(), ref) < 1e-5
+
+
+def test_typed_forward_only_matmul(ak):
+    # float64 / int32 / int64: forward product with broadcasting, no autograd (as in the reference)
+    G, META = load_golden()
+    g = np.random.Generator(np.random.PCG64(77))
+    a64, b64 = g.standard_normal((3, 1, 9, 14)), g.standard_normal((2, 14, 11))
+    c = ak.matmul(ak.from_numpy(a64, "cuda"), ak.from_numpy(b64, "cuda"))
+    assert c.dtype == "float64" and c.shape == [3, 2, 9, 11] and not c.requires_grad
+    assert rel_fro(c.to_numpy(), G["f64_c"]) < 1e-14
+    ai32 = g.integers(-2 ** 20, 2 ** 20, (17, 23)).astype(np.int32)
+    bi32 = g.integers(-2 ** 20, 2 ** 20, (23, 13)).astype(np.int32)
+    np.testing.assert_array_equal(ak.matmul(ak.from_numpy(ai32, "cuda"), ak.from_numpy(bi32, "cuda")).to_numpy(), G["i32_c"])
+    ai64 = g.integers(-2 ** 40, 2 ** 40, (2, 5, 7)).astype(np.int64)
+    bi64 = g.integers(-2 ** 20, 2 ** 20, (7, 4)).astype(np.int64)
+    np.testing.assert_array_equal(ak.matmul(ak.from_numpy(ai64, "cuda"), ak.from_numpy(bi64, "cuda")).to_numpy(), G["i64_c"])
+    with pytest.raises(RuntimeError, match="share one dtype"):
+        ak.matmul(ak.from_numpy(a64, "cuda"), ak.from_numpy(b64.astype(np.float32), "cuda"))
+    with pytest.raises(RuntimeError, match="only float32"):
+        ak.from_numpy(a64, "cuda").tanh()

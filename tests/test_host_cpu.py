@@ -68,9 +68,14 @@ def test_cpu_tensors_never_compute():
         a.tanh()
 
 
-def test_from_numpy_rejects_other_dtypes_and_missing_gpu():
-    with pytest.raises(RuntimeError, match="float32"):
-        ak.from_numpy(np.ones((2, 2), dtype=np.float64), "cpu")
+def test_from_numpy_dtypes_and_missing_gpu():
+    for dt, name in ((np.float32, "float32"), (np.float64, "float64"), (np.int32, "int32"), (np.int64, "int64")):
+        t = ak.from_numpy(np.ones((2, 3), dtype=dt), "cpu")
+        assert t.dtype == name and t.to_numpy().dtype == dt
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        ak.from_numpy(np.ones((2, 2), dtype=np.float16), "cpu")
+    with pytest.raises(RuntimeError, match="Only float32 currently supports gradients"):
+        ak.from_numpy(np.ones((2, 2), dtype=np.float64), "cpu", requires_grad=True)
     if not ak.is_available():
         with pytest.raises(RuntimeError, match="no CPU path"):
             ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cuda")

@@ -109,3 +109,15 @@ def test_batch_offset_broadcast_rules():
     assert mo.batch_offset(3, batch, (2, 7, 4), 28) == 28
     assert mo.batch_offset(4, batch, (3, 1, 5, 7), 35) == 70
     assert mo.batch_offset(4, batch, (2, 7, 4), 28) == 0
+
+
+def test_typed_forward_matches_reference():
+    g = np.random.Generator(np.random.PCG64(77))
+    a64, b64 = g.standard_normal((3, 1, 9, 14)), g.standard_normal((2, 14, 11))
+    assert rel_fro(mo.matmul_forward_typed(a64, b64), G["f64_c"]) < 1e-14
+    ai32 = g.integers(-2 ** 20, 2 ** 20, (17, 23)).astype(np.int32)
+    bi32 = g.integers(-2 ** 20, 2 ** 20, (23, 13)).astype(np.int32)
+    np.testing.assert_array_equal(mo.matmul_forward_typed(ai32, bi32), G["i32_c"])   # wraps like the reference
+    ai64 = g.integers(-2 ** 40, 2 ** 40, (2, 5, 7)).astype(np.int64)
+    bi64 = g.integers(-2 ** 20, 2 ** 20, (7, 4)).astype(np.int64)
+    np.testing.assert_array_equal(mo.matmul_forward_typed(ai64, bi64), G["i64_c"])
