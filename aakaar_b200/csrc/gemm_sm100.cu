@@ -20,6 +20,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -1261,6 +1262,257 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
+// ---------------------------------------------------------------------------------- CTA pairs, TF32 mode
+// One 256 x 256 tile per CTA pair (tcgen05.mma.cta_group::2, M = 256): each CTA holds 128 rows of A
+// and 128 columns of B of every k-block, so per flop a CTA's shared memory takes half the TMA writes
+// and two thirds of the MMA reads of a 128 x 256 tile on one CTA, and each CTA's tensor memory holds
+// TWO 128 x 256 accumulators: the epilogue of a tile overlaps the MMAs of the next (the 256 x 256
+// tile on one CTA fills all 512 columns and cannot do that).
+//   both CTAs: warp 0 loads its own tiles, completion bytes counted on the LEADER's barrier
+//   (cp.async.bulk.tensor ... .cta_group::2, one destination CTA per copy, no multicast);
+//   leader: warp 1 issues the MMAs; tcgen05.commit signals "stage free" / "accumulator complete" to
+//   both CTAs; warps 2..9 of each CTA drain its 128 rows.
+constexpr int DUO_STAGES = 6;
+constexpr int DUO_A_BYTES = 128 * BK * 4, DUO_B_BYTES = 128 * BK * 4;
+constexpr int DUO_STAGE_BYTES = DUO_A_BYTES + DUO_B_BYTES;
+constexpr int DUO_THREADS = 64 + 256;
+constexpr int DUO_EPI_WARPS = 8;
+constexpr int DUO_SMEM = DUO_STAGES * DUO_STAGE_BYTES + DUO_EPI_WARPS * EPI_STAGE_BYTES + 256 + 1024;
+
+template <int MAJA, int MAJB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DUO_THREADS, 1)
+gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    constexpr int S = DUO_STAGES;
+    constexpr int EPI_BYTES = DUO_EPI_WARPS * EPI_STAGE_BYTES;  // staging (1024-byte aligned) before the barriers
+    uint8_t* epi_stage_base = smem + S * DUO_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * DUO_STAGE_BYTES + EPI_BYTES);
+    const uint32_t bar_base = smem_base + S * DUO_STAGE_BYTES + EPI_BYTES;
+    auto ready_bar = [&](int s) { return bar_base + 8u * s; };             // leader: both CTAs' tiles landed
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };       // local: stage may be refilled
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };     // local: accumulator complete
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };  // leader: both CTAs drained it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(ready_bar(s), 1);  // the leader's expect-tx arrive, completed by both CTAs' bytes
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(tfull_bar(b), 1);
+            ptx::mbar_init(tempty_bar(b), 2 * DUO_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+        if (p.c_tma) ptx::prefetch_tensormap(&p.tmC);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair<512>(ptx::smem_u32(tmem_slot));
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_iters = p.red * p.nkb;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (own tiles, leader's barrier)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+                const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+                const int m_row0 = c.m0 + 128 * (int)rank;  // this CTA's rows of A
+                const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
+                for (int it = 0; it < total_iters; ++it) {
+                    const int r = it / p.nkb;
+                    const int k0 = (it - r * p.nkb) * BK;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
+                    const uint32_t lb = ptx::map_to_cta(ready_bar(stage), 0);
+                    if (p.debug & 1) {  // timing experiment: no loads, stale shared memory
+                        if (leader) ptx::mbar_arrive(ready_bar(stage));
+                        if (++stage == S) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
+                    if (leader) ptx::mbar_arrive_expect_tx(ready_bar(stage), 2 * DUO_STAGE_BYTES);
+                    const uint32_t da = smem_base + stage * DUO_STAGE_BYTES;
+                    const uint32_t db = da + DUO_A_BYTES;
+                    const int bcv[4] = {c.i1, c.i0, r, 0};
+                    const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                    const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
+                    if (MAJA == 0) {
+                        ptx::tma_load_5d_pair(da, &p.tmA, lb, k0, m_row0, a0, a1, a2);
+                    } else if (p.a_fold) {
+                        ptx::tma_load_5d_pair(da, &p.tmA, lb, 0, k0, m_row0 / CHUNK, a0, a1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                            ptx::tma_load_5d_pair(da + ch * (BK * 128), &p.tmA, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
+                    }
+                    if (MAJB == 0) {
+                        ptx::tma_load_5d_pair(db, &p.tmB, lb, k0, n_col0, b0, b1, b2);
+                    } else if (p.b_fold) {
+                        ptx::tma_load_5d_pair(db, &p.tmB, lb, 0, k0, n_col0 / CHUNK, b0, b1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                            ptx::tma_load_5d_pair(db + ch * (BK * 128), &p.tmB, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                    }
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                const uint64_t t0 = ptx::globaltimer_ns();  // let copies in flight land (they signal the leader)
+                while (ptx::globaltimer_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
+            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128, b_lbo = MAJB == 0 ? 16 : BK * 128;
+            constexpr uint32_t a_sbo = MAJA == 0 ? 1024 : 512, b_sbo = MAJB == 0 ? 1024 : 512;
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
+                const int buf = local & 1;
+                const uint32_t acc_phase = (local >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) {
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * PAIR_BN;
+                for (int it = 0; it < total_iters; ++it) {
+                    if (!ptx::mbar_wait(ready_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_base + stage * DUO_STAGE_BYTES;
+                    const uint32_t sb = sa + DUO_A_BYTES;
+#pragma unroll
+                    for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                        const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                        const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                        const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
+                        const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                        if (p.debug & 2) {  // timing experiment: loads and hand-shakes only
+                            if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                            continue;
+                        }
+                        ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                    }
+                    ptx::mma_commit_pair(empty_bar(stage));  // both CTAs may refill this stage
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit_pair(tfull_bar(buf));  // accumulator complete in both CTAs' tensor memory
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..9): this CTA's 128 rows
+        const int q = warp & 3;
+        const int slab = (warp - 2) >> 2;
+        const bool vec = p.vec_ok != 0;
+        const bool accumulate = p.accumulate != 0;
+        const bool use_tma = p.c_tma != 0;
+        float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
+        const uint32_t slab_tile_addr = smem_base + S * DUO_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        int local = 0;
+        bool ok = true;
+        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
+            const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1u;
+            bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
+            if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
+            if (!got) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const int row_base = c.m0 + 128 * (int)rank;
+            const int row0 = row_base + q * 32;
+            const int slab_col0 = c.n0 + slab * 128;
+            float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * PAIR_BN + slab * 128;
+            if (row_base < p.M) {  // CTA-uniform: the peer's half may lie below the matrix
+#pragma unroll 1
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int col0 = slab_col0 + ch * 32;
+                    if (col0 < p.N) {
+                        __syncwarp();
+                        uint32_t v[32];
+                        ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                        ptx::tmem_ld_wait();
+                        float f[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                        if (p.debug & 128) continue;  // timing experiment: no stores
+                        if (use_tma)
+                            store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
+                                            lane, q == 0 && lane == 0, 2 + slab);
+                        else
+                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias, accumulate,
+                                             lane);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
+        }
+    }
+
+    // ------------------------------------------------------------ teardown (all paths)
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair<512>(tmem_base);
+    }
+    if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
+}
+
 // ---------------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1406,10 +1658,13 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
     return 0;
 }
 
-template <int MAJA, int MAJB>
+// DUO = false: fp32-accurate pair kernel, true: TF32 pair kernel.
+template <bool DUO, int MAJA, int MAJB>
 int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
-    constexpr int smem = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
-    auto kern = gemm_tf32_pair_kernel<MAJA, MAJB>;
+    constexpr int smem = DUO ? DUO_SMEM
+                             : PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
+    constexpr int threads = DUO ? DUO_THREADS : PAIR_THREADS;
+    auto kern = DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>;
     static bool attr_done = false;
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -1424,7 +1679,7 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
     if (max_pairs == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * 74);
-        cfg.blockDim = dim3(PAIR_THREADS);
+        cfg.blockDim = dim3(threads);
         cfg.dynamicSmemBytes = smem;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -1439,9 +1694,10 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
             n = 64;
         }
         max_pairs = n;
+        if (std::getenv("AKR_B200_VERBOSE")) std::fprintf(stderr, "akr_b200: %d CTA pairs resident (%s kernel)\n", n, DUO ? "tf32 pair" : "fp32 pair");
     }
     if (grid > 2 * max_pairs) grid = 2 * max_pairs;
-    kern<<<grid, PAIR_THREADS, smem, stream>>>(kp);  // cluster of 2 CTAs (compile-time cluster dims)
+    kern<<<grid, threads, smem, stream>>>(kp);  // cluster of 2 CTAs (compile-time cluster dims)
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -1462,6 +1718,22 @@ bool use_pairs(const GemmDesc& g) {
     if (!presplit && !(g.debug & 32)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     return tiles * 4 >= gemm_sm100_num_ctas();
+}
+
+// TF32 mode on CTA pairs: long contractions whose 256 x 256 tiles give most pairs one tile but do not
+// fill the machine with one tile per CTA (those go to the 256 x 256 single-CTA kernel, which is faster
+// over many waves: 1.36 ms against 1.58 ms at 8192^3; the pair's stage hand-over crosses the cluster
+// twice per k-block and its 192 KB of stages do not cover that round trip). In this band the pair kernel
+// is 3-6 % faster than 128 x 256 tiles on single CTAs. Debug bit 10 disables it, bit 11 prefers it
+// wherever it is applicable.
+bool use_duo(const GemmDesc& g) {
+    if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || (g.debug & 1024)) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+    const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
+    if (tiles * 4 < gemm_sm100_num_ctas()) return false;
+    if (g.debug & 2048) return true;
+    // many waves of short contractions: the overlapped epilogue still wins (8192 x 4096 x 1024: 0.109 against 0.118 ms)
+    return iters >= 32 && (tiles < gemm_sm100_num_ctas() || iters < 64);
 }
 
 // 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
@@ -1560,10 +1832,11 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: split launch without scratch");
         return -1;
     }
-    const bool big = use_big_tiles(g);
     GemmDesc gd = g;
     gd.debug |= g_debug_flags;
-    const bool pairs = use_pairs(gd);
+    const bool duo = use_duo(gd);
+    const bool big = !duo && use_big_tiles(gd);
+    const bool pairs = duo || use_pairs(gd);
     const int bn = big ? BIG_BN : (pairs ? PAIR_BN : pick_bn(g));
     const int bm = big ? BIG_BM : (pairs ? PAIR_BM : BM);
     const int bk = g.terms == 3 ? 16 : BK;  // finer stages for the hi+lo mode
@@ -1616,7 +1889,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                     : 0;
     // Output map for the TMA-store epilogue: (N, M, o1, o0), boxes of 32 columns x 128 rows.
     kp.c_tma = 0;
-    if (kp.vec_ok && !g.accumulate && kp.splits == 1 && !pairs && !((g.debug | g_debug_flags) & 256)) {
+    if (kp.vec_ok && !g.accumulate && kp.splits == 1 && (!pairs || duo) && !((g.debug | g_debug_flags) & 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
         cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.o1, (cuuint64_t)g.o0};
@@ -1649,11 +1922,20 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
 
     if (pairs) {
         const int npairs = (int)std::min<long long>(total, ctas / 2);
-        switch (g.A.mn_major * 2 + g.B.mn_major) {
-            case 0: return launch_pair_variant<0, 0>(kp, 2 * npairs, stream, err, errlen);
-            case 1: return launch_pair_variant<0, 1>(kp, 2 * npairs, stream, err, errlen);
-            case 2: return launch_pair_variant<1, 0>(kp, 2 * npairs, stream, err, errlen);
-            default: return launch_pair_variant<1, 1>(kp, 2 * npairs, stream, err, errlen);
+        const int sel = g.A.mn_major * 2 + g.B.mn_major;
+        if (duo) {
+            switch (sel) {
+                case 0: return launch_pair_variant<true, 0, 0>(kp, 2 * npairs, stream, err, errlen);
+                case 1: return launch_pair_variant<true, 0, 1>(kp, 2 * npairs, stream, err, errlen);
+                case 2: return launch_pair_variant<true, 1, 0>(kp, 2 * npairs, stream, err, errlen);
+                default: return launch_pair_variant<true, 1, 1>(kp, 2 * npairs, stream, err, errlen);
+            }
+        }
+        switch (sel) {
+            case 0: return launch_pair_variant<false, 0, 0>(kp, 2 * npairs, stream, err, errlen);
+            case 1: return launch_pair_variant<false, 0, 1>(kp, 2 * npairs, stream, err, errlen);
+            case 2: return launch_pair_variant<false, 1, 0>(kp, 2 * npairs, stream, err, errlen);
+            default: return launch_pair_variant<false, 1, 1>(kp, 2 * npairs, stream, err, errlen);
         }
     }
     if (big) {

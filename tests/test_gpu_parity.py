@@ -360,6 +360,15 @@ def test_bounded_wait_abort_is_reported_and_recoverable():
                 cabi.synchronize()
             assert e.value.code == cabi.ERR_ABORTED
             cabi.synchronize()   # reported once, then clear
+        # the CTA-pair kernel (49 tiles of 256 x 256, 32 k-blocks): both CTAs of every pair give up and
+        # meet at the cluster barrier of the teardown
+        A2, B2 = dev(uniform((1792, 1024), 3)), dev(uniform((1024, 1792), 4))
+        cabi.synchronize()
+        cabi.matmul_fwd(A2, B2, mode=MODE_TF32)
+        with pytest.raises(cabi.AkrError) as e:
+            cabi.synchronize()
+        assert e.value.code == cabi.ERR_ABORTED
+        cabi.synchronize()
     finally:
         cabi.check(lib.akr_debug_configure(0, 0))
     # the context is still usable and results are right again
@@ -388,6 +397,41 @@ def test_experimental_cta_pair_kernel_parity():
         a2, b2 = normal((n, n), 401, s_), normal((n, n), 402, s_)
         c2 = cabi.matmul_fwd(dev(a2), dev(b2), mode=MODE_FP32).to_numpy()
         sampled_rows_check(a2, b2, c2, [0, 129, 2047, 4095], TOL_FP32)
+    finally:
+        cabi.check(lib.akr_debug_configure(0, 0))
+
+
+def test_tf32_cta_pair_kernel_parity():
+    # TF32 products on CTA pairs (cta_group::2, one 256 x 256 tile per pair): ragged edges, all four
+    # operand layouts, bias, C +=, broadcast batches and a summed batch dim (weight gradient), with the
+    # kernel preferred wherever it applies (flag 2048) and under its default routing.
+    lib = cabi.lib()
+    try:
+        for flags in (2048, 0):
+            cabi.check(lib.akr_debug_configure(flags, 0))
+            M, N, K = (1500, 1700, 200) if flags else (2100, 1800, 1100)
+            a, b = uniform((M, K), 81), uniform((K, N), 82)
+            bias = normal((1, N), 83)
+            ref = a.astype(np.float64) @ b.astype(np.float64)
+            A, B = dev(a), dev(b)
+            at, bt = dev(np.ascontiguousarray(a.T)), dev(np.ascontiguousarray(b.T))
+            for Av in (A, at.transpose(0, 1)):
+                for Bv in (B, bt.transpose(0, 1)):
+                    assert rel_fro(cabi.matmul_fwd(Av, Bv, mode=MODE_TF32).to_numpy(), ref) < TOL_TF32
+            assert rel_fro(cabi.matmul_fwd(A, B, bias=dev(bias), mode=MODE_TF32).to_numpy(), ref + bias) < TOL_TF32
+            # ragged sizes that defeat the vector / TMA store path (N % 4 != 0)
+            a3, b3 = uniform((1300, 264), 84), uniform((264, 1299), 85)
+            c3 = cabi.matmul_fwd(dev(a3), dev(b3), mode=MODE_TF32).to_numpy()
+            assert rel_fro(c3, a3.astype(np.float64) @ b3.astype(np.float64)) < TOL_TF32
+        cabi.check(lib.akr_debug_configure(2048, 0))
+        # batched with broadcast: [3,1,520,96] @ [2,96,530] -> 6 x (3 x 3) tiles; backward sums dB over the batch
+        a4, b4 = uniform((3, 1, 520, 96), 86), uniform((2, 96, 530), 87)
+        dc4 = uniform((3, 2, 520, 530), 88)
+        A4, B4, G4 = dev(a4), dev(b4), dev(dc4)
+        assert rel_fro(cabi.matmul_fwd(A4, B4, mode=MODE_TF32).to_numpy(), mo.matmul_forward(a4, b4, np.float64)) < TOL_TF32
+        da, db = cabi.matmul_bwd(A4, B4, G4, mode=MODE_TF32)
+        rda, rdb = mo.matmul_backward(a4, b4, dc4, np.float64)
+        assert rel_fro(da.to_numpy(), rda) < TOL_TF32 and rel_fro(db.to_numpy(), rdb) < TOL_TF32
     finally:
         cabi.check(lib.akr_debug_configure(0, 0))
 
