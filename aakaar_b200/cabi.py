@@ -58,6 +58,8 @@ def load():
         "akr_matmul_at_b": [V, V, V, C.c_int, vp],
         "akr_matmul_fwd_simt": [V, V, V, vp],
         "akr_matmul_fwd_typed": [V, V, V, vp],
+        "akr_matmul_bwd_tanh": [V, V, V, V, V, C.c_int, vp],
+        "akr_matmul_fwd_axpby": [V, V, C.c_float, C.c_float, V, V, C.c_int, vp],
         "akr_matmul_at_b_noalloc": [V, V, V, vp],
         "akr_workspace_bytes": [C.POINTER(sz)],
         "akr_launch_count": [C.c_int],
@@ -265,6 +267,28 @@ def matmul_bwd(a, b, dc, mode=MODE_GLOBAL, need_da=True, need_db=True, da=None, 
                                C.byref(vda) if need_da else None, C.byref(vdb) if need_db else None,
                                mode, _sh(stream)))
     return (da if need_da else None), (db if need_db else None)
+
+
+def matmul_bwd_tanh(a_tanh, b, dc, mode=MODE_GLOBAL, need_dz=True, need_db=True, stream=None):
+    """(dZ, dB) for C = tanh(Z) @ B given A = tanh(Z): dZ = (dC B^T) * (1 - A^2) in the GEMM epilogue."""
+    dz = DeviceArray(a_tanh.shape) if need_dz else None
+    db = DeviceArray(b.shape) if need_db else None
+    va, vb, vg = a_tanh.view(), b.view(), dc.view()
+    vdz = dz.view() if need_dz else None
+    vdb = db.view() if need_db else None
+    check(lib().akr_matmul_bwd_tanh(C.byref(va), C.byref(vb), C.byref(vg), C.byref(vdz) if need_dz else None,
+                                    C.byref(vdb) if need_db else None, mode, _sh(stream)))
+    return dz, db
+
+
+def matmul_axpby(a, b, alpha=1.0, beta=0.0, d=None, mode=MODE_GLOBAL, out=None, stream=None):
+    """alpha * (a @ b) + beta * d in one launch."""
+    c = out if out is not None else DeviceArray(plan(a, b))
+    va, vb, vc = a.view(), b.view(), c.view()
+    vd = d.view() if d is not None else None
+    check(lib().akr_matmul_fwd_axpby(C.byref(va), C.byref(vb), alpha, beta, C.byref(vd) if d is not None else None,
+                                     C.byref(vc), mode, _sh(stream)))
+    return c
 
 
 def matmul_simt(a, b):

@@ -178,10 +178,16 @@ struct Problem {
     int64_t c_bs[AKR_MAX_DIMS] = {0};  // 0 on a dim of extent > 1: summed away
     const float* bias = nullptr;
     int mode = AKR_MODE_TF32;
+    // epilogue: C = op(alpha * AB (+ bias)), op 1: + beta * X, op 2: * (1 - X^2); X has C's shape
+    float alpha = 1.f, beta = 0.f;
+    int aux_op = 0;
+    const float* aux = nullptr;
+    int64_t aux_rs = 0, aux_cs = 1;
+    int64_t aux_bs[AKR_MAX_DIMS] = {0};
 };
 
 struct Dim {
-    int64_t e, a, b, c;
+    int64_t e, a, b, c, x;  // extent; strides of A, B, C and the second epilogue operand
 };
 
 void collapse(std::vector<Dim>& d) {
@@ -189,11 +195,12 @@ void collapse(std::vector<Dim>& d) {
     for (const Dim& x : d) {
         if (!out.empty()) {
             Dim& p = out.back();
-            if (p.a == x.a * x.e && p.b == x.b * x.e && p.c == x.c * x.e) {
+            if (p.a == x.a * x.e && p.b == x.b * x.e && p.c == x.c * x.e && p.x == x.x * x.e) {
                 p.e *= x.e;
                 p.a = x.a;
                 p.b = x.b;
                 p.c = x.c;
+                p.x = x.x;
                 continue;
             }
         }
@@ -292,7 +299,7 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     std::vector<Dim> outd, redd;
     for (int i = 0; i < p.nb; ++i) {
         if (p.bshape[i] == 1) continue;
-        Dim d{p.bshape[i], p.A.bs[i], p.B.bs[i], p.c_bs[i]};
+        Dim d{p.bshape[i], p.A.bs[i], p.B.bs[i], p.c_bs[i], p.aux_op ? p.aux_bs[i] : 0};
         (d.c != 0 ? outd : redd).push_back(d);
     }
     collapse(outd);
@@ -333,6 +340,11 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     g.B = B.op;
     g.ldc = p.c_rs;
     g.bias = p.bias;
+    g.alpha = p.alpha;
+    g.beta = p.beta;
+    g.aux_op = p.aux_op;
+    g.aux_ld = p.aux_rs;
+    g.aux_cs = p.aux_cs;
     g.terms = p.mode == AKR_MODE_FP32 ? 3 : 1;
     g.o0 = g.o1 = g.red = 1;
     for (int i = 0; i < 3; ++i) g.A.bs[i] = g.B.bs[i] = 0;
@@ -345,11 +357,14 @@ int run_problem(const Problem& p, cudaStream_t stream) {
         g.B.bs[1] = B.bs[no - 1];
         g.c_bs0 = outd[no - 2].c;
         g.c_bs1 = outd[no - 1].c;
+        g.aux_bs0 = outd[no - 2].x;
+        g.aux_bs1 = outd[no - 1].x;
     } else if (ko == 1) {
         g.o1 = (int)outd[no - 1].e;
         g.A.bs[1] = A.bs[no - 1];
         g.B.bs[1] = B.bs[no - 1];
         g.c_bs1 = outd[no - 1].c;
+        g.aux_bs1 = outd[no - 1].x;
     }
     if (kr == 1) {
         g.red = (int)redd[nr - 1].e;
@@ -376,13 +391,14 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     for (size_t i = 0; i + kr < nr; ++i) n_rouser *= redd[i].e;
     char err[256] = {0};
     for (int64_t io = 0; io < n_outer; ++io) {
-        int64_t t = io, ao = 0, bo = 0, co = 0;
+        int64_t t = io, ao = 0, bo = 0, co = 0, xo = 0;
         for (int i = (int)(no - ko) - 1; i >= 0; --i) {
             const int64_t idx = t % outd[i].e;
             t /= outd[i].e;
             ao += idx * A.bs[i];
             bo += idx * B.bs[i];
             co += idx * outd[i].c;
+            xo += idx * outd[i].x;
         }
         for (int64_t ir = 0; ir < n_rouser; ++ir) {
             int64_t tr = ir, ar = 0, br = 0;
@@ -399,7 +415,11 @@ int run_problem(const Problem& p, cudaStream_t stream) {
             if (g.B.lo) gi.B.lo = g.B.lo + bo + br;
             gi.C = p.C + co;
             gi.accumulate = ir > 0 ? 1 : 0;
-            if (ir > 0) gi.bias = nullptr;
+            // bias and the second epilogue operand apply once, to the complete sum: on the last launch
+            const bool last = ir + 1 == n_rouser;
+            if (!last) gi.bias = nullptr;
+            gi.aux_op = last ? g.aux_op : 0;
+            gi.aux = (last && p.aux) ? p.aux + xo : nullptr;
             const int lrc = gemm_sm100_launch(gi, stream, status, err, sizeof(err));
             if (lrc != 0) return fail(lrc == -1 ? AKR_ERR_INVALID : AKR_ERR_CUDA, err);
             st->launches++;
@@ -623,8 +643,8 @@ AKR_API int akr_matmul_plan(const akr_view* a, const akr_view* b, int64_t* out_s
     return AKR_OK;
 }
 
-AKR_API int akr_matmul_fwd(const akr_view* a, const akr_view* b, const akr_view* bias, akr_view* c, int mode,
-                   void* stream) {
+static int matmul_fwd_impl(const akr_view* a, const akr_view* b, const akr_view* bias, akr_view* c, float alpha,
+                           float beta, const akr_view* d, int mode, void* stream) {
     Plan pl;
     int rc = make_plan(a, b, &pl);
     if (rc != AKR_OK) return rc;
@@ -665,12 +685,36 @@ AKR_API int akr_matmul_fwd(const akr_view* a, const akr_view* b, const akr_view*
     p.C = (float*)c->data;
     p.c_rs = c->stride[c->ndim - 2];
     p.bias = bias_ptr;
+    p.alpha = alpha;
+    if (d) {
+        if ((rc = check_view(d, "matmul addend", 2)) != AKR_OK) return rc;
+        if (d->ndim != pl.nb + 2) return fail(AKR_ERR_INVALID, "matmul addend must have the shape of the output");
+        for (int i = 0; i < pl.nb + 2; ++i)
+            if (d->shape[i] != oshape[i]) return fail(AKR_ERR_INVALID, "matmul addend must have the shape of the output");
+        p.aux_op = 1;
+        p.beta = beta;
+        p.aux = (const float*)d->data;
+        p.aux_rs = d->stride[d->ndim - 2];
+        p.aux_cs = d->stride[d->ndim - 1];
+        for (int i = 0; i < pl.nb; ++i) p.aux_bs[i] = d->stride[i];
+    }
     p.mode = resolve_mode(mode);
     return run_problem(p, (cudaStream_t)stream);
 }
 
-AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da, akr_view* db,
-                   int mode, void* stream) {
+AKR_API int akr_matmul_fwd(const akr_view* a, const akr_view* b, const akr_view* bias, akr_view* c, int mode,
+                   void* stream) {
+    return matmul_fwd_impl(a, b, bias, c, 1.f, 0.f, nullptr, mode, stream);
+}
+
+AKR_API int akr_matmul_fwd_axpby(const akr_view* a, const akr_view* b, float alpha, float beta, const akr_view* d,
+                                 akr_view* c, int mode, void* stream) {
+    if (beta != 0.f && !d) return fail(AKR_ERR_INVALID, "matmul_fwd_axpby: beta != 0 needs an addend");
+    return matmul_fwd_impl(a, b, nullptr, c, alpha, beta, beta != 0.f ? d : nullptr, mode, stream);
+}
+
+static int matmul_bwd_impl(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da, akr_view* db,
+                           bool a_is_tanh, int mode, void* stream) {
     Plan pl;
     int rc = make_plan(a, b, &pl);
     if (rc != AKR_OK) return rc;
@@ -708,6 +752,13 @@ AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view*
         p.C = (float*)da->data;
         p.c_rs = da->stride[da->ndim - 2];
         p.mode = m;
+        if (a_is_tanh) {  // gradient w.r.t. the tanh's input: (dC B^T) * (1 - A^2), A read where it lies
+            p.aux_op = 2;
+            p.aux = (const float*)a->data;
+            p.aux_rs = a->stride[a->ndim - 2];
+            p.aux_cs = a->stride[a->ndim - 1];
+            for (int i = 0; i < pl.nb; ++i) p.aux_bs[i] = batch_stride(a, pl.nb, i);
+        }
         if ((rc = run_problem(p, (cudaStream_t)stream)) != AKR_OK) return rc;
     }
     if (db) {
@@ -735,6 +786,16 @@ AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view*
         if ((rc = run_problem(p, (cudaStream_t)stream)) != AKR_OK) return rc;
     }
     return AKR_OK;
+}
+
+AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da, akr_view* db,
+                   int mode, void* stream) {
+    return matmul_bwd_impl(a, b, dc, da, db, false, mode, stream);
+}
+
+AKR_API int akr_matmul_bwd_tanh(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* dz, akr_view* db,
+                                int mode, void* stream) {
+    return matmul_bwd_impl(a, b, dc, dz, db, true, mode, stream);
 }
 
 AKR_API int akr_matmul_a_bt(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream) {

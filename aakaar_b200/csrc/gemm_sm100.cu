@@ -43,6 +43,12 @@ struct KernelParams {
     int presplit;              // 1: low parts come from tmAlo / tmBlo, 0: derived in shared memory
     float* C;
     const float* bias;
+    // Second epilogue operand, an array of the output's shape with its own strides (aux_op != 0):
+    // 1: C = alpha * AB + beta * aux, 2: C = alpha * AB * (1 - aux^2) (tanh' of a saved tanh output).
+    const float* aux;
+    long long aux_ld, aux_cs, aux_bs0, aux_bs1;
+    int aux_op, aux_vec;
+    float alpha, beta;
     float* partials;
     int* counters;
     int* status;
@@ -108,13 +114,50 @@ constexpr int EPI_STAGE_BYTES = 32 * 128;
 // lane the LSU touches 32 cache lines per instruction, which capped the output rate of the
 // write-heavy (short-K, batched) products well below what HBM takes.
 // Must be called by all 32 lanes. Optionally adds a bias row vector and / or the previous contents.
+struct Epi {
+    const float* bias;   // row vector added to every row, or null
+    const float* aux;    // element (row, col) of the tile's matrix at aux[row * aux_ld + col * aux_cs]
+    long long aux_ld, aux_cs;
+    int op;              // 0: none, 1: += beta * aux, 2: *= 1 - aux^2
+    float alpha, beta;
+    bool accumulate, aux_vec;
+};
+
+__device__ __forceinline__ Epi plain_epi() {
+    Epi e;
+    e.bias = nullptr; e.aux = nullptr; e.aux_ld = 0; e.aux_cs = 1; e.op = 0; e.alpha = 1.f; e.beta = 0.f;
+    e.accumulate = false; e.aux_vec = false;
+    return e;
+}
+
+__device__ __forceinline__ Epi tile_epi(const KernelParams& p, const Tile& c) {
+    Epi e;
+    e.bias = p.bias;
+    e.op = p.aux_op;
+    e.aux = p.aux_op ? p.aux + c.i0 * p.aux_bs0 + c.i1 * p.aux_bs1 : nullptr;
+    e.aux_ld = p.aux_ld; e.aux_cs = p.aux_cs;
+    e.alpha = p.alpha; e.beta = p.beta;
+    e.accumulate = p.accumulate != 0;
+    e.aux_vec = p.aux_vec != 0;
+    return e;
+}
+
+// value = op(alpha * product + previous contents + bias): one element of the epilogue.
+__device__ __forceinline__ float epi_aux(float v, float a, const Epi& e) {
+    return e.op == 1 ? fmaf(e.beta, a, v) : v * (1.f - a * a);
+}
+
 __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, float* out_base,
                                                  long long ld, int row0, int M, int col0, int N, bool vec,
-                                                 const float* bias, bool accumulate, int lane) {
-    if (bias != nullptr) {
+                                                 const Epi& e, int lane) {
+    if (e.alpha != 1.f) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+    }
+    if (e.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            if (col0 + j < N) v[j] += __ldg(bias + col0 + j);
+            if (col0 + j < N) v[j] += __ldg(e.bias + col0 + j);
     }
     // lane's row -> 8 chunks of 16 bytes, chunk index XOR (row & 7): conflict-free both ways
 #pragma unroll
@@ -135,16 +178,31 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
         if (grow < M && col < N) {
             float* dst = out_base + (long long)grow * ld + col;
             if (vec && col + 3 < N) {
-                if (accumulate) {
+                if (e.accumulate) {
                     const float4 o = *reinterpret_cast<const float4*>(dst);
                     x[i].x += o.x; x[i].y += o.y; x[i].z += o.z; x[i].w += o.w;
                 }
+                if (e.op != 0) {
+                    const float* ap = e.aux + (long long)grow * e.aux_ld + (long long)col * e.aux_cs;
+                    float4 a;
+                    if (e.aux_vec) {
+                        a = *reinterpret_cast<const float4*>(ap);
+                    } else {
+                        a = make_float4(ap[0], ap[e.aux_cs], ap[2 * e.aux_cs], ap[3 * e.aux_cs]);
+                    }
+                    x[i].x = epi_aux(x[i].x, a.x, e); x[i].y = epi_aux(x[i].y, a.y, e);
+                    x[i].z = epi_aux(x[i].z, a.z, e); x[i].w = epi_aux(x[i].w, a.w, e);
+                }
                 *reinterpret_cast<float4*>(dst) = x[i];
             } else {
-                const float e[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+                const float el[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
                 for (int t = 0; t < 4; ++t)
-                    if (col + t < N) dst[t] = accumulate ? dst[t] + e[t] : e[t];
+                    if (col + t < N) {
+                        float val = e.accumulate ? dst[t] + el[t] : el[t];
+                        if (e.op != 0) val = epi_aux(val, e.aux[(long long)grow * e.aux_ld + (long long)(col + t) * e.aux_cs], e);
+                        dst[t] = val;
+                    }
             }
         }
     }
@@ -482,7 +540,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 vec = p.vec_ok != 0;
             }
             const float* bias = split_mode ? nullptr : p.bias;
-            const bool accumulate = !split_mode && p.accumulate != 0;
+            const Epi epi = split_mode ? plain_epi() : tile_epi(p, c);
             const int slab_col0 = c.n0 + slab * 128;
 
             constexpr int ACC_N = KC > 0 ? 128 : 1;  // fp32 promotion registers (unused without chains)
@@ -522,8 +580,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias,
                                                 lane, q == 0 && lane == 0, 2 + slab);
                             } else {
-                                store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
-                                                 accumulate, lane);
+                                store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, epi, lane);
                             }
                         }
                     }
@@ -546,8 +603,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
                                             q == 0 && lane == 0, 2 + slab);
                         else
-                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, bias,
-                                             accumulate, lane);
+                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, epi, lane);
                     }
                 }
             }
@@ -594,8 +650,14 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         }
                         float* dst = cbase + (long long)grow * p.ldc + col;
                         for (int e = 0; e < nv; ++e) {
+                            sum[e] *= p.alpha;
                             if (p.bias != nullptr) sum[e] += __ldg(p.bias + col + e);
                             if (p.accumulate) sum[e] += dst[e];
+                            if (p.aux_op != 0) {
+                                const float a = p.aux[c.i0 * p.aux_bs0 + c.i1 * p.aux_bs1 + (long long)grow * p.aux_ld +
+                                                      (long long)(col + e) * p.aux_cs];
+                                sum[e] = p.aux_op == 1 ? fmaf(p.beta, a, sum[e]) : sum[e] * (1.f - a * a);
+                            }
                         }
                         if (cvec && nv == 4) {
                             *reinterpret_cast<float4*>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
@@ -804,7 +866,6 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         const int q = warp & 3;            // TMEM lane quarter this warp may read
         const int slab = (warp - 2) >> 2;  // 128-column slab of the tile
         const bool vec = p.vec_ok != 0;
-        const bool accumulate = p.accumulate != 0;
         const bool use_tma = p.c_tma != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
         const uint32_t slab_tile_addr = smem_base + BIG_STAGES * BIG_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
@@ -812,6 +873,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
+            const Epi epi = tile_epi(p, c);
             bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
             if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
             if (!got) {
@@ -841,8 +903,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0 + h * 128, c.i1, c.i0, p.N,
                                                 p.bias, lane, q == 0 && lane == 0, 2 + slab);
                             else
-                                store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias,
-                                                 accumulate, lane);
+                                store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
                         }
                     }
                 }
@@ -1197,12 +1258,12 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         const int q = warp & 3;
         const int slab = (warp - 2) >> 2;
         const bool vec = p.vec_ok != 0;
-        const bool accumulate = p.accumulate != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
         int handoff = 0;
         bool ok = true;
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+            const Epi epi = tile_epi(p, c);
             const int row0 = c.m0 + 128 * (int)rank + q * 32;
             const int slab_col0 = c.n0 + slab * 128;
             float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
@@ -1242,8 +1303,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
-                        store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias, accumulate,
-                                         lane);
+                        store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
                     }
                 }
             }
@@ -1450,7 +1510,6 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         const int q = warp & 3;
         const int slab = (warp - 2) >> 2;
         const bool vec = p.vec_ok != 0;
-        const bool accumulate = p.accumulate != 0;
         const bool use_tma = p.c_tma != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
         const uint32_t slab_tile_addr = smem_base + S * DUO_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
@@ -1458,6 +1517,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
+            const Epi epi = tile_epi(p, c);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1u;
             bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
@@ -1489,8 +1549,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                             lane, q == 0 && lane == 0, 2 + slab);
                         else
-                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, p.bias, accumulate,
-                                             lane);
+                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
                     }
                 }
             }
@@ -1828,6 +1887,10 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: operand not readable by TMA (alignment / stride)");
         return -1;
     }
+    if (g.aux_op != 0 && !g.aux) {
+        seterr(err, errlen, "gemm_sm100: epilogue operand missing");
+        return -1;
+    }
     if (g.splits > 1 && (!g.partials || !g.counters)) {
         seterr(err, errlen, "gemm_sm100: split launch without scratch");
         return -1;
@@ -1869,6 +1932,18 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     }
     kp.C = g.C;
     kp.bias = g.bias;
+    kp.aux = g.aux_op ? g.aux : nullptr;
+    kp.aux_op = g.aux_op;
+    kp.aux_ld = g.aux_ld;
+    kp.aux_cs = g.aux_cs;
+    kp.aux_bs0 = g.aux_bs0;
+    kp.aux_bs1 = g.aux_bs1;
+    kp.aux_vec = (g.aux_op && g.aux_cs == 1 && (reinterpret_cast<uintptr_t>(g.aux) & 15u) == 0 && (g.aux_ld & 3) == 0 &&
+                  (g.o0 == 1 || (g.aux_bs0 & 3) == 0) && (g.o1 == 1 || (g.aux_bs1 & 3) == 0))
+                     ? 1
+                     : 0;
+    kp.alpha = g.alpha;
+    kp.beta = g.beta;
     kp.partials = g.partials;
     kp.counters = g.counters;
     kp.status = status_dev;
@@ -1889,7 +1964,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                     : 0;
     // Output map for the TMA-store epilogue: (N, M, o1, o0), boxes of 32 columns x 128 rows.
     kp.c_tma = 0;
-    if (kp.vec_ok && !g.accumulate && kp.splits == 1 && (!pairs || duo) && !((g.debug | g_debug_flags) & 256)) {
+    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo) &&
+        !((g.debug | g_debug_flags) & 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
         cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.o1, (cuuint64_t)g.o0};

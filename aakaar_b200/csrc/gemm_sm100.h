@@ -1,6 +1,7 @@
 // Host-side description of one batched fp32 GEMM for the sm_100a tcgen05 kernels.
 //
-//   D[o0, o1, m, n] (+)= sum_r sum_k A[o0, o1, r, m, k] * B[o0, o1, r, k, n]  (+ bias[n])
+//   D[o0, o1, m, n] = op( alpha * sum_r sum_k A[o0, o1, r, m, k] * B[o0, o1, r, k, n] (+ D) (+ bias[n]) )
+//   op: identity, `+ beta * X[o0, o1, m, n]` or `* (1 - X[o0, o1, m, n]^2)` with a second array X
 //
 // o0/o1 are output batch dims, r is a batch dim that is summed away (the broadcast-batch
 // reduction of a weight gradient). An operand that does not vary along a batch dim has
@@ -28,6 +29,13 @@ struct GemmDesc {
     int64_t ldc = 0, c_bs0 = 0, c_bs1 = 0;
     const float* bias = nullptr;  // optional row vector of N values added to every row
     int accumulate = 0;           // 1: C += result
+    float alpha = 1.f;            // scales the product
+    // Second epilogue operand X (shape of the output, own strides; aux_cs is its column stride):
+    // aux_op 1: result += beta * X; aux_op 2: result *= 1 - X^2 (gradient through a saved tanh output).
+    const float* aux = nullptr;
+    int aux_op = 0;
+    float beta = 0.f;
+    int64_t aux_ld = 0, aux_cs = 1, aux_bs0 = 0, aux_bs1 = 0;
     int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate). With terms == 3 the low parts are
                                   // derived in the kernel unless BOTH operands carry pre-split `lo` arrays
     // Split of the contraction across CTAs (weight gradients with few output tiles):
@@ -40,7 +48,8 @@ struct GemmDesc {
                     // bit 2 disables the folded one-box-per-tile maps of M/N-major operands,
                     // bit 3 the 256 x 256 tile kernel, bit 5 routes fp32-accurate products with in-kernel low parts through the CTA-pair kernel too,
                     // bit 9 disables the CTA-pair kernel altogether,
-                    // bit 7 skips the output stores (timing), bit 8 disables the TMA-store epilogue
+                    // bit 7 skips the output stores (timing), bit 8 disables the TMA-store epilogue,
+                    // bit 10 disables the TF32 CTA-pair kernel, bit 11 prefers it wherever it applies
 };
 
 // True when the operand can be read by TMA as it lies (16-byte aligned base, unit stride on one

@@ -126,6 +126,21 @@ AKR_API int akr_matmul_fwd(const akr_view* a, const akr_view* b, const akr_view*
 AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da_or_null,
                    akr_view* db_or_null, int mode, void* stream);
 
+/* Backward of C = A @ B where A = tanh(Z): returns the gradient with respect to Z,
+ *   dZ = (dC . B^T) * (1 - A^2)   (tanh_backward_kernel, src/elementwise_kernel.cu:517-547, folded into the
+ * epilogue of the dA product; A is read where it lies), and dB as akr_matmul_bwd. In the reference these are
+ * the matmul node's backward followed by the tanh node's backward (src/bindings.cpp:777-806): one full pass
+ * over the activation gradient less. dz has the shape of a; either output may be NULL. */
+AKR_API int akr_matmul_bwd_tanh(const akr_view* a_tanh_out, const akr_view* b, const akr_view* dc,
+                                akr_view* dz_or_null, akr_view* db_or_null, int mode, void* stream);
+
+/* C = alpha * (A @ B) + beta * D in one launch (D: an array of C's shape with any strides, may be NULL when
+ * beta == 0). The two products of the Newton-Schulz iteration of the Muon optimizer
+ * (aakaar/optim.py:533-542: `B = b * A + c * (A @ A)`, `X = a * X + X @ B`), which the reference runs as a
+ * matmul plus two or three elementwise passes. D must not overlap C unless it is C itself. */
+AKR_API int akr_matmul_fwd_axpby(const akr_view* a, const akr_view* b, float alpha, float beta,
+                                 const akr_view* d_or_null, akr_view* c, int mode, void* stream);
+
 /* 2-D products the reference exports separately:
  *   run_cublas_matmul_a_bt, src/matmul_kernel.cu:347-373: C(m,n) = A(m,k) . B(n,k)^T
  *   run_cublas_matmul_at_b, src/matmul_kernel.cu:378-402: C(m,n) = A(k,m)^T . B(k,n) */
@@ -189,7 +204,8 @@ AKR_API int akr_event_destroy(void* event);
  * flag 16 makes the load warp never signal its stages, so that every waiter gives up; flags 1 / 2 / 4 / 8
  * are timing diagnostics (skip loads, skip MMAs, no folded maps, no 256x256 tiles; results invalid with 1 / 2);
  * flag 32 routes every fp32-accurate product through the CTA-pair (cta_group::2) kernel (by default only large
- * pre-split ones use it), flag 512 disables that kernel.
+ * pre-split ones use it), flag 512 disables that kernel; flag 1024 disables the TF32 CTA-pair kernel, flag 2048
+ * prefers it wherever it applies.
  * akr_debug_configure(0, 0) restores normal operation. */
 AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
 

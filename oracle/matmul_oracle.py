@@ -15,6 +15,10 @@ Every function follows one piece of the reference (paths relative to the referen
   src/bindings.cpp:1726-1759 (2-D fast path, otherwise transposed copies + forward + reduction).
 * ``reduce_grad_to_shape``               - src/bindings.cpp:1467-1503.
 * ``linear_forward``                     - aakaar/nn.py:5-18 (y = x @ W + b, W stored (in, out)).
+* ``matmul_backward_tanh``               - matmul node backward followed by the tanh node backward,
+  src/bindings.cpp:1726-1759 then :777-806 (``g * (1 - t^2)``, src/cpu_kernel.cpp:500-514).
+* ``matmul_axpby`` / ``newton_schulz``   - the Newton-Schulz chain of the Muon optimizer,
+  aakaar/optim.py:533-542 (matmul + scalar multiply + add, composed as the reference composes them).
 * ``tanh`` / ``mse_loss`` / ``sgd_step`` - src/cpu_kernel.cpp:484-514, aakaar/__init__.py:222-224,
   src/optim_kernels_cpu.cpp:7-28 (support ops of the Linear training step).
 
@@ -40,6 +44,9 @@ __all__ = [
     "matmul_a_bt",
     "matmul_at_b",
     "matmul_backward",
+    "matmul_backward_tanh",
+    "matmul_axpby",
+    "newton_schulz",
     "reduce_grad_to_shape",
     "linear_forward",
     "tanh",
@@ -192,6 +199,35 @@ def matmul_backward(a, b, grad_out, acc=np.float32):
     db_full = matmul_forward(aT, grad_out, acc)
     return (reduce_grad_to_shape(da_full, a.shape, 2, acc),
             reduce_grad_to_shape(db_full, b.shape, 2, acc))
+
+
+def matmul_backward_tanh(a_tanh, b, grad_out, acc=np.float32):
+    """(dZ, dB) for C = tanh(Z) @ B, given A = tanh(Z): the matmul backward, then dZ = dA * (1 - A^2)."""
+    da, db = matmul_backward(a_tanh, b, grad_out, acc)
+    a = np.asarray(a_tanh).astype(acc, copy=False)
+    return (da.astype(acc, copy=False) * (1.0 - a * a)).astype(np.float32), db
+
+
+def matmul_axpby(a, b, alpha, beta, d, acc=np.float32):
+    """alpha * (a @ b) + beta * d, the shape of one Newton-Schulz line (``b * A + c * (A @ A)``)."""
+    prod = matmul_forward(np.ascontiguousarray(a), np.ascontiguousarray(b), acc).astype(acc, copy=False)
+    out = acc(alpha) * prod
+    if d is not None and beta != 0:
+        out = out + acc(beta) * np.asarray(d).astype(acc, copy=False)
+    return out.astype(np.float32)
+
+
+def newton_schulz(G, steps, acc=np.float32):
+    """Muon._newton_schulz_orthogonalize: X = G / (|G|_F + 1e-7); then `steps` times
+    A = X^T X, B = b A + c A A, X = a X + X B."""
+    G = np.asarray(G).astype(acc, copy=False)
+    X = G / (np.sqrt((G * G).sum(dtype=acc)) + acc(1e-7))
+    a, b, c = 3.4445, -4.7750, 2.0315
+    for _ in range(steps):
+        A = X.T @ X
+        B = acc(b) * A + acc(c) * (A @ A)
+        X = acc(a) * X + X @ B
+    return X.astype(np.float32)
 
 
 # ---------------------------------------------------------------- Linear training step support

@@ -125,6 +125,22 @@ ai64 = g.integers(-2 ** 40, 2 ** 40, (2, 5, 7)).astype(np.int64)
 bi64 = g.integers(-2 ** 20, 2 ** 20, (7, 4)).astype(np.int64)
 out["i64_c"] = ref.cpu_matmul(ref.from_numpy(ai64, "cpu", False), ref.from_numpy(bi64, "cpu", False)).to_numpy()
 
+# 8c. backward through tanh then matmul (the two autograd nodes the fused epilogue replaces), and the
+#     Newton-Schulz chain of Muon composed from the reference's own tensor ops (aakaar/optim.py:533-542)
+z, b, dc = normal((13, 9), 41), uniform((9, 7), 42), normal((13, 7), 43)
+Z, B = T(z, True), T(b, True)
+Cm = ref.cpu_matmul(Z.tanh(), B)
+Cm.backward(T(dc))
+out["tanhmm_dz"], out["tanhmm_db"] = Z.grad.to_numpy(), B.grad.to_numpy()
+g0 = normal((24, 40), 44)
+G0 = T(g0)
+X = G0 / ((G0 * G0).sum().sqrt() + 1e-7)
+for _ in range(5):
+    A_ = X.transpose(0, 1).contiguous() @ X
+    B_ = -4.7750 * A_ + 2.0315 * (A_ @ A_)
+    X = 3.4445 * X + X @ B_
+out["muon_ns5"] = X.to_numpy()
+
 # 9. error behaviour of the reference (messages the C ABI reproduces)
 errs = {}
 def err_of(fn):

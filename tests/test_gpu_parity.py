@@ -507,3 +507,67 @@ def test_typed_forward_through_abi(dt):
         np.testing.assert_array_equal(got, want)
     with pytest.raises(RuntimeError, match="share one dtype"):
         cabi.matmul_typed(a, bt.astype(np.float32))
+
+
+# ------------------------------------------------------------------ fused epilogues
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_backward_through_tanh_in_the_epilogue(mode, tol):
+    # dZ = (dC B^T) * (1 - A^2) with A = tanh(Z): 2-D, ragged, a transposed A view, a broadcast-batch A
+    # (reduced first, multiplied once), and a shape that takes the split-contraction path
+    cases = [((200, 96), (96, 72), False), ((130, 257), (257, 33), False), ((96, 200), (96, 72), True),
+             ((1, 40, 24), (5, 24, 56), False), ((3, 2, 48, 40), (2, 40, 64), False), ((64, 2048), (2048, 16), False)]
+    for sa, sb, transposed in cases:
+        z = normal(sa, 7)
+        a = np.tanh(z).astype(np.float32)
+        A = dev(a)
+        if transposed:
+            A = A.transpose(0, 1)
+            a = np.ascontiguousarray(a.T)
+        b = uniform(sb, 8)
+        batch, M, K, N = mo.plan_nd_matmul(a.shape, sb)
+        dc = normal(tuple(batch) + (M, N), 9)
+        dz, db = cabi.matmul_bwd_tanh(A, dev(b), dev(dc), mode=mode)
+        rdz, rdb = mo.matmul_backward_tanh(a, b, dc, np.float64)
+        assert dz.shape == a.shape and db.shape == sb
+        assert rel_fro(dz.to_numpy(), rdz) < tol, (sa, sb)
+        assert rel_fro(db.to_numpy(), rdb) < tol, (sa, sb)
+    # only dZ
+    dz, db = cabi.matmul_bwd_tanh(dev(a), dev(b), dev(dc), mode=mode, need_db=False)
+    assert db is None and rel_fro(dz.to_numpy(), rdz) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_alpha_beta_epilogue(mode, tol):
+    # C = alpha * (A @ B) + beta * D: small, ragged, batched with a broadcast addend view, CTA-pair sized
+    for sa, sb in [((64, 64), (64, 64)), ((129, 70), (70, 257)), ((2, 3, 40, 24), (3, 24, 56)), ((1500, 1100), (1100, 1700))]:
+        a, b = uniform(sa, 21), uniform(sb, 22)
+        batch, M, K, N = mo.plan_nd_matmul(sa, sb)
+        d = normal(tuple(batch) + (M, N), 23)
+        got = cabi.matmul_axpby(dev(a), dev(b), 2.0315, -4.775, dev(d), mode=mode).to_numpy()
+        assert rel_fro(got, mo.matmul_axpby(a, b, 2.0315, -4.775, d, np.float64)) < tol, (sa, sb)
+        got = cabi.matmul_axpby(dev(a), dev(b), 0.5, 0.0, None, mode=mode).to_numpy()
+        assert rel_fro(got, mo.matmul_axpby(a, b, 0.5, 0.0, None, np.float64)) < tol
+    # addend given as a transposed view (column stride != 1)
+    a, b, dt = uniform((96, 40), 24), uniform((40, 72), 25), normal((72, 96), 26)
+    got = cabi.matmul_axpby(dev(a), dev(b), 1.0, 3.4445, dev(dt).transpose(0, 1), mode=mode).to_numpy()
+    assert rel_fro(got, mo.matmul_axpby(a, b, 1.0, 3.4445, np.ascontiguousarray(dt.T), np.float64)) < tol
+    with pytest.raises(cabi.AkrError):
+        cabi.matmul_axpby(dev(a), dev(b), 1.0, 1.0, dev(dt), mode=mode)   # wrong addend shape
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_newton_schulz_chain_with_fused_epilogues(mode, tol):
+    # Muon's orthogonalisation (aakaar/optim.py:533-542), three launches per iteration: X^T X through a
+    # transposed view, b A + c A A and a X + X B through the alpha / beta epilogue
+    g = normal((192, 320), 31)
+    X = dev((g / (np.sqrt((g.astype(np.float64) ** 2).sum()) + 1e-7)).astype(np.float32))
+    a_, b_, c_ = 3.4445, -4.7750, 2.0315
+    for _ in range(5):
+        A = cabi.matmul_fwd(X.transpose(0, 1), X, mode=mode)
+        B = cabi.matmul_axpby(A, A, c_, b_, A, mode=mode)
+        X = cabi.matmul_axpby(X, B, 1.0, a_, X, mode=mode)
+    ref = mo.newton_schulz(g, 5, np.float64)
+    assert rel_fro(X.to_numpy(), ref) < 20 * tol    # five chained iterations amplify the rounding of each product
+    s = np.linalg.svd(X.to_numpy().astype(np.float64), compute_uv=False)
+    assert 0.5 < s.min() and s.max() < 1.5          # singular values pushed towards 1

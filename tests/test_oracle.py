@@ -121,3 +121,12 @@ def test_typed_forward_matches_reference():
     ai64 = g.integers(-2 ** 40, 2 ** 40, (2, 5, 7)).astype(np.int64)
     bi64 = g.integers(-2 ** 20, 2 ** 20, (7, 4)).astype(np.int64)
     np.testing.assert_array_equal(mo.matmul_forward_typed(ai64, bi64), G["i64_c"])
+
+
+def test_tanh_backward_and_newton_schulz_match_reference():
+    z, b, dc = normal((13, 9), 41), uniform((9, 7), 42), normal((13, 7), 43)
+    dz, db = mo.matmul_backward_tanh(np.tanh(z).astype(np.float32), b, dc)
+    assert rel_fro(dz, G["tanhmm_dz"]) < 2e-6 and rel_fro(db, G["tanhmm_db"]) < 2e-6
+    assert rel_fro(mo.newton_schulz(normal((24, 40), 44), 5), G["muon_ns5"]) < 1e-5
+    a, b2, d = uniform((5, 4), 1), uniform((4, 6), 2), normal((5, 6), 3)
+    np.testing.assert_allclose(mo.matmul_axpby(a, b2, 2.0, -3.0, d), 2.0 * (a @ b2) - 3.0 * d, rtol=1e-5, atol=1e-6)
