@@ -332,6 +332,9 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     // The kernel takes the two innermost output dims and the innermost summed dim; any further
     // dims are looped here (summed ones as accumulating launches).
     const size_t ko = std::min<size_t>(no, 2), kr = std::min<size_t>(nr, 1);
+    // The fp32-accurate kernels have no second-operand epilogue: there the operand is applied by an
+    // elementwise pass over the finished output (what the reference does in every mode).
+    const bool aux_after = p.aux_op != 0 && p.mode == AKR_MODE_FP32;
     GemmDesc g;
     g.M = (int)p.M;
     g.N = (int)p.N;
@@ -342,7 +345,7 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     g.bias = p.bias;
     g.alpha = p.alpha;
     g.beta = p.beta;
-    g.aux_op = p.aux_op;
+    g.aux_op = aux_after ? 0 : p.aux_op;
     g.aux_ld = p.aux_rs;
     g.aux_cs = p.aux_cs;
     g.terms = p.mode == AKR_MODE_FP32 ? 3 : 1;
@@ -419,11 +422,33 @@ int run_problem(const Problem& p, cudaStream_t stream) {
             const bool last = ir + 1 == n_rouser;
             if (!last) gi.bias = nullptr;
             gi.aux_op = last ? g.aux_op : 0;
-            gi.aux = (last && p.aux) ? p.aux + xo : nullptr;
+            gi.aux = (last && p.aux && !aux_after) ? p.aux + xo : nullptr;
             const int lrc = gemm_sm100_launch(gi, stream, status, err, sizeof(err));
             if (lrc != 0) return fail(lrc == -1 ? AKR_ERR_INVALID : AKR_ERR_CUDA, err);
             st->launches++;
         }
+    }
+    if (aux_after) {
+        EpiApply ea;
+        ea.c = p.C;
+        ea.x = p.aux;
+        for (int i = 0; i < p.nb; ++i) {
+            if (p.bshape[i] == 1 || p.c_bs[i] == 0) continue;  // extent 1, or summed away
+            ea.bshape[ea.nb] = p.bshape[i];
+            ea.c_bs[ea.nb] = p.c_bs[i];
+            ea.x_bs[ea.nb] = p.aux_bs[i];
+            ++ea.nb;
+        }
+        ea.M = p.M;
+        ea.N = p.N;
+        ea.c_rs = p.c_rs;
+        ea.x_rs = p.aux_rs;
+        ea.x_cs = p.aux_cs;
+        ea.op = p.aux_op;
+        ea.beta = p.beta;
+        cudaError_t e = launch_epi_apply(ea, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "epilogue pass launch");
+        st->launches++;
     }
     return AKR_OK;
 }

@@ -360,7 +360,7 @@ __global__ void mse_partial_kernel(const float* __restrict__ p, const float* __r
     float acc = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float d = p[i] - t[i];
+        const float d = t ? p[i] - t[i] : p[i];
         acc = fmaf(d, d, acc);
     }
     const float s = block_sum(acc);
@@ -591,6 +591,32 @@ cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, floa
     mse_final_kernel<<<1, kThreads, 0, s>>>(partials, blocks, (float)n, loss_out);
     return cudaGetLastError();
 }
+__global__ void epi_apply_kernel(EpiApply a, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t n = (int64_t)(i % (size_t)a.N);
+        size_t r = i / (size_t)a.N;
+        const int64_t m = (int64_t)(r % (size_t)a.M);
+        r /= (size_t)a.M;
+        int64_t co = m * a.c_rs + n, xo = m * a.x_rs + n * a.x_cs;
+        for (int d = a.nb - 1; d >= 0; --d) {
+            const int64_t idx = (int64_t)(r % (size_t)a.bshape[d]);
+            r /= (size_t)a.bshape[d];
+            co += idx * a.c_bs[d];
+            xo += idx * a.x_bs[d];
+        }
+        const float x = a.x[xo], c = a.c[co];
+        a.c[co] = a.op == 1 ? fmaf(a.beta, x, c) : c * (1.f - x * x);
+    }
+}
+cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
+    size_t total = (size_t)a.M * (size_t)a.N;
+    for (int d = 0; d < a.nb; ++d) total *= (size_t)a.bshape[d];
+    if (total == 0) return cudaSuccess;
+    epi_apply_kernel<<<grid_for(total), kThreads, 0, s>>>(a, total);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
                            cudaStream_t s) {
     if (n == 0) return cudaSuccess;

@@ -55,6 +55,19 @@ cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float*
 size_t colsum_partial_floats(int64_t rows, int64_t cols);
 cudaError_t launch_colsum(const float* g, int64_t rows, int64_t cols, float* out, float* partials, cudaStream_t s);
 
+// In-place second-operand epilogue over a strided batched matrix, for products whose kernel has no such
+// epilogue (the fp32-accurate mode): op 1: c += beta * x, op 2: c *= 1 - x^2. Batch dims as in StridedView.
+struct EpiApply {
+    float* c = nullptr;
+    const float* x = nullptr;
+    int nb = 0;
+    int64_t bshape[kMaxDims] = {0}, c_bs[kMaxDims] = {0}, x_bs[kMaxDims] = {0};
+    int64_t M = 0, N = 0, c_rs = 0, x_rs = 0, x_cs = 1;
+    int op = 0;
+    float beta = 0.f;
+};
+cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s);
+
 cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s);
 cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s);
 cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s);

@@ -130,6 +130,15 @@ __device__ __forceinline__ Epi plain_epi() {
     return e;
 }
 
+// For the kernels without the second-operand path: scaling, bias and `C +=` only.
+__device__ __forceinline__ Epi lean_epi(const KernelParams& p) {
+    Epi e = plain_epi();
+    e.bias = p.bias;
+    e.alpha = p.alpha;
+    e.accumulate = p.accumulate != 0;
+    return e;
+}
+
 __device__ __forceinline__ Epi tile_epi(const KernelParams& p, const Tile& c) {
     Epi e;
     e.bias = p.bias;
@@ -147,6 +156,9 @@ __device__ __forceinline__ float epi_aux(float v, float a, const Epi& e) {
     return e.op == 1 ? fmaf(e.beta, a, v) : v * (1.f - a * a);
 }
 
+// AUX = false (the fp32-accurate kernels, which have no registers to spare next to their promotion
+// accumulators): the second-operand path is compiled out; the host applies it in a separate pass.
+template <bool AUX>
 __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, float* out_base,
                                                  long long ld, int row0, int M, int col0, int N, bool vec,
                                                  const Epi& e, int lane) {
@@ -164,45 +176,84 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
     for (int j = 0; j < 8; ++j)
         stage[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     __syncwarp();
+    // Phase 2: this lane owns rows row0 + 4 i + (lane >> 3), four columns from `col`.
     const int c4 = lane & 7;
     const int col = col0 + 4 * c4;
-    float4 x[8];
+    const int rsub = lane >> 3;
+    const bool fast = vec && col + 3 < N;
+    if (!AUX || (e.op == 0 && !e.accumulate)) {
+        float4 x[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // all eight reads in flight before the first global store
-        const int r = 4 * i + (lane >> 3);
-        x[i] = stage[r * 8 + (c4 ^ (r & 7))];
-    }
+        for (int i = 0; i < 8; ++i) {  // all eight reads in flight before the first global store
+            const int r = 4 * i + rsub;
+            x[i] = stage[r * 8 + (c4 ^ (r & 7))];
+        }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int grow = row0 + 4 * i + (lane >> 3);
-        if (grow < M && col < N) {
-            float* dst = out_base + (long long)grow * ld + col;
-            if (vec && col + 3 < N) {
-                if (e.accumulate) {
-                    const float4 o = *reinterpret_cast<const float4*>(dst);
-                    x[i].x += o.x; x[i].y += o.y; x[i].z += o.z; x[i].w += o.w;
+        for (int i = 0; i < 8; ++i) {
+            const int grow = row0 + 4 * i + rsub;
+            if (grow < M && col < N) {
+                float* dst = out_base + (long long)grow * ld + col;
+                if (fast) {
+                    if (!AUX && e.accumulate) {
+                        const float4 o = *reinterpret_cast<const float4*>(dst);
+                        x[i].x += o.x; x[i].y += o.y; x[i].z += o.z; x[i].w += o.w;
+                    }
+                    *reinterpret_cast<float4*>(dst) = x[i];
+                } else {
+                    const float el[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                        if (col + t < N) dst[t] = (!AUX && e.accumulate) ? dst[t] + el[t] : el[t];
                 }
-                if (e.op != 0) {
-                    const float* ap = e.aux + (long long)grow * e.aux_ld + (long long)col * e.aux_cs;
-                    float4 a;
-                    if (e.aux_vec) {
-                        a = *reinterpret_cast<const float4*>(ap);
+            }
+        }
+    } else {
+        // With a second operand and / or `C +=`: four rows at a time, their global loads issued together
+        // ahead of the first use (one load per row followed by its use and store would be eight serial
+        // round trips per block).
+        const bool aux_fast = e.op != 0 && fast && e.aux_vec;
+        const bool acc_fast = e.accumulate && fast;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            float4 a[4], o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int grow = row0 + 4 * (4 * h + i) + rsub;
+                if (aux_fast && grow < M) a[i] = *reinterpret_cast<const float4*>(e.aux + (long long)grow * e.aux_ld + col);
+                if (acc_fast && grow < M) o[i] = *reinterpret_cast<const float4*>(out_base + (long long)grow * ld + col);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * (4 * h + i) + rsub;
+                const int grow = row0 + r;
+                float4 x = stage[r * 8 + (c4 ^ (r & 7))];
+                if (grow < M && col < N) {
+                    float* dst = out_base + (long long)grow * ld + col;
+                    if (fast) {
+                        if (e.accumulate) {
+                            x.x += o[i].x; x.y += o[i].y; x.z += o[i].z; x.w += o[i].w;
+                        }
+                        if (e.op != 0) {
+                            if (!aux_fast) {
+                                const float* ap = e.aux + (long long)grow * e.aux_ld + (long long)col * e.aux_cs;
+                                a[i] = make_float4(ap[0], ap[e.aux_cs], ap[2 * e.aux_cs], ap[3 * e.aux_cs]);
+                            }
+                            x.x = epi_aux(x.x, a[i].x, e); x.y = epi_aux(x.y, a[i].y, e);
+                            x.z = epi_aux(x.z, a[i].z, e); x.w = epi_aux(x.w, a[i].w, e);
+                        }
+                        *reinterpret_cast<float4*>(dst) = x;
                     } else {
-                        a = make_float4(ap[0], ap[e.aux_cs], ap[2 * e.aux_cs], ap[3 * e.aux_cs]);
-                    }
-                    x[i].x = epi_aux(x[i].x, a.x, e); x[i].y = epi_aux(x[i].y, a.y, e);
-                    x[i].z = epi_aux(x[i].z, a.z, e); x[i].w = epi_aux(x[i].w, a.w, e);
-                }
-                *reinterpret_cast<float4*>(dst) = x[i];
-            } else {
-                const float el[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+                        const float el[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                for (int t = 0; t < 4; ++t)
-                    if (col + t < N) {
-                        float val = e.accumulate ? dst[t] + el[t] : el[t];
-                        if (e.op != 0) val = epi_aux(val, e.aux[(long long)grow * e.aux_ld + (long long)(col + t) * e.aux_cs], e);
-                        dst[t] = val;
+                        for (int t = 0; t < 4; ++t)
+                            if (col + t < N) {
+                                float val = e.accumulate ? dst[t] + el[t] : el[t];
+                                if (e.op != 0)
+                                    val = epi_aux(val, e.aux[(long long)grow * e.aux_ld + (long long)(col + t) * e.aux_cs], e);
+                                dst[t] = val;
+                            }
                     }
+                }
             }
         }
     }
@@ -540,7 +591,6 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 vec = p.vec_ok != 0;
             }
             const float* bias = split_mode ? nullptr : p.bias;
-            const Epi epi = split_mode ? plain_epi() : tile_epi(p, c);
             const int slab_col0 = c.n0 + slab * 128;
 
             constexpr int ACC_N = KC > 0 ? 128 : 1;  // fp32 promotion registers (unused without chains)
@@ -580,7 +630,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias,
                                                 lane, q == 0 && lane == 0, 2 + slab);
                             } else {
-                                store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, epi, lane);
+                                store_block_warp<TERMS == 1>(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec,
+                                                             split_mode ? plain_epi() : (TERMS == 1 ? tile_epi(p, c) : lean_epi(p)), lane);
                             }
                         }
                     }
@@ -603,7 +654,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
                                             q == 0 && lane == 0, 2 + slab);
                         else
-                            store_block_warp(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, epi, lane);
+                            store_block_warp<TERMS == 1>(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec,
+                                                         split_mode ? plain_epi() : (TERMS == 1 ? tile_epi(p, c) : lean_epi(p)), lane);
                     }
                 }
             }
@@ -653,7 +705,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             sum[e] *= p.alpha;
                             if (p.bias != nullptr) sum[e] += __ldg(p.bias + col + e);
                             if (p.accumulate) sum[e] += dst[e];
-                            if (p.aux_op != 0) {
+                            if (TERMS == 1 && p.aux_op != 0) {
                                 const float a = p.aux[c.i0 * p.aux_bs0 + c.i1 * p.aux_bs1 + (long long)grow * p.aux_ld +
                                                       (long long)(col + e) * p.aux_cs];
                                 sum[e] = p.aux_op == 1 ? fmaf(p.beta, a, sum[e]) : sum[e] * (1.f - a * a);
@@ -903,7 +955,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0 + h * 128, c.i1, c.i0, p.N,
                                                 p.bias, lane, q == 0 && lane == 0, 2 + slab);
                             else
-                                store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
+                                store_block_warp<true>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
                         }
                     }
                 }
@@ -1263,7 +1315,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
-            const Epi epi = tile_epi(p, c);
             const int row0 = c.m0 + 128 * (int)rank + q * 32;
             const int slab_col0 = c.n0 + slab * 128;
             float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
@@ -1303,7 +1354,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
-                        store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
+                        store_block_warp<false>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, lean_epi(p), lane);
                     }
                 }
             }
@@ -1549,7 +1600,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                             lane, q == 0 && lane == 0, 2 + slab);
                         else
-                            store_block_warp(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
+                            store_block_warp<true>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
                     }
                 }
             }
@@ -1887,8 +1938,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: operand not readable by TMA (alignment / stride)");
         return -1;
     }
-    if (g.aux_op != 0 && !g.aux) {
-        seterr(err, errlen, "gemm_sm100: epilogue operand missing");
+    if (g.aux_op != 0 && (!g.aux || g.terms != 1)) {
+        seterr(err, errlen, "gemm_sm100: second epilogue operand missing, or requested in the fp32-accurate mode");
         return -1;
     }
     if (g.splits > 1 && (!g.partials || !g.counters)) {

@@ -227,6 +227,8 @@ TensorPtr op_sum_all(const TensorPtr& t) {
 // ------------------------------------------------------------------ matmul
 
 int g_matmul_mode_override = AKR_MODE_GLOBAL;
+// Backward fusion across two autograd nodes (tanh' into the epilogue of the next layer's dA product).
+bool g_fuse_backward = true;
 
 // dispatch_matmul of the reference (src/bindings.cpp:1686-1764): forward product plus the autograd
 // node. The backward closure calls the fused backward on the original strided operands: no
@@ -268,7 +270,7 @@ TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr
     if (g_grad_enabled && (a->requires_grad || b->requires_grad || bias_grad)) {
         std::vector<TensorPtr> inputs{a, b};
         if (bias) inputs.push_back(bias);
-        attach(out, bias ? "linear" : "matmul", inputs, [a, b, bias, mode](TensorPtr g) {
+        auto bw = [a, b, bias, mode](TensorPtr g, bool a_is_tanh) {
             require_cuda(g, "matmul backward");
             TensorPtr da, db, dbias;
             if (a->requires_grad) da = make_cuda(a->shape);
@@ -278,19 +280,55 @@ TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr
             if (da) vda = da->view();
             if (db) vdb = db->view();
             if (da || db)
-                check(akr_matmul_bwd(&va, &vb, &vg, da ? &vda : nullptr, db ? &vdb : nullptr, mode, nullptr));
+                check((a_is_tanh ? akr_matmul_bwd_tanh : akr_matmul_bwd)(&va, &vb, &vg, da ? &vda : nullptr,
+                                                                         db ? &vdb : nullptr, mode, nullptr));
             std::vector<TensorPtr> grads{da, db};
             if (bias) {
                 if (bias->requires_grad) dbias = op_sum_to(g, bias->shape);
                 grads.push_back(dbias);
             }
             return grads;
-        });
+        };
+        attach(out, bias ? "linear" : "matmul", inputs, [bw](TensorPtr g) { return bw(g, false); });
+        out->grad_fn->backward_through_tanh = [bw](TensorPtr g) { return bw(g, true); };
     }
     return out;
 }
 
 TensorPtr op_matmul(const TensorPtr& a, const TensorPtr& b) { return op_matmul_bias(a, b, nullptr); }
+
+// alpha * (a @ b) + beta * d in one launch; no autograd (used inside optimizer steps).
+TensorPtr op_matmul_axpby(const TensorPtr& a, const TensorPtr& b, float alpha, float beta, const TensorPtr& d) {
+    require_cuda(a, "matmul_axpby");
+    require_f32(a, "matmul_axpby");
+    require_cuda(b, "matmul_axpby");
+    require_f32(b, "matmul_axpby");
+    if (g_grad_enabled && (a->requires_grad || b->requires_grad || (d && d->requires_grad)))
+        throw std::runtime_error("matmul_axpby records no gradient: call it under no_grad()");
+    akr_view va = a->view(), vb = b->view(), vd;
+    if (d) {
+        require_cuda(d, "matmul_axpby addend");
+        require_f32(d, "matmul_axpby addend");
+        vd = d->view();
+    }
+    int64_t oshape[AKR_MAX_DIMS + 2];
+    int32_t ond = 0;
+    check(akr_matmul_plan(&va, &vb, oshape, &ond));
+    auto out = make_cuda(std::vector<int64_t>(oshape, oshape + ond));
+    akr_view vo = out->view();
+    check(akr_matmul_fwd_axpby(&va, &vb, alpha, beta, d ? &vd : nullptr, &vo, g_matmul_mode_override, nullptr));
+    return out;
+}
+
+// mean of squares of a contiguous tensor as a 1-element tensor (no autograd).
+TensorPtr op_mean_square(const TensorPtr& t) {
+    require_cuda(t, "mean_square");
+    require_f32(t, "mean_square");
+    auto src = t->is_contiguous() ? t : op_contiguous(t);
+    auto out = make_cuda({1});
+    check(akr_mse_fwd(src->data, nullptr, out->data, (size_t)src->size, nullptr));
+    return out;
+}
 
 TensorPtr cpu_matmul_refused(const TensorPtr&, const TensorPtr&) {
     throw std::runtime_error(
@@ -366,6 +404,13 @@ void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_g
             stack.pop_back();
         }
     }
+    // How many nodes of this graph consume each tensor: a tanh output that feeds exactly one matmul can
+    // have its backward folded into that matmul's.
+    std::unordered_map<Tensor*, int> uses;
+    for (const TensorPtr& t : topo)
+        if (t->grad_fn)
+            for (const TensorPtr& inp : t->grad_fn->inputs)
+                if (inp) ++uses[inp.get()];
     const bool prev = g_grad_enabled;
     g_grad_enabled = false;  // gradient arithmetic is not itself recorded
     try {
@@ -386,9 +431,19 @@ void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_g
                         "intermediate results needed have already been freed. Pass retain_graph=True to "
                         "backward() the first time if you need to backward through this part of the graph "
                         "more than once.");
-                auto in_grads = t->grad_fn->backward_fn(g);
+                // tanh -> matmul: when this node's first input is a tanh output nobody else consumes, ask for
+                // the gradient with respect to the tanh's INPUT directly and skip the tanh node.
+                TensorPtr through;
+                if (g_fuse_backward && t->grad_fn->backward_through_tanh && !t->grad_fn->inputs.empty()) {
+                    const TensorPtr& h = t->grad_fn->inputs[0];
+                    if (h && h.get() != root.get() && h->requires_grad && h->grad_fn && !h->grad_fn->freed &&
+                        h->grad_fn->op_name == "tanh" && uses[h.get()] == 1 && !grads.count(h.get()) &&
+                        h->grad_fn->inputs.size() == 1 && h->grad_fn->inputs[0] && h->grad_fn->inputs[0]->requires_grad)
+                        through = h->grad_fn->inputs[0];
+                }
+                auto in_grads = through ? t->grad_fn->backward_through_tanh(g) : t->grad_fn->backward_fn(g);
                 for (size_t i = 0; i < t->grad_fn->inputs.size(); ++i) {
-                    const TensorPtr& inp = t->grad_fn->inputs[i];
+                    const TensorPtr& inp = (through && i == 0) ? through : t->grad_fn->inputs[i];
                     if (!inp || !inp->requires_grad || i >= in_grads.size() || !in_grads[i]) continue;
                     auto ex = grads.find(inp.get());
                     if (ex == grads.end()) grads[inp.get()] = in_grads[i];
@@ -663,9 +718,14 @@ PYBIND11_MODULE(_C, m) {
         .def("__matmul__", &op_matmul);
 
     m.def("_set_grad_enabled", [](bool e) { g_grad_enabled = e; });
+    m.def("_set_backward_fusion", [](bool e) { g_fuse_backward = e; },
+          "tanh' folded into the next matmul's dA epilogue during backward (default on)");
     m.def("_is_grad_enabled", []() { return g_grad_enabled; });
     m.def("cuda_matmul", &op_matmul, "tcgen05 GPU matrix multiplication (autograd-aware)");
     m.def("cpu_matmul", &cpu_matmul_refused, "not available: this build has no CPU matmul");
+    m.def("matmul_axpby", &op_matmul_axpby, py::arg("a"), py::arg("b"), py::arg("alpha") = 1.0f, py::arg("beta") = 0.0f,
+          py::arg("d") = nullptr, "alpha * (a @ b) + beta * d in one launch (no autograd)");
+    m.def("_mean_square", &op_mean_square);
     m.def("linear", &op_matmul_bias, py::arg("x"), py::arg("weight"), py::arg("bias") = nullptr,
           "x @ weight + bias with the bias add fused into the GEMM epilogue");
     m.def("from_numpy", &from_numpy, py::arg("array"), py::arg("device") = "cuda", py::arg("requires_grad") = false);

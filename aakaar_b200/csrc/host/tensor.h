@@ -21,6 +21,10 @@ using TensorPtr = std::shared_ptr<Tensor>;
 
 struct Node {
     std::function<std::vector<TensorPtr>(TensorPtr)> backward_fn;
+    // Set by matmul / linear nodes only: the same backward, except that input 0 is known to be the
+    // output of a tanh node and entry 0 of the result is the gradient with respect to THAT node's
+    // input (the tanh' factor is applied in the epilogue of the dA product).
+    std::function<std::vector<TensorPtr>(TensorPtr)> backward_through_tanh;
     std::vector<TensorPtr> inputs;
     std::string op_name;
     bool freed = false;

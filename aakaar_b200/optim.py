@@ -1,4 +1,8 @@
-"""``optim.SGD`` of the reference (aakaar/optim.py:5-50) on the fused update kernel."""
+"""``optim.SGD`` (aakaar/optim.py:5-50) and ``optim.Muon`` (aakaar/optim.py:516-568) of the reference.
+
+SGD runs on the fused update kernel. Muon's Newton-Schulz chain is three launches per iteration: the
+transposed operand of ``X^T X`` is read in place and the scalar multiplies and adds of
+``b * A + c * (A @ A)`` and ``a * X + X @ B`` are folded into the epilogue of their products."""
 from __future__ import annotations
 
 from . import _C, no_grad
@@ -29,6 +33,55 @@ class SGD:
                     self._velocity[i] = grad * 0.0
                 _C._sgd_step_fused(p, grad, self._velocity[i], self.lr, self.momentum, self.weight_decay,
                                    self.dampening, int(self.nesterov), int(self.momentum != 0), int(initialized))
+
+    def zero_grad(self):
+        for p in self.parameters:
+            p.zero_grad()
+
+
+class Muon:
+    """Momentum, then an orthogonalised update for 2-D parameters (Newton-Schulz iteration); other
+    parameters take the plain momentum update. Same arguments and arithmetic as the reference."""
+
+    def __init__(self, parameters, lr=0.02, momentum=0.95, ns_steps=5, weight_decay=0.0):
+        self.parameters = list(parameters)
+        self.lr = lr
+        self.momentum = momentum
+        self.ns_steps = ns_steps
+        self.weight_decay = weight_decay
+        self._buf = [None] * len(self.parameters)
+
+    @staticmethod
+    def _newton_schulz_orthogonalize(G, steps):
+        norm = (float(_C._mean_square(G).item()) * G.size) ** 0.5
+        X = G * (1.0 / (norm + 1e-7))
+        a, b, c = 3.4445, -4.7750, 2.0315
+        for _ in range(steps):
+            A = _C.cuda_matmul(X.transpose(0, 1), X)         # X^T X, the transposed view read in place
+            B = _C.matmul_axpby(A, A, c, b, A)               # b * A + c * (A @ A)
+            X = _C.matmul_axpby(X, B, 1.0, a, X)             # a * X + X @ B
+        return X
+
+    def step(self):
+        with no_grad():
+            for i, p in enumerate(self.parameters):
+                if p.grad is None:
+                    continue
+                grad = p.grad
+                if self.weight_decay != 0:
+                    grad = grad + p * self.weight_decay
+                if self._buf[i] is None:
+                    self._buf[i] = grad
+                else:
+                    self._buf[i] = self._buf[i] * self.momentum + grad * (1 - self.momentum)
+                if len(p.shape) == 2:
+                    update = self._newton_schulz_orthogonalize(self._buf[i], self.ns_steps)
+                else:
+                    update = self._buf[i]
+                if not p.is_contiguous():
+                    raise ValueError("Muon.step: parameters must be contiguous")
+                upd = update if update.is_contiguous() else update.contiguous()
+                _C._sgd_step_fused(p, upd, None, self.lr, 0.0, 0.0, 0.0, 0, 0, 0)   # p -= lr * update
 
     def zero_grad(self):
         for p in self.parameters:

@@ -638,8 +638,12 @@ def run_config(args):
         xn = normal((4096, 1024), 201, 1.0)
         tn = normal((4096, 1024), 202, 1.0)
         flop_step = 5 * 2 * 4096 * 1024 * 4096
-        for name, tf32 in (("tf32", True), ("fp32_3xtf32", False)):
+        # *_unfused: the tanh node's backward as its own elementwise pass (the reference's graph);
+        # default: folded into the epilogue of the second layer's dA product
+        for name, tf32, fused in (("tf32", True, True), ("fp32_3xtf32", False, True),
+                                  ("tf32_unfused", True, False), ("fp32_3xtf32_unfused", False, False)):
             ak.set_tf32(tf32)
+            ak._C._set_backward_fusion(fused)
             np.random.seed(203)
             l1, l2 = ak.nn.Linear(1024, 4096), ak.nn.Linear(4096, 1024)
             x, t = ak.from_numpy(xn, "cuda"), ak.from_numpy(tn, "cuda")
@@ -652,6 +656,7 @@ def run_config(args):
                 opt.step()
             ms, launches = timed(step, args.steps, args.warmup)
             results[name] = {"ms_per_step": ms, "tflops": flop_step / ms / 1e9, "gpu_launches_per_step": launches / args.steps}
+        ak._C._set_backward_fusion(True)
         ak.set_tf32(False)
         out.update({"workload": "MLP step: x[4096,1024] -> Linear 1024->4096 -> tanh -> Linear 4096->1024 -> MSE, backward, SGD",
                     "bound": "tensor", "flop_per_step": flop_step, "flop_note": "5 needed GEMMs (the reference runs 6)",

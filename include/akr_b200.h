@@ -228,6 +228,8 @@ AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream);
 AKR_API int akr_scale(const float* x, float alpha, float* y, size_t n, void* stream);
 AKR_API int akr_tanh_fwd(const float* x, float* y, size_t n, void* stream);
 AKR_API int akr_tanh_bwd(const float* grad, const float* y, float* dx, size_t n, void* stream);
+/* loss_out[0] = sum((pred - target)^2) / n; target == NULL gives the mean of squares of pred (the Frobenius
+ * norm the Muon optimizer divides by, aakaar/optim.py:534). */
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream);
 AKR_API int akr_mse_bwd(const float* pred, const float* target, const float* grad_scalar, float* dpred,
                 size_t n, void* stream);

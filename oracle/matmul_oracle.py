@@ -47,6 +47,7 @@ __all__ = [
     "matmul_backward_tanh",
     "matmul_axpby",
     "newton_schulz",
+    "muon_step",
     "reduce_grad_to_shape",
     "linear_forward",
     "tanh",
@@ -228,6 +229,16 @@ def newton_schulz(G, steps, acc=np.float32):
         B = acc(b) * A + acc(c) * (A @ A)
         X = acc(a) * X + X @ B
     return X.astype(np.float32)
+
+
+def muon_step(param, grad, buf, lr=0.02, momentum=0.95, ns_steps=5, weight_decay=0.0, acc=np.float32):
+    """One Muon.step for one parameter (aakaar/optim.py:544-564). Returns (new_param, new_buf)."""
+    p, g = np.asarray(param).astype(acc, copy=False), np.asarray(grad).astype(acc, copy=False)
+    if weight_decay != 0:
+        g = g + p * acc(weight_decay)
+    buf = g if buf is None else np.asarray(buf).astype(acc, copy=False) * acc(momentum) + g * acc(1 - momentum)
+    update = newton_schulz(buf, ns_steps, acc).astype(acc) if p.ndim == 2 else buf
+    return (p - update * acc(lr)).astype(np.float32), buf.astype(np.float32)
 
 
 # ---------------------------------------------------------------- Linear training step support

@@ -141,6 +141,21 @@ for _ in range(5):
     X = 3.4445 * X + X @ B_
 out["muon_ns5"] = X.to_numpy()
 
+# 8d. two Muon steps on one [24, 40] weight, composed from the reference's tensor ops exactly as
+#     aakaar/optim.py:544-564 composes them (lr 0.02, momentum 0.95, 5 Newton-Schulz steps, weight decay 0.01)
+P = T(uniform((24, 40), 45))
+buf = None
+for step_seed in (46, 47):
+    grad = T(normal((24, 40), step_seed)) + P * 0.01
+    buf = grad if buf is None else buf * 0.95 + grad * (1 - 0.95)
+    X = buf / ((buf * buf).sum().sqrt() + 1e-7)
+    for _ in range(5):
+        A_ = X.transpose(0, 1).contiguous() @ X
+        B_ = -4.7750 * A_ + 2.0315 * (A_ @ A_)
+        X = 3.4445 * X + X @ B_
+    P = P - X * 0.02
+out["muon_p2"] = P.to_numpy()
+
 # 9. error behaviour of the reference (messages the C ABI reproduces)
 errs = {}
 def err_of(fn):

@@ -179,3 +179,64 @@ def test_typed_forward_only_matmul(ak):
         ak.matmul(ak.from_numpy(a64, "cuda"), ak.from_numpy(b64.astype(np.float32), "cuda"))
     with pytest.raises(RuntimeError, match="only float32"):
         ak.from_numpy(a64, "cuda").tanh()
+
+
+def test_tanh_backward_folded_into_next_matmul(ak):
+    # Linear -> tanh -> Linear -> MSE: with the fusion the tanh node's backward runs inside the epilogue
+    # of the second layer's dA product (TF32 mode: one launch less; the fp32-accurate kernels apply it in a
+    # separate pass, same launch count), gradients unchanged
+    from aakaar_b200 import _C
+    x, tgt = normal((96, 40), 1), normal((96, 24), 2)
+    w1, b1 = uniform((40, 72), 3) * 0.2, uniform((1, 72), 4) * 0.1
+    w2, b2 = uniform((72, 24), 5) * 0.2, uniform((1, 24), 6) * 0.1
+    _, _, ref = mo.mlp_step(x, tgt, w1, b1, w2, b2, 0.0, np.float64)
+    for tf32, tol in ((False, TOL_FP32), (True, TOL_TF32)):
+        results = {}
+        ak.set_tf32(tf32)
+        try:
+            for fused in (False, True):
+                _C._set_backward_fusion(fused)
+                X, Tg = ak.from_numpy(x), ak.from_numpy(tgt)
+                P = [ak.from_numpy(v, requires_grad=True) for v in (w1, b1, w2, b2)]
+                h = _C.linear(X, P[0], P[1]).tanh()
+                loss = ak.mse_loss(_C.linear(h, P[2], P[3]), Tg)
+                ak.synchronize()
+                _C._launch_count(True)
+                loss.backward()
+                ak.synchronize()
+                results[fused] = ([p.grad.to_numpy() for p in P], _C._launch_count(True))
+        finally:
+            _C._set_backward_fusion(True)
+            ak.set_tf32(False)
+        (g0, n0), (g1, n1) = results[False], results[True]
+        assert n1 == n0 - (1 if tf32 else 0)
+        for got0, got1, key in zip(g0, g1, ("w1", "b1", "w2", "b2")):
+            assert rel_fro(got1, ref[key]) < tol, key
+            assert rel_fro(got1, got0) < tol, key
+    # a tanh output with a second consumer is not fused (its gradient has two contributions)
+    Z = ak.from_numpy(normal((16, 8), 7), requires_grad=True)
+    W = ak.from_numpy(uniform((8, 8), 8), requires_grad=True)
+    h = Z.tanh()
+    out = (_C.cuda_matmul(h, W) + h).sum()
+    out.backward()
+    zn, wn = normal((16, 8), 7).astype(np.float64), uniform((8, 8), 8).astype(np.float64)
+    hn = np.tanh(zn)
+    dz = (np.ones((16, 8)) @ wn.T + 1.0) * (1 - hn * hn)
+    assert rel_fro(Z.grad.to_numpy(), dz) < TOL_FP32
+
+
+def test_muon_optimizer_matches_reference(ak):
+    G, META = load_golden()
+    P = ak.from_numpy(uniform((24, 40), 45), requires_grad=True)
+    vec = ak.from_numpy(uniform((40,), 49), requires_grad=True)          # 1-D parameter: plain momentum update
+    opt = ak.optim.Muon([P, vec], lr=0.02, momentum=0.95, ns_steps=5, weight_decay=0.01)
+    v_ref, v_buf = uniform((40,), 49), None
+    for seed in (46, 47):
+        P.grad = ak.from_numpy(normal((24, 40), seed))
+        vec.grad = ak.from_numpy(normal((40,), seed + 10))
+        opt.step()
+        v_ref, v_buf = mo.muon_step(v_ref, normal((40,), seed + 10), v_buf, weight_decay=0.01)
+    assert rel_fro(P.to_numpy(), G["muon_p2"]) < TOL_FP32
+    assert rel_fro(vec.to_numpy(), v_ref) < TOL_FP32
+    opt.zero_grad()
+    assert P.grad is None

@@ -130,3 +130,10 @@ def test_tanh_backward_and_newton_schulz_match_reference():
     assert rel_fro(mo.newton_schulz(normal((24, 40), 44), 5), G["muon_ns5"]) < 1e-5
     a, b2, d = uniform((5, 4), 1), uniform((4, 6), 2), normal((5, 6), 3)
     np.testing.assert_allclose(mo.matmul_axpby(a, b2, 2.0, -3.0, d), 2.0 * (a @ b2) - 3.0 * d, rtol=1e-5, atol=1e-6)
+
+
+def test_muon_steps_match_reference():
+    p, buf = uniform((24, 40), 45), None
+    for seed in (46, 47):
+        p, buf = mo.muon_step(p, normal((24, 40), seed), buf, lr=0.02, momentum=0.95, ns_steps=5, weight_decay=0.01)
+    assert rel_fro(p, G["muon_p2"]) < 1e-5
