@@ -399,6 +399,14 @@ def run_gpu_arm(args):
         s_in, s_c, s_out = cabi.Stream(), cabi.Stream(), cabi.Stream()
         rows = N_SQ // nch
         mode = cabi.MODE_TF32
+        # One GPU: two sets of device buffers, so that step i's downloads overlap step i+1's uploads
+        # (PCIe is full duplex; within one step the dB download can only start when all uploads are in).
+        nsets = 2 if n_gpus == 1 else 1
+        sets = [(A, B, DC, Cd, DAd, DBd)]
+        if nsets == 2:
+            sets.append(tuple(cabi.DeviceArray((N_SQ, N_SQ)) for _ in range(6)))
+        in_free = [None] * nsets    # event: the GEMMs that read this set's inputs have finished
+        out_free = [None] * nsets   # event: this set's outputs have been downloaded
 
         def rowv(x, i):
             return x.as_strided((rows, N_SQ), (N_SQ, 1), offset=i * rows * N_SQ)
@@ -406,53 +414,68 @@ def run_gpu_arm(args):
         def colv(x, j):
             return x.as_strided((N_SQ, rows), (N_SQ, 1), offset=j * rows)
 
-        def step():
+        def step(k):
+            A_, B_, DC_, C_, DA_, DB_ = sets[k % nsets]
             ev = lambda: cabi.Event()   # noqa: E731
+            if in_free[k % nsets] is not None:
+                s_in.wait_event(in_free[k % nsets])
+            if out_free[k % nsets] is not None:
+                s_c.wait_event(out_free[k % nsets])
             e_b = ev()
-            cabi.h2d(B, hB, s_in); e_b.record(s_in)
+            cabi.h2d(B_, hB, s_in); e_b.record(s_in)
             e_a, e_dc = [], []
             for i in range(nch):
-                cabi.h2d(A, hA[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
+                cabi.h2d(A_, hA[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
                 e_a.append(ev().record(s_in))
             for i in range(nch):
-                cabi.h2d(DC, hDC[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
+                cabi.h2d(DC_, hDC[i * rows:(i + 1) * rows], s_in, i * rows * N_SQ)
                 e_dc.append(ev().record(s_in))
             s_c.wait_event(e_b)
             for i in range(nch):                                   # forward, chunk by chunk
                 s_c.wait_event(e_a[i])
-                cabi.matmul_fwd(rowv(A, i), B, mode=mode, out=rowv(Cd, i), stream=s_c)
+                cabi.matmul_fwd(rowv(A_, i), B_, mode=mode, out=rowv(C_, i), stream=s_c)
                 e = ev().record(s_c)
                 s_out.wait_event(e)
-                cabi.d2h(hC[i * rows:(i + 1) * rows], Cd, s_out, i * rows * N_SQ)
+                cabi.d2h(hC[i * rows:(i + 1) * rows], C_, s_out, i * rows * N_SQ)
             for i in range(nch):                                   # dA, chunk by chunk
                 s_c.wait_event(e_dc[i])
-                cabi.matmul_bwd(rowv(A, i), B, rowv(DC, i), mode=mode, need_da=True, need_db=False,
-                                da=rowv(DAd, i), stream=s_c)
+                cabi.matmul_bwd(rowv(A_, i), B_, rowv(DC_, i), mode=mode, need_da=True, need_db=False,
+                                da=rowv(DA_, i), stream=s_c)
                 e = ev().record(s_c)
                 s_out.wait_event(e)
-                cabi.d2h(hDA[i * rows:(i + 1) * rows], DAd, s_out, i * rows * N_SQ)
+                cabi.d2h(hDA[i * rows:(i + 1) * rows], DA_, s_out, i * rows * N_SQ)
             if n_gpus == 1:
                 for j in range(nch):                               # dB in row panels (k range j of A)
-                    cabi.matmul_bwd(colv(A, j), rowv(B, j), DC, mode=mode, need_da=False, need_db=True,
-                                    db=rowv(DBd, j), stream=s_c)
+                    cabi.matmul_bwd(colv(A_, j), rowv(B_, j), DC_, mode=mode, need_da=False, need_db=True,
+                                    db=rowv(DB_, j), stream=s_c)
                     e = ev().record(s_c)
                     s_out.wait_event(e)
-                    cabi.d2h(hDB[j * rows:(j + 1) * rows], DBd, s_out, j * rows * N_SQ)
+                    cabi.d2h(hDB[j * rows:(j + 1) * rows], DB_, s_out, j * rows * N_SQ)
+                in_free[k % nsets] = ev().record(s_c)
+                out_free[k % nsets] = ev().record(s_out)
+                if prev_done[0] is not None:
+                    prev_done[0].synchronize()     # at most two steps in flight: bounds the host's run-ahead
+                prev_done[0] = out_free[k % nsets]
             else:
-                cabi.matmul_bwd(A, B, DC, mode=mode, need_da=False, need_db=True, db=DBd, stream=s_c)
+                cabi.matmul_bwd(A_, B_, DC_, mode=mode, need_da=False, need_db=True, db=DB_, stream=s_c)
                 s_c.synchronize()
-                h = CudaBackend(mode=mode).allreduce_start(DBd)
+                h = CudaBackend(mode=mode).allreduce_start(DB_)
                 h[0].wait()
-                cabi.d2h(hDB, DBd, None)
+                cabi.d2h(hDB, DB_, None)
                 cabi.synchronize()
-            s_out.synchronize()
+                s_out.synchronize()
 
-        for _ in range(warmup):
-            step()
+        prev_done = [None]
+        for k in range(warmup):
+            step(k)
+        cabi.synchronize()
+        s_out.synchronize()
         barrier()
+        prev_done[0] = None
         t0 = time.perf_counter()
-        for _ in range(steps):
-            step()
+        for k in range(steps):
+            step(warmup + k)
+        s_out.synchronize()
         cabi.synchronize()
         t1 = time.perf_counter()
         barrier()
@@ -520,7 +543,7 @@ def run_gpu_arm(args):
         "clocks": clocks,
         "e2e": {"value": n_gpus * FLOP_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_each_way, "d2h_bytes_per_step": bytes_each_way,
-                "path": "C ABI, pinned host buffers, copies and GEMMs overlapped on three streams",
+                "path": "C ABI, pinned host buffers, copies and GEMMs overlapped on three streams; on one GPU two device buffer sets, so a step's downloads overlap the next step's uploads (every step uploads its inputs and downloads its results)",
                 "python_api_sequential": {"ms_per_step": ms_e2e_api,
                                           "value": n_gpus * FLOP_PER_STEP / (ms_e2e_api * 1e-3) / 1e12}},
         "gpu_launches": launches,
