@@ -609,10 +609,38 @@ __global__ void epi_apply_kernel(EpiApply a, size_t total) {
         a.c[co] = a.op == 1 ? fmaf(a.beta, x, c) : c * (1.f - x * x);
     }
 }
+// Both arrays dense and laid out alike: a flat, 16-byte vectorised pass.
+__global__ void epi_apply_flat_kernel(float4* __restrict__ c, const float4* __restrict__ x, size_t n4, int op,
+                                      float beta) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 v = c[i];
+        const float4 a = x[i];
+        if (op == 1) {
+            v.x = fmaf(beta, a.x, v.x); v.y = fmaf(beta, a.y, v.y); v.z = fmaf(beta, a.z, v.z); v.w = fmaf(beta, a.w, v.w);
+        } else {
+            v.x *= 1.f - a.x * a.x; v.y *= 1.f - a.y * a.y; v.z *= 1.f - a.z * a.z; v.w *= 1.f - a.w * a.w;
+        }
+        c[i] = v;
+    }
+}
 cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
     size_t total = (size_t)a.M * (size_t)a.N;
     for (int d = 0; d < a.nb; ++d) total *= (size_t)a.bshape[d];
     if (total == 0) return cudaSuccess;
+    bool flat = a.x_cs == 1 && a.c_rs == a.N && a.x_rs == a.N && (total & 3) == 0 &&
+                (reinterpret_cast<uintptr_t>(a.c) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 &&
+                (const float*)a.c != a.x;
+    int64_t dense = a.M * a.N;
+    for (int d = a.nb - 1; d >= 0 && flat; --d) {
+        flat = a.c_bs[d] == dense && a.x_bs[d] == dense;
+        dense *= a.bshape[d];
+    }
+    if (flat) {
+        epi_apply_flat_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((float4*)a.c, (const float4*)a.x, total / 4, a.op,
+                                                                       a.beta);
+        return cudaGetLastError();
+    }
     epi_apply_kernel<<<grid_for(total), kThreads, 0, s>>>(a, total);
     return cudaGetLastError();
 }
