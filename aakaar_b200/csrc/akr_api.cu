@@ -378,13 +378,11 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     if (g.splits > 1) {
         size_t pbytes = 0, ncnt = 0;
         gemm_sm100_split_scratch(g, &pbytes, &ncnt);
-        void *pp = nullptr, *pc = nullptr;
+        void* pp = nullptr;
         rc = ws_get(st, WS_PARTIALS, pbytes, &pp);
         if (rc != AKR_OK) return rc;
-        rc = ws_get(st, WS_COUNTERS, ncnt * sizeof(int), &pc, true);
-        if (rc != AKR_OK) return rc;
-        g.partials = (float*)pp;
-        g.counters = (int*)pc;
+        g.partials = (float*)pp;   // no tile counters: the partials are added up by the GPU-wide reduction kernel
+        (void)ncnt;
     }
 
     // Host loops over the leftover dims.
@@ -425,7 +423,7 @@ int run_problem(const Problem& p, cudaStream_t stream) {
             gi.aux = (last && p.aux && !aux_after) ? p.aux + xo : nullptr;
             const int lrc = gemm_sm100_launch(gi, stream, status, err, sizeof(err));
             if (lrc != 0) return fail(lrc == -1 ? AKR_ERR_INVALID : AKR_ERR_CUDA, err);
-            st->launches++;
+            st->launches += gi.splits > 1 ? 2 : 1;  // a split contraction is followed by its reduction kernel
         }
     }
     if (aux_after) {

@@ -19,6 +19,7 @@
 #include "sm100_ptx.cuh"
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -350,6 +351,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Set-up done (shared memory, tensor memory, barriers only). Let the next kernel of the stream begin its own
+    // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
 
     const int total_iters = p.red * p.nkb;  // contraction steps of one output tile
 
@@ -660,8 +665,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 }
             }
 
-            if (split_mode && ok) {
-                // Last CTA to finish this tile adds the partials in split order (deterministic).
+            if (split_mode && ok && p.counters != nullptr) {
+                // Single-launch variant (caller gave tile counters): the last CTA to finish this tile adds the
+                // partials in split order (deterministic). Without counters a second kernel adds them up.
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
                 const int tile_id = (t / p.splits);
@@ -684,37 +690,62 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     const int col = slab_col0 + lane * 4;
                     const bool pvec = (p.N & 3) == 0;
                     const bool cvec = p.vec_ok != 0;
-                    for (int r = 0; r < 32; ++r) {
-                        const int grow = row0 + r;
-                        if (grow >= p.M) break;
+                    // Four rows at a time, their loads issued together and the split loop unrolled: the sums
+                    // of a row depend on each other, the loads do not (one row and one split at a time was
+                    // a chain of dependent L2 round trips: 87 us for a 512 x 512 x 4096 product).
+                    for (int r0 = 0; r0 < 32; r0 += 4) {
+                        if (row0 + r0 >= p.M) break;
                         if (col >= p.N) continue;
-                        const float* prow = pbase + (size_t)grow * p.N + col;
-                        float sum[4] = {0.f, 0.f, 0.f, 0.f};
                         const int nv = min(4, p.N - col);
-                        for (int sp = 0; sp < p.splits; ++sp) {
-                            const float* q4 = prow + (size_t)sp * split_stride;
-                            if (pvec) {
-                                const float4 x = __ldcg(reinterpret_cast<const float4*>(q4));
-                                sum[0] += x.x; sum[1] += x.y; sum[2] += x.z; sum[3] += x.w;
-                            } else {
-                                for (int e = 0; e < nv; ++e) sum[e] += __ldcg(q4 + e);
+                        float sum[4][4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) sum[u][e] = 0.f;
+                        const float* prow = pbase + (size_t)(row0 + r0) * p.N + col;
+                        if (pvec && nv == 4) {
+#pragma unroll 4
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                float4 x[4];
+#pragma unroll
+                                for (int u = 0; u < 4; ++u)
+                                    x[u] = (row0 + r0 + u < p.M)
+                                               ? __ldcg(reinterpret_cast<const float4*>(prow + (size_t)sp * split_stride + (size_t)u * p.N))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                for (int u = 0; u < 4; ++u) {
+                                    sum[u][0] += x[u].x; sum[u][1] += x[u].y; sum[u][2] += x[u].z; sum[u][3] += x[u].w;
+                                }
                             }
-                        }
-                        float* dst = cbase + (long long)grow * p.ldc + col;
-                        for (int e = 0; e < nv; ++e) {
-                            sum[e] *= p.alpha;
-                            if (p.bias != nullptr) sum[e] += __ldg(p.bias + col + e);
-                            if (p.accumulate) sum[e] += dst[e];
-                            if (TERMS == 1 && p.aux_op != 0) {
-                                const float a = p.aux[c.i0 * p.aux_bs0 + c.i1 * p.aux_bs1 + (long long)grow * p.aux_ld +
-                                                      (long long)(col + e) * p.aux_cs];
-                                sum[e] = p.aux_op == 1 ? fmaf(p.beta, a, sum[e]) : sum[e] * (1.f - a * a);
-                            }
-                        }
-                        if (cvec && nv == 4) {
-                            *reinterpret_cast<float4*>(dst) = make_float4(sum[0], sum[1], sum[2], sum[3]);
                         } else {
-                            for (int e = 0; e < nv; ++e) dst[e] = sum[e];
+                            for (int sp = 0; sp < p.splits; ++sp)
+#pragma unroll
+                                for (int u = 0; u < 4; ++u)
+                                    if (row0 + r0 + u < p.M)
+                                        for (int e = 0; e < nv; ++e)
+                                            sum[u][e] += __ldcg(prow + (size_t)sp * split_stride + (size_t)u * p.N + e);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int grow = row0 + r0 + u;
+                            if (grow >= p.M) break;
+                            float* dst = cbase + (long long)grow * p.ldc + col;
+                            for (int e = 0; e < nv; ++e) {
+                                float v = sum[u][e] * p.alpha;
+                                if (p.bias != nullptr) v += __ldg(p.bias + col + e);
+                                if (p.accumulate) v += dst[e];
+                                if (TERMS == 1 && p.aux_op != 0) {
+                                    const float a = p.aux[c.i0 * p.aux_bs0 + c.i1 * p.aux_bs1 + (long long)grow * p.aux_ld +
+                                                          (long long)(col + e) * p.aux_cs];
+                                    v = p.aux_op == 1 ? fmaf(p.beta, a, v) : v * (1.f - a * a);
+                                }
+                                sum[u][e] = v;
+                            }
+                            if (cvec && nv == 4) {
+                                *reinterpret_cast<float4*>(dst) = make_float4(sum[u][0], sum[u][1], sum[u][2], sum[u][3]);
+                            } else {
+                                for (int e = 0; e < nv; ++e) dst[e] = sum[u][e];
+                            }
                         }
                     }
                 }
@@ -791,6 +822,10 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Set-up done (shared memory, tensor memory, barriers only). Let the next kernel of the stream begin its own
+    // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int total_iters = p.red * p.nkb;
 
     if (warp == 0) {
@@ -1050,6 +1085,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Set-up done (shared memory, tensor memory, barriers only). Let the next kernel of the stream begin its own
+    // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int total_iters = p.red * p.nkb;
     const bool presplit = p.presplit != 0;
     const int kc = (p.debug & 64) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
@@ -1441,6 +1480,10 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Set-up done (shared memory, tensor memory, barriers only). Let the next kernel of the stream begin its own
+    // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
     const int total_iters = p.red * p.nkb;
 
     if (warp == 0) {
@@ -1623,6 +1666,70 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
+// ---------------------------------------------------------------------------------- split-K reduction
+// C = epilogue(sum over splits of the partial tiles), in split order (deterministic), by the whole GPU:
+// one CTA adding up all partials of its tile alone is a chain of L2 round trips on a single SM
+// (2.6 us per 128 KB partial), which capped the split count and left long-K, small-output products
+// (weight gradients) several times slower than their loads.
+struct SplitReduceParams {
+    const float* partials;  // [splits][nbatch][M][N], dense
+    float* C;
+    const float* bias;
+    const float* aux;
+    long long ldc, c_bs0, c_bs1, aux_ld, aux_cs, aux_bs0, aux_bs1;
+    int M, N, o1, nbatch, splits;
+    int accumulate, aux_op;
+    float alpha, beta;
+};
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const SplitReduceParams p) {
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();  // the partials come from the kernel before this one
+    constexpr int W = VEC ? 4 : 1;
+    const size_t ncol = (size_t)(p.N / W);
+    const size_t total = (size_t)p.nbatch * p.M * ncol;
+    const size_t split_stride = (size_t)p.nbatch * p.M * p.N;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int n = (int)(idx % ncol) * W;
+        const size_t rm = idx / ncol;
+        const int m = (int)(rm % (size_t)p.M);
+        const int b = (int)(rm / (size_t)p.M);
+        const float* src = p.partials + ((size_t)b * p.M + m) * p.N + n;
+        float sum[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) sum[e] = 0.f;
+#pragma unroll 8
+        for (int sp = 0; sp < p.splits; ++sp) {
+            if (VEC) {
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * split_stride));
+                sum[0] += x.x; sum[W > 1 ? 1 : 0] += x.y; sum[W > 2 ? 2 : 0] += x.z; sum[W > 3 ? 3 : 0] += x.w;
+            } else {
+                sum[0] += __ldcg(src + (size_t)sp * split_stride);
+            }
+        }
+        const int i0 = b / p.o1, i1 = b - i0 * p.o1;
+        float* dst = p.C + i0 * p.c_bs0 + i1 * p.c_bs1 + (long long)m * p.ldc + n;
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            float v = sum[e] * p.alpha;
+            if (p.bias != nullptr) v += __ldg(p.bias + n + e);
+            if (p.accumulate) v += dst[e];
+            if (p.aux_op != 0) {
+                const float a = p.aux[i0 * p.aux_bs0 + i1 * p.aux_bs1 + (long long)m * p.aux_ld + (long long)(n + e) * p.aux_cs];
+                v = p.aux_op == 1 ? fmaf(p.beta, a, v) : v * (1.f - a * a);
+            }
+            sum[e] = v;
+        }
+        if (VEC) {
+            *reinterpret_cast<float4*>(dst) = make_float4(sum[0], sum[W > 1 ? 1 : 0], sum[W > 2 ? 2 : 0], sum[W > 3 ? 3 : 0]);
+        } else {
+            dst[0] = sum[0];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1711,6 +1818,25 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const 
     return r == CUDA_SUCCESS;
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in
+// the stream drains (its set-up overlaps that tail); it synchronises on the predecessor itself
+// (grid_dep_wait) before its first access to global memory. Debug bit 12 launches normally.
+bool g_pdl_off = false;
+template <typename K>
+void launch_pdl(K kern, int grid, int threads, int smem, cudaStream_t stream, const KernelParams& kp) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g_pdl_off ? 0 : 1;
+    cudaLaunchKernelEx(&cfg, kern, kp);
+}
+
 template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS, BKT>;
@@ -1725,7 +1851,7 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
         }
         attr_done = true;
     }
-    kern<<<grid, num_threads<BN, TERMS>(), smem, stream>>>(kp);
+    launch_pdl(kern, grid, num_threads<BN, TERMS>(), smem, stream, kp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -1759,7 +1885,7 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
         }
         attr_done = true;
     }
-    kern<<<grid, BIG_THREADS, smem, stream>>>(kp);
+    launch_pdl(kern, grid, BIG_THREADS, smem, stream, kp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -1807,7 +1933,7 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
         if (std::getenv("AKR_B200_VERBOSE")) std::fprintf(stderr, "akr_b200: %d CTA pairs resident (%s kernel)\n", n, DUO ? "tf32 pair" : "fp32 pair");
     }
     if (grid > 2 * max_pairs) grid = 2 * max_pairs;
-    kern<<<grid, threads, smem, stream>>>(kp);  // cluster of 2 CTAs (compile-time cluster dims)
+    launch_pdl(kern, grid, threads, smem, stream, kp);  // cluster of 2 CTAs (compile-time cluster dims)
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         seterr(err, errlen, cudaGetErrorString(e));
@@ -1874,11 +2000,14 @@ int pick_bn(const GemmDesc& g) {
 }  // namespace
 
 static int g_cta_limit = 0;
+static double g_split_ratio = 0.0;  // tuning override (environment AKR_B200_SPLIT_RATIO), 0 = built-in
 static int g_debug_flags = 0;
 static unsigned long long g_wait_limit_ns = DEFAULT_WAIT_LIMIT_NS;
 
 void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms) {
+    if (const char* r = std::getenv("AKR_B200_SPLIT_RATIO")) g_split_ratio = std::atof(r);
     g_debug_flags = flags;
+    g_pdl_off = (flags & 4096) != 0;
     g_wait_limit_ns = wait_limit_ms ? (unsigned long long)wait_limit_ms * 1000000ull : DEFAULT_WAIT_LIMIT_NS;
 }
 
@@ -1916,6 +2045,13 @@ int gemm_sm100_pick_splits(const GemmDesc& g) {
     long long s = ctas / tiles;
     const long long max_by_work = iters / 16;  // keep at least 16 k-blocks per split
     if (s > max_by_work) s = max_by_work;
+    // (With tile counters, i.e. the single-launch variant, the last CTA of a tile adds up all its partials
+    // alone, which costs about as much per partial as ten k-blocks: that caller should also cap the count
+    // near sqrt(0.2 * iters).)
+    if (g_split_ratio > 0.0) {
+        const long long s_bal = (long long)(std::sqrt(g_split_ratio * (double)iters) + 0.5);
+        if (s > s_bal) s = s_bal;
+    }
     if (s > 64) s = 64;
     return s < 1 ? 1 : (int)s;
 }
@@ -1942,7 +2078,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: second epilogue operand missing, or requested in the fp32-accurate mode");
         return -1;
     }
-    if (g.splits > 1 && (!g.partials || !g.counters)) {
+    if (g.splits > 1 && !g.partials) {
         seterr(err, errlen, "gemm_sm100: split launch without scratch");
         return -1;
     }
@@ -2074,12 +2210,50 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         }
     }
     // fp32-accurate mode: 16-deep k-blocks, chains of 4 of them (64 deep) inside the tensor core.
+    int rc;
     if (g.terms == 3) {
-        if (bn == 256) return launch_major<256, 3, 4, 4, 16>(g, kp, grid, stream, err, errlen);
-        return launch_major<128, 3, 6, 4, 16>(g, kp, grid, stream, err, errlen);
+        rc = bn == 256 ? launch_major<256, 3, 4, 4, 16>(g, kp, grid, stream, err, errlen)
+                       : launch_major<128, 3, 6, 4, 16>(g, kp, grid, stream, err, errlen);
+    } else {
+        rc = bn == 256 ? launch_major<256, 1, 4, 0, 32>(g, kp, grid, stream, err, errlen)
+                       : launch_major<128, 1, 6, 0, 32>(g, kp, grid, stream, err, errlen);
     }
-    if (bn == 256) return launch_major<256, 1, 4, 0, 32>(g, kp, grid, stream, err, errlen);
-    return launch_major<128, 1, 6, 0, 32>(g, kp, grid, stream, err, errlen);
+    if (rc != 0 || kp.splits == 1 || g.counters != nullptr) return rc;
+
+    // Split contraction without tile counters: the partial tiles are added up by a second, GPU-wide kernel.
+    SplitReduceParams rp;
+    std::memset(&rp, 0, sizeof(rp));
+    rp.partials = g.partials;
+    rp.C = g.C;
+    rp.bias = g.bias;
+    rp.aux = g.aux_op ? g.aux : nullptr;
+    rp.ldc = g.ldc; rp.c_bs0 = g.c_bs0; rp.c_bs1 = g.c_bs1;
+    rp.aux_ld = g.aux_ld; rp.aux_cs = g.aux_cs; rp.aux_bs0 = g.aux_bs0; rp.aux_bs1 = g.aux_bs1;
+    rp.M = g.M; rp.N = g.N; rp.o1 = g.o1; rp.nbatch = g.o0 * g.o1; rp.splits = kp.splits;
+    rp.accumulate = g.accumulate; rp.aux_op = g.aux_op;
+    rp.alpha = g.alpha; rp.beta = g.beta;
+    const bool vec = kp.vec_ok && (g.N & 3) == 0;
+    const size_t work = (size_t)rp.nbatch * g.M * (size_t)(vec ? g.N / 4 : g.N);
+    size_t blocks = (work + 255) / 256;
+    const size_t cap = (size_t)gemm_sm100_num_ctas() * 8;
+    if (blocks > cap) blocks = cap;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = g_pdl_off ? 0 : 1;
+    if (vec) cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<true>, rp);
+    else cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<false>, rp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        seterr(err, errlen, cudaGetErrorString(e));
+        return -3;
+    }
+    return 0;
 }
 
 }  // namespace akr

@@ -39,8 +39,10 @@ struct GemmDesc {
     int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate). With terms == 3 the low parts are
                                   // derived in the kernel unless BOTH operands carry pre-split `lo` arrays
     // Split of the contraction across CTAs (weight gradients with few output tiles):
-    // splits > 1 writes fp32 partials to `partials` ([splits][o0*o1][M][N]) and the last CTA
-    // to finish a tile adds them up in split order. `counters` holds one int per output tile.
+    // splits > 1 writes fp32 partials to `partials` ([splits][o0*o1][M][N]); they are added up in split
+    // order (deterministic) by a second, GPU-wide kernel launched right behind the GEMM - or, when the
+    // caller passes `counters` (one zeroed int per output tile, left at zero), inside the GEMM by the last
+    // CTA to finish each tile: a single launch, slower for many splits.
     int splits = 1;
     float* partials = nullptr;
     int* counters = nullptr;

@@ -11,6 +11,7 @@
 
 #include "gemm_sm100.h"
 
+#include <cmath>
 #include <cstdio>
 #include <mutex>
 #include <string>
@@ -144,6 +145,14 @@ AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_vi
     g.ldc = c->stride[0];
     g.terms = 1;  // TF32 products; the fp32-accurate mode needs split operands (scratch of operand size)
     g.splits = gemm_sm100_pick_splits(g);
+    {
+        // This entry point keeps the single-launch variant (tile counters, the last CTA of a tile adds up its
+        // partials alone), whose reduction time grows with the split count: balance it against the
+        // contraction left per split.
+        const long long iters = (K + 31) / 32;
+        const int s_bal = (int)(std::sqrt(0.2 * (double)iters) + 0.5);
+        if (g.splits > s_bal) g.splits = s_bal < 1 ? 1 : s_bal;
+    }
     size_t pbytes = 0, ncnt = 0;
     gemm_sm100_split_scratch(g, &pbytes, &ncnt);
     if (pbytes > kPartialFloats * sizeof(float) || ncnt > kCounters) {
