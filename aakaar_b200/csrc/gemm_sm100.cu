@@ -266,6 +266,9 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
 // single 16 KB box. The warps are free again as soon as the box has been read from shared memory;
 // the write itself drains asynchronously, clipped at the matrix edge by the hardware.
 // Must be called by all 128 threads of the slab (named barrier `bar_id`).
+// BUFS == 2: the caller alternates between two staging tiles per slab, and the issuer only waits for
+// the box BEFORE the one it just sent, so staging a block overlaps the TMA unit reading the previous one.
+template <int BUFS = 1>
 __device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile, uint32_t slab_tile_addr,
                                                 const CUtensorMap* tmC, int col0, int row_base, int i1, int i0,
                                                 int N, const float* bias, int lane, bool issuer, int bar_id) {
@@ -282,9 +285,10 @@ __device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile,
     if (issuer) {
         ptx::tma_store_4d(tmC, slab_tile_addr, col0, row_base, i1, i0);
         ptx::bulk_commit_group();
-        ptx::bulk_wait_read_all();
+        if (BUFS == 2) ptx::bulk_wait_read_1();
+        else ptx::bulk_wait_read_all();
     }
-    ptx::named_barrier_sync(bar_id, 128);  // the tile may be overwritten
+    ptx::named_barrier_sync(bar_id, 128);  // the (other) tile may be overwritten
 }
 
 // KC > 0: the tensor core only accumulates KC k-blocks at a time; the epilogue warps add those
@@ -294,6 +298,15 @@ __device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile,
 // BKT: fp32 per k-block. 32 = one 128-byte swizzle row per K-major tile row; 16 = 64-byte rows
 // (64-byte swizzle), used by the fp32-accurate mode to have four finer stages in flight instead of
 // two coarse ones (its stages carry hi and lo parts and are twice as large per k).
+// Staging tiles per slab of the general kernel: two when shared memory has room for them.
+template <int BN, int TERMS, int STAGES, int BKT>
+struct EpiBufs {
+    static constexpr int value =
+        (TERMS == 1 && STAGES * SmemLayout<BN, TERMS, BKT>::STAGE_BYTES + 2 * (BN / 128) * 4 * EPI_STAGE_BYTES + 2048 <= 232448)
+            ? 2
+            : 1;
+};
+
 template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 __global__ void __launch_bounds__(num_threads<BN, TERMS>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
@@ -310,8 +323,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
 
-    // [stages][epilogue staging: one 16 KB tile per 128-column slab, 1024-byte aligned][barriers]
-    constexpr int EPI_BYTES = (BN / 128) * 4 * EPI_STAGE_BYTES;
+    // [stages][epilogue staging: one 16 KB tile per 128-column slab (two where they fit: the TMA-store
+    // epilogue then alternates between them), 1024-byte aligned][barriers]
+    constexpr int EPI_BUFS = EpiBufs<BN, TERMS, STAGES, BKT>::value;
+    constexpr int EPI_BYTES = EPI_BUFS * (BN / 128) * 4 * EPI_STAGE_BYTES;
     uint8_t* epi_stage_base = smem + STAGES * L::STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES + EPI_BYTES);
     const uint32_t bar_base = smem_base + STAGES * L::STAGE_BYTES + EPI_BYTES;
@@ -575,6 +590,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         const bool split_mode = p.splits > 1;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
         const uint32_t slab_tile_addr = smem_base + STAGES * L::STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        constexpr int EPI_ALT = (BN / 128) * 4 * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
+        int epi_buf = 0;                                           // which set the next TMA-store block uses
         const bool use_tma = p.c_tma != 0 && !split_mode;  // kernel-uniform
         int handoff = 0;
         bool ok = true;
@@ -632,8 +649,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             if (p.debug & 128) {
                                 // bit 7: timing experiment without the output stores
                             } else if (use_tma) {
-                                store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias,
-                                                lane, q == 0 && lane == 0, 2 + slab);
+                                store_block_tma<EPI_BUFS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
+                                                          &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
+                                                          q == 0 && lane == 0, 2 + slab);
+                                if (EPI_BUFS == 2) epi_buf ^= 1;
                             } else {
                                 store_block_warp<TERMS == 1>(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec,
                                                              split_mode ? plain_epi() : (TERMS == 1 ? tile_epi(p, c) : lean_epi(p)), lane);
@@ -655,12 +674,15 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ACC_N > 1 ? ch * 32 + j : 0];
-                        if (use_tma)
-                            store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
-                                            q == 0 && lane == 0, 2 + slab);
-                        else
+                        if (use_tma) {
+                            store_block_tma<EPI_BUFS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
+                                                      &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane, q == 0 && lane == 0,
+                                                      2 + slab);
+                            if (EPI_BUFS == 2) epi_buf ^= 1;
+                        } else {
                             store_block_warp<TERMS == 1>(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec,
                                                          split_mode ? plain_epi() : (TERMS == 1 ? tile_epi(p, c) : lean_epi(p)), lane);
+                        }
                     }
                 }
             }
@@ -1840,7 +1862,7 @@ void launch_pdl(K kern, int grid, int threads, int smem, cudaStream_t stream, co
 template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS, BKT>;
-    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256 + (BN / 128) * 4 * EPI_STAGE_BYTES;
+    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256 + EpiBufs<BN, TERMS, STAGES, BKT>::value * (BN / 128) * 4 * EPI_STAGE_BYTES;
     auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
@@ -2215,7 +2237,11 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         rc = bn == 256 ? launch_major<256, 3, 4, 4, 16>(g, kp, grid, stream, err, errlen)
                        : launch_major<128, 3, 6, 4, 16>(g, kp, grid, stream, err, errlen);
     } else {
-        rc = bn == 256 ? launch_major<256, 1, 4, 0, 32>(g, kp, grid, stream, err, errlen)
+        // Short contractions are write-heavy: three stages are plenty and leave room for a second set of
+        // epilogue staging tiles.
+        const bool short_k = (long long)kp.red * kp.nkb <= 8 && kp.splits == 1;
+        rc = bn == 256 ? (short_k ? launch_major<256, 1, 3, 0, 32>(g, kp, grid, stream, err, errlen)
+                                  : launch_major<256, 1, 4, 0, 32>(g, kp, grid, stream, err, errlen))
                        : launch_major<128, 1, 6, 0, 32>(g, kp, grid, stream, err, errlen);
     }
     if (rc != 0 || kp.splits == 1 || g.counters != nullptr) return rc;
