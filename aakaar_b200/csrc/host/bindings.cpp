@@ -23,6 +23,8 @@ namespace {
 
 bool g_grad_enabled = true;
 
+enum class DTypeEnum : int { float32 = AKR_DTYPE_F32, float64 = AKR_DTYPE_F64, int32 = AKR_DTYPE_I32, int64 = AKR_DTYPE_I64 };
+
 TensorPtr make_cuda(const std::vector<int64_t>& shape) { return std::make_shared<Tensor>(shape, "cuda"); }
 
 bool needs_graph(const TensorPtr& a) { return g_grad_enabled && a->requires_grad; }
@@ -655,11 +657,22 @@ std::string repr(const TensorPtr& t) {
 PYBIND11_MODULE(_C, m) {
     m.doc() = "aakaar_b200: B200-native fp32 matmul path behind the Aakaar API";
 
+    // DType of the reference (src/dtype.h:6, bound at src/bindings.cpp:2473-2477).
+    py::enum_<DTypeEnum>(m, "DType")
+        .value("float32", DTypeEnum::float32)
+        .value("float64", DTypeEnum::float64)
+        .value("int32", DTypeEnum::int32)
+        .value("int64", DTypeEnum::int64);
+
     py::class_<Tensor, TensorPtr>(m, "Tensor")
         .def(py::init([](std::vector<int64_t> shape, std::string device) {
                  return std::make_shared<Tensor>(shape, device);
              }),
              py::arg("shape"), py::arg("device") = "cuda")
+        .def(py::init([](std::vector<int64_t> shape, std::string device, DTypeEnum dt) {
+                 return std::make_shared<Tensor>(shape, device, (int)dt);
+             }),
+             py::arg("shape"), py::arg("device"), py::arg("dtype"))
         .def_property_readonly("dtype", [](Tensor& t) { return std::string(dtype_name(t.dtype)); })
         .def_readonly("device", &Tensor::device)
         .def_readonly("size", &Tensor::size)

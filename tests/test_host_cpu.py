@@ -81,6 +81,14 @@ def test_from_numpy_dtypes_and_missing_gpu():
             ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cuda")
 
 
+def test_dtype_enum_and_typed_constructor():
+    from aakaar_b200 import _C
+    assert [n for n in ("float32", "float64", "int32", "int64") if hasattr(_C.DType, n)] == ["float32", "float64", "int32", "int64"]
+    t = _C.Tensor([2, 3], "cpu", _C.DType.int64)
+    assert t.dtype == "int64" and t.shape == [2, 3] and t.to_numpy().dtype == np.int64
+    assert _C.Tensor([4], "cpu").dtype == "float32"
+
+
 def test_sgd_argument_check():
     with pytest.raises(ValueError):
         ak.optim.SGD([], nesterov=True)
