@@ -290,6 +290,42 @@ def test_config5a_batched_slice(mode, tol):
         assert rel_fro(gb[i], a[i].astype(np.float64).T @ ones) < tol
 
 
+def test_largest_benchmark_square_16384_sampled_rows():
+    # the largest size of the benchmark sweep (16384^3, 1 GiB per matrix): sampled rows of C, dA and dB against
+    # float64, TF32 mode and the fp32-accurate mode (the latter splits its operands up front at this size)
+    n = 16384
+    g = np.random.Generator(np.random.PCG64(404))
+    s = np.float32(1.0 / np.sqrt(n))
+    a = g.standard_normal((n, n), dtype=np.float32) * s
+    b = g.standard_normal((n, n), dtype=np.float32) * s
+    A, B = dev(a), dev(b)
+    rows = [0, 4097, n - 1]
+    for mode, tol in MODES:
+        c = cabi.matmul_fwd(A, B, mode=mode)
+        got = np.stack([c.as_strided((n,), (1,), offset=r * n).to_numpy() for r in rows])
+        sampled_rows_check(a, b, _Rows(got, rows), rows, tol)
+        # dA rows and dB rows with dC := C (any dense matrix will do)
+        da, db = cabi.matmul_bwd(A, B, c, mode=mode)
+        cn = np.stack([c.as_strided((n,), (1,), offset=r * n).to_numpy() for r in rows])
+        got_da = np.stack([da.as_strided((n,), (1,), offset=r * n).to_numpy() for r in rows])
+        assert rel_fro(got_da, cn.astype(np.float64) @ b.astype(np.float64).T) < tol
+        del da
+        full_c = c.to_numpy()
+        got_db = np.stack([db.as_strided((n,), (1,), offset=r * n).to_numpy() for r in rows])
+        assert rel_fro(got_db, a[:, rows].astype(np.float64).T @ full_c.astype(np.float64)) < tol
+        del db, c, full_c
+
+
+class _Rows:
+    """Lets sampled_rows_check index a few downloaded rows as if they were the whole matrix."""
+
+    def __init__(self, data, rows):
+        self.data, self.rows = data, list(rows)
+
+    def __getitem__(self, rows):
+        return self.data[[self.rows.index(r) for r in rows]]
+
+
 def test_linearity_and_transpose_identity_8192():
     # Size-independent properties at the headline size, TF32 mode:
     #   (A @ B)^T == B^T @ A^T evaluated through transposed VIEWS (exercises the other operand majors)
