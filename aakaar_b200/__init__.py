@@ -67,6 +67,48 @@ def mse_loss(pred, target):
     return _C._mse_fused(pred, target)
 
 
+def im2col_1d(x, kernel_size, stride, padding, dilation, out_length):
+    """(B, C, L) -> (B, C*kernel_size, L_out) sliding windows (aakaar/__init__.py:285-288)."""
+    return _C.im2col_1d(x, kernel_size, stride, padding, dilation, out_length)
+
+
+def im2col_2d(x, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW):
+    """(B, C, H, W) -> (B, C*KH*KW, OH*OW) sliding windows (aakaar/__init__.py:325-328)."""
+    return _C.im2col_2d(x, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW)
+
+
+def conv1d(x, weight, stride=1, padding=0, dilation=1):
+    """Conv1d forward + backward as unfold + matmul, the reference's path without cuDNN
+    (aakaar/__init__.py:289-307): ``[1, C_out, C_in*K] @ [B, C_in*K, L_out]`` is ONE batched launch with the
+    weights broadcast (stride 0), and the weight gradient is summed over the batch inside its GEMM."""
+    C_out, C_in, K = weight.shape
+    B, _, L_in = x.shape
+    L_out = (L_in + 2 * padding - dilation * (K - 1) - 1) // stride + 1
+    if L_out <= 0:
+        raise ValueError(f"conv1d: computed output length {L_out} <= 0")
+    col = im2col_1d(x, K, stride, padding, dilation, L_out)
+    w_flat = weight.reshape([1, C_out, C_in * K])
+    return matmul(w_flat, col)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv2d(x, weight, stride=(1, 1), padding=(0, 0), dilation=(1, 1)):
+    """Conv2d forward + backward as unfold + matmul (aakaar/__init__.py:330-352)."""
+    (SH, SW), (PH, PW), (DH, DW) = _pair(stride), _pair(padding), _pair(dilation)
+    C_out, C_in, KH, KW = weight.shape
+    B, _, H, W = x.shape
+    OH = (H + 2 * PH - DH * (KH - 1) - 1) // SH + 1
+    OW = (W + 2 * PW - DW * (KW - 1) - 1) // SW + 1
+    if OH <= 0 or OW <= 0:
+        raise ValueError(f"conv2d: computed output size ({OH},{OW}) <= 0")
+    col = im2col_2d(x, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW)
+    w_flat = weight.reshape([1, C_out, C_in * KH * KW])
+    return matmul(w_flat, col).reshape([B, C_out, OH, OW])
+
+
 def from_numpy(array, device: str = "cuda", requires_grad: bool = False):
     return _C.from_numpy(array, device, requires_grad)
 
@@ -107,5 +149,5 @@ from . import nn, optim, losses  # noqa: E402
 __all__ = [
     "Tensor", "matmul", "add", "sub", "no_grad", "is_grad_enabled", "mse_loss", "from_numpy",
     "zero_grad_all", "set_tf32", "is_tf32_enabled", "synchronize", "is_available", "device_count",
-    "empty_cache", "nn", "optim", "losses",
+    "empty_cache", "nn", "optim", "losses", "conv1d", "conv2d", "im2col_1d", "im2col_2d",
 ]

@@ -1114,6 +1114,42 @@ AKR_API int akr_tanh_fwd(const float* x, float* y, size_t n, void* stream) {
 AKR_API int akr_tanh_bwd(const float* grad, const float* y, float* dx, size_t n, void* stream) {
     AKR_LAUNCH(launch_tanh_bwd(grad, y, dx, n, (cudaStream_t)stream), "tanh backward launch");
 }
+static int window_geom(const akr_window* w, WindowGeom* g) {
+    if (!w) return fail(AKR_ERR_INVALID, "im2col: null geometry");
+    if (w->B <= 0 || w->C <= 0 || w->H <= 0 || w->W <= 0 || w->KH <= 0 || w->KW <= 0 || w->SH <= 0 || w->SW <= 0 ||
+        w->DH <= 0 || w->DW <= 0 || w->PH < 0 || w->PW < 0 || w->OH <= 0 || w->OW <= 0)
+        return fail(AKR_ERR_INVALID, "im2col: sizes, strides and dilations must be positive, padding non-negative");
+    g->B = w->B; g->C = w->C; g->H = w->H; g->W = w->W;
+    g->KH = w->KH; g->KW = w->KW; g->SH = w->SH; g->SW = w->SW;
+    g->PH = w->PH; g->PW = w->PW; g->DH = w->DH; g->DW = w->DW;
+    g->OH = w->OH; g->OW = w->OW;
+    return AKR_OK;
+}
+AKR_API int akr_im2col(const float* x, float* col, const akr_window* geom, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    WindowGeom g;
+    if ((rc = window_geom(geom, &g)) != AKR_OK) return rc;
+    if (!x || !col) return fail(AKR_ERR_INVALID, "im2col: null data pointer");
+    cudaError_t e = launch_im2col(x, col, g, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "im2col launch");
+    st->launches++;
+    return AKR_OK;
+}
+AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* geom, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    WindowGeom g;
+    if ((rc = window_geom(geom, &g)) != AKR_OK) return rc;
+    if (!grad_col || !grad_x) return fail(AKR_ERR_INVALID, "col2im: null data pointer");
+    cudaError_t e = launch_col2im(grad_col, grad_x, g, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "col2im launch");
+    st->launches++;
+    return AKR_OK;
+}
+
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream) {
     if (n == 0) return fail(AKR_ERR_RUNTIME, "MSELoss: cannot reduce an empty tensor");
     DeviceState* st = nullptr;

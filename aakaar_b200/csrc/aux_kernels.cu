@@ -645,6 +645,70 @@ cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+// One thread per output element of `col`, consecutive threads along the window position (coalesced writes;
+// reads are coalesced too when the stride along W is 1).
+__global__ void im2col_kernel(const float* __restrict__ x, float* __restrict__ col, WindowGeom g, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int64_t OHW = g.OH * g.OW;
+    const int64_t rows = g.C * g.KH * g.KW;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t o = (int64_t)(i % (size_t)OHW);
+        size_t r = i / (size_t)OHW;
+        const int64_t row = (int64_t)(r % (size_t)rows);
+        const int64_t b = (int64_t)(r / (size_t)rows);
+        const int kw = (int)(row % g.KW);
+        const int kh = (int)((row / g.KW) % g.KH);
+        const int64_t c = row / (g.KW * g.KH);
+        const int64_t oh = o / g.OW, ow = o - oh * g.OW;
+        const int64_t h = oh * g.SH - g.PH + (int64_t)kh * g.DH;
+        const int64_t w = ow * g.SW - g.PW + (int64_t)kw * g.DW;
+        float v = 0.f;
+        if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = x[((b * g.C + c) * g.H + h) * g.W + w];
+        col[i] = v;
+    }
+}
+// One thread per input element: sums, in (kh, kw) order, the window entries that read it.
+__global__ void col2im_kernel(const float* __restrict__ gc, float* __restrict__ gx, WindowGeom g, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int64_t OHW = g.OH * g.OW;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t w = (int64_t)(i % (size_t)g.W);
+        size_t r = i / (size_t)g.W;
+        const int64_t h = (int64_t)(r % (size_t)g.H);
+        r /= (size_t)g.H;
+        const int64_t c = (int64_t)(r % (size_t)g.C);
+        const int64_t b = (int64_t)(r / (size_t)g.C);
+        const float* base = gc + ((size_t)(b * g.C + c) * g.KH * g.KW) * OHW;
+        float acc = 0.f;
+        for (int kh = 0; kh < g.KH; ++kh) {
+            const int64_t nh = h + g.PH - (int64_t)kh * g.DH;
+            if (nh < 0 || nh % g.SH != 0) continue;
+            const int64_t oh = nh / g.SH;
+            if (oh >= g.OH) continue;
+            for (int kw = 0; kw < g.KW; ++kw) {
+                const int64_t nw = w + g.PW - (int64_t)kw * g.DW;
+                if (nw < 0 || nw % g.SW != 0) continue;
+                const int64_t ow = nw / g.SW;
+                if (ow >= g.OW) continue;
+                acc += base[(size_t)(kh * g.KW + kw) * OHW + oh * g.OW + ow];
+            }
+        }
+        gx[i] = acc;
+    }
+}
+cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaStream_t s) {
+    const size_t total = (size_t)g.B * g.C * g.KH * g.KW * g.OH * g.OW;
+    if (total == 0) return cudaSuccess;
+    im2col_kernel<<<grid_for(total), kThreads, 0, s>>>(x, col, g, total);
+    return cudaGetLastError();
+}
+cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s) {
+    const size_t total = (size_t)g.B * g.C * g.H * g.W;
+    if (total == 0) return cudaSuccess;
+    col2im_kernel<<<grid_for(total), kThreads, 0, s>>>(grad_col, grad_x, g, total);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
                            cudaStream_t s) {
     if (n == 0) return cudaSuccess;

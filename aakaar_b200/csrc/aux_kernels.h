@@ -68,6 +68,16 @@ struct EpiApply {
 };
 cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s);
 
+// Sliding-window unfold of a contiguous (B, C, H, W) array into (B, C*KH*KW, OH*OW) and its adjoint
+// (gather form: every input element sums the window entries that read it). 1-D is H = KH = OH = 1.
+struct WindowGeom {
+    int64_t B = 0, C = 0, H = 0, W = 0;
+    int KH = 1, KW = 1, SH = 1, SW = 1, PH = 0, PW = 0, DH = 1, DW = 1;
+    int64_t OH = 0, OW = 0;
+};
+cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaStream_t s);
+cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s);
+
 cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s);
 cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s);
 cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s);

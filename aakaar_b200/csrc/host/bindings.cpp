@@ -338,6 +338,46 @@ TensorPtr cpu_matmul_refused(const TensorPtr&, const TensorPtr&) {
         "Create the tensors with device='cuda'.");
 }
 
+// ------------------------------------------------------------------ convolution callers of the matmul path
+
+// im2col_1d / im2col_2d of the reference (dispatch_im2col_1d, src/bindings.cpp:988-1039; dispatch_im2col_2d,
+// :1169-1225): unfold into the (B, C*K, L_out) matrix the convolution fallback multiplies by the flattened
+// weights; the backward of the node is the adjoint fold (col2im).
+TensorPtr op_im2col(const TensorPtr& x_in, akr_window w, const char* what) {
+    require_cuda(x_in, what);
+    require_f32(x_in, what);
+    auto x = x_in->is_contiguous() ? x_in : op_contiguous(x_in);
+    auto col = make_cuda({w.B, w.C * w.KH * w.KW, w.OH * w.OW});
+    check(akr_im2col(x->data, col->data, &w, nullptr));
+    if (needs_graph(x)) {
+        const auto in_shape = x->shape;
+        attach(col, what, {x}, [w, in_shape](TensorPtr g) {
+            auto gc = g->is_contiguous() ? g : op_contiguous(g);
+            auto gx = make_cuda(in_shape);
+            check(akr_col2im(gc->data, gx->data, &w, nullptr));
+            return std::vector<TensorPtr>{gx};
+        });
+    }
+    return col;
+}
+
+TensorPtr op_im2col_1d(const TensorPtr& x, int K, int S, int P, int D, int64_t L_out) {
+    if (x->shape.size() != 3)
+        throw std::invalid_argument("im2col_1d: expected input of shape (batch, channels, length), got rank " +
+                                    std::to_string(x->shape.size()));
+    akr_window w{x->shape[0], x->shape[1], 1, x->shape[2], 1, K, 1, S, 0, P, 1, D, 1, L_out};
+    return op_im2col(x, w, "im2col_1d");
+}
+
+TensorPtr op_im2col_2d(const TensorPtr& x, int KH, int KW, int SH, int SW, int PH, int PW, int DH, int DW, int64_t OH,
+                       int64_t OW) {
+    if (x->shape.size() != 4)
+        throw std::invalid_argument("im2col_2d: expected input of shape (batch, channels, H, W), got rank " +
+                                    std::to_string(x->shape.size()));
+    akr_window w{x->shape[0], x->shape[1], x->shape[2], x->shape[3], KH, KW, SH, SW, PH, PW, DH, DW, OH, OW};
+    return op_im2col(x, w, "im2col_2d");
+}
+
 // ------------------------------------------------------------------ losses / optimiser
 
 // _mse_fused of the reference (src/bindings.cpp:2821, src/elementwise_kernel.cu:2253-2300).
@@ -739,6 +779,9 @@ PYBIND11_MODULE(_C, m) {
     m.def("matmul_axpby", &op_matmul_axpby, py::arg("a"), py::arg("b"), py::arg("alpha") = 1.0f, py::arg("beta") = 0.0f,
           py::arg("d") = nullptr, "alpha * (a @ b) + beta * d in one launch (no autograd)");
     m.def("_mean_square", &op_mean_square);
+    m.def("im2col_1d", &op_im2col_1d, py::arg("x"), py::arg("kernel_size"), py::arg("stride"), py::arg("padding"),
+          py::arg("dilation"), py::arg("out_length"));
+    m.def("im2col_2d", &op_im2col_2d);
     m.def("linear", &op_matmul_bias, py::arg("x"), py::arg("weight"), py::arg("bias") = nullptr,
           "x @ weight + bias with the bias add fused into the GEMM epilogue");
     m.def("from_numpy", &from_numpy, py::arg("array"), py::arg("device") = "cuda", py::arg("requires_grad") = false);

@@ -228,6 +228,19 @@ AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream);
 AKR_API int akr_scale(const float* x, float alpha, float* y, size_t n, void* stream);
 AKR_API int akr_tanh_fwd(const float* x, float* y, size_t n, void* stream);
 AKR_API int akr_tanh_bwd(const float* grad, const float* y, float* dx, size_t n, void* stream);
+/* Sliding-window unfold and its adjoint: the im2col / col2im primitives in front of the matmul in the
+ * reference's convolution fallback (aakaar/__init__.py:285-352; src/conv_kernel.cpp:15-60,
+ * src/conv2d_kernel.cpp:7-70 and their .cu twins). x: contiguous (B, C, H, W); col: contiguous
+ * (B, C*KH*KW, OH*OW), row (c, kh, kw), column (oh, ow), zero where the window leaves the input.
+ * The 1-D forms are H = KH = OH = 1, SH = DH = 1, PH = 0. */
+typedef struct akr_window {
+    int64_t B, C, H, W;
+    int32_t KH, KW, SH, SW, PH, PW, DH, DW;
+    int64_t OH, OW;
+} akr_window;
+AKR_API int akr_im2col(const float* x, float* col, const akr_window* geom, void* stream);
+AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* geom, void* stream);
+
 /* loss_out[0] = sum((pred - target)^2) / n; target == NULL gives the mean of squares of pred (the Frobenius
  * norm the Muon optimizer divides by, aakaar/optim.py:534). */
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream);

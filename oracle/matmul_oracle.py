@@ -19,6 +19,9 @@ Every function follows one piece of the reference (paths relative to the referen
   src/bindings.cpp:1726-1759 then :777-806 (``g * (1 - t^2)``, src/cpu_kernel.cpp:500-514).
 * ``matmul_axpby`` / ``newton_schulz``   - the Newton-Schulz chain of the Muon optimizer,
   aakaar/optim.py:533-542 (matmul + scalar multiply + add, composed as the reference composes them).
+* ``im2col_2d`` / ``col2im_2d`` / ``conv2d_forward_backward`` - the convolution fallback that calls
+  the matmul path: src/conv2d_kernel.cpp:7-70 (and src/conv_kernel.cpp:15-60 for 1-D = one row),
+  aakaar/__init__.py:289-307, 330-352.
 * ``tanh`` / ``mse_loss`` / ``sgd_step`` - src/cpu_kernel.cpp:484-514, aakaar/__init__.py:222-224,
   src/optim_kernels_cpu.cpp:7-28 (support ops of the Linear training step).
 
@@ -48,6 +51,9 @@ __all__ = [
     "matmul_axpby",
     "newton_schulz",
     "muon_step",
+    "im2col_2d",
+    "col2im_2d",
+    "conv2d_forward_backward",
     "reduce_grad_to_shape",
     "linear_forward",
     "tanh",
@@ -239,6 +245,58 @@ def muon_step(param, grad, buf, lr=0.02, momentum=0.95, ns_steps=5, weight_decay
     buf = g if buf is None else np.asarray(buf).astype(acc, copy=False) * acc(momentum) + g * acc(1 - momentum)
     update = newton_schulz(buf, ns_steps, acc).astype(acc) if p.ndim == 2 else buf
     return (p - update * acc(lr)).astype(np.float32), buf.astype(np.float32)
+
+
+def im2col_2d(x, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW):
+    """(B, C, H, W) -> (B, C*KH*KW, OH*OW); row (c, kh, kw), zero outside the input."""
+    x = np.asarray(x)
+    B, C, H, W = x.shape
+    col = np.zeros((B, C, KH, KW, OH, OW), dtype=x.dtype)
+    for kh in range(KH):
+        for kw in range(KW):
+            for oh in range(OH):
+                h = oh * SH - PH + kh * DH
+                if h < 0 or h >= H:
+                    continue
+                for ow in range(OW):
+                    w = ow * SW - PW + kw * DW
+                    if 0 <= w < W:
+                        col[:, :, kh, kw, oh, ow] = x[:, :, h, w]
+    return col.reshape(B, C * KH * KW, OH * OW)
+
+
+def col2im_2d(gcol, C, H, W, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW):
+    """Adjoint of im2col_2d: every input element sums the window entries that read it."""
+    gcol = np.asarray(gcol)
+    B = gcol.shape[0]
+    g = gcol.reshape(B, C, KH, KW, OH, OW)
+    gx = np.zeros((B, C, H, W), dtype=np.float64)
+    for kh in range(KH):
+        for kw in range(KW):
+            for oh in range(OH):
+                h = oh * SH - PH + kh * DH
+                if h < 0 or h >= H:
+                    continue
+                for ow in range(OW):
+                    w = ow * SW - PW + kw * DW
+                    if 0 <= w < W:
+                        gx[:, :, h, w] += g[:, :, kh, kw, oh, ow]
+    return gx.astype(np.float32)
+
+
+def conv2d_forward_backward(x, weight, grad_out, stride=(1, 1), padding=(0, 0), dilation=(1, 1), acc=np.float32):
+    """y = conv2d(x, weight) as unfold + matmul, and (dx, dweight) for a given dy."""
+    (SH, SW), (PH, PW), (DH, DW) = stride, padding, dilation
+    C_out, C_in, KH, KW = weight.shape
+    B, _, H, W = x.shape
+    OH = (H + 2 * PH - DH * (KH - 1) - 1) // SH + 1
+    OW = (W + 2 * PW - DW * (KW - 1) - 1) // SW + 1
+    col = im2col_2d(x, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW)
+    w_flat = np.ascontiguousarray(weight).reshape(1, C_out, C_in * KH * KW)
+    y = matmul_forward(w_flat, col, acc).reshape(B, C_out, OH, OW)
+    dw_flat, dcol = matmul_backward(w_flat, col, np.ascontiguousarray(grad_out).reshape(B, C_out, OH * OW), acc)
+    dx = col2im_2d(dcol, C_in, H, W, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW)
+    return y, dx, dw_flat.reshape(weight.shape)
 
 
 # ---------------------------------------------------------------- Linear training step support

@@ -156,6 +156,23 @@ for step_seed in (46, 47):
     P = P - X * 0.02
 out["muon_p2"] = P.to_numpy()
 
+# 8e. the convolution fallback that calls the matmul path (aakaar/__init__.py:289-307, 330-352), composed from
+#     the reference's own im2col + reshape + matmul ops, forward and backward
+xc, wc = normal((3, 4, 19), 51), uniform((5, 4, 3), 52)
+X1, W1 = T(xc, True), T(wc, True)
+L_out = (19 + 2 * 2 - 2 * (3 - 1) - 1) // 2 + 1
+Y1 = ref.cpu_matmul(W1.reshape([1, 5, 12]), ref.im2col_1d(X1, 3, 2, 2, 2, L_out))
+dy1 = normal(tuple(Y1.shape), 53)
+Y1.backward(T(dy1))
+out["conv1d_y"], out["conv1d_dx"], out["conv1d_dw"] = Y1.to_numpy(), X1.grad.to_numpy(), W1.grad.to_numpy()
+xc2, wc2 = normal((2, 3, 9, 11), 54), uniform((4, 3, 3, 2), 55)
+X2, W2 = T(xc2, True), T(wc2, True)
+OH2, OW2 = (9 + 2 * 1 - 1 * (3 - 1) - 1) // 2 + 1, (11 + 2 * 0 - 2 * (2 - 1) - 1) // 1 + 1
+Y2 = ref.cpu_matmul(W2.reshape([1, 4, 18]), ref.im2col_2d(X2, 3, 2, 2, 1, 1, 0, 1, 2, OH2, OW2)).reshape([2, 4, OH2, OW2])
+dy2 = normal(tuple(Y2.shape), 56)
+Y2.backward(T(dy2))
+out["conv2d_y"], out["conv2d_dx"], out["conv2d_dw"] = Y2.to_numpy(), X2.grad.to_numpy(), W2.grad.to_numpy()
+
 # 9. error behaviour of the reference (messages the C ABI reproduces)
 errs = {}
 def err_of(fn):

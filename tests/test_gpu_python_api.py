@@ -240,3 +240,37 @@ def test_muon_optimizer_matches_reference(ak):
     assert rel_fro(vec.to_numpy(), v_ref) < TOL_FP32
     opt.zero_grad()
     assert P.grad is None
+
+
+@pytest.mark.parametrize("tf32,tol", [(False, TOL_FP32), (True, TOL_TF32)])
+def test_conv_fallback_callers(ak, tf32, tol):
+    # conv1d / conv2d as unfold + ONE broadcast-batched matmul, forward and backward, against the vectors of
+    # the reference's own im2col + matmul composition
+    G, META = load_golden()
+    ak.set_tf32(tf32)
+    try:
+        X1 = ak.from_numpy(normal((3, 4, 19), 51), requires_grad=True)
+        W1 = ak.from_numpy(uniform((5, 4, 3), 52), requires_grad=True)
+        Y1 = ak.conv1d(X1, W1, stride=2, padding=2, dilation=2)
+        assert Y1.shape == list(G["conv1d_y"].shape)
+        Y1.backward(ak.from_numpy(normal(tuple(Y1.shape), 53)))
+        assert rel_fro(Y1.to_numpy(), G["conv1d_y"]) < tol
+        assert rel_fro(X1.grad.to_numpy(), G["conv1d_dx"]) < tol and rel_fro(W1.grad.to_numpy(), G["conv1d_dw"]) < tol
+        X2 = ak.from_numpy(normal((2, 3, 9, 11), 54), requires_grad=True)
+        W2 = ak.from_numpy(uniform((4, 3, 3, 2), 55), requires_grad=True)
+        Y2 = ak.conv2d(X2, W2, stride=(2, 1), padding=(1, 0), dilation=(1, 2))
+        assert Y2.shape == list(G["conv2d_y"].shape)
+        Y2.backward(ak.from_numpy(normal(tuple(Y2.shape), 56)))
+        assert rel_fro(Y2.to_numpy(), G["conv2d_y"]) < tol
+        assert rel_fro(X2.grad.to_numpy(), G["conv2d_dx"]) < tol and rel_fro(W2.grad.to_numpy(), G["conv2d_dw"]) < tol
+        # a larger case against the oracle: 3x3, 64 -> 128 channels, 32 x 32 images, batch 8
+        x, w = normal((8, 64, 32, 32), 57), uniform((128, 64, 3, 3), 58) * 0.05
+        dy = normal((8, 128, 32, 32), 59)
+        X, W = ak.from_numpy(x, requires_grad=True), ak.from_numpy(w, requires_grad=True)
+        Y = ak.conv2d(X, W, padding=(1, 1))
+        Y.backward(ak.from_numpy(dy))
+        ry, rdx, rdw = mo.conv2d_forward_backward(x, w, dy, (1, 1), (1, 1), (1, 1), np.float64)
+        assert rel_fro(Y.to_numpy(), ry) < tol
+        assert rel_fro(X.grad.to_numpy(), rdx) < tol and rel_fro(W.grad.to_numpy(), rdw) < tol
+    finally:
+        ak.set_tf32(False)

@@ -137,3 +137,16 @@ def test_muon_steps_match_reference():
     for seed in (46, 47):
         p, buf = mo.muon_step(p, normal((24, 40), seed), buf, lr=0.02, momentum=0.95, ns_steps=5, weight_decay=0.01)
     assert rel_fro(p, G["muon_p2"]) < 1e-5
+
+
+def test_conv_fallback_matches_reference():
+    # 1-D = one image row: stride 2, padding 2, dilation 2
+    x, w = normal((3, 4, 19), 51), uniform((5, 4, 3), 52)
+    y, dx, dw = mo.conv2d_forward_backward(x[:, :, None, :], w[:, :, None, :], normal((3, 5, 10), 53)[:, :, None, :],
+                                           (1, 2), (0, 2), (1, 2))
+    assert rel_fro(y[:, :, 0, :], G["conv1d_y"]) < 2e-6
+    assert rel_fro(dx[:, :, 0, :], G["conv1d_dx"]) < 2e-6 and rel_fro(dw[:, :, 0, :], G["conv1d_dw"]) < 2e-6
+    x2, w2 = normal((2, 3, 9, 11), 54), uniform((4, 3, 3, 2), 55)
+    y2, dx2, dw2 = mo.conv2d_forward_backward(x2, w2, normal(G["conv2d_y"].shape, 56), (2, 1), (1, 0), (1, 2))
+    assert rel_fro(y2, G["conv2d_y"]) < 2e-6
+    assert rel_fro(dx2, G["conv2d_dx"]) < 2e-6 and rel_fro(dw2, G["conv2d_dw"]) < 2e-6
