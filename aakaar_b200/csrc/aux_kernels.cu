@@ -645,67 +645,113 @@ cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
     return cudaGetLastError();
 }
 
-// One thread per output element of `col`, consecutive threads along the window position (coalesced writes;
-// reads are coalesced too when the stride along W is 1).
-__global__ void im2col_kernel(const float* __restrict__ x, float* __restrict__ col, WindowGeom g, size_t total) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const int64_t OHW = g.OH * g.OW;
-    const int64_t rows = g.C * g.KH * g.KW;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t o = (int64_t)(i % (size_t)OHW);
-        size_t r = i / (size_t)OHW;
-        const int64_t row = (int64_t)(r % (size_t)rows);
-        const int64_t b = (int64_t)(r / (size_t)rows);
-        const int kw = (int)(row % g.KW);
-        const int kh = (int)((row / g.KW) % g.KH);
-        const int64_t c = row / (g.KW * g.KH);
-        const int64_t oh = o / g.OW, ow = o - oh * g.OW;
-        const int64_t h = oh * g.SH - g.PH + (int64_t)kh * g.DH;
-        const int64_t w = ow * g.SW - g.PW + (int64_t)kw * g.DW;
-        float v = 0.f;
-        if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = x[((b * g.C + c) * g.H + h) * g.W + w];
-        col[i] = v;
-    }
-}
-// One thread per input element: sums, in (kh, kw) order, the window entries that read it.
-__global__ void col2im_kernel(const float* __restrict__ gc, float* __restrict__ gx, WindowGeom g, size_t total) {
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    const int64_t OHW = g.OH * g.OW;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t w = (int64_t)(i % (size_t)g.W);
-        size_t r = i / (size_t)g.W;
-        const int64_t h = (int64_t)(r % (size_t)g.H);
-        r /= (size_t)g.H;
-        const int64_t c = (int64_t)(r % (size_t)g.C);
-        const int64_t b = (int64_t)(r / (size_t)g.C);
-        const float* base = gc + ((size_t)(b * g.C + c) * g.KH * g.KW) * OHW;
-        float acc = 0.f;
-        for (int kh = 0; kh < g.KH; ++kh) {
-            const int64_t nh = h + g.PH - (int64_t)kh * g.DH;
-            if (nh < 0 || nh % g.SH != 0) continue;
-            const int64_t oh = nh / g.SH;
-            if (oh >= g.OH) continue;
-            for (int kw = 0; kw < g.KW; ++kw) {
-                const int64_t nw = w + g.PW - (int64_t)kw * g.DW;
-                if (nw < 0 || nw % g.SW != 0) continue;
-                const int64_t ow = nw / g.SW;
-                if (ow >= g.OW) continue;
-                acc += base[(size_t)(kh * g.KW + kw) * OHW + oh * g.OW + ow];
+// Unfold: one block per (b, c, kh, kw) row of `col` (blockIdx.x), every thread four consecutive window
+// positions at a time (one 16-byte store): 32-bit index arithmetic, coalesced writes, reads that hit L1 / L2
+// (each input plane is read KH*KW times).
+template <bool VEC>
+__global__ void im2col_kernel(const float* __restrict__ x, float* __restrict__ col, WindowGeom g) {
+    const unsigned row = blockIdx.x;  // ((b * C + c) * KH + kh) * KW + kw
+    const int kw = (int)(row % (unsigned)g.KW);
+    const unsigned r1 = row / (unsigned)g.KW;
+    const int kh = (int)(r1 % (unsigned)g.KH);
+    const unsigned plane = r1 / (unsigned)g.KH;  // b * C + c
+    const int OW = (int)g.OW, OHW = (int)(g.OH * g.OW), H = (int)g.H, W = (int)g.W;
+    const float* xp = x + (size_t)plane * H * W;
+    float* cp = col + (size_t)row * OHW;
+    const int h_off = kh * g.DH - g.PH, w_off = kw * g.DW - g.PW;
+    constexpr int V = VEC ? 4 : 1;
+    for (int o0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; o0 < OHW; o0 += gridDim.y * blockDim.x * V) {
+        float v[V];
+        int oh = o0 / OW, ow = o0 - oh * OW;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const int h = oh * g.SH + h_off, w = ow * g.SW + w_off;
+            v[e] = (h >= 0 && h < H && w >= 0 && w < W) ? __ldg(xp + h * W + w) : 0.f;
+            if (++ow == OW) {
+                ow = 0;
+                ++oh;
             }
         }
-        gx[i] = acc;
+        if (VEC) *reinterpret_cast<float4*>(cp + o0) = make_float4(v[0], v[V > 1 ? 1 : 0], v[V > 2 ? 2 : 0], v[V > 3 ? 3 : 0]);
+        else cp[o0] = v[0];
+    }
+}
+// Fold (adjoint): one block row per (b, c) plane, every thread four consecutive elements of a plane at a time;
+// each sums, in (kh, kw) order, the window entries that read it.
+// S1: both strides are 1 (no divisions on the way back from an input position to the windows that read it).
+template <bool VEC, bool S1>
+__global__ void col2im_kernel(const float* __restrict__ gc, float* __restrict__ gx, WindowGeom g) {
+    const unsigned plane = blockIdx.x;  // b * C + c
+    const int OW = (int)g.OW, OH = (int)g.OH, OHW = OH * OW, H = (int)g.H, W = (int)g.W;
+    const float* base = gc + (size_t)plane * g.KH * g.KW * OHW;
+    float* gp = gx + (size_t)plane * H * W;
+    constexpr int V = VEC ? 4 : 1;
+    for (int i0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; i0 < H * W; i0 += gridDim.y * blockDim.x * V) {
+        float acc[V];
+        int hs[V], ws[V];
+        {
+            int h = i0 / W, w = i0 - h * W;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                acc[e] = 0.f;
+                hs[e] = h;
+                ws[e] = w;
+                if (++w == W) {
+                    w = 0;
+                    ++h;
+                }
+            }
+        }
+        for (int kh = 0; kh < g.KH; ++kh) {
+            int ohs[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {  // window row that reads input row hs[e] through tap kh, or -1
+                const int nh = hs[e] + g.PH - kh * g.DH;
+                int oh = S1 ? nh : nh / g.SH;
+                if (nh < 0 || oh >= OH || (!S1 && oh * g.SH != nh)) oh = -1;
+                ohs[e] = oh;
+            }
+            for (int kw = 0; kw < g.KW; ++kw) {
+                const float* tap = base + (size_t)(kh * g.KW + kw) * OHW;
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    const int nw = ws[e] + g.PW - kw * g.DW;
+                    const int ow = S1 ? nw : nw / g.SW;
+                    if (ohs[e] < 0 || nw < 0 || ow >= OW || (!S1 && ow * g.SW != nw)) continue;
+                    acc[e] += __ldg(tap + ohs[e] * OW + ow);
+                }
+            }
+        }
+        if (VEC) *reinterpret_cast<float4*>(gp + i0) = make_float4(acc[0], acc[V > 1 ? 1 : 0], acc[V > 2 ? 2 : 0], acc[V > 3 ? 3 : 0]);
+        else gp[i0] = acc[0];
     }
 }
 cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaStream_t s) {
-    const size_t total = (size_t)g.B * g.C * g.KH * g.KW * g.OH * g.OW;
-    if (total == 0) return cudaSuccess;
-    im2col_kernel<<<grid_for(total), kThreads, 0, s>>>(x, col, g, total);
+    const size_t rows = (size_t)g.B * g.C * g.KH * g.KW;
+    const size_t ohw = (size_t)g.OH * g.OW;
+    if (rows == 0 || ohw == 0) return cudaSuccess;
+    if (rows > 0x7fffffffull || ohw > 0x7fffffffull || (size_t)g.H * g.W > 0x7fffffffull) return cudaErrorInvalidValue;
+    const bool vec = (ohw & 3) == 0 && (reinterpret_cast<uintptr_t>(col) & 15u) == 0;
+    const size_t per_block = (size_t)kThreads * (vec ? 4 : 1) * 4;  // about four rounds per thread
+    const unsigned gy = (unsigned)std::min<size_t>((ohw + per_block - 1) / per_block, 64);
+    if (vec) im2col_kernel<true><<<dim3((unsigned)rows, gy), kThreads, 0, s>>>(x, col, g);
+    else im2col_kernel<false><<<dim3((unsigned)rows, gy), kThreads, 0, s>>>(x, col, g);
     return cudaGetLastError();
 }
 cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s) {
-    const size_t total = (size_t)g.B * g.C * g.H * g.W;
-    if (total == 0) return cudaSuccess;
-    col2im_kernel<<<grid_for(total), kThreads, 0, s>>>(grad_col, grad_x, g, total);
+    const size_t planes = (size_t)g.B * g.C;
+    const size_t hw = (size_t)g.H * g.W;
+    if (planes == 0 || hw == 0) return cudaSuccess;
+    if (planes > 0x7fffffffull || hw > 0x7fffffffull || (size_t)g.OH * g.OW > 0x7fffffffull) return cudaErrorInvalidValue;
+    const bool vec = (hw & 3) == 0 && (reinterpret_cast<uintptr_t>(grad_x) & 15u) == 0;
+    const size_t per_block = (size_t)kThreads * (vec ? 4 : 1);
+    const unsigned gy = (unsigned)std::min<size_t>((hw + per_block - 1) / per_block, 64);
+    const bool s1 = g.SH == 1 && g.SW == 1;
+    const dim3 grid((unsigned)planes, gy);
+    if (vec && s1) col2im_kernel<true, true><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
+    else if (vec) col2im_kernel<true, false><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
+    else if (s1) col2im_kernel<false, true><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
+    else col2im_kernel<false, false><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
     return cudaGetLastError();
 }
 

@@ -657,6 +657,36 @@ def run_config(args):
         out.update({"workload": f"8192 independent [256x256]@[256x256] products, batch split over {world} rank(s), fwd + dA + dB",
                     "bound": "hbm", "algorithmic_bytes_per_step": bytes_step, "hbm_peak_gbs": peaks["hbm_gbs"],
                     "peak_source": peak_src, "scaling": "strong"})
+    elif args.config == "conv2d":
+        # caller of the path: 3x3 convolution, 64 -> 128 channels, 56 x 56 images, batch 32, as unfold + matmul
+        Bn, Ci, Co, Hh, Ww, Kk = 32, 64, 128, 56, 56, 3
+        xn = normal((Bn, Ci, Hh, Ww), 601, 1.0)
+        wn = uniform((Co, Ci, Kk, Kk), 602) * np.float32(1.0 / np.sqrt(Ci * Kk * Kk))
+        dyn = normal((Bn, Co, Hh, Ww), 603, 1.0)
+        col_b = Bn * Ci * Kk * Kk * Hh * Ww * 4
+        x_b, y_b, w_b = xn.nbytes, dyn.nbytes, wn.nbytes
+        # unfold (x -> col), forward (col, W -> y), dW (dy, col -> dW), dcol (W, dy -> dcol), fold (dcol -> dx)
+        bytes_step = (x_b + col_b) + (col_b + w_b + y_b) + (y_b + col_b + w_b) + (w_b + y_b + col_b) + (col_b + x_b)
+        flop_step = 3 * 2 * Bn * Co * (Ci * Kk * Kk) * (Hh * Ww)
+        for name, tf32 in (("tf32", True), ("fp32_3xtf32", False)):
+            ak.set_tf32(tf32)
+            x = ak.from_numpy(xn, "cuda", requires_grad=True)
+            w = ak.from_numpy(wn, "cuda", requires_grad=True)
+            dy = ak.from_numpy(dyn, "cuda")
+
+            def step():
+                x.zero_grad()
+                w.zero_grad()
+                ak.conv2d(x, w, padding=(1, 1)).backward(dy)
+            ms, launches = timed(step, args.steps, args.warmup)
+            results[name] = {"ms_per_step": ms, "gbs": bytes_step / ms / 1e6, "tflops": flop_step / ms / 1e9,
+                             "frac_of_hbm": bytes_step / ms / 1e6 / peaks["hbm_gbs"],
+                             "gpu_launches_per_step": launches / args.steps}
+        ak.set_tf32(False)
+        out.update({"workload": "conv2d 3x3 pad 1, x[32,64,56,56], w[128,64,3,3]: unfold + [1,128,576]@[32,576,3136], backward to x and w",
+                    "bound": "hbm", "algorithmic_bytes_per_step": bytes_step, "flop_per_step": flop_step,
+                    "bytes_note": "with the unfolded matrix materialised, as in the reference's fallback (9x the input)",
+                    "hbm_peak_gbs": peaks["hbm_gbs"], "peak_source": peak_src, "scaling": "n/a"})
     else:  # c2
         xn = normal((4096, 1024), 201, 1.0)
         tn = normal((4096, 1024), 202, 1.0)
@@ -699,8 +729,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--config", default="sq8192", choices=["sq8192", "c2", "c3", "c5a"],
-                    help="sq8192 = the benchmark; c2 / c3 / c5a = secondary configurations (own JSON format)")
+    ap.add_argument("--config", default="sq8192", choices=["sq8192", "c2", "c3", "c5a", "conv2d"],
+                    help="sq8192 = the benchmark; c2 / c3 / c5a / conv2d = secondary configurations (own JSON format)")
     ap.add_argument("--size", type=int, default=8192, help="square size (profiling only; the benchmark is 8192)")
     ap.add_argument("--profile", default="", choices=["", "tf32", "fp32"],
                     help="profiler capture run: one device phase only, warm-up not forced to 3")
