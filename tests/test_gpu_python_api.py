@@ -274,3 +274,26 @@ def test_conv_fallback_callers(ak, tf32, tol):
         assert rel_fro(X.grad.to_numpy(), rdx) < tol and rel_fro(W.grad.to_numpy(), rdw) < tol
     finally:
         ak.set_tf32(False)
+
+
+def test_conv_modules_with_bias(ak):
+    np.random.seed(7)
+    conv = ak.nn.Conv2d(3, 5, (3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2))
+    np.random.seed(7)
+    w = np.random.uniform(-1 / np.sqrt(18), 1 / np.sqrt(18), (5, 3, 3, 2)).astype(np.float32)
+    b = np.random.uniform(-1 / np.sqrt(18), 1 / np.sqrt(18), (1, 5, 1, 1)).astype(np.float32)
+    np.testing.assert_array_equal(conv.weight.to_numpy(), w)
+    np.testing.assert_array_equal(conv.bias.to_numpy(), b)
+    x = normal((2, 3, 9, 11), 61)
+    X = ak.from_numpy(x, requires_grad=True)
+    y = conv(X)
+    dy = normal(tuple(y.shape), 62)
+    y.backward(ak.from_numpy(dy))
+    ry, rdx, rdw = mo.conv2d_forward_backward(x, w, dy, (2, 1), (1, 0), (1, 2), np.float64)
+    assert rel_fro(y.to_numpy(), ry + b) < TOL_FP32
+    assert rel_fro(X.grad.to_numpy(), rdx) < TOL_FP32 and rel_fro(conv.weight.grad.to_numpy(), rdw) < TOL_FP32
+    assert rel_fro(conv.bias.grad.to_numpy(), dy.sum(axis=(0, 2, 3), keepdims=True)) < TOL_FP32
+    c1 = ak.nn.Conv1d(4, 6, 3, padding=1, bias=False)
+    assert c1(ak.from_numpy(normal((2, 4, 16), 63))).shape == [2, 6, 16] and len(c1.parameters()) == 1
+    with pytest.raises(ValueError, match="input channels"):
+        c1(ak.from_numpy(normal((2, 5, 16), 64)))
