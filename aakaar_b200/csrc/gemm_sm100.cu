@@ -1840,6 +1840,8 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const 
     return r == CUDA_SUCCESS;
 }
 
+bool gemm_sm100_cta_limit_active();
+
 // Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in
 // the stream drains (its set-up overlaps that tail); it synchronises on the predecessor itself
 // (grid_dep_wait) before its first access to global memory. Debug bit 12 launches normally.
@@ -1855,7 +1857,10 @@ void launch_pdl(K kern, int grid, int threads, int smem, cudaStream_t stream, co
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = g_pdl_off ? 0 : 1;
+    static const bool env_off = std::getenv("AKR_B200_NO_PDL") != nullptr;  // A/B switch for measurements
+    // Not while a CTA limit is set: that is the phase in which a collective runs beside the GEMM, and there an
+    // early-started GEMM measured 6 % slower (2 GPUs: 3.45-3.67 ms against 3.27-3.40 ms for dB + all-reduce + dA).
+    cfg.numAttrs = (g_pdl_off || env_off || gemm_sm100_cta_limit_active()) ? 0 : 1;
     cudaLaunchKernelEx(&cfg, kern, kp);
 }
 
@@ -2034,6 +2039,9 @@ void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms) {
 }
 
 void gemm_sm100_set_cta_limit(int ctas) { g_cta_limit = ctas > 0 ? ctas : 0; }
+namespace {
+bool gemm_sm100_cta_limit_active() { return g_cta_limit > 0; }
+}  // namespace
 
 int gemm_sm100_num_ctas() {
     static int sms = 0;
@@ -2271,7 +2279,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = g_pdl_off ? 0 : 1;
+    cfg.numAttrs = (g_pdl_off || gemm_sm100_cta_limit_active()) ? 0 : 1;
     if (vec) cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<true>, rp);
     else cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<false>, rp);
     cudaError_t e = cudaGetLastError();
