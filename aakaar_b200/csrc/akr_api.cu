@@ -1030,7 +1030,14 @@ AKR_API int akr_contiguous(const akr_view* src, float* dst, void* stream) {
     AKR_LAUNCH(launch_gather(to_strided(src), dst, (cudaStream_t)stream), "gather launch");
 }
 
+static int binary_op(const akr_view* a, const akr_view* b, akr_view* out, void* stream, bool multiply);
 AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* stream) {
+    return binary_op(a, b, out, stream, false);
+}
+AKR_API int akr_mul(const akr_view* a, const akr_view* b, akr_view* out, void* stream) {
+    return binary_op(a, b, out, stream, true);
+}
+static int binary_op(const akr_view* a, const akr_view* b, akr_view* out, void* stream, bool multiply) {
     int rc;
     if ((rc = check_view(a, "add a", 0)) != AKR_OK) return rc;
     if ((rc = check_view(b, "add b", 0)) != AKR_OK) return rc;
@@ -1053,7 +1060,7 @@ AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* s
         if (out->shape[i] != 1 && out->stride[i] != expect) return fail(AKR_ERR_INVALID, "add: output must be contiguous");
         expect *= out->shape[i];
     }
-    AKR_LAUNCH(launch_add(sa, sb, (float*)out->data, nd, out->shape, (cudaStream_t)stream), "add launch");
+    AKR_LAUNCH(launch_add(sa, sb, (float*)out->data, nd, out->shape, (cudaStream_t)stream, multiply), "add launch");
 }
 
 AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream) {

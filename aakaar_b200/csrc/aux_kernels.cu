@@ -204,6 +204,7 @@ struct AddArgs {
     int64_t total;
 };
 
+template <bool MUL>
 __global__ void add_kernel(const AddArgs p) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
@@ -214,16 +215,18 @@ __global__ void add_kernel(const AddArgs p) {
             ao += idx * p.as[d];
             bo += idx * p.bs[d];
         }
-        p.out[i] = __ldg(p.a + ao) + __ldg(p.b + bo);
+        p.out[i] = MUL ? __ldg(p.a + ao) * __ldg(p.b + bo) : __ldg(p.a + ao) + __ldg(p.b + bo);
     }
 }
 
+template <bool MUL>
 __global__ void add_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                 float4* __restrict__ o, int64_t n4) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 x = __ldg(a + i), y = __ldg(b + i);
-        o[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+        o[i] = MUL ? make_float4(x.x * y.x, x.y * y.y, x.z * y.z, x.w * y.w)
+                   : make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
     }
 }
 
@@ -486,7 +489,7 @@ cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s) {
 }
 
 cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
-                       const int64_t* shape, cudaStream_t s) {
+                       const int64_t* shape, cudaStream_t s, bool multiply) {
     AddArgs p;
     p.a = a.ptr;
     p.b = b.ptr;
@@ -510,12 +513,14 @@ cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, i
     }
     if (p.total == 0) return cudaSuccess;
     if (flat && (p.total & 3) == 0 && (((uintptr_t)a.ptr | (uintptr_t)b.ptr | (uintptr_t)out) & 15u) == 0) {
-        add_flat_kernel<<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(
-            reinterpret_cast<const float4*>(a.ptr), reinterpret_cast<const float4*>(b.ptr),
-            reinterpret_cast<float4*>(out), p.total / 4);
+        const float4 *a4 = reinterpret_cast<const float4*>(a.ptr), *b4 = reinterpret_cast<const float4*>(b.ptr);
+        float4* o4 = reinterpret_cast<float4*>(out);
+        if (multiply) add_flat_kernel<true><<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(a4, b4, o4, p.total / 4);
+        else add_flat_kernel<false><<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(a4, b4, o4, p.total / 4);
         return cudaGetLastError();
     }
-    add_kernel<<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
+    if (multiply) add_kernel<true><<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
+    else add_kernel<false><<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
     return cudaGetLastError();
 }
 

@@ -47,7 +47,7 @@ struct StridedView {
 cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s);
 // out[i] = a[bcast(i)] + b[bcast(i)], out contiguous with shape `shape`
 cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
-                       const int64_t* shape, cudaStream_t s);
+                       const int64_t* shape, cudaStream_t s, bool multiply = false);
 // out (contiguous `out_shape`, same rank as g, dims of size 1 where reduced) = sum of g over reduced dims
 cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float* out, cudaStream_t s);
 // Column sums of a dense [rows][cols] matrix (the bias gradient of a Linear layer): out[c] = sum_r g[r][c].

@@ -46,7 +46,7 @@ void attach(const TensorPtr& out, const char* name, std::vector<TensorPtr> input
 
 TensorPtr op_contiguous(const TensorPtr& t);
 
-TensorPtr op_add_raw(const TensorPtr& a, const TensorPtr& b) {
+TensorPtr op_add_raw(const TensorPtr& a, const TensorPtr& b, bool multiply = false) {
     require_cuda(a, "add");
     require_f32(a, "add");
     require_cuda(b, "add");
@@ -61,7 +61,7 @@ TensorPtr op_add_raw(const TensorPtr& a, const TensorPtr& b) {
     }
     auto out = make_cuda(shape);
     akr_view va = a->view(), vb = b->view(), vo = out->view();
-    check(akr_add(&va, &vb, &vo, nullptr));
+    check((multiply ? akr_mul : akr_add)(&va, &vb, &vo, nullptr));
     return out;
 }
 
@@ -82,6 +82,20 @@ TensorPtr op_add(const TensorPtr& a, const TensorPtr& b) {
         const auto sa = a->shape, sb = b->shape;
         attach(out, "add", {a, b}, [sa, sb](TensorPtr g) {
             return std::vector<TensorPtr>{op_sum_to(g, sa), op_sum_to(g, sb)};
+        });
+    }
+    return out;
+}
+
+// Elementwise product with broadcasting; gradients g * b and g * a, each summed back to its operand's shape.
+TensorPtr op_mul(const TensorPtr& a, const TensorPtr& b) {
+    auto out = op_add_raw(a, b, true);
+    if (needs_graph(a, b)) {
+        attach(out, "mul", {a, b}, [a, b](TensorPtr g) {
+            TensorPtr ga, gb;
+            if (a->requires_grad) ga = op_sum_to(op_add_raw(g, b, true), a->shape);
+            if (b->requires_grad) gb = op_sum_to(op_add_raw(g, a, true), b->shape);
+            return std::vector<TensorPtr>{ga, gb};
         });
     }
     return out;
@@ -765,6 +779,7 @@ PYBIND11_MODULE(_C, m) {
         .def("__radd__", [](TensorPtr a, float s) { return op_add(a, scalar_tensor(s)); })
         .def("__sub__", [](TensorPtr a, TensorPtr b) { return op_sub(a, b); })
         .def("__sub__", [](TensorPtr a, float s) { return op_add(a, scalar_tensor(-s)); })
+        .def("__mul__", [](TensorPtr a, TensorPtr b) { return op_mul(a, b); })
         .def("__mul__", [](TensorPtr a, float s) { return op_scale(a, s); })
         .def("__rmul__", [](TensorPtr a, float s) { return op_scale(a, s); })
         .def("__truediv__", [](TensorPtr a, float s) { return op_scale(a, 1.0f / s); })

@@ -224,6 +224,8 @@ AKR_API int64_t akr_launch_count(int reset);
  *   sgd_step      : src/optim_kernels.cu:21-55 (plain / weight decay / momentum) */
 AKR_API int akr_contiguous(const akr_view* src, float* dst, void* stream);
 AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* stream);
+/* out = a * b elementwise with the broadcasting of akr_add (mul_broadcast_kernel, src/elementwise_kernel.cu). */
+AKR_API int akr_mul(const akr_view* a, const akr_view* b, akr_view* out, void* stream);
 AKR_API int akr_sum_to(const akr_view* grad, akr_view* out, void* stream);
 AKR_API int akr_scale(const float* x, float alpha, float* y, size_t n, void* stream);
 AKR_API int akr_tanh_fwd(const float* x, float* y, size_t n, void* stream);

@@ -173,6 +173,31 @@ dy2 = normal(tuple(Y2.shape), 56)
 Y2.backward(T(dy2))
 out["conv2d_y"], out["conv2d_dx"], out["conv2d_dw"] = Y2.to_numpy(), X2.grad.to_numpy(), W2.grad.to_numpy()
 
+# 8f. the README's training example (README.md:101-137): Linear(1,16) -> tanh -> Linear(16,1) on sin(x), its own
+#     mse (diff * diff).sum() / n, plain SGD lr 0.05, 300 epochs; weights drawn as aakaar/nn.py:5-13 draws them
+np.random.seed(0)
+xs = np.linspace(-3, 3, 64).reshape(64, 1).astype(np.float32)
+Xs, Ys = T(xs), T(np.sin(xs).astype(np.float32))
+params = []
+for fin, fout in ((1, 16), (16, 1)):
+    lim = 1.0 / np.sqrt(fin)
+    params.append(T(np.random.uniform(-lim, lim, (fin, fout)).astype(np.float32), True))
+    params.append(T(np.zeros((1, fout), dtype=np.float32), True))
+losses = []
+for epoch in range(300):
+    for p_ in params:
+        p_.zero_grad()
+    h_ = (ref.cpu_matmul(Xs, params[0]) + params[1]).tanh()
+    diff = (ref.cpu_matmul(h_, params[2]) + params[3]) - Ys
+    loss_ = (diff * diff).sum() / 64
+    loss_.backward()
+    losses.append(float(loss_.item()))
+    ref._set_grad_enabled(False)
+    for p_ in params:
+        p_.copy_(p_ - p_.grad * 0.05)
+    ref._set_grad_enabled(True)
+out["readme_losses"] = np.array([losses[0], losses[1], losses[2], losses[99], losses[299]], dtype=np.float64)
+
 # 9. error behaviour of the reference (messages the C ABI reproduces)
 errs = {}
 def err_of(fn):

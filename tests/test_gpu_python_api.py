@@ -297,3 +297,37 @@ def test_conv_modules_with_bias(ak):
     assert c1(ak.from_numpy(normal((2, 4, 16), 63))).shape == [2, 6, 16] and len(c1.parameters()) == 1
     with pytest.raises(ValueError, match="input channels"):
         c1(ak.from_numpy(normal((2, 5, 16), 64)))
+
+
+def test_readme_training_example(ak):
+    # README.md:101-137 of the reference, verbatim apart from the import: K = 1 and N = 1 products, the
+    # example's own mse through tensor * tensor, 300 SGD steps; losses against the reference's own run
+    G, META = load_golden()
+    from aakaar_b200.nn import Linear
+    from aakaar_b200.optim import SGD
+    np.random.seed(0)
+    N = 64
+    x_np = np.linspace(-3, 3, N).reshape(N, 1).astype(np.float32)
+    y_np = np.sin(x_np).astype(np.float32)
+    x, y = ak.from_numpy(x_np), ak.from_numpy(y_np)
+    fc1, fc2 = Linear(1, 16), Linear(16, 1)
+
+    def forward(x):
+        return fc2(fc1(x).tanh())
+
+    def mse_loss(pred, target):
+        diff = pred - target
+        return (diff * diff).sum() / pred.size
+
+    opt = SGD(fc1.parameters() + fc2.parameters(), lr=0.05)
+    losses = []
+    for epoch in range(300):
+        opt.zero_grad()
+        loss = mse_loss(forward(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    got = np.array([losses[0], losses[1], losses[2], losses[99], losses[299]])
+    np.testing.assert_allclose(got[:3], G["readme_losses"][:3], rtol=1e-5)
+    np.testing.assert_allclose(got[3:], G["readme_losses"][3:], rtol=2e-3)   # 100 - 300 chained fp32 steps
+    assert got[-1] < 0.05 * got[0]
