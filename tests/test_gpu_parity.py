@@ -607,3 +607,35 @@ def test_newton_schulz_chain_with_fused_epilogues(mode, tol):
     assert rel_fro(X.to_numpy(), ref) < 20 * tol    # five chained iterations amplify the rounding of each product
     s = np.linalg.svd(X.to_numpy().astype(np.float64), compute_uv=False)
     assert 0.5 < s.min() and s.max() < 1.5          # singular values pushed towards 1
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_random_mid_size_shapes_sampled(mode, tol):
+    # Sizes that reach the CTA-pair, 256 x 256 and split-contraction kernels (ragged edges, K not a multiple of
+    # the k-block, batches, transposed operands, bias / addend epilogues); sampled rows against float64.
+    rng = np.random.Generator(np.random.PCG64(777 + mode))
+    for case in range(10):
+        M, N = int(rng.integers(129, 2600)), int(rng.integers(129, 2600))
+        K = int(rng.integers(64, 6000)) if case % 3 else int(rng.integers(6000, 40000))
+        if case % 3 == 0:
+            M, N = int(rng.integers(64, 600)), int(rng.integers(64, 600))     # long contraction, small output
+        nb = int(rng.integers(1, 3)) if M * N * K < 2e9 else 1
+        ta, tb = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        a = uniform((nb, K, M) if ta else (nb, M, K), 1000 + case)
+        b = uniform((N, K) if tb else (K, N), 2000 + case)
+        A, B = dev(a), dev(b)
+        Av = A.transpose(1, 2) if ta else A
+        Bv = B.transpose(0, 1) if tb else B
+        an = np.swapaxes(a, 1, 2) if ta else a
+        bn = b.T if tb else b
+        rows = sorted(set(int(r) for r in rng.integers(0, M, 5)) | {0, M - 1})
+        ref = an[:, rows].astype(np.float64) @ bn.astype(np.float64)
+        what = (case, M, N, K, nb, ta, tb)
+        c = cabi.matmul_fwd(Av, Bv, mode=mode).to_numpy()
+        assert rel_fro(c[:, rows], ref) < tol, what
+        d = normal((nb, M, N), 3000 + case)
+        c2 = cabi.matmul_axpby(Av, Bv, 0.75, -1.5, dev(d), mode=mode).to_numpy()
+        assert rel_fro(c2[:, rows], 0.75 * ref - 1.5 * d[:, rows]) < tol, what
+        bias = normal((1, N), 4000 + case)
+        c3 = cabi.matmul_fwd(Av, Bv, bias=dev(bias), mode=mode).to_numpy()
+        assert rel_fro(c3[:, rows], ref + bias) < tol, what
