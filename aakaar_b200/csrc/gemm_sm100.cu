@@ -1444,12 +1444,15 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
 //   (cp.async.bulk.tensor ... .cta_group::2, one destination CTA per copy, no multicast);
 //   leader: warp 1 issues the MMAs; tcgen05.commit signals "stage free" / "accumulator complete" to
 //   both CTAs; warps 2..9 of each CTA drain its 128 rows.
-constexpr int DUO_STAGES = 6;
+constexpr int DUO_STAGES = 6;      // ring of load stages when a pair computes several tiles
+constexpr int DUO_STAGES_MAX = 7;  // one tile per pair: the epilogue staging area is a seventh stage until the
+                                   // main loop is over (nothing is loaded ahead for a next tile)
 constexpr int DUO_A_BYTES = 128 * BK * 4, DUO_B_BYTES = 128 * BK * 4;
 constexpr int DUO_STAGE_BYTES = DUO_A_BYTES + DUO_B_BYTES;
 constexpr int DUO_THREADS = 64 + 256;
 constexpr int DUO_EPI_WARPS = 8;
-constexpr int DUO_SMEM = DUO_STAGES * DUO_STAGE_BYTES + DUO_EPI_WARPS * EPI_STAGE_BYTES + 256 + 1024;
+static_assert(DUO_EPI_WARPS * EPI_STAGE_BYTES == DUO_STAGE_BYTES, "the staging area doubles as a load stage");
+constexpr int DUO_SMEM = DUO_STAGES_MAX * DUO_STAGE_BYTES + 256 + 1024;
 
 template <int MAJA, int MAJB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DUO_THREADS, 1)
@@ -1459,16 +1462,16 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    constexpr int S = DUO_STAGES;
-    constexpr int EPI_BYTES = DUO_EPI_WARPS * EPI_STAGE_BYTES;  // staging (1024-byte aligned) before the barriers
-    uint8_t* epi_stage_base = smem + S * DUO_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * DUO_STAGE_BYTES + EPI_BYTES);
-    const uint32_t bar_base = smem_base + S * DUO_STAGE_BYTES + EPI_BYTES;
+    constexpr int SM = DUO_STAGES_MAX;
+    // [6 stages][staging area = 7th stage][barriers]
+    uint8_t* epi_stage_base = smem + DUO_STAGES * DUO_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM * DUO_STAGE_BYTES);
+    const uint32_t bar_base = smem_base + SM * DUO_STAGE_BYTES;
     auto ready_bar = [&](int s) { return bar_base + 8u * s; };             // leader: both CTAs' tiles landed
-    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };       // local: stage may be refilled
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };     // local: accumulator complete
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };  // leader: both CTAs drained it
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    auto empty_bar = [&](int s) { return bar_base + 8u * (SM + s); };      // local: stage may be refilled
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * SM + b); };    // local: accumulator complete
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * SM + 2 + b); };  // leader: both CTAs drained it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SM + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -1477,9 +1480,10 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     const bool leader = rank == 0;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    const int S = p.total_tiles <= num_pairs ? DUO_STAGES_MAX : DUO_STAGES;  // grid-uniform
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < SM; ++s) {
             ptx::mbar_init(ready_bar(s), 1);  // the leader's expect-tx arrive, completed by both CTAs' bytes
             ptx::mbar_init(empty_bar(s), 1);
         }
@@ -1628,7 +1632,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         const bool vec = p.vec_ok != 0;
         const bool use_tma = p.c_tma != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
-        const uint32_t slab_tile_addr = smem_base + S * DUO_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        const uint32_t slab_tile_addr = smem_base + DUO_STAGES * DUO_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
         int local = 0;
         bool ok = true;
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
