@@ -334,6 +334,37 @@ __global__ void tanh_fwd_kernel(const float* __restrict__ x, float* __restrict__
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = tanhf(x[i]);
 }
+// 16-byte variants for dense, aligned arrays whose length is a multiple of four.
+__global__ void tanh_fwd_vec_kernel(const float4* __restrict__ x, float4* __restrict__ y, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 v = x[i];
+        y[i] = make_float4(tanhf(v.x), tanhf(v.y), tanhf(v.z), tanhf(v.w));
+    }
+}
+__global__ void tanh_bwd_vec_kernel(const float4* __restrict__ g, const float4* __restrict__ y,
+                                    float4* __restrict__ dx, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 t = y[i], q = g[i];
+        dx[i] = make_float4(q.x * (1.0f - t.x * t.x), q.y * (1.0f - t.y * t.y), q.z * (1.0f - t.z * t.z),
+                            q.w * (1.0f - t.w * t.w));
+    }
+}
+// Plain SGD (no momentum, optional weight decay), 16 bytes per thread and round.
+__global__ void sgd_plain_vec_kernel(float4* __restrict__ p, const float4* __restrict__ grad, float lr, float wd,
+                                     size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 w = p[i];
+        float4 g = grad[i];
+        if (wd != 0.0f) {
+            g.x += w.x * wd; g.y += w.y * wd; g.z += w.z * wd; g.w += w.w * wd;
+        }
+        w.x -= g.x * lr; w.y -= g.y * lr; w.z -= g.z * lr; w.w -= g.w * lr;
+        p[i] = w;
+    }
+}
 __global__ void tanh_bwd_kernel(const float* __restrict__ g, const float* __restrict__ y,
                                 float* __restrict__ dx, size_t n) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -580,12 +611,18 @@ cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s) {
 }
 cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    tanh_fwd_kernel<<<grid_for(n), kThreads, 0, s>>>(x, y, n);
+    if ((n & 3) == 0 && (((uintptr_t)x | (uintptr_t)y) & 15u) == 0)
+        tanh_fwd_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((const float4*)x, (float4*)y, n / 4);
+    else
+        tanh_fwd_kernel<<<grid_for(n), kThreads, 0, s>>>(x, y, n);
     return cudaGetLastError();
 }
 cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    tanh_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(g, y, dx, n);
+    if ((n & 3) == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)dx) & 15u) == 0)
+        tanh_bwd_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((const float4*)g, (const float4*)y, (float4*)dx, n / 4);
+    else
+        tanh_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(g, y, dx, n);
     return cudaGetLastError();
 }
 cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
@@ -770,6 +807,10 @@ cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float mom
                        float dampening, int nesterov, int has_momentum, int vel_init, size_t n,
                        cudaStream_t s) {
     if (n == 0) return cudaSuccess;
+    if (!has_momentum && (n & 3) == 0 && (((uintptr_t)p | (uintptr_t)g) & 15u) == 0) {
+        sgd_plain_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((float4*)p, (const float4*)g, lr, wd, n / 4);
+        return cudaGetLastError();
+    }
     sgd_kernel<<<grid_for(n), kThreads, 0, s>>>(p, g, vel, lr, momentum, wd, dampening, nesterov,
                                                  has_momentum, vel_init, n);
     return cudaGetLastError();
