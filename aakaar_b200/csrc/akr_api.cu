@@ -1157,7 +1157,16 @@ AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* g
     return AKR_OK;
 }
 
+static int mse_forward(const float* pred, const float* target, float* loss_out, float* dpred, size_t n, void* stream);
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream) {
+    return mse_forward(pred, target, loss_out, nullptr, n, stream);
+}
+AKR_API int akr_mse_fwd_grad(const float* pred, const float* target, float* loss_out, float* dpred, size_t n,
+                             void* stream) {
+    if (!dpred) return fail(AKR_ERR_INVALID, "mse_fwd_grad: null gradient buffer");
+    return mse_forward(pred, target, loss_out, dpred, n, stream);
+}
+static int mse_forward(const float* pred, const float* target, float* loss_out, float* dpred, size_t n, void* stream) {
     if (n == 0) return fail(AKR_ERR_RUNTIME, "MSELoss: cannot reduce an empty tensor");
     DeviceState* st = nullptr;
     int rc = need_gpu(&st);
@@ -1167,7 +1176,7 @@ AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out,
         std::lock_guard<std::mutex> lock(st->mu);
         if ((rc = ws_get(st, WS_MISC, 4096 * sizeof(float), &partials)) != AKR_OK) return rc;
     }
-    cudaError_t e = launch_mse_fwd(pred, target, loss_out, (float*)partials, n, (cudaStream_t)stream);
+    cudaError_t e = launch_mse_fwd(pred, target, loss_out, (float*)partials, n, (cudaStream_t)stream, dpred);
     if (e != cudaSuccess) return cuda_fail(e, "mse launch");
     st->launches += 2;
     return AKR_OK;

@@ -283,6 +283,7 @@ __global__ void colsum_partial_kernel(const float* __restrict__ g, int64_t rows,
     const int64_t r1 = min(rows, r0 + rows_per_chunk);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (col + 3 < cols && (cols & 3) == 0) {
+#pragma unroll 8
         for (int64_t r = r0 + warp; r < r1; r += 8) {
             const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * cols + col));
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -389,13 +390,15 @@ __device__ __forceinline__ float block_sum(float v) {
     return s;  // valid in thread 0
 }
 
+// dp (optional): the gradient of the mean with respect to p, 2 (p - t) / n, written in the same pass.
 __global__ void mse_partial_kernel(const float* __restrict__ p, const float* __restrict__ t,
-                                   float* __restrict__ partials, size_t n) {
+                                   float* __restrict__ partials, float* __restrict__ dp, float two_over_n, size_t n) {
     float acc = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float d = t ? p[i] - t[i] : p[i];
         acc = fmaf(d, d, acc);
+        if (dp) dp[i] = d * two_over_n;
     }
     const float s = block_sum(acc);
     if (threadIdx.x == 0) partials[blockIdx.x] = s;
@@ -626,10 +629,10 @@ cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n,
     return cudaGetLastError();
 }
 cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
-                           cudaStream_t s) {
+                           cudaStream_t s, float* dp) {
     int blocks = grid_for(n);
     if (blocks > 1024) blocks = 1024;
-    mse_partial_kernel<<<blocks, kThreads, 0, s>>>(p, t, partials, n);
+    mse_partial_kernel<<<blocks, kThreads, 0, s>>>(p, t, partials, dp, 2.0f * (1.0f / (float)n), n);
     mse_final_kernel<<<1, kThreads, 0, s>>>(partials, blocks, (float)n, loss_out);
     return cudaGetLastError();
 }

@@ -84,7 +84,7 @@ cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s);
 cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n, cudaStream_t s);
 // loss_out[0] = sum((p-t)^2)/n ; uses `partials` (>= 1024 floats) as scratch
 cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
-                           cudaStream_t s);
+                           cudaStream_t s, float* dp = nullptr);
 cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
                            cudaStream_t s);
 cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float momentum, float wd,

@@ -22,6 +22,9 @@ using namespace akrhost;
 namespace {
 
 bool g_grad_enabled = true;
+// The all-ones gradient tensor_backward creates for a scalar root (null otherwise): a node that sees it knows
+// its incoming gradient is exactly 1 without reading device memory.
+const void* g_unit_root_grad = nullptr;
 
 enum class DTypeEnum : int { float32 = AKR_DTYPE_F32, float64 = AKR_DTYPE_F64, int32 = AKR_DTYPE_I32, int64 = AKR_DTYPE_I64 };
 
@@ -404,13 +407,19 @@ TensorPtr op_mse(const TensorPtr& pred, const TensorPtr& target) {
     if (!pred->is_contiguous() || !target->is_contiguous())
         throw std::invalid_argument("MSELoss requires contiguous tensors. Call .contiguous() first.");
     auto out = make_cuda({1});
-    check(akr_mse_fwd(pred->data, target->data, out->data, (size_t)pred->size, nullptr));
     if (needs_graph(pred)) {
-        attach(out, "mse", {pred}, [pred, target](TensorPtr g) {
+        // The gradient for an incoming gradient of 1 is written in the forward pass; backward() from this loss
+        // (its usual place, the root) then has nothing left to compute.
+        auto dp1 = make_cuda(pred->shape);
+        check(akr_mse_fwd_grad(pred->data, target->data, out->data, dp1->data, (size_t)pred->size, nullptr));
+        attach(out, "mse", {pred}, [pred, target, dp1](TensorPtr g) {
+            if (g.get() == g_unit_root_grad) return std::vector<TensorPtr>{dp1};
             auto dp = make_cuda(pred->shape);
             check(akr_mse_bwd(pred->data, target->data, g->data, dp->data, (size_t)pred->size, nullptr));
             return std::vector<TensorPtr>{dp};
         });
+    } else {
+        check(akr_mse_fwd(pred->data, target->data, out->data, (size_t)pred->size, nullptr));
     }
     return out;
 }
@@ -439,6 +448,7 @@ void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_g
         require_cuda(root, "backward");
         grad_output = make_cuda(root->shape);
         check(akr_fill(grad_output->data, 1.0f, 1, nullptr));
+        g_unit_root_grad = grad_output.get();
     }
     std::vector<TensorPtr> topo;
     std::unordered_set<Tensor*> seen;
@@ -509,9 +519,11 @@ void tensor_backward(const TensorPtr& root, TensorPtr grad_output, bool retain_g
         }
     } catch (...) {
         g_grad_enabled = prev;
+        g_unit_root_grad = nullptr;
         throw;
     }
     g_grad_enabled = prev;
+    g_unit_root_grad = nullptr;
     if (!retain_graph)
         for (auto& t : topo)
             if (t->grad_fn) t->grad_fn->freed = true;

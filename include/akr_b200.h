@@ -246,6 +246,10 @@ AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* g
 /* loss_out[0] = sum((pred - target)^2) / n; target == NULL gives the mean of squares of pred (the Frobenius
  * norm the Muon optimizer divides by, aakaar/optim.py:534). */
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream);
+/* The same, and in the same pass dpred = 2 (pred - target) / n: the gradient of the loss when the incoming
+ * gradient is 1 (a loss at the root of backward()), which saves the backward pass over pred and target. */
+AKR_API int akr_mse_fwd_grad(const float* pred, const float* target, float* loss_out, float* dpred, size_t n,
+                             void* stream);
 AKR_API int akr_mse_bwd(const float* pred, const float* target, const float* grad_scalar, float* dpred,
                 size_t n, void* stream);
 AKR_API int akr_sgd_step(float* param, const float* grad, float* velocity_or_null, float lr, float momentum,
