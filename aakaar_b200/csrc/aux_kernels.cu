@@ -4,12 +4,35 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 
 namespace akr {
 
 namespace {
 
 constexpr int kThreads = 256;
+
+// Every kernel of this file is launched with programmatic stream serialization and starts with dep_sync():
+// it may be scheduled while the kernel before it in the stream drains, lets the kernel after it do the same,
+// and touches global memory only once its predecessor has completed.
+__device__ __forceinline__ void dep_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename K, typename... Args>
+void launch_dep(K kernel, dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    static const bool off = std::getenv("AKR_B200_NO_PDL") != nullptr;
+    cfg.numAttrs = off ? 0 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 int grid_for(size_t n, int per_thread = 4) {
     static int sms = 0;
@@ -46,6 +69,7 @@ struct PackArgs {
 };
 
 __global__ void pack_split_kernel(const PackArgs a) {
+    dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
         const int64_t c = i % a.ld;
@@ -83,6 +107,7 @@ __device__ __forceinline__ void split4(const float4 v, float4& h, float4& l) {
 
 __global__ void split_vec4_kernel(const float4* __restrict__ src, float4* __restrict__ hi,
                                   float4* __restrict__ lo, int64_t n4) {
+    dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     for (; i + 3 * stride < n4; i += 4 * stride) {
@@ -107,6 +132,7 @@ __global__ void split_vec4_kernel(const float4* __restrict__ src, float4* __rest
 constexpr int ST = 16;  // SIMT reference GEMM tile
 
 __global__ void simt_gemm_kernel(const SimtGemm g) {
+    dep_sync();
     __shared__ float As[ST][ST + 1];
     __shared__ float Bs[ST][ST + 1];
     int64_t t = blockIdx.z;
@@ -141,6 +167,7 @@ __global__ void simt_gemm_kernel(const SimtGemm g) {
 // (src/matmul_kernel.cu:219-341); float64 stands in for its cublasDgemm loop (:151-191).
 template <typename T, typename Acc>
 __global__ void simt_gemm_typed_kernel(const SimtGemm g) {
+    dep_sync();
     __shared__ T As[ST][ST + 1];
     __shared__ T Bs[ST][ST + 1];
     const T* A = reinterpret_cast<const T*>(g.A);
@@ -183,6 +210,7 @@ struct GatherArgs {
 };
 
 __global__ void gather_kernel(const GatherArgs a) {
+    dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
         int64_t t = i, off = 0;
@@ -206,6 +234,7 @@ struct AddArgs {
 
 template <bool MUL>
 __global__ void add_kernel(const AddArgs p) {
+    dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total; i += stride) {
         int64_t t = i, ao = 0, bo = 0;
@@ -222,6 +251,7 @@ __global__ void add_kernel(const AddArgs p) {
 template <bool MUL>
 __global__ void add_flat_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                 float4* __restrict__ o, int64_t n4) {
+    dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 x = __ldg(a + i), y = __ldg(b + i);
@@ -242,6 +272,7 @@ struct SumArgs {
 };
 
 __global__ void sum_to_kernel(const SumArgs a) {
+    dep_sync();
     __shared__ float part[8][33];
     const int64_t o = (int64_t)blockIdx.x * 32 + threadIdx.x;
     float acc = 0.f;
@@ -276,6 +307,7 @@ __global__ void sum_to_kernel(const SumArgs a) {
 // of its chunk reading 512 contiguous bytes per row, the 8 warps are combined in shared memory.
 __global__ void colsum_partial_kernel(const float* __restrict__ g, int64_t rows, int64_t cols,
                                       int64_t rows_per_chunk, float* __restrict__ partials) {
+    dep_sync();
     __shared__ float4 part[8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t col = (int64_t)blockIdx.x * 128 + lane * 4;
@@ -316,6 +348,7 @@ __global__ void colsum_partial_kernel(const float* __restrict__ g, int64_t rows,
 // stage 2: out[c] = sum over chunks, in chunk order
 __global__ void colsum_final_kernel(const float* __restrict__ partials, int chunks, int64_t cols,
                                     float* __restrict__ out) {
+    dep_sync();
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) return;
     float s = 0.f;
@@ -324,19 +357,23 @@ __global__ void colsum_final_kernel(const float* __restrict__ partials, int chun
 }
 
 __global__ void scale_kernel(const float* __restrict__ x, float alpha, float* __restrict__ y, size_t n) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = x[i] * alpha;
 }
 __global__ void fill_kernel(float* __restrict__ x, float v, size_t n) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = v;
 }
 __global__ void tanh_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, size_t n) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) y[i] = tanhf(x[i]);
 }
 // 16-byte variants for dense, aligned arrays whose length is a multiple of four.
 __global__ void tanh_fwd_vec_kernel(const float4* __restrict__ x, float4* __restrict__ y, size_t n4) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 v = x[i];
@@ -345,6 +382,7 @@ __global__ void tanh_fwd_vec_kernel(const float4* __restrict__ x, float4* __rest
 }
 __global__ void tanh_bwd_vec_kernel(const float4* __restrict__ g, const float4* __restrict__ y,
                                     float4* __restrict__ dx, size_t n4) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 t = y[i], q = g[i];
@@ -355,6 +393,7 @@ __global__ void tanh_bwd_vec_kernel(const float4* __restrict__ g, const float4* 
 // Plain SGD (no momentum, optional weight decay), 16 bytes per thread and round.
 __global__ void sgd_plain_vec_kernel(float4* __restrict__ p, const float4* __restrict__ grad, float lr, float wd,
                                      size_t n4) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 w = p[i];
@@ -368,6 +407,7 @@ __global__ void sgd_plain_vec_kernel(float4* __restrict__ p, const float4* __res
 }
 __global__ void tanh_bwd_kernel(const float* __restrict__ g, const float* __restrict__ y,
                                 float* __restrict__ dx, size_t n) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float t = y[i];
@@ -393,6 +433,7 @@ __device__ __forceinline__ float block_sum(float v) {
 // dp (optional): the gradient of the mean with respect to p, 2 (p - t) / n, written in the same pass.
 __global__ void mse_partial_kernel(const float* __restrict__ p, const float* __restrict__ t,
                                    float* __restrict__ partials, float* __restrict__ dp, float two_over_n, size_t n) {
+    dep_sync();
     float acc = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -405,6 +446,7 @@ __global__ void mse_partial_kernel(const float* __restrict__ p, const float* __r
 }
 __global__ void mse_final_kernel(const float* __restrict__ partials, int count, float n,
                                  float* __restrict__ out) {
+    dep_sync();
     float acc = 0.f;
     for (int i = threadIdx.x; i < count; i += blockDim.x) acc += partials[i];
     const float s = block_sum(acc);
@@ -413,6 +455,7 @@ __global__ void mse_final_kernel(const float* __restrict__ partials, int count, 
 __global__ void mse_bwd_kernel(const float* __restrict__ p, const float* __restrict__ t,
                                const float* __restrict__ gscalar, float inv_n, float* __restrict__ dp,
                                size_t n) {
+    dep_sync();
     const float scale = 2.0f * inv_n * (gscalar ? gscalar[0] : 1.0f);
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
@@ -422,6 +465,7 @@ __global__ void mse_bwd_kernel(const float* __restrict__ p, const float* __restr
 __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ grad, float* __restrict__ vel,
                            float lr, float momentum, float wd, float dampening, int nesterov,
                            int has_momentum, int vel_init, size_t n) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         float g = grad[i];
@@ -457,7 +501,7 @@ cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t 
     }
     if (dense) {
         const int64_t n4 = total / 4;
-        split_vec4_kernel<<<grid_for((size_t)n4, 2), kThreads, 0, s>>>(
+        launch_dep(split_vec4_kernel, grid_for((size_t)n4, 2), kThreads, s, 
             reinterpret_cast<const float4*>(src.ptr), reinterpret_cast<float4*>(hi),
             reinterpret_cast<float4*>(lo), n4);
         return cudaGetLastError();
@@ -477,7 +521,7 @@ cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t 
     a.row_stride = src.row_stride;
     a.col_stride = src.col_stride;
     a.total = total;
-    pack_split_kernel<<<grid_for((size_t)total, 2), kThreads, 0, s>>>(a);
+    launch_dep(pack_split_kernel, grid_for((size_t)total, 2), kThreads, s, a);
     return cudaGetLastError();
 }
 
@@ -487,7 +531,7 @@ cudaError_t launch_simt_gemm(const SimtGemm& g, cudaStream_t s) {
     if (batch > 65535) return cudaErrorInvalidValue;
     dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, (unsigned)batch);
     if (grid.y > 65535) return cudaErrorInvalidValue;
-    simt_gemm_kernel<<<grid, dim3(ST, ST), 0, s>>>(g);
+    launch_dep(simt_gemm_kernel, grid, dim3(ST, ST), s, g);
     return cudaGetLastError();
 }
 
@@ -498,9 +542,9 @@ cudaError_t launch_simt_gemm_typed(const SimtGemm& g, int dtype, cudaStream_t s)
     dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, (unsigned)batch);
     if (grid.y > 65535) return cudaErrorInvalidValue;
     switch (dtype) {
-        case 1: simt_gemm_typed_kernel<double, double><<<grid, dim3(ST, ST), 0, s>>>(g); break;
-        case 2: simt_gemm_typed_kernel<int, long long><<<grid, dim3(ST, ST), 0, s>>>(g); break;
-        case 3: simt_gemm_typed_kernel<long long, long long><<<grid, dim3(ST, ST), 0, s>>>(g); break;
+        case 1: launch_dep(simt_gemm_typed_kernel<double, double>, grid, dim3(ST, ST), s, g); break;
+        case 2: launch_dep(simt_gemm_typed_kernel<int, long long>, grid, dim3(ST, ST), s, g); break;
+        case 3: launch_dep(simt_gemm_typed_kernel<long long, long long>, grid, dim3(ST, ST), s, g); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
@@ -518,7 +562,7 @@ cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s) {
         a.total *= a.shape[d];
     }
     if (a.total == 0) return cudaSuccess;
-    gather_kernel<<<grid_for((size_t)a.total, 2), kThreads, 0, s>>>(a);
+    launch_dep(gather_kernel, grid_for((size_t)a.total, 2), kThreads, s, a);
     return cudaGetLastError();
 }
 
@@ -549,12 +593,12 @@ cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, i
     if (flat && (p.total & 3) == 0 && (((uintptr_t)a.ptr | (uintptr_t)b.ptr | (uintptr_t)out) & 15u) == 0) {
         const float4 *a4 = reinterpret_cast<const float4*>(a.ptr), *b4 = reinterpret_cast<const float4*>(b.ptr);
         float4* o4 = reinterpret_cast<float4*>(out);
-        if (multiply) add_flat_kernel<true><<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(a4, b4, o4, p.total / 4);
-        else add_flat_kernel<false><<<grid_for((size_t)p.total / 4, 2), kThreads, 0, s>>>(a4, b4, o4, p.total / 4);
+        if (multiply) launch_dep(add_flat_kernel<true>, grid_for((size_t)p.total / 4, 2), kThreads, s, a4, b4, o4, p.total / 4);
+        else launch_dep(add_flat_kernel<false>, grid_for((size_t)p.total / 4, 2), kThreads, s, a4, b4, o4, p.total / 4);
         return cudaGetLastError();
     }
-    if (multiply) add_kernel<true><<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
-    else add_kernel<false><<<grid_for((size_t)p.total, 2), kThreads, 0, s>>>(p);
+    if (multiply) launch_dep(add_kernel<true>, grid_for((size_t)p.total, 2), kThreads, s, p);
+    else launch_dep(add_kernel<false>, grid_for((size_t)p.total, 2), kThreads, s, p);
     return cudaGetLastError();
 }
 
@@ -580,7 +624,7 @@ cudaError_t launch_sum_to(const StridedView& g, const int64_t* out_shape, float*
     }
     if (a.nkept == 0) return cudaSuccess;
     const unsigned blocks = (unsigned)((a.nkept + 31) / 32);
-    sum_to_kernel<<<blocks, dim3(32, 8), 0, s>>>(a);
+    launch_dep(sum_to_kernel, blocks, dim3(32, 8), s, a);
     return cudaGetLastError();
 }
 
@@ -597,46 +641,47 @@ cudaError_t launch_colsum(const float* g, int64_t rows, int64_t cols, float* out
     const int chunks = colsum_chunks(rows, cols);
     const int64_t rpc = (rows + chunks - 1) / chunks;
     dim3 grid((unsigned)((cols + 127) / 128), (unsigned)chunks);
-    colsum_partial_kernel<<<grid, 256, 0, s>>>(g, rows, cols, rpc, partials);
-    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, chunks, cols, out);
+    launch_dep(colsum_partial_kernel, grid, 256, s, g, rows, cols, rpc, partials);
+    launch_dep(colsum_final_kernel, (unsigned)((cols + 255) / 256), 256, s, partials, chunks, cols, out);
     return cudaGetLastError();
 }
 
 cudaError_t launch_scale(const float* x, float alpha, float* y, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    scale_kernel<<<grid_for(n), kThreads, 0, s>>>(x, alpha, y, n);
+    launch_dep(scale_kernel, grid_for(n), kThreads, s, x, alpha, y, n);
     return cudaGetLastError();
 }
 cudaError_t launch_fill(float* x, float v, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    fill_kernel<<<grid_for(n), kThreads, 0, s>>>(x, v, n);
+    launch_dep(fill_kernel, grid_for(n), kThreads, s, x, v, n);
     return cudaGetLastError();
 }
 cudaError_t launch_tanh_fwd(const float* x, float* y, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     if ((n & 3) == 0 && (((uintptr_t)x | (uintptr_t)y) & 15u) == 0)
-        tanh_fwd_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((const float4*)x, (float4*)y, n / 4);
+        launch_dep(tanh_fwd_vec_kernel, grid_for(n / 4, 2), kThreads, s, (const float4*)x, (float4*)y, n / 4);
     else
-        tanh_fwd_kernel<<<grid_for(n), kThreads, 0, s>>>(x, y, n);
+        launch_dep(tanh_fwd_kernel, grid_for(n), kThreads, s, x, y, n);
     return cudaGetLastError();
 }
 cudaError_t launch_tanh_bwd(const float* g, const float* y, float* dx, size_t n, cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     if ((n & 3) == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)dx) & 15u) == 0)
-        tanh_bwd_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((const float4*)g, (const float4*)y, (float4*)dx, n / 4);
+        launch_dep(tanh_bwd_vec_kernel, grid_for(n / 4, 2), kThreads, s, (const float4*)g, (const float4*)y, (float4*)dx, n / 4);
     else
-        tanh_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(g, y, dx, n);
+        launch_dep(tanh_bwd_kernel, grid_for(n), kThreads, s, g, y, dx, n);
     return cudaGetLastError();
 }
 cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, float* partials, size_t n,
                            cudaStream_t s, float* dp) {
     int blocks = grid_for(n);
     if (blocks > 1024) blocks = 1024;
-    mse_partial_kernel<<<blocks, kThreads, 0, s>>>(p, t, partials, dp, 2.0f * (1.0f / (float)n), n);
-    mse_final_kernel<<<1, kThreads, 0, s>>>(partials, blocks, (float)n, loss_out);
+    launch_dep(mse_partial_kernel, blocks, kThreads, s, p, t, partials, dp, 2.0f * (1.0f / (float)n), n);
+    launch_dep(mse_final_kernel, 1, kThreads, s, partials, blocks, (float)n, loss_out);
     return cudaGetLastError();
 }
 __global__ void epi_apply_kernel(EpiApply a, size_t total) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int64_t n = (int64_t)(i % (size_t)a.N);
@@ -657,6 +702,7 @@ __global__ void epi_apply_kernel(EpiApply a, size_t total) {
 // Both arrays dense and laid out alike: a flat, 16-byte vectorised pass.
 __global__ void epi_apply_flat_kernel(float4* __restrict__ c, const float4* __restrict__ x, size_t n4, int op,
                                       float beta) {
+    dep_sync();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         float4 v = c[i];
@@ -682,11 +728,11 @@ cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
         dense *= a.bshape[d];
     }
     if (flat) {
-        epi_apply_flat_kernel<<<grid_for(total / 4), kThreads, 0, s>>>((float4*)a.c, (const float4*)a.x, total / 4, a.op,
+        launch_dep(epi_apply_flat_kernel, grid_for(total / 4), kThreads, s, (float4*)a.c, (const float4*)a.x, total / 4, a.op,
                                                                        a.beta);
         return cudaGetLastError();
     }
-    epi_apply_kernel<<<grid_for(total), kThreads, 0, s>>>(a, total);
+    launch_dep(epi_apply_kernel, grid_for(total), kThreads, s, a, total);
     return cudaGetLastError();
 }
 
@@ -695,6 +741,7 @@ cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s) {
 // (each input plane is read KH*KW times).
 template <bool VEC>
 __global__ void im2col_kernel(const float* __restrict__ x, float* __restrict__ col, WindowGeom g) {
+    dep_sync();
     const unsigned row = blockIdx.x;  // ((b * C + c) * KH + kh) * KW + kw
     const int kw = (int)(row % (unsigned)g.KW);
     const unsigned r1 = row / (unsigned)g.KW;
@@ -726,6 +773,7 @@ __global__ void im2col_kernel(const float* __restrict__ x, float* __restrict__ c
 // S1: both strides are 1 (no divisions on the way back from an input position to the windows that read it).
 template <bool VEC, bool S1>
 __global__ void col2im_kernel(const float* __restrict__ gc, float* __restrict__ gx, WindowGeom g) {
+    dep_sync();
     const unsigned plane = blockIdx.x;  // b * C + c
     const int OW = (int)g.OW, OH = (int)g.OH, OHW = OH * OW, H = (int)g.H, W = (int)g.W;
     const float* base = gc + (size_t)plane * g.KH * g.KW * OHW;
@@ -779,8 +827,8 @@ cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaS
     const bool vec = (ohw & 3) == 0 && (reinterpret_cast<uintptr_t>(col) & 15u) == 0;
     const size_t per_block = (size_t)kThreads * (vec ? 4 : 1) * 4;  // about four rounds per thread
     const unsigned gy = (unsigned)std::min<size_t>((ohw + per_block - 1) / per_block, 64);
-    if (vec) im2col_kernel<true><<<dim3((unsigned)rows, gy), kThreads, 0, s>>>(x, col, g);
-    else im2col_kernel<false><<<dim3((unsigned)rows, gy), kThreads, 0, s>>>(x, col, g);
+    if (vec) launch_dep(im2col_kernel<true>, dim3((unsigned)rows, gy), kThreads, s, x, col, g);
+    else launch_dep(im2col_kernel<false>, dim3((unsigned)rows, gy), kThreads, s, x, col, g);
     return cudaGetLastError();
 }
 cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s) {
@@ -793,17 +841,17 @@ cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom
     const unsigned gy = (unsigned)std::min<size_t>((hw + per_block - 1) / per_block, 64);
     const bool s1 = g.SH == 1 && g.SW == 1;
     const dim3 grid((unsigned)planes, gy);
-    if (vec && s1) col2im_kernel<true, true><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
-    else if (vec) col2im_kernel<true, false><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
-    else if (s1) col2im_kernel<false, true><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
-    else col2im_kernel<false, false><<<grid, kThreads, 0, s>>>(grad_col, grad_x, g);
+    if (vec && s1) launch_dep(col2im_kernel<true, true>, grid, kThreads, s, grad_col, grad_x, g);
+    else if (vec) launch_dep(col2im_kernel<true, false>, grid, kThreads, s, grad_col, grad_x, g);
+    else if (s1) launch_dep(col2im_kernel<false, true>, grid, kThreads, s, grad_col, grad_x, g);
+    else launch_dep(col2im_kernel<false, false>, grid, kThreads, s, grad_col, grad_x, g);
     return cudaGetLastError();
 }
 
 cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
                            cudaStream_t s) {
     if (n == 0) return cudaSuccess;
-    mse_bwd_kernel<<<grid_for(n), kThreads, 0, s>>>(p, t, gscalar, 1.0f / (float)n, dp, n);
+    launch_dep(mse_bwd_kernel, grid_for(n), kThreads, s, p, t, gscalar, 1.0f / (float)n, dp, n);
     return cudaGetLastError();
 }
 cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float momentum, float wd,
@@ -811,10 +859,10 @@ cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float mom
                        cudaStream_t s) {
     if (n == 0) return cudaSuccess;
     if (!has_momentum && (n & 3) == 0 && (((uintptr_t)p | (uintptr_t)g) & 15u) == 0) {
-        sgd_plain_vec_kernel<<<grid_for(n / 4, 2), kThreads, 0, s>>>((float4*)p, (const float4*)g, lr, wd, n / 4);
+        launch_dep(sgd_plain_vec_kernel, grid_for(n / 4, 2), kThreads, s, (float4*)p, (const float4*)g, lr, wd, n / 4);
         return cudaGetLastError();
     }
-    sgd_kernel<<<grid_for(n), kThreads, 0, s>>>(p, g, vel, lr, momentum, wd, dampening, nesterov,
+    launch_dep(sgd_kernel, grid_for(n), kThreads, s, p, g, vel, lr, momentum, wd, dampening, nesterov,
                                                  has_momentum, vel_init, n);
     return cudaGetLastError();
 }
