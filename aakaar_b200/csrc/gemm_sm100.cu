@@ -291,6 +291,31 @@ __device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile,
     ptx::named_barrier_sync(bar_id, 128);  // the (other) tile may be overwritten
 }
 
+// Per-warp variant for write-heavy short contractions: every epilogue warp stages its own 32 x 32 block
+// (4 KB, same swizzle) and its lane 0 sends it as a box of 32 rows; no barrier between warps at all. The
+// caller alternates between two staging tiles per warp; the lane waits for the box before the one it just
+// sent. Needs an output map encoded with 32-row boxes.
+__device__ __forceinline__ void store_block_tma_warp(float (&v)[32], float4* my_tile, uint32_t my_tile_addr,
+                                                     const CUtensorMap* tmC, int col0, int row0, int i1, int i0, int N,
+                                                     const float* bias, int lane) {
+    if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) v[j] += __ldg(bias + col0 + j);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        my_tile[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        ptx::tma_store_4d(tmC, my_tile_addr, col0, row0, i1, i0);
+        ptx::bulk_commit_group();
+        ptx::bulk_wait_read_1();
+    }
+    __syncwarp();  // the other staging tile of this warp may be overwritten
+}
+
 // KC > 0: the tensor core only accumulates KC k-blocks at a time; the epilogue warps add those
 // partial tiles into fp32 registers with round-to-nearest. The accumulator inside the tensor core
 // truncates on every add, which over a long contraction costs more accuracy than the fp32-accurate
@@ -592,6 +617,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         const uint32_t slab_tile_addr = smem_base + STAGES * L::STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
         constexpr int EPI_ALT = (BN / 128) * 4 * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
         int epi_buf = 0;                                           // which set the next TMA-store block uses
+        // three-stage instantiation (short, write-heavy contractions): every warp sends its own 32-row boxes
+        constexpr bool WARP_STORE = EPI_BUFS == 2 && STAGES == 3;
+        const uint32_t my_stage_addr = smem_base + STAGES * L::STAGE_BYTES + (slab * 4 + q) * EPI_STAGE_BYTES;
         const bool use_tma = p.c_tma != 0 && !split_mode;  // kernel-uniform
         int handoff = 0;
         bool ok = true;
@@ -623,8 +651,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
                 bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
-                // the TMA-store path synchronises the four warps of a slab: they must leave together
-                if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);
+                // the slab-wide TMA-store path synchronises the four warps of a slab: they must leave together
+                if (use_tma && !WARP_STORE) got = ptx::named_barrier_and(2 + slab, 128, got);
                 if (!got) {
                     ok = false;
                     break;
@@ -648,6 +676,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                             if (p.debug & 128) {
                                 // bit 7: timing experiment without the output stores
+                            } else if (use_tma && WARP_STORE) {
+                                store_block_tma_warp(f, my_stage + epi_buf * (EPI_ALT / 16), my_stage_addr + epi_buf * EPI_ALT,
+                                                     &p.tmC, col0, row0, c.i1, c.i0, p.N, bias, lane);
+                                epi_buf ^= 1;
                             } else if (use_tma) {
                                 store_block_tma<EPI_BUFS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
                                                           &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
@@ -775,8 +807,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         }
     }
 
-    // the thread that issued bulk stores waits for them before the CTA winds down
-    if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    // the threads that issued bulk stores wait for them before the CTA winds down
+    if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && lane == 0 &&
+        ((EpiBufs<BN, TERMS, STAGES, BKT>::value == 2 && STAGES == 3) || (warp & 3) == 0))
+        ptx::bulk_wait_all();
 
     // ------------------------------------------------------------ teardown (all paths)
     ptx::tc_fence_before();
@@ -2192,7 +2226,9 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.o1, (cuuint64_t)g.o0};
         cuuint64_t strides[3] = {ldc_b, (cuuint64_t)(g.o1 > 1 ? g.c_bs1 * 4 : (long long)ldc_b),
                                  (cuuint64_t)(g.o0 > 1 ? g.c_bs0 * 4 : (long long)ldc_b)};
-        cuuint32_t box[4] = {32u, 128u, 1u, 1u};
+        // the three-stage instantiation for short contractions sends one box per warp (32 rows)
+        const bool warp_boxes = g.terms == 1 && !big && !pairs && bn == 256 && (long long)g.red * ((g.K + bk - 1) / bk) <= 8;
+        cuuint32_t box[4] = {32u, warp_boxes ? 32u : 128u, 1u, 1u};
         cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
         if (enc && enc(&kp.tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
