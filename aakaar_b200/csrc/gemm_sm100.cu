@@ -1107,7 +1107,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     uint8_t* epi_stage_base = smem + S * PAIR_STAGE_BYTES + 256;
 
-    const int warp = threadIdx.x >> 5;
+    // Roles by hardware warp: 0..7 epilogue, 8 producer, 9 MMA, 10..11 converters, so that the two epilogue
+    // warpgroups can take the registers the third one gives back. `warp` is the role index used below
+    // (0 producer, 1 MMA, 2..9 epilogue, 10..11 converters).
+    const int hw_warp = threadIdx.x >> 5;
+    const int warp = hw_warp < 8 ? hw_warp + 2 : (hw_warp < 10 ? hw_warp - 8 : hw_warp);
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
     const bool leader = rank == 0;
@@ -1149,6 +1153,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     const bool presplit = p.presplit != 0;
     const int kc = (p.debug & 64) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
 
+    // 128 promotion accumulators per epilogue thread do not fit the uniform 168 registers of a 12-warp CTA (they
+    // spilled into the chain loop); the third warpgroup (producer, MMA, converters) needs far fewer and gives
+    // them back first.
+    if (hw_warp >= 8) {
+    ptx::reg_dealloc<96>();
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (own tiles, local barriers)
         if (lane == 0) {
@@ -1400,9 +1409,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                 }
             }
         }
+    }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..9), fp32 promotion
-        const int q = warp & 3;
+        ptx::reg_alloc<200>();
+        // ------------------------------------------------------------ epilogue (roles 2..9), fp32 promotion
+        const int q = hw_warp & 3;  // TMEM lane quarter of this hardware warp
         const int slab = (warp - 2) >> 2;
         const bool vec = p.vec_ok != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
