@@ -364,7 +364,14 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
-    const int warp = threadIdx.x >> 5;
+    // `warp` is the role index: 0 producer, 1 MMA, 2 .. 2+EPI_WARPS-1 epilogue, then the converters. The
+    // fp32-accurate 256-wide instantiation has twelve warps, capped at 168 registers each unless the epilogue
+    // warps (128 promotion accumulators per thread) sit in warpgroups of their own and take registers the
+    // third warpgroup gives back: there hardware warps 0..7 are the epilogue, 8 the producer, 9 the MMA warp,
+    // 10..11 the converters.
+    constexpr bool REMAP = TERMS == 3 && BN == 256;
+    const int hw_warp = threadIdx.x >> 5;
+    const int warp = !REMAP ? hw_warp : (hw_warp < 8 ? hw_warp + 2 : (hw_warp < 10 ? hw_warp - 8 : hw_warp));
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -398,6 +405,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 
     const int total_iters = p.red * p.nkb;  // contraction steps of one output tile
 
+    if (warp < 2 || warp >= 2 + EPI_WARPS) {
+    if (REMAP) ptx::reg_dealloc<96>();
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -607,9 +616,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 }
             }
         }
+    }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2 ..)
-        const int q = warp & 3;             // TMEM lane quarter this warp may read
+        if (REMAP) ptx::reg_alloc<200>();
+        // ------------------------------------------------------------ epilogue (roles 2 ..)
+        const int q = hw_warp & 3;          // TMEM lane quarter this hardware warp may read
         const int slab = (warp - 2) >> 2;   // which 128-column slab of the tile
         const int nbatch = p.o0 * p.o1;
         const bool split_mode = p.splits > 1;
@@ -809,7 +820,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 
     // the threads that issued bulk stores wait for them before the CTA winds down
     if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && lane == 0 &&
-        ((EpiBufs<BN, TERMS, STAGES, BKT>::value == 2 && STAGES == 3) || (warp & 3) == 0))
+        ((EpiBufs<BN, TERMS, STAGES, BKT>::value == 2 && STAGES == 3) || (hw_warp & 3) == 0))
         ptx::bulk_wait_all();
 
     // ------------------------------------------------------------ teardown (all paths)
