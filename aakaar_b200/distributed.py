@@ -88,7 +88,8 @@ class RowShardedMatmul:
     rank: int
     backend: object = None
     overlap: bool = True
-    comm_ctas: int = 20     # SMs left free for the collective while it overlaps the dA GEMM
+    # SMs left free for the collective while it overlaps the dA GEMM (AKR_B200_COMM_CTAS overrides, for tuning)
+    comm_ctas: int = int(__import__("os").environ.get("AKR_B200_COMM_CTAS", "20"))
 
     def __post_init__(self):
         self.lo, self.hi = shard_range(self.total_m, self.world, self.rank)
