@@ -92,3 +92,35 @@ def test_dtype_enum_and_typed_constructor():
 def test_sgd_argument_check():
     with pytest.raises(ValueError):
         ak.optim.SGD([], nesterov=True)
+
+
+def test_conv_callers_argument_checks_without_gpu():
+    # shape logic and error behaviour of the convolution callers run on the host; computing needs the GPU
+    x = ak.from_numpy(np.ones((2, 3, 8), dtype=np.float32), "cpu")
+    w = ak.from_numpy(np.ones((4, 3, 9), dtype=np.float32), "cpu")
+    with pytest.raises(ValueError, match="computed output length"):
+        ak.conv1d(x, w)                                   # kernel longer than the input
+    with pytest.raises(ValueError, match="expected input of shape"):
+        ak.im2col_1d(ak.from_numpy(np.ones((2, 3), dtype=np.float32), "cpu"), 3, 1, 0, 1, 1)
+    with pytest.raises(ValueError, match="expected input of shape"):
+        ak.im2col_2d(x, 3, 3, 1, 1, 0, 0, 1, 1, 1, 1)
+    conv = ak.nn.Conv1d(3, 4, 3, device="cpu")
+    assert conv.weight.shape == [4, 3, 3] and conv.bias.shape == [1, 4, 1] and len(conv.parameters()) == 2
+    with pytest.raises(ValueError, match="input channels"):
+        conv(ak.from_numpy(np.ones((2, 5, 8), dtype=np.float32), "cpu"))
+    with pytest.raises(RuntimeError):
+        conv(x)                                           # CPU tensors do not compute
+    with pytest.raises(RuntimeError, match="float32 only"):
+        ak.nn.Conv2d(3, 4, 3, device="cpu", dtype="float64")
+
+
+def test_muon_and_fusion_switch_exist():
+    from aakaar_b200 import _C
+    _C._set_backward_fusion(False)
+    _C._set_backward_fusion(True)
+    opt = ak.optim.Muon([ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cpu", requires_grad=True)])
+    opt.step()          # no gradients yet: nothing to do
+    opt.zero_grad()
+    with pytest.raises(RuntimeError):
+        _C.matmul_axpby(ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cpu"),
+                        ak.from_numpy(np.ones((2, 2), dtype=np.float32), "cpu"), 1.0, 0.0, None)
