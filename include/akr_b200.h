@@ -205,7 +205,9 @@ AKR_API int akr_event_destroy(void* event);
  * are timing diagnostics (skip loads, skip MMAs, no folded maps, no 256x256 tiles; results invalid with 1 / 2);
  * flag 32 routes every fp32-accurate product through the CTA-pair (cta_group::2) kernel (by default only large
  * pre-split ones use it), flag 512 disables that kernel; flag 1024 disables the TF32 CTA-pair kernel, flag 2048
- * prefers it wherever it applies.
+ * prefers it wherever it applies; flag 4096 launches the GEMM kernels without programmatic stream serialization;
+ * flags 64 / 128 / 256 are further timing diagnostics (one accumulation chain per tile in the fp32 pair kernel, no
+ * output stores, no TMA-store epilogue).
  * akr_debug_configure(0, 0) restores normal operation. */
 AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
 
