@@ -43,9 +43,9 @@ def set_size(n):
     FLOP_PER_STEP = 3 * 2 * n ** 3
     WORKLOAD = WORKLOAD.replace("8192", str(n))
 
-# DRAM bytes moved by one launch of the dominant kernel (dB = A^T.dC at 8192^3, TF32 mode), from
+# DRAM bytes moved by one launch of the dominant kernel (dA = dC.B^T at 8192^3, TF32 mode), from
 # an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/. None = not captured.
-NCU_TRAFFIC_BYTES = 1887909632  # dA launch at 8192^3: 1 653 852 160 read + 234 057 472 written
+NCU_TRAFFIC_BYTES = 1886157312  # dA launch at 8192^3: 1 652 729 088 read + 233 428 224 written (forward and dB within 0.5 %)
 
 
 
