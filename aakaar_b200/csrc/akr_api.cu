@@ -313,10 +313,15 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     // costs shared-memory bandwidth. Large compute-bound products are faster when hi / lo are split
     // once up front (an extra HBM pass over the operands) and both fetched by TMA.
     bool split = false;
-    if (p.mode == AKR_MODE_FP32) {
-        const double flop = 2.0 * (double)p.M * (double)p.N * (double)p.K;
-        const double bytes = 4.0 * ((double)p.M * p.K + (double)p.K * p.N + (double)p.M * p.N);
-        split = flop / bytes >= 512.0;
+    if (p.mode == AKR_MODE_FP32 && redd.empty() && outd.size() <= 2) {
+        GemmDesc shape;
+        shape.M = (int)p.M;
+        shape.N = (int)p.N;
+        shape.K = (int)p.K;
+        shape.terms = 3;
+        if (outd.size() >= 1) shape.o1 = (int)outd.back().e;
+        if (outd.size() == 2) shape.o0 = (int)outd[0].e;
+        split = gemm_sm100_presplit_pays(shape);
     }
     Prepared A, B;
     rc = prepare_operand(st, p.A, p.M, p.K, all, true, split, stream, &A);
@@ -491,6 +496,9 @@ int need_gpu(DeviceState** st) { return get_state(st); }
 namespace akr {
 // Lets the library's other translation units record the message akr_last_error() returns.
 void set_last_error(const std::string& msg) { g_err = msg; }
+// The lock that serialises kernel launches (and the host-side state behind them) of one device.
+std::mutex& device_launch_mutex(int dev) { return g_dev[dev >= 0 && dev < kMaxDevices ? dev : 0].mu; }
+int noalloc_take_status(int dev);  // csrc/noalloc.cu
 }  // namespace akr
 
 extern "C" {
@@ -524,15 +532,19 @@ AKR_API int akr_synchronize(void) {
     if (rc != AKR_OK) return rc;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+    bool aborted = false;
     if (st->status) {
         int flag = 0;
         e = cudaMemcpy(&flag, st->status, sizeof(int), cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) return cuda_fail(e, "status read");
         if (flag != 0) {
             cudaMemset(st->status, 0, sizeof(int));
-            return fail(AKR_ERR_ABORTED, "a GEMM kernel gave up on a bounded wait; its output is invalid");
+            aborted = true;
         }
     }
+    // kernels of the allocation-free entry point report through a status word of their own
+    if (akr::noalloc_take_status((int)(st - g_dev)) != 0) aborted = true;
+    if (aborted) return fail(AKR_ERR_ABORTED, "a GEMM kernel gave up on a bounded wait; its output is invalid");
     return AKR_OK;
 }
 

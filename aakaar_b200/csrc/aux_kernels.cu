@@ -29,16 +29,21 @@ void launch_dep(K kernel, dim3 grid, dim3 block, cudaStream_t stream, Args... ar
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    static const bool off = std::getenv("AKR_B200_NO_PDL") != nullptr;
+#ifdef AKR_B200_DIAG
+    static const bool off = std::getenv("AKR_B200_NO_PDL") != nullptr;  // A/B switch for measurements
+#else
+    constexpr bool off = false;
+#endif
     cfg.numAttrs = off ? 0 : 1;
     cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 int grid_for(size_t n, int per_thread = 4) {
-    static int sms = 0;
+    static int sms_dev[64] = {};  // per device: a process may drive several GPUs
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    int& sms = sms_dev[dev];
     if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }

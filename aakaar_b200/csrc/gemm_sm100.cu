@@ -36,6 +36,15 @@ constexpr int CHUNK = 32;      // M/N elements per 128-byte row of an MN-major t
 constexpr int GROUP_M = 16;    // tile rasterisation: m-tiles per group (L2 reuse of B panels)
 constexpr uint64_t DEFAULT_WAIT_LIMIT_NS = 4000000000ull;  // a wait longer than this aborts the kernel
 
+// Timing experiments (skip the MMAs, skip the stores, force or forbid a kernel variant ...) are compiled in
+// only with -DAKR_B200_DIAG; the shipped build keeps the four documented hooks of GemmDesc::debug and none
+// of the experiment branches in its main loops.
+#ifdef AKR_B200_DIAG
+#define AKR_DIAG(flags, bit) (((flags) & (bit)) != 0)
+#else
+#define AKR_DIAG(flags, bit) false
+#endif
+
 struct KernelParams {
     CUtensorMap tmA, tmB;
     CUtensorMap tmC;           // output map for the TMA-store epilogue (valid when c_tma != 0)
@@ -63,7 +72,7 @@ struct KernelParams {
     int a_fold, b_fold;
     int accumulate, vec_ok;
     int mt, nt, nkb, total_tiles;
-    int debug;  // diagnostics: bit 0 = skip TMA loads, bit 1 = skip MMAs (timing experiments only),
+    int debug;  // bit 0 = skip the TMA loads (MMA-only timing: the measured tensor-pipe ceiling),
                 // bit 4 = the producer never signals a stage (exercises the bounded-wait abort path)
     unsigned long long wait_limit_ns;
 };
@@ -93,18 +102,27 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     return c;
 }
 
+// One load stage holds the raw fp32 tiles of A and B as TMA delivers them, in every mode. The
+// fp32-accurate mode keeps the derived low parts in a second, shorter ring of the same tile size (LO
+// slots): a low-part tile only lives from its conversion to the end of its MMAs, so shared memory goes
+// to raw stages - bytes in flight from HBM - rather than to a low copy per stage.
 template <int BN, int TERMS, int BKT>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BKT * 4;
     static constexpr int B_BYTES = BN * BKT * 4;
-    static constexpr int STAGE_BYTES = (TERMS == 3 ? 2 : 1) * (A_BYTES + B_BYTES);
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
+constexpr int BAR_BYTES = 512;  // mbarriers + TMEM slot + flags behind the tiles
+
+// 128-column slabs of a tile (a narrower tile is one slab) and the columns of one slab.
+__host__ __device__ constexpr int slabs_of(int bn) { return bn >= 128 ? bn / 128 : 1; }
+__host__ __device__ constexpr int slab_cols(int bn) { return bn >= 128 ? 128 : bn; }
 
 // Threads of one CTA: producer warp, MMA warp and one epilogue warp per (TMEM lane quarter,
 // 128-column slab of the tile).
 // plus, in the fp32-accurate mode, two converter warps that derive the low parts in shared memory.
 template <int BN, int TERMS = 1>
-constexpr int num_threads() { return 64 + (BN / 128) * 128 + (TERMS == 3 ? 64 : 0); }
+constexpr int num_threads() { return 64 + slabs_of(BN) * 128 + (TERMS == 3 ? 64 : 0); }
 
 // Bytes of shared memory each epilogue warp uses to turn "one row per lane" into coalesced stores.
 constexpr int EPI_STAGE_BYTES = 32 * 128;
@@ -327,20 +345,24 @@ __device__ __forceinline__ void store_block_tma_warp(float (&v)[32], float4* my_
 template <int BN, int TERMS, int STAGES, int BKT>
 struct EpiBufs {
     static constexpr int value =
-        (TERMS == 1 && STAGES * SmemLayout<BN, TERMS, BKT>::STAGE_BYTES + 2 * (BN / 128) * 4 * EPI_STAGE_BYTES + 2048 <= 232448)
+        (TERMS == 1 && STAGES * SmemLayout<BN, TERMS, BKT>::STAGE_BYTES + 2 * slabs_of(BN) * 4 * EPI_STAGE_BYTES + 2048 <= 232448)
             ? 2
             : 1;
 };
 
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
+// LO: slots of the low-part ring (fp32-accurate mode; 0 in TF32 mode).
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT, int LO>
 __global__ void __launch_bounds__(num_threads<BN, TERMS>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     using L = SmemLayout<BN, TERMS, BKT>;
-    constexpr int EPI_WARPS = (BN / 128) * 4;
+    constexpr int SLABS = slabs_of(BN);
+    constexpr int SLAB_W = slab_cols(BN);
+    constexpr int EPI_WARPS = SLABS * 4;
     constexpr int CONV_WARPS = TERMS == 3 ? 2 : 0;
     constexpr int CHUNK_ITERS = KC > 0 ? KC : 0x7fffffff;
     constexpr int TMEM_COLS = 2 * BN;  // two accumulators
-    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
+    static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
+    static_assert((TERMS == 3) == (LO > 0), "the low-part ring exists exactly in the fp32-accurate mode");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -350,17 +372,22 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 
     // [stages][epilogue staging: one 16 KB tile per 128-column slab (two where they fit: the TMA-store
     // epilogue then alternates between them), 1024-byte aligned][barriers]
+    // [raw stages][low-part slots][epilogue staging ...][barriers]
     constexpr int EPI_BUFS = EpiBufs<BN, TERMS, STAGES, BKT>::value;
-    constexpr int EPI_BYTES = EPI_BUFS * (BN / 128) * 4 * EPI_STAGE_BYTES;
-    uint8_t* epi_stage_base = smem + STAGES * L::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES + EPI_BYTES);
-    const uint32_t bar_base = smem_base + STAGES * L::STAGE_BYTES + EPI_BYTES;
+    constexpr int EPI_BYTES = EPI_BUFS * SLABS * 4 * EPI_STAGE_BYTES;
+    constexpr int TILE_BYTES = (STAGES + LO) * L::STAGE_BYTES;
+    constexpr int LO_BASE = STAGES * L::STAGE_BYTES;
+    uint8_t* epi_stage_base = smem + TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TILE_BYTES + EPI_BYTES);
+    const uint32_t bar_base = smem_base + TILE_BYTES + EPI_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-    auto conv_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 4 + s); };  // low parts written
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
+    auto conv_bar = [&](int l) { return bar_base + 8u * (2 * STAGES + 4 + l); };          // low parts written
+    auto lofree_bar = [&](int l) { return bar_base + 8u * (2 * STAGES + 4 + LO + l); };   // low-part slot reusable
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 2 * LO);
+    static_assert((2 * STAGES + 4 + 2 * LO) * 8 + 16 <= BAR_BYTES, "barrier area too small");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -378,7 +405,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(full_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
-            ptx::mbar_init(conv_bar(s), CONV_WARPS > 0 ? CONV_WARPS : 1);
+        }
+        for (int l = 0; l < LO; ++l) {
+            ptx::mbar_init(conv_bar(l), CONV_WARPS > 0 ? CONV_WARPS : 1);
+            ptx::mbar_init(lofree_bar(l), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
@@ -436,18 +466,17 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         }
                         continue;
                     }
-                    ptx::mbar_arrive_expect_tx(fb, (TERMS == 3 && p.presplit) ? L::STAGE_BYTES : L::A_BYTES + L::B_BYTES);
+                    ptx::mbar_arrive_expect_tx(fb, L::STAGE_BYTES);
                     const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                     const uint32_t sb = sa + L::A_BYTES;
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
                     const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-                    const int nterm = (TERMS == 3 && p.presplit) ? 2 : 1;
-                    for (int term = 0; term < nterm; ++term) {
-                        const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
-                        const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
-                        const uint32_t da = sa + term * (L::A_BYTES + L::B_BYTES);
-                        const uint32_t db = sb + term * (L::A_BYTES + L::B_BYTES);
+                    {
+                        const CUtensorMap* ma = &p.tmA;
+                        const CUtensorMap* mb = &p.tmB;
+                        const uint32_t da = sa;
+                        const uint32_t db = sb;
                         if (MAJA == 0) {
                             ptx::tma_load_5d(da, ma, fb, k0, c.m0, a0, a1, a2);
                         } else if (p.a_fold) {
@@ -499,6 +528,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BN, MAJA, MAJB);
             int stage = 0;
             uint32_t phase = 0;
+            int lo_slot = 0;        // low-part ring position (fp32-accurate mode)
+            uint32_t lo_phase = 0;
             int handoff = 0;  // accumulator hand-offs so far (one per chunk of the contraction)
             bool ok = true;
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
@@ -516,17 +547,18 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     ptx::tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * BN;
                     for (int it = cs; it < ce; ++it) {
-                        // fp32-accurate mode: the stage is ready once the converter warps wrote the low parts
-                        if (!ptx::mbar_wait((TERMS == 3 && !p.presplit) ? conv_bar(stage) : full_bar(stage), phase, abort_flag,
-                                            p.wait_limit_ns)) {
+                        // fp32-accurate mode: the stage is ready once the converter warps wrote its low parts
+                        // (they waited for the raw tiles themselves)
+                        if (!ptx::mbar_wait(TERMS == 3 ? conv_bar(lo_slot) : full_bar(stage), TERMS == 3 ? lo_phase : phase,
+                                            abort_flag, p.wait_limit_ns)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
                         const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                         const uint32_t sb = sa + L::A_BYTES;
-                        const uint32_t sa_lo = sa + L::A_BYTES + L::B_BYTES;
-                        const uint32_t sb_lo = sb + L::A_BYTES + L::B_BYTES;
+                        const uint32_t sa_lo = smem_base + LO_BASE + lo_slot * L::STAGE_BYTES;
+                        const uint32_t sb_lo = sa_lo + L::A_BYTES;
 #pragma unroll
                         for (int k8 = 0; k8 < BKT / UMMA_K; ++k8) {
                             // K-major: step 32 bytes inside the 128-byte swizzle row.
@@ -545,7 +577,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
-                            if (p.debug & 2) {
+                            if (AKR_DIAG(p.debug, 2)) {
                                 if (k8 == 0 && it == cs) ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 0u);
                             } else if (TERMS == 3) {
                                 const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
@@ -562,6 +594,13 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             stage = 0;
                             phase ^= 1u;
                         }
+                        if (TERMS == 3) {
+                            ptx::mma_commit(lofree_bar(lo_slot));  // and so is the low-part slot
+                            if (++lo_slot == LO) {
+                                lo_slot = 0;
+                                lo_phase ^= 1u;
+                            }
+                        }
                     }
                     if (ok) ptx::mma_commit(tfull_bar(buf));  // this chunk's accumulator is complete
                     ++handoff;
@@ -574,24 +613,26 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         // part trunc(x). These warps write lo = x - trunc(x) (exact in fp32) beside it, at the same
         // offset, so the swizzled tile layout is preserved without knowing it.
         const int ct = (warp - 2 - EPI_WARPS) * 32 + lane;
-        constexpr int RAW_BYTES = L::A_BYTES + L::B_BYTES;
-        int stage = 0;
-        uint32_t phase = 0;
+        constexpr int RAW_BYTES = L::STAGE_BYTES;
+        constexpr int LOS = LO > 0 ? LO : 1;
+        int stage = 0, lo_slot = 0;
+        uint32_t phase = 0, lo_phase = 0;
         bool ok = true;
-        // with pre-split operands the low parts arrive by TMA and these warps have nothing to do
-        for (int t = blockIdx.x; t < p.total_tiles && ok && !p.presplit; t += gridDim.x) {
+        for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
             const Tile c = decode_tile(t, p, BN);
             const int it0 = (int)((long long)total_iters * c.split / p.splits);
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             for (int it = it0; it < it1; ++it) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns))) {
+                // the raw tiles have landed, and the MMAs that read this low-part slot last have finished
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
+                    !__all_sync(0xffffffffu, ptx::mbar_wait(lofree_bar(lo_slot), lo_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
                 const float4* src = reinterpret_cast<const float4*>(smem + stage * L::STAGE_BYTES);
-                float4* dst = reinterpret_cast<float4*>(smem + stage * L::STAGE_BYTES + RAW_BYTES);
+                float4* dst = reinterpret_cast<float4*>(smem + LO_BASE + lo_slot * L::STAGE_BYTES);
                 constexpr int PER_THREAD = RAW_BYTES / 16 / (CONV_WARPS > 0 ? CONV_WARPS * 32 : 1);
-                constexpr int BATCH = 8;  // loads in flight per thread
+                constexpr int BATCH = PER_THREAD % 8 == 0 ? 8 : (PER_THREAD % 6 == 0 ? 6 : 4);  // loads in flight per thread
                 static_assert(PER_THREAD % BATCH == 0 || CONV_WARPS == 0, "converter work must divide evenly");
 #pragma unroll 1
                 for (int b0 = 0; b0 < PER_THREAD; b0 += BATCH) {
@@ -609,10 +650,14 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 }
                 ptx::fence_proxy_async_smem();  // generic-proxy writes -> visible to the MMA's reads
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(conv_bar(stage));
+                if (lane == 0) ptx::mbar_arrive(conv_bar(lo_slot));
                 if (++stage == STAGES) {
                     stage = 0;
                     phase ^= 1u;
+                }
+                if (++lo_slot == LOS) {
+                    lo_slot = 0;
+                    lo_phase ^= 1u;
                 }
             }
         }
@@ -625,12 +670,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         const int nbatch = p.o0 * p.o1;
         const bool split_mode = p.splits > 1;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
-        const uint32_t slab_tile_addr = smem_base + STAGES * L::STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
-        constexpr int EPI_ALT = (BN / 128) * 4 * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
+        const uint32_t slab_tile_addr = smem_base + TILE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        constexpr int EPI_ALT = SLABS * 4 * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
         int epi_buf = 0;                                           // which set the next TMA-store block uses
         // three-stage instantiation (short, write-heavy contractions): every warp sends its own 32-row boxes
         constexpr bool WARP_STORE = EPI_BUFS == 2 && STAGES == 3;
-        const uint32_t my_stage_addr = smem_base + STAGES * L::STAGE_BYTES + (slab * 4 + q) * EPI_STAGE_BYTES;
+        const uint32_t my_stage_addr = smem_base + TILE_BYTES + (slab * 4 + q) * EPI_STAGE_BYTES;
         const bool use_tma = p.c_tma != 0 && !split_mode;  // kernel-uniform
         int handoff = 0;
         bool ok = true;
@@ -654,7 +699,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const float* bias = split_mode ? nullptr : p.bias;
             const int slab_col0 = c.n0 + slab * 128;
 
-            constexpr int ACC_N = KC > 0 ? 128 : 1;  // fp32 promotion registers (unused without chains)
+            constexpr int ACC_N = KC > 0 ? SLAB_W : 1;  // fp32 promotion registers (unused without chains)
             float acc[ACC_N];
 #pragma unroll
             for (int j = 0; j < ACC_N; ++j) acc[j] = 0.f;
@@ -671,7 +716,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                 ptx::tc_fence_after();
                 const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * BN + slab * 128;
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < SLAB_W / 32; ++ch) {
                     const int col0 = slab_col0 + ch * 32;
                     if (col0 < p.N) {  // warp-uniform
                         __syncwarp();  // tcgen05.ld needs the whole warp converged
@@ -685,7 +730,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            if (p.debug & 128) {
+                            if (AKR_DIAG(p.debug, 128)) {
                                 // bit 7: timing experiment without the output stores
                             } else if (use_tma && WARP_STORE) {
                                 store_block_tma_warp(f, my_stage + epi_buf * (EPI_ALT / 16), my_stage_addr + epi_buf * EPI_ALT,
@@ -711,7 +756,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             }
             if (KC > 0 && ok) {
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+                for (int ch = 0; ch < SLAB_W / 32; ++ch) {
                     const int col0 = slab_col0 + ch * 32;
                     if (col0 < p.N) {
                         float f[32];
@@ -913,6 +958,15 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                     }
                     const uint32_t fb = full_bar(stage);
                     if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
+                    if (p.debug & 1) {           // MMA-only timing: no loads, stale shared memory
+                        ptx::mbar_arrive(fb);
+                        ++issued;
+                        if (++stage == BIG_STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     ptx::mbar_arrive_expect_tx(fb, BIG_STAGE_BYTES);
                     const uint32_t da = smem_base + stage * BIG_STAGE_BYTES;
                     const uint32_t db = da + BIG_A_BYTES;
@@ -1162,7 +1216,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     ptx::grid_dep_wait();
     const int total_iters = p.red * p.nkb;
     const bool presplit = p.presplit != 0;
-    const int kc = (p.debug & 64) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
+    const int kc = (AKR_DIAG(p.debug, 64)) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
 
     // 128 promotion accumulators per epilogue thread do not fit the uniform 168 registers of a 12-warp CTA (they
     // spilled into the chain loop); the third warpgroup (producer, MMA, converters) needs far fewer and gives
@@ -1354,7 +1408,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t da_lo = ptx::smem_desc(sa + PAIR_RAW_BYTES + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db_lo = ptx::smem_desc(sb + PAIR_RAW_BYTES + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
-                            if (p.debug & 2) {  // timing experiment: loads and hand-shakes only
+                            if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
                                 if (first == 0u) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
                                 continue;
                             }
@@ -1666,7 +1720,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
                         const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                         const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
-                        if (p.debug & 2) {  // timing experiment: loads and hand-shakes only
+                        if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
                             if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
                             continue;
                         }
@@ -1720,7 +1774,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                        if (p.debug & 128) continue;  // timing experiment: no stores
+                        if (AKR_DIAG(p.debug, 128)) continue;  // timing experiment: no stores
                         if (use_tma)
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                             lane, q == 0 && lane == 0, 2 + slab);
@@ -1902,6 +1956,15 @@ bool make_map(CUtensorMap* out, const float* base, const GemmOperand& op, const 
 
 bool gemm_sm100_cta_limit_active();
 
+// Per-device caches (function attributes, resident cluster counts, SM counts) are indexed by the current
+// device: cudaFuncSetAttribute applies to the device that is current when it is called.
+constexpr int kMaxDev = 64;
+int cur_dev() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDev) d = 0;
+    return d;
+}
+
 // Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in
 // the stream drains (its set-up overlaps that tail); it synchronises on the predecessor itself
 // (grid_dep_wait) before its first access to global memory. Debug bit 12 launches normally.
@@ -1917,19 +1980,26 @@ void launch_pdl(K kern, int grid, int threads, int smem, cudaStream_t stream, co
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
+#ifdef AKR_B200_DIAG
     static const bool env_off = std::getenv("AKR_B200_NO_PDL") != nullptr;  // A/B switch for measurements
+#else
+    constexpr bool env_off = false;
+#endif
     // Not while a CTA limit is set: that is the phase in which a collective runs beside the GEMM, and there an
     // early-started GEMM measured 6 % slower (2 GPUs: 3.45-3.67 ms against 3.27-3.40 ms for dB + all-reduce + dA).
     cfg.numAttrs = (g_pdl_off || env_off || gemm_sm100_cta_limit_active()) ? 0 : 1;
     cudaLaunchKernelEx(&cfg, kern, kp);
 }
 
-template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT>
+template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT, int LO>
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS, BKT>;
-    constexpr int smem = STAGES * L::STAGE_BYTES + 1024 + 256 + EpiBufs<BN, TERMS, STAGES, BKT>::value * (BN / 128) * 4 * EPI_STAGE_BYTES;
-    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT>;
-    static bool attr_done = false;  // per instantiation
+    constexpr int smem = (STAGES + LO) * L::STAGE_BYTES + 1024 + BAR_BYTES +
+                         EpiBufs<BN, TERMS, STAGES, BKT>::value * slabs_of(BN) * 4 * EPI_STAGE_BYTES;
+    static_assert(smem <= 232448, "more shared memory than one CTA may have");
+    auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT, LO>;
+    static bool attr_done_dev[kMaxDev] = {};  // per instantiation and device
+    bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -1947,15 +2017,15 @@ int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* 
     return 0;
 }
 
-template <int BN, int TERMS, int STAGES, int KC, int BKT>
+template <int BN, int TERMS, int STAGES, int KC, int BKT, int LO = 0>
 int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream_t s, char* err,
                  int errlen) {
     const int key = g.A.mn_major * 2 + g.B.mn_major;
     switch (key) {
-        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
-        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
-        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
-        default: return launch_variant<BN, 1, 1, TERMS, STAGES, KC, BKT>(kp, grid, s, err, errlen);
+        case 0: return launch_variant<BN, 0, 0, TERMS, STAGES, KC, BKT, LO>(kp, grid, s, err, errlen);
+        case 1: return launch_variant<BN, 0, 1, TERMS, STAGES, KC, BKT, LO>(kp, grid, s, err, errlen);
+        case 2: return launch_variant<BN, 1, 0, TERMS, STAGES, KC, BKT, LO>(kp, grid, s, err, errlen);
+        default: return launch_variant<BN, 1, 1, TERMS, STAGES, KC, BKT, LO>(kp, grid, s, err, errlen);
     }
 }
 
@@ -1963,7 +2033,8 @@ template <int MAJA, int MAJB>
 int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     constexpr int smem = BIG_STAGES * BIG_STAGE_BYTES + 1024 + 256 + 8 * EPI_STAGE_BYTES;
     auto kern = gemm_tf32_big_kernel<MAJA, MAJB>;
-    static bool attr_done = false;
+    static bool attr_done_dev[kMaxDev] = {};
+    bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -1988,7 +2059,8 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
                              : PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
     constexpr int threads = DUO ? DUO_THREADS : PAIR_THREADS;
     auto kern = DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>;
-    static bool attr_done = false;
+    static bool attr_done_dev[kMaxDev] = {};
+    bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -1998,7 +2070,8 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
         attr_done = true;
     }
     // How many 2-CTA clusters can be resident at once (SM counts per GPC need not be even).
-    static int max_pairs = 0;
+    static int max_pairs_dev[kMaxDev] = {};
+    int& max_pairs = max_pairs_dev[cur_dev()];
     if (max_pairs == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * 74);
@@ -2017,7 +2090,9 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
             n = 64;
         }
         max_pairs = n;
+#ifdef AKR_B200_DIAG
         if (std::getenv("AKR_B200_VERBOSE")) std::fprintf(stderr, "akr_b200: %d CTA pairs resident (%s kernel)\n", n, DUO ? "tf32 pair" : "fp32 pair");
+#endif
     }
     if (grid > 2 * max_pairs) grid = 2 * max_pairs;
     launch_pdl(kern, grid, threads, smem, stream, kp);  // cluster of 2 CTAs (compile-time cluster dims)
@@ -2036,7 +2111,7 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
 // of a stage while shared memory holds about 3 us of look-ahead), so that combination is opt-in
 // (debug bit 5).
 bool use_pairs(const GemmDesc& g) {
-    if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || (g.debug & 512)) return false;
+    if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
     const bool presplit = g.A.lo != nullptr && g.B.lo != nullptr;
     if (!presplit && !(g.debug & 32)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
@@ -2050,7 +2125,7 @@ bool use_pairs(const GemmDesc& g) {
 // is 3-6 % faster than 128 x 256 tiles on single CTAs. Debug bit 10 disables it, bit 11 prefers it
 // wherever it is applicable.
 bool use_duo(const GemmDesc& g) {
-    if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || (g.debug & 1024)) return false;
+    if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 1024)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
     if (tiles * 4 < gemm_sm100_num_ctas()) return false;
@@ -2062,7 +2137,7 @@ bool use_duo(const GemmDesc& g) {
 // 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
 // amortise the accumulator hand-over between tiles.
 bool use_big_tiles(const GemmDesc& g) {
-    if (g.terms != 1 || g.splits > 1 || (g.debug & 8)) return false;
+    if (g.terms != 1 || g.splits > 1 || AKR_DIAG(g.debug, 8)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + BIG_BM - 1) / BIG_BM) * ((g.N + BIG_BN - 1) / BIG_BN);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
     return tiles >= gemm_sm100_num_ctas() && iters >= 32;
@@ -2070,6 +2145,7 @@ bool use_big_tiles(const GemmDesc& g) {
 
 int pick_bn(const GemmDesc& g) {
     // Wide tiles when there is enough work to fill the machine with them, else narrow ones.
+    if (g.N <= 64) return 64;
     if (g.N <= 128) return 128;
     // A split contraction was sized (gemm_sm100_pick_splits) for 256-wide tiles: keep them, so that
     // tiles x splits stays one balanced wave of CTAs.
@@ -2092,9 +2168,11 @@ static int g_debug_flags = 0;
 static unsigned long long g_wait_limit_ns = DEFAULT_WAIT_LIMIT_NS;
 
 void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms) {
+#ifdef AKR_B200_DIAG
     if (const char* r = std::getenv("AKR_B200_SPLIT_RATIO")) g_split_ratio = std::atof(r);
+#endif
     g_debug_flags = flags;
-    g_pdl_off = (flags & 4096) != 0;
+    g_pdl_off = AKR_DIAG(flags, 4096);
     g_wait_limit_ns = wait_limit_ms ? (unsigned long long)wait_limit_ms * 1000000ull : DEFAULT_WAIT_LIMIT_NS;
 }
 
@@ -2104,10 +2182,11 @@ bool gemm_sm100_cta_limit_active() { return g_cta_limit > 0; }
 }  // namespace
 
 int gemm_sm100_num_ctas() {
-    static int sms = 0;
+    static int sms_dev[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    int& sms = sms_dev[dev];
     if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         int v = 0;
         if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
         sms = v;
@@ -2126,8 +2205,21 @@ bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch
     return true;
 }
 
+// Large compute-bound fp32-accurate products run fastest with their operands split into high and low parts
+// up front (an extra pass over the operands) and both fetched by TMA; only the CTA-pair kernel reads such
+// operands, so the shapes are the ones that kernel takes.
+bool gemm_sm100_presplit_pays(const GemmDesc& g) {
+    if (g.terms != 3) return false;
+    const double flop = 2.0 * (double)g.M * (double)g.N * (double)g.K;
+    const double bytes = 4.0 * ((double)g.M * g.K + (double)g.K * g.N + (double)g.M * g.N);
+    if (flop / bytes < 512.0) return false;
+    if (g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug | g_debug_flags, 512)) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+    return tiles * 4 >= gemm_sm100_num_ctas();
+}
+
 int gemm_sm100_pick_splits(const GemmDesc& g) {
-    const int bn = g.N <= 128 ? 128 : 256;
+    const int bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
     const int ctas = gemm_sm100_num_ctas();
@@ -2187,9 +2279,13 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
-    MapPlan pa = plan_map(g.A, g.M, batch, g.debug & 4 ? false : true);
-    MapPlan pb = plan_map(g.B, g.N, batch, g.debug & 4 ? false : true);
+    MapPlan pa = plan_map(g.A, g.M, batch, !AKR_DIAG(g.debug, 4));
+    MapPlan pb = plan_map(g.B, g.N, batch, !AKR_DIAG(g.debug, 4));
     const bool presplit = g.terms == 3 && g.A.lo != nullptr && g.B.lo != nullptr;
+    if (presplit && !pairs) {
+        seterr(err, errlen, "gemm_sm100: pre-split operands are read by the CTA-pair kernel only (see gemm_sm100_presplit_pays)");
+        return -1;
+    }
     auto build = [&](CUtensorMap* hi, CUtensorMap* lo, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
         bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
         if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
@@ -2246,7 +2342,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     // Output map for the TMA-store epilogue: (N, M, o1, o0), boxes of 32 columns x 128 rows.
     kp.c_tma = 0;
     if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo) &&
-        !((g.debug | g_debug_flags) & 256)) {
+        !AKR_DIAG(g.debug | g_debug_flags, 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
         cuuint64_t dims[4] = {(cuuint64_t)g.N, (cuuint64_t)g.M, (cuuint64_t)g.o1, (cuuint64_t)g.o0};
@@ -2308,8 +2404,12 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     // fp32-accurate mode: 16-deep k-blocks, chains of 4 of them (64 deep) inside the tensor core.
     int rc;
     if (g.terms == 3) {
-        rc = bn == 256 ? launch_major<256, 3, 4, 4, 16>(g, kp, grid, stream, err, errlen)
-                       : launch_major<128, 3, 6, 4, 16>(g, kp, grid, stream, err, errlen);
+        // raw stages x 24 / 16 / 12 KB in flight from HBM + a short ring of low-part tiles
+        rc = bn == 256 ? launch_major<256, 3, 6, 4, 16, 2>(g, kp, grid, stream, err, errlen)
+             : bn == 128 ? launch_major<128, 3, 10, 4, 16, 3>(g, kp, grid, stream, err, errlen)
+                         : launch_major<64, 3, 12, 4, 16, 3>(g, kp, grid, stream, err, errlen);
+    } else if (bn == 64) {
+        rc = launch_major<64, 1, 8, 0, 32>(g, kp, grid, stream, err, errlen);
     } else {
         // Short contractions are write-heavy: three stages are plenty and leave room for a second set of
         // epilogue staging tiles.

@@ -46,12 +46,13 @@ struct GemmDesc {
     int splits = 1;
     float* partials = nullptr;
     int* counters = nullptr;
-    int debug = 0;  // timing experiments: bit 0 skips the TMA loads, bit 1 the MMAs (results invalid);
-                    // bit 2 disables the folded one-box-per-tile maps of M/N-major operands,
-                    // bit 3 the 256 x 256 tile kernel, bit 5 routes fp32-accurate products with in-kernel low parts through the CTA-pair kernel too,
-                    // bit 9 disables the CTA-pair kernel altogether,
-                    // bit 7 skips the output stores (timing), bit 8 disables the TMA-store epilogue,
-                    // bit 10 disables the TF32 CTA-pair kernel, bit 11 prefers it wherever it applies
+    int debug = 0;  // hooks: bit 0 skips the TMA loads (MMA-only timing, results invalid), bit 4 makes the load
+                    // warp never signal (bounded-wait test), bit 5 routes fp32-accurate products with in-kernel low
+                    // parts through the CTA-pair kernel, bit 11 prefers the TF32 CTA-pair kernel wherever it applies.
+                    // Builds with -DAKR_B200_DIAG add timing experiments: bit 1 skips the MMAs, bit 2 disables the
+                    // folded one-box-per-tile maps, bit 3 the 256 x 256 tile kernel, bit 6 one chain per tile in the
+                    // fp32 pair kernel, bit 7 skips the output stores, bit 8 disables the TMA-store epilogue, bit 9
+                    // the fp32 CTA-pair kernel, bit 10 the TF32 CTA-pair kernel, bit 12 dependent launch.
 };
 
 // True when the operand can be read by TMA as it lies (16-byte aligned base, unit stride on one
@@ -77,5 +78,9 @@ void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* 
 
 // Picks a split factor for `g` (1 when the output already fills the GPU).
 int gemm_sm100_pick_splits(const GemmDesc& g);
+
+// True when an fp32-accurate product of this shape (M, N, K, o0, o1, terms set; operands not needed) should be
+// given pre-split operands (GemmOperand::lo): large compute-bound products that the CTA-pair kernel takes.
+bool gemm_sm100_presplit_pays(const GemmDesc& g);
 
 }  // namespace akr

@@ -18,6 +18,7 @@
 
 namespace akr {
 void set_last_error(const std::string& msg);  // defined beside akr_last_error()
+std::mutex& device_launch_mutex(int dev);     // the lock every launching entry point of a device takes
 }
 using namespace akr;
 
@@ -64,6 +65,28 @@ int setup_device(int dev, DeviceScratch** out) {
 
 }  // namespace
 
+namespace akr {
+// Called by akr_synchronize() after the device has gone idle: reports (and clears) the status word of this
+// entry point's kernels on `dev`. Returns 1 when a kernel had given up on a bounded wait. Touches nothing on
+// a device where the entry point was never called.
+int noalloc_take_status(int dev) {
+    if (dev < 0 || dev >= kMaxDevices) return 0;
+    int* status = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!g_scratch[dev].ready) return 0;
+        status = g_scratch[dev].status;
+    }
+    int flag = 0;
+    if (cudaMemcpy(&flag, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    if (flag != 0) cudaMemset(status, 0, sizeof(int));
+    return flag != 0 ? 1 : 0;
+}
+}  // namespace akr
+
 extern "C" {
 
 AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_view* c, void* stream) {
@@ -85,6 +108,13 @@ AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_vi
         return report(na_fail(AKR_ERR_INVALID, "matmul_at_b_noalloc: output rows must be contiguous"));
     if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
         return report(na_fail(AKR_ERR_INVALID, "matmul_at_b_noalloc: dimension exceeds 2^31-1"));
+    // Same refusals as the regular entry points make before they touch the GPU: a null pointer would be
+    // encoded into a tensor map and fault on the device.
+    if (!a->data) return report(na_fail(AKR_ERR_INVALID, "matmul_at_b a: null data pointer"));
+    if (!b->data) return report(na_fail(AKR_ERR_INVALID, "matmul_at_b b: null data pointer"));
+    if (!c->data) return report(na_fail(AKR_ERR_INVALID, "matmul_at_b output: null data pointer"));
+    if (M > 1 && c->stride[0] < N)
+        return report(na_fail(AKR_ERR_INVALID, "matmul_at_b_noalloc: output row stride is smaller than a row"));
 
     int ndev = 0, dev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
@@ -97,20 +127,6 @@ AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_vi
     int rc = setup_device(dev, &sc);
     if (rc != AKR_OK) return report(rc);
     cudaStream_t st = (cudaStream_t)stream;
-
-    // A previous call whose kernel gave up on a bounded wait left the status word set. It is only
-    // looked at when the stream is idle, so the check never blocks behind queued work.
-    if (cudaStreamQuery(st) == cudaSuccess) {
-        int flag = 0;
-        if (cudaMemcpy(&flag, sc->status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && flag != 0) {
-            cudaMemset(sc->status, 0, sizeof(int));
-            return report(na_fail(AKR_ERR_ABORTED,
-                                  "matmul_at_b_noalloc: the previous call's kernel gave up on a bounded wait; "
-                                  "its output is invalid"));
-        }
-    } else {
-        cudaGetLastError();
-    }
 
     // Operands are read in place through TMA; a layout that would need a packed copy needs scratch
     // of the operand's own size, which the fixed arrays do not provide.
@@ -173,6 +189,7 @@ AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_vi
             return report(na_fail(AKR_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e)));
     }
     char err[256] = {0};
+    std::lock_guard<std::mutex> launch_lock(akr::device_launch_mutex(dev));
     const int lrc = gemm_sm100_launch(g, st, sc->status, err, sizeof(err));
     if (lrc != 0) return report(na_fail(lrc == -1 ? AKR_ERR_INVALID : AKR_ERR_CUDA, err));
     return AKR_OK;

@@ -163,13 +163,37 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------- reference (CPU) arm
 
+def host_cores():
+    """Host cores this process may run on (the affinity mask, not the machine's total)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
+
+
 def load_reference_module():
+    """Imports the reference's CPU build with OpenBLAS / OpenMP set to every core this process may use.
+    A launcher such as torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; OpenBLAS reads
+    that variable when it is loaded, so it is overridden BEFORE the import and set again through
+    OpenBLAS's own API afterwards. Returns (module or None, threads OpenBLAS reports)."""
     ref_dir = os.path.join(ROOT, "oracle", "_ref")
     if not any(f.startswith("_C") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
-        return None
+        return None, None
+    cores = host_cores()
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "GOTO_NUM_THREADS"):
+        os.environ[var] = str(cores)
     sys.path.insert(0, ref_dir)
     import _C as ref  # the reference's own pybind11 module, CPU build
-    return ref
+    threads = None
+    try:
+        import ctypes
+        with open(os.path.join(ref_dir, "openblas_path.txt")) as f:
+            blas = ctypes.CDLL(f.read().strip())     # already loaded by the import above: same handle
+        blas.openblas_set_num_threads(int(cores))
+        threads = int(blas.openblas_get_num_threads())
+    except Exception:  # noqa: BLE001
+        pass
+    return ref, threads
 
 
 def cpu_step(ref, a_np, b_np, dc_np):
@@ -208,9 +232,9 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    ref = load_reference_module()
+    ref, blas_threads = load_reference_module()
     kind = "reference" if ref is not None else "port"
-    cores = os.cpu_count()
+    cores = blas_threads or host_cores()
     total_steps = args.steps + args.warmup
     rows = pick_cpu_rows(ref, target_s=max(0.5, 150.0 / max(total_steps, 1)))
     a, b, dc = cpu_inputs(rows)
@@ -226,7 +250,8 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "device": "host CPU", "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample,
+                         "openblas_threads": blas_threads, "host_cores": host_cores()},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -236,14 +261,108 @@ def run_reference_arm(args):
 
 def cpu_baseline_child():
     """Bounded CPU sample, run in a child process so that OpenBLAS threads do not linger."""
-    ref = load_reference_module()
+    ref, blas_threads = load_reference_module()
     rows = pick_cpu_rows(ref, target_s=12.0)
     a, b, dc = cpu_inputs(rows)
     t = cpu_step(ref, a, b, dc)
     flop = 3 * 2 * rows * N_SQ * N_SQ
-    print(json.dumps({"value": flop / t / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+    print(json.dumps({"value": flop / t / 1e12, "unit": "TFLOP/s", "cores": blas_threads or host_cores(),
+                      "openblas_threads": blas_threads, "host_cores": host_cores(),
                       "kind": "reference" if ref is not None else "port",
                       "sample": f"one fwd+dA+dB step on {rows} of 8192 rows of A and dC against the full B ({t:.1f} s)"}))
+
+
+# ---------------------------------------------------------------------------------- batch-sharded config
+
+def c5a_phase(cabi, lib, dist, rank, world, max_over_ranks, barrier, total=8192, steps=10, warmup=3):
+    """8192 independent [256x256]@[256x256] products (fwd + dA + dB) split along the batch over the
+    ranks, no collective: the strong-scaling row of the workload list. Returns per mode the whole-job
+    time at `world` ranks, the time of the full batch on ONE GPU measured in the same run (rank 0 alone
+    while the others wait) and their ratio. Inputs: a seeded 256-batch slab of uniform[-1,1) values
+    repeated along the batch (the timing does not depend on the values), dC = ones."""
+    import ctypes as C
+    from aakaar_b200.distributed import shard_range, BatchShardedMatmul, CudaBackend
+    peaks, _ = measured_peaks()
+    slab_n = 256
+
+    def filled(nb, seed):
+        g = np.random.Generator(np.random.PCG64(seed))
+        slab = g.random((slab_n, 256, 256), dtype=np.float32) * np.float32(2.0) - np.float32(1.0)
+        dev = cabi.DeviceArray((nb, 256, 256))
+        first = min(nb, slab_n)
+        cabi.h2d(dev, slab[:first], None, 0)
+        done = first
+        while done < nb:            # repeat on the device
+            n = min(done, nb - done)
+            cabi.check(lib.akr_memcpy_d2d(dev.ptr + 4 * done * 65536, dev.ptr, 4 * n * 65536, None))
+            done += n
+        cabi.synchronize()
+        return dev, slab
+
+    def ones(nb):
+        dev = cabi.DeviceArray((nb, 256, 256))
+        cabi.check(lib.akr_fill(C.cast(dev.ptr, C.POINTER(C.c_float)), 1.0, nb * 65536, None))
+        return dev
+
+    def run(nb, sh_world, sh_rank, sync_ranks):
+        A, a_slab = filled(nb, 501 + sh_rank)
+        B, b_slab = filled(nb, 502 + 1000 * (sh_rank + 1))
+        DC = ones(nb)
+        Cd, DAd, DBd = (cabi.DeviceArray((nb, 256, 256)) for _ in range(3))
+        res = {}
+        for name, mode, tol in (("tf32", cabi.MODE_TF32, 2e-3), ("fp32_3xtf32", cabi.MODE_FP32, 1e-5)):
+            sh = BatchShardedMatmul(total_batch=nb * sh_world, world=sh_world, rank=sh_rank, backend=CudaBackend(mode=mode))
+
+            def step():
+                sh.forward(A, B, out=Cd)
+                sh.backward(A, B, DC, da=DAd, db=DBd)
+            for _ in range(warmup):
+                step()
+            if sync_ranks:
+                barrier()
+            else:
+                cabi.synchronize()
+            e0, e1 = cabi.Event().record(), cabi.Event()
+            for _ in range(steps):
+                step()
+            e1.record()
+            e1.synchronize()
+            ms = e0.elapsed_ms(e1) / steps
+            if sync_ranks:
+                ms = max_over_ranks(ms)
+            # one batch entry of each result against float64
+            got = np.empty((3, 256, 256), np.float32)
+            for j, dev in enumerate((Cd, DAd, DBd)):
+                cabi.d2h(got[j], dev, None, (nb - 1) * 65536)
+            cabi.synchronize()
+            a64, b64 = a_slab[(nb - 1) % slab_n].astype(np.float64), b_slab[(nb - 1) % slab_n].astype(np.float64)
+            one = np.ones((256, 256))
+            refs = (a64 @ b64, one @ b64.T, a64.T @ one)
+            err = max(float(np.linalg.norm(got[j] - r) / np.linalg.norm(r)) for j, r in enumerate(refs))
+            if not err < tol:
+                raise RuntimeError(f"bench.py: batch-sharded config, mode {name}: parity {err} > {tol}")
+            res[name] = {"ms": ms, "rel_frobenius_err": err}
+        return res
+
+    lo, hi = shard_range(total, world, rank)
+    sharded = run(hi - lo, world, rank, True)
+    single = sharded
+    if world > 1:
+        barrier()
+        single = run(total, 1, 0, False) if rank == 0 else None
+        barrier()
+    if rank != 0:
+        return None
+    bytes_step = 9 * total * 256 * 256 * 4      # whole job: 3 products x (2 operands + 1 result)
+    out = {"workload": f"{total} independent [256x256]@[256x256] fp32 products, fwd + dA + dB, batch split over "
+                       f"{world} rank(s), no collective", "scaling": "strong", "bound": "hbm",
+           "algorithmic_bytes_per_step": bytes_step, "steps": steps, "warmup": warmup}
+    for name in ("tf32", "fp32_3xtf32"):
+        ms, ms1 = sharded[name]["ms"], single[name]["ms"]
+        out[name] = {"ms": ms, "gbs": bytes_step / ms / 1e6, "frac_of_hbm": bytes_step / ms / 1e6 / (peaks["hbm_gbs"] * world),
+                     "ms_1gpu_same_run": ms1, "speedup_vs_1gpu": ms1 / ms,
+                     "rel_frobenius_err": sharded[name]["rel_frobenius_err"]}
+    return out
 
 
 # ---------------------------------------------------------------------------------- GPU arm
@@ -346,7 +465,36 @@ def run_gpu_arm(args):
         kern_ms = [sum(p[j] for p in per) / steps for j in range(3)]
         return ms, kern_ms, launches, (t_wall0, t_wall1)
 
+    # ---- parity of what the timed phases leave in the output buffers (outside every timed region):
+    # sampled rows of C, dA and dB against float64 on the host. dB is the sum over ranks, so every
+    # rank contributes A_r[:, rows]^T . dC_r and the references are summed with a small all-reduce.
+    def parity_check(tol):
+        cabi.synchronize()
+        rows = np.array([3, N_SQ // 3 + 1, (2 * N_SQ) // 3 + 5, N_SQ - 1])
+        a64 = np.asarray(hA)[rows].astype(np.float64)
+        dc64 = np.asarray(hDC)[rows].astype(np.float64)
+        b64 = np.asarray(hB).astype(np.float64)
+        ref_c, ref_da = a64 @ b64, dc64 @ b64.T
+        del b64
+        ref_db = np.asarray(hA)[:, rows].astype(np.float64).T @ np.asarray(hDC).astype(np.float64)
+        if dist is not None:
+            import torch
+            t = torch.from_numpy(ref_db).cuda()
+            dist.all_reduce(t)
+            ref_db = t.cpu().numpy()
+        got = np.empty((3, len(rows), N_SQ), np.float32)
+        for j, dev in enumerate((Cd, DAd, DBd)):
+            for i, r in enumerate(rows):
+                cabi.d2h(got[j, i], dev, None, int(r) * N_SQ)
+        cabi.synchronize()
+        errs = [float(np.linalg.norm(got[j].astype(np.float64) - ref) / np.linalg.norm(ref))
+                for j, ref in enumerate((ref_c, ref_da, ref_db))]
+        worst = max_over_ranks(max(errs))
+        return {"rel_frobenius": {"C": errs[0], "dA": errs[1], "dB_summed_over_ranks": errs[2]},
+                "worst_over_ranks": worst, "tol": tol, "rows": [int(r) for r in rows], "ok": bool(worst < tol)}
+
     ms_tf32, kern_tf32, launches, wall = device_phase(cabi.MODE_TF32, args.steps, args.warmup)
+    parity = {"tf32": parity_check(2e-3)} if not args.profile else {}
     if args.profile:
         # profiler capture: only the TF32 device phase (optionally the fp32-accurate one instead)
         if args.profile == "fp32":
@@ -360,6 +508,32 @@ def run_gpu_arm(args):
         return 0
     steps32 = max(3, args.steps // 4)
     ms_fp32, kern_fp32, launches32, _ = device_phase(cabi.MODE_FP32, steps32, max(3, args.warmup))
+    parity["fp32_3xtf32"] = parity_check(1e-5)
+    if not all(p["ok"] for p in parity.values()):
+        print(json.dumps({"parity": parity}), file=sys.stderr, flush=True)
+        raise RuntimeError("bench.py: the timed path's results disagree with the float64 reference")
+
+    # ---- measured TF32 ceiling: the forward kernel issuing its MMAs back to back with the TMA loads
+    # switched off (operands are whatever shared memory holds; the result is not used).
+    def mma_only_ms(reps=10):
+        cabi.check(lib.akr_debug_configure(1, 0))
+        try:
+            for _ in range(3):
+                cabi.matmul_fwd(A, B, mode=cabi.MODE_TF32, out=Cd)
+            cabi.synchronize()
+            e0, e1 = cabi.Event().record(), cabi.Event()
+            for _ in range(reps):
+                cabi.matmul_fwd(A, B, mode=cabi.MODE_TF32, out=Cd)
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_ms(e1) / reps
+        finally:
+            cabi.check(lib.akr_debug_configure(0, 0))
+    t_m0 = time.time()
+    ms_mma_only = mma_only_ms()
+    t_m1 = time.time()
+
+    c5a = c5a_phase(cabi, lib, dist, rank, n_gpus, max_over_ranks, barrier)
 
     # ---- end to end through the Python API, host buffers in, host buffers out
     def e2e_phase(steps, warmup):
@@ -505,7 +679,12 @@ def run_gpu_arm(args):
         clocks = sampler.summary(0, float("inf"))
         clocks["note"] = "timed region shorter than the sampling period; samples cover the whole run"
     peaks, peak_src = measured_peaks()
-    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0   # no TF32 figure is measured: dense TF32 = bf16 / 2
+    # Denominator: MEASURED_PEAKS.json holds no TF32 figure; dense TF32 is half of dense bf16. The burst
+    # figure applies when the SM clock stayed at its maximum through the timed region, the sustained
+    # (power-capped) one otherwise.
+    at_max = (clocks.get("sm_mhz") or 0) >= 0.97 * (clocks.get("sm_max_mhz") or 1e9)
+    peak_kind = "bf16_tflops" if at_max else "bf16_tflops_sustained"
+    tf32_peak = peaks[peak_kind] / 2.0
     value = n_gpus * FLOP_PER_STEP / (ms_tf32 * 1e-3) / 1e12
     names = ["fwd C=A.B (K-major A, N-major B)", "dA=dC.B^T (K-major, K-major)", "dB=A^T.dC (M-major, N-major)"]
     if n_gpus > 1:
@@ -513,13 +692,28 @@ def run_gpu_arm(args):
     dom = max(range(3), key=lambda j: kern_tf32[j]) if n_gpus == 1 else 0
     per_launch_flop = 2 * N_SQ ** 3
     achieved = per_launch_flop / (kern_tf32[dom] * 1e-3) / 1e12
+    mma_clk = sampler.summary(t_m0, t_m1)
+    mma_only_tf = per_launch_flop / (ms_mma_only * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": names[dom], "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
                 "frac": achieved / tf32_peak,
-                "peak_source": f"MEASURED_PEAKS.json bf16_tflops_sustained/2 ({peak_src}); nominal dense TF32 1125",
-                "traffic": NCU_TRAFFIC_BYTES,
+                "peak_source": f"MEASURED_PEAKS.json {peak_kind}/2 ({peak_src}; "
+                               f"{'burst: median SM clock at maximum' if at_max else 'sustained: SM clock below maximum'}"
+                               f" in the timed region); nominal dense TF32 1125",
+                "frac_of_burst_div2": achieved / (peaks["bf16_tflops"] / 2.0),
+                "frac_of_sustained_div2": achieved / (peaks["bf16_tflops_sustained"] / 2.0),
+                "frac_of_nominal_1125": achieved / 1125.0,
+                "peak_tf32_mma_only": {"tflops": mma_only_tf, "ms_per_launch": ms_mma_only,
+                                       "sm_mhz": mma_clk.get("sm_mhz"), "frac": achieved / mma_only_tf,
+                                       "how": "the forward kernel of this workload with its TMA loads switched off "
+                                              "(tcgen05.mma kind::tf32 issued back to back), CUDA events, 10 launches"},
+                "traffic": NCU_TRAFFIC_BYTES, "traffic_over_algorithmic": NCU_TRAFFIC_BYTES / (3 * N_SQ * N_SQ * 4.0),
                 "by_kernel": [{"kernel": names[j], "ms": kern_tf32[j],
                                "tflops": per_launch_flop / (kern_tf32[j] * 1e-3) / 1e12 if n_gpus == 1 else None}
-                              for j in range(3)]}
+                              for j in range(3)]
+                + [{"kernel": "fp32-accurate (3xTF32) " + names[j], "ms": kern_fp32[j],
+                    "tflops": per_launch_flop / (kern_fp32[j] * 1e-3) / 1e12,
+                    "frac_of_peak_div3": per_launch_flop / (kern_fp32[j] * 1e-3) / 1e12 / (tf32_peak / 3.0)}
+                   for j in range(3) if n_gpus == 1]}
 
     cpu = None
     if n_gpus == 1 and not args.no_cpu_baseline:
@@ -528,7 +722,7 @@ def run_gpu_arm(args):
                                  text=True, timeout=600)
             cpu = json.loads(out.stdout.strip().splitlines()[-1])
         except Exception as exc:  # noqa: BLE001
-            cpu = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "reference",
+            cpu = {"value": None, "unit": "TFLOP/s", "cores": host_cores(), "kind": "reference",
                    "sample": f"failed: {exc}"}
 
     bytes_each_way = 3 * N_SQ * N_SQ * 4
@@ -548,6 +742,8 @@ def run_gpu_arm(args):
                                           "value": n_gpus * FLOP_PER_STEP / (ms_e2e_api * 1e-3) / 1e12}},
         "gpu_launches": launches,
         "roofline": roofline,
+        "parity": parity,
+        "c5a": c5a,
         "cpu_baseline": cpu,
         "modes": {
             "tf32": {"ms_per_step": ms_tf32, "tflops": value, "frac_of_peak": value / n_gpus / tf32_peak,

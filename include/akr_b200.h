@@ -163,8 +163,9 @@ AKR_API int akr_matmul_at_b(const akr_view* a, const akr_view* b, akr_view* c, i
  *   - All calls on a device share the one array, which keeps the previous call's contents (what must
  *     start at zero is cleared on every call): two calls that overlap on the GPU, on different
  *     streams, race. Keep them on one stream or order them yourself.
- *   - A kernel that gave up on a bounded wait is reported by the next call on that device that finds
- *     the stream idle (AKR_ERR_ABORTED). */
+ *   - The call itself never waits for the GPU and reads nothing back. A kernel that gave up on a
+ *     bounded wait is reported, like those of every other entry point, by the next akr_synchronize()
+ *     on that device (AKR_ERR_ABORTED). */
 AKR_API int akr_matmul_at_b_noalloc(const akr_view* a, const akr_view* b, akr_view* c, void* stream);
 
 /* Forward-only matmul of the reference's other dtypes, with the same broadcasting:
@@ -198,17 +199,18 @@ AKR_API int akr_event_synchronize(void* event);
 AKR_API int akr_event_elapsed_ms(void* start, void* end, float* ms);
 AKR_API int akr_event_destroy(void* event);
 
-/* Test hook for the failure path. Every wait inside the GEMM kernels is bounded; a kernel whose wait
- * runs out stops, frees its tensor memory and sets a status word that akr_synchronize() reports as
- * AKR_ERR_ABORTED, leaving the context usable. `wait_limit_ms` sets that bound (0 = default, 4 s);
- * flag 16 makes the load warp never signal its stages, so that every waiter gives up; flags 1 / 2 / 4 / 8
- * are timing diagnostics (skip loads, skip MMAs, no folded maps, no 256x256 tiles; results invalid with 1 / 2);
- * flag 32 routes every fp32-accurate product through the CTA-pair (cta_group::2) kernel (by default only large
- * pre-split ones use it), flag 512 disables that kernel; flag 1024 disables the TF32 CTA-pair kernel, flag 2048
- * prefers it wherever it applies; flag 4096 launches the GEMM kernels without programmatic stream serialization;
- * flags 64 / 128 / 256 are further timing diagnostics (one accumulation chain per tile in the fp32 pair kernel, no
- * output stores, no TMA-store epilogue).
- * akr_debug_configure(0, 0) restores normal operation. */
+/* Test and measurement hooks (no counterpart in the reference). Every wait inside the GEMM kernels is
+ * bounded; a kernel whose wait runs out stops, frees its tensor memory and sets a status word that
+ * akr_synchronize() reports as AKR_ERR_ABORTED, leaving the context usable. `wait_limit_ms` sets that
+ * bound (0 = default, 4 s). Flags (or-ed):
+ *    1  the GEMM kernels skip their TMA loads and multiply whatever shared memory holds: times the
+ *       tcgen05.mma issue rate alone (the measured tensor-pipe ceiling a benchmark divides by); results invalid
+ *   16  the load warp never signals its stages, so that every waiter gives up (failure-path test)
+ *   32  fp32-accurate products run on the CTA-pair (cta_group::2) kernel even with in-kernel low parts
+ *       (by default only large pre-split products use it)
+ * 2048  TF32 products run on the CTA-pair kernel wherever it applies (by default a band of shapes)
+ * akr_debug_configure(0, 0) restores normal operation. Further timing switches exist only in builds
+ * compiled with -DAKR_B200_DIAG. */
 AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
 
 /* Bytes of scratch the library currently holds on this device (operand splits, split-K partials). */

@@ -290,6 +290,67 @@ def test_config5a_batched_slice(mode, tol):
         assert rel_fro(gb[i], a[i].astype(np.float64).T @ ones) < tol
 
 
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_headline_size_8192_backward_sampled_rows(mode, tol):
+    # The size every throughput figure is quoted on (8192^3, seeds of the benchmark): sampled rows of C,
+    # dA = dC . B^T and dB = A^T . dC against float64, in both modes.
+    n = 8192
+    s = np.float32(1.0 / np.sqrt(n))
+    a = np.random.Generator(np.random.PCG64(401)).standard_normal((n, n), dtype=np.float32) * s
+    b = np.random.Generator(np.random.PCG64(402)).standard_normal((n, n), dtype=np.float32) * s
+    dc = np.random.Generator(np.random.PCG64(403)).standard_normal((n, n), dtype=np.float32)
+    A, B, DC = dev(a), dev(b), dev(dc)
+    rows = [0, 2731, 4100, n - 1]
+
+    def pick(x):
+        return np.stack([x.as_strided((n,), (1,), offset=r * n).to_numpy() for r in rows])
+    c = cabi.matmul_fwd(A, B, mode=mode)
+    b64 = b.astype(np.float64)
+    assert rel_fro(pick(c), a[rows].astype(np.float64) @ b64) < tol
+    del c
+    ga, gb = cabi.matmul_bwd(A, B, DC, mode=mode)
+    assert rel_fro(pick(ga), dc[rows].astype(np.float64) @ b64.T) < tol
+    del b64
+    assert rel_fro(pick(gb), a[:, rows].astype(np.float64).T @ dc.astype(np.float64)) < tol
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_config5a_full_batch(mode, tol):
+    # All 8192 independent [256x256]@[256x256] pairs on one GPU (2 GiB per array): sampled batch entries of
+    # C, dA and dB against float64, and a checksum of checksums over the whole result: with dC = ones,
+    # sum(dA[i]) = 256 * sum(B[i]) and sum(dB[i]) = 256 * sum(A[i]) for every batch entry i.
+    nb = 8192
+    ga_ = np.random.Generator(np.random.PCG64(501))
+    gb_ = np.random.Generator(np.random.PCG64(502))
+    a = ga_.random((nb, 256, 256), dtype=np.float32) * np.float32(2) - np.float32(1)
+    b = gb_.random((nb, 256, 256), dtype=np.float32) * np.float32(2) - np.float32(1)
+    A, B = dev(a), dev(b)
+    c = cabi.matmul_fwd(A, B, mode=mode)
+    cn = c.to_numpy()
+    for i in (0, 4095, 4096, nb - 1):
+        assert rel_fro(cn[i], a[i].astype(np.float64) @ b[i].astype(np.float64)) < tol
+    # every batch entry: sum of C[i] = rowsum-of-A . colsum-of-B
+    want = np.einsum("bk,bk->b", a.sum(axis=1, dtype=np.float64), b.sum(axis=2, dtype=np.float64))
+    got = cn.sum(axis=(1, 2), dtype=np.float64)
+    scale = np.sqrt(np.mean(want ** 2))
+    assert np.max(np.abs(got - want)) / scale < (50 * tol)
+    del cn, c
+    DC = DA((nb, 256, 256))
+    import ctypes as C
+    cabi.check(cabi.lib().akr_fill(C.cast(DC.ptr, C.POINTER(C.c_float)), 1.0, nb * 65536, None))
+    ga, gb = cabi.matmul_bwd(A, B, DC, mode=mode)
+    gan = ga.to_numpy()
+    ones = np.ones((256, 256))
+    for i in (3, 5000, nb - 1):
+        assert rel_fro(gan[i], ones @ b[i].astype(np.float64).T) < tol
+    assert rel_fro(gan.sum(axis=(1, 2), dtype=np.float64), 256.0 * b.sum(axis=(1, 2), dtype=np.float64)) < tol
+    del gan, ga
+    gbn = gb.to_numpy()
+    for i in (3, 5000, nb - 1):
+        assert rel_fro(gbn[i], a[i].astype(np.float64).T @ ones) < tol
+    assert rel_fro(gbn.sum(axis=(1, 2), dtype=np.float64), 256.0 * a.sum(axis=(1, 2), dtype=np.float64)) < tol
+
+
 def test_largest_benchmark_square_16384_sampled_rows():
     # the largest size of the benchmark sweep (16384^3, 1 GiB per matrix): sampled rows of C, dA and dB against
     # float64, TF32 mode and the fp32-accurate mode (the latter splits its operands up front at this size)
