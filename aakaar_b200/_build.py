@@ -30,7 +30,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "-cudart", "static",
 ]
-CUDA_SOURCES = ["gemm_sm100.cu", "aux_kernels.cu", "akr_api.cu", "noalloc.cu"]
+CUDA_SOURCES = ["gemm_sm100.cu", "aux_kernels.cu", "akr_api.cu", "noalloc.cu", "multi_gpu.cu"]
 CUDA_HEADERS = ["gemm_sm100.h", "aux_kernels.h", "sm100_ptx.cuh"]
 
 

@@ -87,6 +87,13 @@ def load():
         "akr_event_synchronize": [vp],
         "akr_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
         "akr_event_destroy": [vp],
+        "akr_mg_get_unique_id": [vp],
+        "akr_mg_init": [C.c_int, C.c_int, vp],
+        "akr_mg_allreduce": [vp, sz, C.c_int, C.c_int, vp],
+        "akr_mg_allreduce_sum": [fp, sz, vp],
+        "akr_mg_world": [C.POINTER(C.c_int), C.POINTER(C.c_int)],
+        "akr_mg_nccl_version": [C.POINTER(C.c_int)],
+        "akr_mg_finalize": [],
     }
     for name, args in sigs.items():
         getattr(lib, name).argtypes = args
@@ -232,6 +239,16 @@ class Event:
         if _lib is not None and self.h:
             _lib.akr_event_destroy(self.h)
             self.h = None
+
+
+MG_UNIQUE_ID_BYTES = 128
+MG_SUM, MG_MAX = 0, 1
+DTYPE_F32, DTYPE_F64 = 0, 1
+
+
+def stream_wait_event(stream, ev: "Event"):
+    """Makes `stream` (a Stream, or None for the legacy default stream) wait for `ev`."""
+    check(lib().akr_stream_wait_event(_sh(stream), ev.h))
 
 
 def plan(a: DeviceArray, b: DeviceArray):

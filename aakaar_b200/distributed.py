@@ -11,7 +11,8 @@ surface. Two layouts cover the path:
   reduced number of CTAs so that the collective's kernels find free SMs.
 
 Compute and communication are injected as small backends so that the partitioning / reduction
-logic is testable on CPU ranks (gloo); the default backend is the CUDA library through its C ABI.
+logic is testable on CPU ranks (gloo); the default backend is the CUDA library through its C ABI,
+with the collective issued by the library itself (`NodeComm` over akr_mg_*).
 """
 from __future__ import annotations
 
@@ -27,14 +28,104 @@ def shard_range(total: int, world: int, rank: int):
     return lo, lo + base + (1 if rank < rem else 0)
 
 
-class CudaBackend:
-    """Local products on this rank's GPU through the C ABI; collectives through torch.distributed."""
+def _ptr_count(x):
+    """(device pointer, element count) of a float32 device array: a cabi.DeviceArray or anything that
+    exports __cuda_array_interface__ (the pybind Tensor does). Must be contiguous."""
+    if hasattr(x, "ptr") and hasattr(x, "size"):
+        return int(x.ptr), int(x.size)
+    cai = x.__cuda_array_interface__
+    n = 1
+    for d in cai["shape"]:
+        n *= int(d)
+    return int(cai["data"][0]), n
 
-    def __init__(self, mode=-1, group=None):
+
+class NodeComm:
+    """The ranks of one node joined through the library's own collective entry points (akr_mg_*: NCCL
+    called from C++ behind the C ABI - no torch on this path).
+
+    `exchange` carries the 128-byte rendezvous id from rank 0 to the others: a callable that takes the
+    id (bytes) on rank 0 and None elsewhere and returns the id on every rank. Under a launcher that
+    provides a key-value store or a CPU process group this is a one-line broadcast
+    (see `exchange_via_torch_store`); a file or a socket works as well.
+    """
+
+    def __init__(self, rank, world, exchange):
+        import ctypes as C
+        from . import cabi
+        self.cabi, self.rank, self.world = cabi, int(rank), int(world)
+        lib = cabi.lib()
+        buf = C.create_string_buffer(cabi.MG_UNIQUE_ID_BYTES)
+        uid = None
+        if self.rank == 0:
+            cabi.check(lib.akr_mg_get_unique_id(buf))
+            uid = bytes(buf.raw)
+        uid = exchange(uid)
+        if not isinstance(uid, (bytes, bytearray)) or len(uid) != cabi.MG_UNIQUE_ID_BYTES:
+            raise ValueError("NodeComm: the exchange must return the 128-byte id on every rank")
+        cabi.check(lib.akr_mg_init(self.rank, self.world, C.c_char_p(bytes(uid))))
+        self.stream = cabi.Stream()   # collectives run here, beside the compute stream
+        self._scratch = None
+
+    def allreduce_sum_async(self, x, after=None):
+        """In-place float32 sum of the device array `x` over all ranks on the communication stream, ordered
+        after everything enqueued so far on the compute stream `after` (None = the legacy default stream).
+        Returns the event to wait for."""
+        cabi = self.cabi
+        import ctypes as C
+        ready = cabi.Event().record(after)
+        self.stream.wait_event(ready)
+        ptr, n = _ptr_count(x)
+        cabi.check(cabi.lib().akr_mg_allreduce_sum(C.cast(ptr, C.POINTER(C.c_float)), n, self.stream.h))
+        return cabi.Event().record(self.stream)
+
+    def allreduce_sum_on(self, x, stream):
+        """The same collective enqueued directly on `stream` (no overlap; for pipelines that order it themselves)."""
+        import ctypes as C
+        ptr, n = _ptr_count(x)
+        self.cabi.check(self.cabi.lib().akr_mg_allreduce_sum(C.cast(ptr, C.POINTER(C.c_float)), n,
+                                                             stream.h if stream is not None else None))
+
+    def reduce_scalar(self, value, op="max"):
+        """One double reduced over all ranks through the device (timings: the maximum over ranks)."""
+        import ctypes as C
+        import numpy as np
+        cabi = self.cabi
+        if self._scratch is None:
+            self._scratch = cabi.DeviceArray((2,))      # 8 bytes: one float64
+        host = np.array([value], dtype=np.float64)
+        cabi.check(cabi.lib().akr_memcpy_h2d(self._scratch.ptr, host.ctypes.data, 8, None))
+        cabi.check(cabi.lib().akr_mg_allreduce(self._scratch.ptr, 1, cabi.DTYPE_F64,
+                                               cabi.MG_MAX if op == "max" else cabi.MG_SUM, None))
+        cabi.check(cabi.lib().akr_memcpy_d2h(host.ctypes.data, self._scratch.ptr, 8, None))
+        cabi.synchronize()
+        return float(host[0])
+
+    def barrier(self):
+        self.cabi.synchronize()
+        self.reduce_scalar(0.0, "sum")
+
+    def close(self):
+        self.cabi.check(self.cabi.lib().akr_mg_finalize())
+
+
+def exchange_via_torch_store(uid):
+    """Rendezvous-id broadcast over an initialised torch.distributed group (any backend, gloo included).
+    torch is the launcher's plumbing here, not part of the compute or collective path."""
+    import torch.distributed as dist
+    box = [uid]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
+class CudaBackend:
+    """Local products on this rank's GPU through the C ABI; the dB reduction through a NodeComm."""
+
+    def __init__(self, mode=-1, comm=None):
         from . import cabi
         self.cabi = cabi
         self.mode = mode
-        self.group = group
+        self.comm = comm
 
     def fwd(self, a, b, out=None):
         return self.cabi.matmul_fwd(a, b, mode=self.mode, out=out)
@@ -46,14 +137,12 @@ class CudaBackend:
         self.cabi.check(self.cabi.lib().akr_set_gemm_cta_limit(int(n)))
 
     def allreduce_start(self, x):
-        import torch
-        import torch.distributed as dist
-        t = torch.as_tensor(x, device="cuda")   # zero-copy alias of the library's buffer
-        return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group, async_op=True), t
+        if self.comm is None:
+            raise RuntimeError("CudaBackend: a NodeComm is needed to sum a gradient over ranks")
+        return self.comm.allreduce_sum_async(x)
 
     def allreduce_wait(self, handle):
-        work, _t = handle
-        work.wait()   # orders the collective before later work on the current (default) stream
+        self.cabi.stream_wait_event(None, handle)   # later work on the compute stream sees the summed gradient
 
 
 @dataclass
@@ -88,8 +177,9 @@ class RowShardedMatmul:
     rank: int
     backend: object = None
     overlap: bool = True
-    # SMs left free for the collective while it overlaps the dA GEMM (AKR_B200_COMM_CTAS overrides, for tuning)
-    comm_ctas: int = int(__import__("os").environ.get("AKR_B200_COMM_CTAS", "20"))
+    # SMs left free for the collective while it overlaps the dA GEMM: 128 CTAs run the 1024 tiles of an
+    # 8192 x 8192 output in exactly 8 rounds (any count from 129 to 146 needs 8 rounds as well)
+    comm_ctas: int = 20
 
     def __post_init__(self):
         self.lo, self.hi = shard_range(self.total_m, self.world, self.rank)

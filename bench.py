@@ -66,16 +66,18 @@ class _StdoutToStderr:
         return False
 
 
-def _init_nccl(local_rank):
-    import torch
+def _init_ranks(rank, world):
+    """Joins the ranks of the node. torch.distributed (gloo, CPU) is only the launcher's plumbing: it carries
+    the 128-byte rendezvous id and small host-side sums. The collective of the data path - the dB all-reduce -
+    and the barriers / max-over-ranks around the timed regions are the library's own (akr_mg_*: NCCL called
+    from C++ behind the C ABI). Returns (dist, comm)."""
     import torch.distributed as dist
+    from aakaar_b200.distributed import NodeComm, exchange_via_torch_store
     with _StdoutToStderr():
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        t = torch.zeros(1, device="cuda")
-        dist.all_reduce(t)          # forces communicator creation (and its banner) now
-        torch.cuda.synchronize()
-    return dist
+        dist.init_process_group("gloo")
+        comm = NodeComm(rank, world, exchange_via_torch_store)
+        comm.barrier()               # forces communicator set-up (and NCCL's banner) now
+    return dist, comm
 
 def normal(shape, seed, sigma):
     g = np.random.Generator(np.random.PCG64(seed))
@@ -385,23 +387,23 @@ def run_gpu_arm(args):
         raise RuntimeError("bench.py: no CUDA device; the product path has no CPU fallback")
     cabi.check(lib.akr_set_device(local_rank))
 
-    dist = None
+    dist, comm = None, None
     if world > 1:
-        dist = _init_nccl(local_rank)
+        dist, comm = _init_ranks(rank, world)
 
     def barrier():
         cabi.synchronize()
-        if dist is not None:
-            dist.barrier()
-            cabi.synchronize()
+        if comm is not None:
+            comm.barrier()
 
     def max_over_ranks(x):
-        if dist is None:
-            return x
-        import torch
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return x if comm is None else comm.reduce_scalar(x, "max")
+
+    def finish():
+        if comm is not None:
+            comm.close()
+        if dist is not None:
+            dist.destroy_process_group()
 
     # ---- inputs: generated on the host into PINNED buffers (also the source of the e2e copies)
     s = 1.0 / np.sqrt(N_SQ)
@@ -425,7 +427,7 @@ def run_gpu_arm(args):
         sampler.start()
 
     def device_phase(mode, steps, warmup):
-        be = CudaBackend(mode=mode)
+        be = CudaBackend(mode=mode, comm=comm)
         sh = RowShardedMatmul(total_m=N_SQ * n_gpus, world=n_gpus, rank=rank, backend=be)
         ev = [[cabi.Event() for _ in range(4)] for _ in range(steps)]
 
@@ -479,9 +481,9 @@ def run_gpu_arm(args):
         ref_db = np.asarray(hA)[:, rows].astype(np.float64).T @ np.asarray(hDC).astype(np.float64)
         if dist is not None:
             import torch
-            t = torch.from_numpy(ref_db).cuda()
-            dist.all_reduce(t)
-            ref_db = t.cpu().numpy()
+            t = torch.from_numpy(np.ascontiguousarray(ref_db))
+            dist.all_reduce(t)          # float64 on the host (gloo): the reference, not the path under test
+            ref_db = t.numpy()
         got = np.empty((3, len(rows), N_SQ), np.float32)
         for j, dev in enumerate((Cd, DAd, DBd)):
             for i, r in enumerate(rows):
@@ -503,8 +505,7 @@ def run_gpu_arm(args):
             sampler.stop()
             print(json.dumps({"profile_run": True, "size": N_SQ, "ms_per_step": ms_tf32, "kernel_ms": kern_tf32,
                               "gpu_launches": launches}), flush=True)
-        if dist is not None:
-            dist.destroy_process_group()
+        finish()
         return 0
     steps32 = max(3, args.steps // 4)
     ms_fp32, kern_fp32, launches32, _ = device_phase(cabi.MODE_FP32, steps32, max(3, args.warmup))
@@ -538,7 +539,8 @@ def run_gpu_arm(args):
     # ---- end to end through the Python API, host buffers in, host buffers out
     def e2e_phase(steps, warmup):
         ak.set_tf32(True)
-        sh = RowShardedMatmul(total_m=N_SQ * n_gpus, world=n_gpus, rank=rank, backend=CudaBackend(mode=cabi.MODE_TF32))
+        sh = RowShardedMatmul(total_m=N_SQ * n_gpus, world=n_gpus, rank=rank,
+                              backend=CudaBackend(mode=cabi.MODE_TF32, comm=comm))
 
         def step():
             a = _C.from_pinned(hA, True)
@@ -547,8 +549,7 @@ def run_gpu_arm(args):
             c = ak.matmul(a, b)
             c.backward(dc)
             if n_gpus > 1:
-                h = sh.backend.allreduce_start(b.grad)
-                sh.backend.allreduce_wait(h)
+                comm.allreduce_sum_on(b.grad, None)    # on the compute stream: this path runs one thing at a time
             c.copy_to_host(hC)
             a.grad.copy_to_host(hDA)
             b.grad.copy_to_host(hDB)
@@ -575,10 +576,8 @@ def run_gpu_arm(args):
         mode = cabi.MODE_TF32
         # One GPU: two sets of device buffers, so that step i's downloads overlap step i+1's uploads
         # (PCIe is full duplex; within one step the dB download can only start when all uploads are in).
-        nsets = 2 if n_gpus == 1 else 1
-        sets = [(A, B, DC, Cd, DAd, DBd)]
-        if nsets == 2:
-            sets.append(tuple(cabi.DeviceArray((N_SQ, N_SQ)) for _ in range(6)))
+        nsets = 2
+        sets = [(A, B, DC, Cd, DAd, DBd), tuple(cabi.DeviceArray((N_SQ, N_SQ)) for _ in range(6))]
         in_free = [None] * nsets    # event: the GEMMs that read this set's inputs have finished
         out_free = [None] * nsets   # event: this set's outputs have been downloaded
 
@@ -618,26 +617,19 @@ def run_gpu_arm(args):
                 e = ev().record(s_c)
                 s_out.wait_event(e)
                 cabi.d2h(hDA[i * rows:(i + 1) * rows], DA_, s_out, i * rows * N_SQ)
-            if n_gpus == 1:
-                for j in range(nch):                               # dB in row panels (k range j of A)
-                    cabi.matmul_bwd(colv(A_, j), rowv(B_, j), DC_, mode=mode, need_da=False, need_db=True,
-                                    db=rowv(DB_, j), stream=s_c)
-                    e = ev().record(s_c)
-                    s_out.wait_event(e)
-                    cabi.d2h(hDB[j * rows:(j + 1) * rows], DB_, s_out, j * rows * N_SQ)
-                in_free[k % nsets] = ev().record(s_c)
-                out_free[k % nsets] = ev().record(s_out)
-                if prev_done[0] is not None:
-                    prev_done[0].synchronize()     # at most two steps in flight: bounds the host's run-ahead
-                prev_done[0] = out_free[k % nsets]
-            else:
-                cabi.matmul_bwd(A_, B_, DC_, mode=mode, need_da=False, need_db=True, db=DB_, stream=s_c)
-                s_c.synchronize()
-                h = CudaBackend(mode=mode).allreduce_start(DB_)
-                h[0].wait()
-                cabi.d2h(hDB, DB_, None)
-                cabi.synchronize()
-                s_out.synchronize()
+            for j in range(nch):                                   # dB in row panels (k range j of A)
+                cabi.matmul_bwd(colv(A_, j), rowv(B_, j), DC_, mode=mode, need_da=False, need_db=True,
+                                db=rowv(DB_, j), stream=s_c)
+                if comm is not None:                               # the panel's sum over ranks, in stream order
+                    comm.allreduce_sum_on(rowv(DB_, j), s_c)
+                e = ev().record(s_c)
+                s_out.wait_event(e)
+                cabi.d2h(hDB[j * rows:(j + 1) * rows], DB_, s_out, j * rows * N_SQ)
+            in_free[k % nsets] = ev().record(s_c)
+            out_free[k % nsets] = ev().record(s_out)
+            if prev_done[0] is not None:
+                prev_done[0].synchronize()     # at most two steps in flight: bounds the host's run-ahead
+            prev_done[0] = out_free[k % nsets]
 
         prev_done = [None]
         for k in range(warmup):
@@ -664,14 +656,13 @@ def run_gpu_arm(args):
     # the overlapped path must deliver the same results as the sequential one
     e2e_dev = max(float(np.abs(np.array(h[r]) - s0).max() / (np.abs(s0).max() + 1e-30))
                   for h, r, s0 in zip((hC, hDA, hDB), probe_rows, snap))
-    if n_gpus == 1 and not e2e_dev < 1e-5:
+    if not e2e_dev < 1e-5:
         raise RuntimeError(f"bench.py: overlapped end-to-end path disagrees with the sequential one ({e2e_dev})")
     if rank == 0:
         sampler.stop()
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        finish()
         return 0
 
     clocks = sampler.summary(*wall)
@@ -733,11 +724,11 @@ def run_gpu_arm(args):
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "mode": "set_tf32(True)", "l2": "inputs (768 MB) larger than L2 (126 MB)",
                    "sharding": "none" if n_gpus == 1 else f"M = {N_SQ * n_gpus} split along M over {n_gpus} ranks, "
-                                                          "B replicated, dB all-reduced (NCCL)"},
+                                                          "B replicated, dB all-reduced (NCCL through akr_mg_allreduce_sum)"},
         "clocks": clocks,
         "e2e": {"value": n_gpus * FLOP_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e, "h2d_bytes_per_step": bytes_each_way, "d2h_bytes_per_step": bytes_each_way,
-                "path": "C ABI, pinned host buffers, copies and GEMMs overlapped on three streams; on one GPU two device buffer sets, so a step's downloads overlap the next step's uploads (every step uploads its inputs and downloads its results)",
+                "path": "C ABI, pinned host buffers, copies and GEMMs overlapped on three streams, two device buffer sets so that a step's downloads overlap the next step's uploads (every step uploads its inputs and downloads its results; at N > 1 every dB panel is summed over the ranks before its download)",
                 "python_api_sequential": {"ms_per_step": ms_e2e_api,
                                           "value": n_gpus * FLOP_PER_STEP / (ms_e2e_api * 1e-3) / 1e12}},
         "gpu_launches": launches,
@@ -755,8 +746,7 @@ def run_gpu_arm(args):
         },
     }
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    finish()
     return 0
 
 
@@ -774,9 +764,9 @@ def run_config(args):
     from aakaar_b200.distributed import shard_range
     lib = cabi.lib()
     cabi.check(lib.akr_set_device(local_rank))
-    dist = None
+    dist, comm = None, None
     if world > 1:
-        dist = _init_nccl(local_rank)
+        dist, comm = _init_ranks(rank, world)
     peaks, peak_src = measured_peaks()
 
     def uniform(shape, seed):
@@ -787,9 +777,8 @@ def run_config(args):
         for _ in range(warmup):
             fn()
         cabi.synchronize()
-        if dist is not None:
-            dist.barrier()
-            cabi.synchronize()
+        if comm is not None:
+            comm.barrier()
         lib.akr_launch_count(1)
         e0, e1 = cabi.Event().record(), cabi.Event()
         for _ in range(steps):
@@ -798,11 +787,8 @@ def run_config(args):
         e1.synchronize()
         ms = e0.elapsed_ms(e1) / steps
         launches = int(lib.akr_launch_count(0))
-        if dist is not None:
-            import torch
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        if comm is not None:
+            ms = comm.reduce_scalar(ms, "max")
         return ms, launches
 
     out = {"config": args.config, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
@@ -913,6 +899,8 @@ def run_config(args):
     out["results"] = results
     if rank == 0:
         print(json.dumps(out), flush=True)
+    if comm is not None:
+        comm.close()
     if dist is not None:
         dist.destroy_process_group()
     return 0

@@ -184,6 +184,32 @@ AKR_API int akr_matmul_fwd_simt(const akr_view* a, const akr_view* b, akr_view* 
  * 0 restores the default. No counterpart in the reference (it has no multi-GPU path). */
 AKR_API int akr_set_gemm_cta_limit(int ctas);
 
+/* ------------------------------------------------------------------ multi-GPU
+ * The path shards over the GPUs of one node, one process (or thread) per GPU: independent batched products
+ * split along the batch need no exchange at all; a large product split along M with the weight B replicated
+ * leaves every GPU a partial dB = A_r^T . dC_r, summed by ONE all-reduce. These entry points are that
+ * exchange: NCCL (rings / trees / in-switch reduction over NVLink), loaded at run time from libnccl.so.2
+ * (environment AKR_B200_NCCL_LIB names another file). No counterpart in the reference, which is single-GPU
+ * (docs/limitations.md:15); its one replicated-weight reduction would be the sum_axis of
+ * src/bindings.cpp:1467-1503 carried across devices.
+ *   akr_mg_get_unique_id : rank 0 creates the 128-byte rendezvous id and hands it to the other ranks by any
+ *                          means the host has (a file, a socket, a launcher's key-value store).
+ *   akr_mg_init          : every rank, with its device current; collective (returns when all ranks called it).
+ *   akr_mg_allreduce     : in-place reduction of `count` elements (AKR_DTYPE_F32 or AKR_DTYPE_F64) over all ranks,
+ *                          enqueued on `stream`; AKR_MG_SUM or AKR_MG_MAX. Ranks must issue their collectives
+ *                          in the same order.
+ *   akr_mg_allreduce_sum : the float32 sum (the dB reduction).
+ *   akr_mg_finalize      : waits for the device and destroys the communicator. */
+#define AKR_MG_UNIQUE_ID_BYTES 128
+enum { AKR_MG_SUM = 0, AKR_MG_MAX = 1 };
+AKR_API int akr_mg_get_unique_id(void* id_out);
+AKR_API int akr_mg_init(int rank, int world, const void* unique_id);
+AKR_API int akr_mg_allreduce(void* data, size_t count, int dtype, int op, void* stream);
+AKR_API int akr_mg_allreduce_sum(float* data, size_t n, void* stream);
+AKR_API int akr_mg_world(int* rank, int* world);
+AKR_API int akr_mg_nccl_version(int* version);
+AKR_API int akr_mg_finalize(void);
+
 /* Extra streams for hosts that overlap host<->device copies with the GEMMs (the reference issues
  * everything on the default stream; no counterpart there). Streams are non-blocking with respect to
  * the default stream; order them with events. */
