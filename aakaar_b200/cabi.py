@@ -59,6 +59,9 @@ def load():
         "akr_matmul_fwd_simt": [V, V, V, vp],
         "akr_matmul_fwd_typed": [V, V, V, vp],
         "akr_matmul_bwd_tanh": [V, V, V, V, V, C.c_int, vp],
+        "akr_matmul_bwd_colsum": [V, V, V, V, V, fp, C.c_int, C.c_int, vp],
+        "akr_mse_fwd_grad_colsum": [fp, fp, fp, fp, fp, C.c_int64, C.c_int64, vp],
+        "akr_mse_fwd_grad": [fp, fp, fp, fp, sz, vp],
         "akr_matmul_fwd_axpby": [V, V, C.c_float, C.c_float, V, V, C.c_int, vp],
         "akr_matmul_at_b_noalloc": [V, V, V, vp],
         "akr_workspace_bytes": [C.POINTER(sz)],
@@ -296,6 +299,25 @@ def matmul_bwd_tanh(a_tanh, b, dc, mode=MODE_GLOBAL, need_dz=True, need_db=True,
     check(lib().akr_matmul_bwd_tanh(C.byref(va), C.byref(vb), C.byref(vg), C.byref(vdz) if need_dz else None,
                                     C.byref(vdb) if need_db else None, mode, _sh(stream)))
     return dz, db
+
+
+def fptr(x: DeviceArray):
+    """The array's base pointer typed as float* for the entry points that take raw pointers."""
+    return C.cast(x.ptr, C.POINTER(C.c_float))
+
+
+def matmul_bwd_colsum(a, b, dc, a_is_tanh=False, mode=MODE_GLOBAL, need_db=True, stream=None):
+    """(dA or dZ, dB, column sums of the first): the backward of C = A @ B that hands the bias gradient of the
+    Linear layer behind A along (``akr_matmul_bwd_colsum``)."""
+    da = DeviceArray(a.shape)
+    db = DeviceArray(b.shape) if need_db else None
+    cs = DeviceArray((a.shape[-1],))
+    va, vb, vg, vda = a.view(), b.view(), dc.view(), da.view()
+    vdb = db.view() if need_db else None
+    check(lib().akr_matmul_bwd_colsum(C.byref(va), C.byref(vb), C.byref(vg), C.byref(vda),
+                                      C.byref(vdb) if need_db else None, fptr(cs), 1 if a_is_tanh else 0, mode,
+                                      _sh(stream)))
+    return da, db, cs
 
 
 def matmul_axpby(a, b, alpha=1.0, beta=0.0, d=None, mode=MODE_GLOBAL, out=None, stream=None):

@@ -31,7 +31,7 @@ int cuda_fail(cudaError_t e, const char* what) {
     return fail(AKR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-enum WsSlot { WS_A_HI = 0, WS_A_LO, WS_B_HI, WS_B_LO, WS_PARTIALS, WS_COUNTERS, WS_MISC, WS_COUNT };
+enum WsSlot { WS_A_HI = 0, WS_A_LO, WS_B_HI, WS_B_LO, WS_PARTIALS, WS_COUNTERS, WS_MISC, WS_COLPART, WS_COUNT };
 
 struct Region {
     void* ptr = nullptr;
@@ -184,6 +184,10 @@ struct Problem {
     const float* aux = nullptr;
     int64_t aux_rs = 0, aux_cs = 1;
     int64_t aux_bs[AKR_MAX_DIMS] = {0};
+    // Optional by-product: colsum_out[n] = sum over all rows and batch entries of C[.., n] (N floats). Produced
+    // by the GEMM's epilogue when the kernel can (colsum_done = true); otherwise the caller adds a separate pass.
+    float* colsum_out = nullptr;
+    mutable bool colsum_done = false;
 };
 
 struct Dim {
@@ -380,6 +384,15 @@ int run_problem(const Problem& p, cudaStream_t stream) {
         g.B.bs[2] = B.bs[no + nr - 1];
     }
     g.splits = gemm_sm100_pick_splits(g);
+    // Column sums in the epilogue: TF32 kernels, one launch (no host loop over leftover dims), no split.
+    int colpart_rows = 0;
+    if (p.colsum_out && p.mode == AKR_MODE_TF32 && g.splits == 1 && no <= 2 && nr == 0 && !aux_after) {
+        colpart_rows = g.o0 * g.o1 * ((g.M + 31) / 32);
+        void* cp = nullptr;
+        rc = ws_get(st, WS_COLPART, (size_t)colpart_rows * (size_t)g.N * sizeof(float), &cp);
+        if (rc != AKR_OK) return rc;
+        g.colpart = (float*)cp;
+    }
     if (g.splits > 1) {
         size_t pbytes = 0, ncnt = 0;
         gemm_sm100_split_scratch(g, &pbytes, &ncnt);
@@ -430,6 +443,12 @@ int run_problem(const Problem& p, cudaStream_t stream) {
             if (lrc != 0) return fail(lrc == -1 ? AKR_ERR_INVALID : AKR_ERR_CUDA, err);
             st->launches += gi.splits > 1 ? 2 : 1;  // a split contraction is followed by its reduction kernel
         }
+    }
+    if (g.colpart) {
+        cudaError_t e = launch_colsum_final(g.colpart, colpart_rows, g.N, p.colsum_out, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "column-sum launch");
+        st->launches++;
+        p.colsum_done = true;
     }
     if (aux_after) {
         EpiApply ea;
@@ -749,7 +768,7 @@ AKR_API int akr_matmul_fwd_axpby(const akr_view* a, const akr_view* b, float alp
 }
 
 static int matmul_bwd_impl(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da, akr_view* db,
-                           bool a_is_tanh, int mode, void* stream) {
+                           bool a_is_tanh, int mode, void* stream, float* da_colsum = nullptr) {
     Plan pl;
     int rc = make_plan(a, b, &pl);
     if (rc != AKR_OK) return rc;
@@ -794,7 +813,20 @@ static int matmul_bwd_impl(const akr_view* a, const akr_view* b, const akr_view*
             p.aux_cs = a->stride[a->ndim - 1];
             for (int i = 0; i < pl.nb; ++i) p.aux_bs[i] = batch_stride(a, pl.nb, i);
         }
+        p.colsum_out = da_colsum;
         if ((rc = run_problem(p, (cudaStream_t)stream)) != AKR_OK) return rc;
+        if (da_colsum && !p.colsum_done) {
+            // the kernel that ran has no column-sum epilogue (fp32-accurate mode, split contraction, ...): one
+            // more pass over the finished gradient
+            akr_view out;
+            std::memset(&out, 0, sizeof(out));
+            out.data = da_colsum;
+            out.ndim = 1;
+            out.dtype = AKR_DTYPE_F32;
+            out.shape[0] = pl.K;
+            out.stride[0] = 1;
+            if ((rc = akr_sum_to(da, &out, stream)) != AKR_OK) return rc;
+        }
     }
     if (db) {
         if ((rc = check_out(db, b->ndim, b->shape, "matmul grad b")) != AKR_OK) return rc;
@@ -831,6 +863,13 @@ AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view*
 AKR_API int akr_matmul_bwd_tanh(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* dz, akr_view* db,
                                 int mode, void* stream) {
     return matmul_bwd_impl(a, b, dc, dz, db, true, mode, stream);
+}
+
+AKR_API int akr_matmul_bwd_colsum(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da,
+                                  akr_view* db_or_null, float* da_colsum, int a_is_tanh_output, int mode, void* stream) {
+    if (!da) return fail(AKR_ERR_INVALID, "matmul_bwd_colsum: the gradient whose column sums are wanted must be requested");
+    if (!da_colsum) return fail(AKR_ERR_INVALID, "matmul_bwd_colsum: null column-sum buffer");
+    return matmul_bwd_impl(a, b, dc, da, db_or_null, a_is_tanh_output != 0, mode, stream, da_colsum);
 }
 
 AKR_API int akr_matmul_a_bt(const akr_view* a, const akr_view* b, akr_view* c, int mode, void* stream) {
@@ -1170,6 +1209,40 @@ AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* g
 }
 
 static int mse_forward(const float* pred, const float* target, float* loss_out, float* dpred, size_t n, void* stream);
+AKR_API int akr_mse_fwd_grad_colsum(const float* pred, const float* target, float* loss_out, float* dpred,
+                                    float* dpred_colsum, int64_t rows, int64_t cols, void* stream) {
+    if (!pred || !target || !loss_out || !dpred || !dpred_colsum)
+        return fail(AKR_ERR_INVALID, "mse_fwd_grad_colsum: null pointer");
+    if (rows <= 0 || cols <= 0) return fail(AKR_ERR_RUNTIME, "MSELoss: cannot reduce an empty tensor");
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(pred) | reinterpret_cast<uintptr_t>(target) |
+                           reinterpret_cast<uintptr_t>(dpred) | reinterpret_cast<uintptr_t>(dpred_colsum)) & 15u) == 0;
+    if ((cols & 3) != 0 || !aligned) {
+        // odd widths: the plain loss + gradient pass, then a column sum of the gradient
+        if ((rc = mse_forward(pred, target, loss_out, dpred, (size_t)rows * (size_t)cols, stream)) != AKR_OK) return rc;
+        akr_view g, out;
+        std::memset(&g, 0, sizeof(g));
+        std::memset(&out, 0, sizeof(out));
+        g.data = dpred; g.ndim = 2; g.dtype = AKR_DTYPE_F32;
+        g.shape[0] = rows; g.shape[1] = cols; g.stride[0] = cols; g.stride[1] = 1;
+        out.data = dpred_colsum; out.ndim = 1; out.dtype = AKR_DTYPE_F32; out.shape[0] = cols; out.stride[0] = 1;
+        return akr_sum_to(&g, &out, stream);
+    }
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(st->mu);
+        if ((rc = ws_get(st, WS_MISC, std::max<size_t>(mse_colsum_scratch_floats(rows, cols), 4096) * sizeof(float),
+                         &scratch)) != AKR_OK)
+            return rc;
+    }
+    cudaError_t e = launch_mse_fwd_colsum(pred, target, loss_out, dpred, dpred_colsum, rows, cols, (float*)scratch,
+                                          (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "mse launch");
+    st->launches += 2;
+    return AKR_OK;
+}
 AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out, size_t n, void* stream) {
     return mse_forward(pred, target, loss_out, nullptr, n, stream);
 }

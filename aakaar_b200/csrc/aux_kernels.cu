@@ -457,6 +457,65 @@ __global__ void mse_final_kernel(const float* __restrict__ partials, int count, 
     const float s = block_sum(acc);
     if (threadIdx.x == 0) out[0] = s / n;
 }
+// The same with the column sums of dp (the bias gradient of the Linear layer that produced p) taken in the same
+// pass. Block (x = 128-column strip, y = row chunk), one float4 per thread and row; the eight warps of a block
+// are combined in shared memory and write one partial row per chunk (deterministic: no atomics).
+__global__ void mse_colsum_partial_kernel(const float* __restrict__ p, const float* __restrict__ t,
+                                          float* __restrict__ loss_partials, float* __restrict__ dp,
+                                          float* __restrict__ col_partials, float two_over_n, int64_t rows,
+                                          int64_t cols, int64_t rows_per_chunk) {
+    dep_sync();
+    __shared__ float4 part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col = (int64_t)blockIdx.x * 128 + lane * 4;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_chunk;
+    const int64_t r1 = min(rows, r0 + rows_per_chunk);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float loss = 0.f;
+    if (col < cols) {  // cols is a multiple of 4 (checked by the launcher)
+#pragma unroll 4
+        for (int64_t r = r0 + warp; r < r1; r += 8) {
+            const float4 a = __ldcs(reinterpret_cast<const float4*>(p + r * cols + col));
+            const float4 b = __ldcs(reinterpret_cast<const float4*>(t + r * cols + col));
+            const float4 d = make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w);
+            loss = fmaf(d.x, d.x, loss); loss = fmaf(d.y, d.y, loss); loss = fmaf(d.z, d.z, loss); loss = fmaf(d.w, d.w, loss);
+            const float4 g = make_float4(d.x * two_over_n, d.y * two_over_n, d.z * two_over_n, d.w * two_over_n);
+            *reinterpret_cast<float4*>(dp + r * cols + col) = g;
+            acc.x += g.x; acc.y += g.y; acc.z += g.z; acc.w += g.w;
+        }
+    }
+    part[warp][lane] = acc;
+    const float s = block_sum(loss);   // contains the barrier that also orders `part`
+    if (threadIdx.x == 0) loss_partials[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = s;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 c = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+            const float4 v = part[w][lane];
+            c.x += v.x; c.y += v.y; c.z += v.z; c.w += v.w;
+        }
+        *reinterpret_cast<float4*>(col_partials + (int64_t)blockIdx.y * cols + col) = c;
+    }
+}
+// stage 2 of the above: column sums in chunk order; block 0 also finishes the loss.
+__global__ void mse_colsum_final_kernel(const float* __restrict__ loss_partials, int loss_count, float n,
+                                        float* __restrict__ loss_out, const float* __restrict__ col_partials,
+                                        int chunks, int64_t cols, float* __restrict__ colsum_out) {
+    dep_sync();
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < cols) {
+        float s = 0.f;
+        for (int k = 0; k < chunks; ++k) s += col_partials[(int64_t)k * cols + c];
+        colsum_out[c] = s;
+    }
+    if (blockIdx.x == 0) {
+        float acc = 0.f;
+        for (int i = threadIdx.x; i < loss_count; i += blockDim.x) acc += loss_partials[i];
+        const float s = block_sum(acc);
+        if (threadIdx.x == 0) loss_out[0] = s / n;
+    }
+}
 __global__ void mse_bwd_kernel(const float* __restrict__ p, const float* __restrict__ t,
                                const float* __restrict__ gscalar, float inv_n, float* __restrict__ dp,
                                size_t n) {
@@ -683,6 +742,32 @@ cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, floa
     if (blocks > 1024) blocks = 1024;
     launch_dep(mse_partial_kernel, blocks, kThreads, s, p, t, partials, dp, 2.0f * (1.0f / (float)n), n);
     launch_dep(mse_final_kernel, 1, kThreads, s, partials, blocks, (float)n, loss_out);
+    return cudaGetLastError();
+}
+size_t mse_colsum_scratch_floats(int64_t rows, int64_t cols) {
+    const int chunks = colsum_chunks(rows, cols);
+    const size_t strips = (size_t)((cols + 127) / 128);
+    return (size_t)chunks * (size_t)cols + (size_t)chunks * strips + 64;
+}
+cudaError_t launch_mse_fwd_colsum(const float* p, const float* t, float* loss_out, float* dp, float* colsum_out,
+                                  int64_t rows, int64_t cols, float* scratch, cudaStream_t s) {
+    const int chunks = colsum_chunks(rows, cols);
+    const int64_t rpc = (rows + chunks - 1) / chunks;
+    const unsigned strips = (unsigned)((cols + 127) / 128);
+    float* col_partials = scratch;
+    float* loss_partials = scratch + (size_t)chunks * (size_t)cols;
+    const double n = (double)rows * (double)cols;
+    dim3 grid(strips, (unsigned)chunks);
+    launch_dep(mse_colsum_partial_kernel, grid, 256, s, p, t, loss_partials, dp, col_partials, (float)(2.0 / n), rows, cols,
+               rpc);
+    launch_dep(mse_colsum_final_kernel, (unsigned)((cols + 255) / 256), 256, s, (const float*)loss_partials,
+               (int)(chunks * strips), (float)n, loss_out, (const float*)col_partials, chunks, cols, colsum_out);
+    return cudaGetLastError();
+}
+// out[c] = sum over `chunks` rows of a [chunks][cols] array of partial column sums, in row order.
+cudaError_t launch_colsum_final(const float* partials, int chunks, int64_t cols, float* out, cudaStream_t s) {
+    if (cols == 0) return cudaSuccess;
+    launch_dep(colsum_final_kernel, (unsigned)((cols + 255) / 256), 256, s, partials, chunks, cols, out);
     return cudaGetLastError();
 }
 __global__ void epi_apply_kernel(EpiApply a, size_t total) {

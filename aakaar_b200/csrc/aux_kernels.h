@@ -87,6 +87,15 @@ cudaError_t launch_mse_fwd(const float* p, const float* t, float* loss_out, floa
                            cudaStream_t s, float* dp = nullptr);
 cudaError_t launch_mse_bwd(const float* p, const float* t, const float* gscalar, float* dp, size_t n,
                            cudaStream_t s);
+// Loss, its gradient dp = 2 (p - t) / n and the column sums of dp over a dense [rows][cols] layout in one pass
+// (two launches, no atomics). cols must be a multiple of 4, all pointers 16-byte aligned; `scratch` holds
+// mse_colsum_scratch_floats(rows, cols) floats.
+size_t mse_colsum_scratch_floats(int64_t rows, int64_t cols);
+cudaError_t launch_mse_fwd_colsum(const float* p, const float* t, float* loss_out, float* dp, float* colsum_out,
+                                  int64_t rows, int64_t cols, float* scratch, cudaStream_t s);
+// out[c] = sum over the `chunks` rows of a dense [chunks][cols] array (second stage of a column sum whose
+// first stage another kernel produced, e.g. a GEMM epilogue).
+cudaError_t launch_colsum_final(const float* partials, int chunks, int64_t cols, float* out, cudaStream_t s);
 cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float momentum, float wd,
                        float dampening, int nesterov, int has_momentum, int vel_init, size_t n,
                        cudaStream_t s);

@@ -62,6 +62,7 @@ struct KernelParams {
     float* partials;
     int* counters;
     int* status;
+    float* colpart;  // [o0 * o1 * ceil(M / 32)][N] column sums per 32-row block of the output, or null
     long long ldc, c_bs0, c_bs1;
     int M, N, K;
     int o0, o1, red, splits;
@@ -140,12 +141,17 @@ struct Epi {
     int op;              // 0: none, 1: += beta * aux, 2: *= 1 - aux^2
     float alpha, beta;
     bool accumulate, aux_vec;
+    // Column sums of the stored values (the bias gradient of the Linear layer that produced the operand this
+    // output is the gradient of): row (row0 / 32) of this [row blocks][N] array receives the sums over the 32
+    // rows of each block; a small second kernel adds the rows up. Null: not wanted.
+    float* colpart;
 };
 
 __device__ __forceinline__ Epi plain_epi() {
     Epi e;
     e.bias = nullptr; e.aux = nullptr; e.aux_ld = 0; e.aux_cs = 1; e.op = 0; e.alpha = 1.f; e.beta = 0.f;
     e.accumulate = false; e.aux_vec = false;
+    e.colpart = nullptr;
     return e;
 }
 
@@ -167,6 +173,8 @@ __device__ __forceinline__ Epi tile_epi(const KernelParams& p, const Tile& c) {
     e.alpha = p.alpha; e.beta = p.beta;
     e.accumulate = p.accumulate != 0;
     e.aux_vec = p.aux_vec != 0;
+    // rows of the partial array: batch-major, then 32-row blocks of the matrix
+    e.colpart = p.colpart ? p.colpart + (size_t)c.batch * (size_t)((p.M + 31) / 32) * (size_t)p.N : nullptr;
     return e;
 }
 
@@ -200,12 +208,18 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
     const int col = col0 + 4 * c4;
     const int rsub = lane >> 3;
     const bool fast = vec && col + 3 < N;
+    float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);  // this lane's four columns summed over its eight rows
     if (!AUX || (e.op == 0 && !e.accumulate)) {
         float4 x[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {  // all eight reads in flight before the first global store
             const int r = 4 * i + rsub;
             x[i] = stage[r * 8 + (c4 ^ (r & 7))];
+        }
+        if (AUX && e.colpart != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (row0 + 4 * i + rsub < M) { cs.x += x[i].x; cs.y += x[i].y; cs.z += x[i].z; cs.w += x[i].w; }
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -260,6 +274,7 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
                             x.x = epi_aux(x.x, a[i].x, e); x.y = epi_aux(x.y, a[i].y, e);
                             x.z = epi_aux(x.z, a[i].z, e); x.w = epi_aux(x.w, a[i].w, e);
                         }
+                        cs.x += x.x; cs.y += x.y; cs.z += x.z; cs.w += x.w;
                         *reinterpret_cast<float4*>(dst) = x;
                     } else {
                         const float el[4] = {x.x, x.y, x.z, x.w};
@@ -270,10 +285,28 @@ __device__ __forceinline__ void store_block_warp(float (&v)[32], float4* stage, 
                                 if (e.op != 0)
                                     val = epi_aux(val, e.aux[(long long)grow * e.aux_ld + (long long)(col + t) * e.aux_cs], e);
                                 dst[t] = val;
+                                if (t == 0) cs.x += val;
+                                else if (t == 1) cs.y += val;
+                                else if (t == 2) cs.z += val;
+                                else cs.w += val;
                             }
                     }
                 }
             }
+        }
+    }
+    if (AUX && e.colpart != nullptr) {
+        // lanes c4, c4 + 8, c4 + 16, c4 + 24 hold the same four columns for different rows
+        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 8); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 8);
+        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 8); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 8);
+        cs.x += __shfl_xor_sync(0xffffffffu, cs.x, 16); cs.y += __shfl_xor_sync(0xffffffffu, cs.y, 16);
+        cs.z += __shfl_xor_sync(0xffffffffu, cs.z, 16); cs.w += __shfl_xor_sync(0xffffffffu, cs.w, 16);
+        if (lane < 8 && row0 < M) {
+            float* dst = e.colpart + (size_t)(row0 >> 5) * (size_t)N + col;
+            if (col < N) dst[0] = cs.x;
+            if (col + 1 < N) dst[1] = cs.y;
+            if (col + 2 < N) dst[2] = cs.z;
+            if (col + 3 < N) dst[3] = cs.w;
         }
     }
     __syncwarp();  // the tile is reused by the next block
@@ -2323,6 +2356,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     kp.beta = g.beta;
     kp.partials = g.partials;
     kp.counters = g.counters;
+    kp.colpart = g.colpart;
     kp.status = status_dev;
     kp.ldc = g.ldc;
     kp.c_bs0 = g.c_bs0;
@@ -2341,7 +2375,11 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                     : 0;
     // Output map for the TMA-store epilogue: (N, M, o1, o0), boxes of 32 columns x 128 rows.
     kp.c_tma = 0;
-    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo) &&
+    if (g.colpart != nullptr && (g.terms != 1 || kp.splits != 1)) {
+        seterr(err, errlen, "gemm_sm100: column sums of the output are produced by the TF32 kernels without a split contraction only");
+        return -1;
+    }
+    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo) && g.colpart == nullptr &&
         !AKR_DIAG(g.debug | g_debug_flags, 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;

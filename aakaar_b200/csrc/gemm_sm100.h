@@ -36,6 +36,9 @@ struct GemmDesc {
     int aux_op = 0;
     float beta = 0.f;
     int64_t aux_ld = 0, aux_cs = 1, aux_bs0 = 0, aux_bs1 = 0;
+    // Optional by-product: column sums of the stored output per 32-row block, `colpart` = [o0 * o1 * ceil(M / 32)][N]
+    // floats (every entry is written). TF32 mode without a split contraction only.
+    float* colpart = nullptr;
     int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate). With terms == 3 the low parts are
                                   // derived in the kernel unless BOTH operands carry pre-split `lo` arrays
     // Split of the contraction across CTAs (weight gradients with few output tiles):

@@ -252,6 +252,14 @@ bool g_fuse_backward = true;
 // dispatch_matmul of the reference (src/bindings.cpp:1686-1764): forward product plus the autograd
 // node. The backward closure calls the fused backward on the original strided operands: no
 // transposed copies, no unreduced [batch..., K, N] intermediate, and only the gradients needed.
+// True when `t` is the output of a Linear node (x W + b) whose bias wants a gradient: whoever writes the
+// gradient of `t` can hand the bias gradient (its column sums) along.
+bool feeds_bias_grad(const TensorPtr& t) {
+    if (!g_fuse_backward || !t || !t->grad_fn || t->grad_fn->freed || t->grad_fn->op_name != "linear") return false;
+    const auto& in = t->grad_fn->inputs;
+    return in.size() == 3 && in[2] && in[2]->requires_grad && t->shape.size() >= 2 && t->is_contiguous();
+}
+
 TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr& bias) {
     if (a->device != b->device) throw std::runtime_error("Both tensors must be on the same device!");
     require_cuda(a, "matmul");
@@ -298,12 +306,28 @@ TensorPtr op_matmul_bias(const TensorPtr& a, const TensorPtr& b, const TensorPtr
             akr_view vda, vdb;
             if (da) vda = da->view();
             if (db) vdb = db->view();
-            if (da || db)
+            // The gradient this node produces for `a` flows into the tensor that made `a` (through the tanh when
+            // that node is folded in): when that is a Linear output, take its bias gradient in the same launch.
+            TensorPtr producer = a;
+            if (a_is_tanh && a->grad_fn && !a->grad_fn->inputs.empty()) producer = a->grad_fn->inputs[0];
+            if (da && producer->shape == a->shape && feeds_bias_grad(producer)) {
+                da->colsum = make_cuda({a->shape.back()});
+                check(akr_matmul_bwd_colsum(&va, &vb, &vg, &vda, db ? &vdb : nullptr, da->colsum->data, a_is_tanh ? 1 : 0,
+                                            mode, nullptr));
+            } else if (da || db) {
                 check((a_is_tanh ? akr_matmul_bwd_tanh : akr_matmul_bwd)(&va, &vb, &vg, da ? &vda : nullptr,
                                                                          db ? &vdb : nullptr, mode, nullptr));
+            }
             std::vector<TensorPtr> grads{da, db};
             if (bias) {
-                if (bias->requires_grad) dbias = op_sum_to(g, bias->shape);
+                if (bias->requires_grad) {
+                    // column sums of g: handed along by the kernel that wrote g, else one pass over g
+                    if (g->colsum && g->colsum->size == bias->size && g->shape.back() == bias->shape.back()) {
+                        dbias = std::make_shared<Tensor>(g->colsum, 0, bias->shape, contiguous_strides(bias->shape));
+                    } else {
+                        dbias = op_sum_to(g, bias->shape);
+                    }
+                }
                 grads.push_back(dbias);
             }
             return grads;
@@ -411,7 +435,15 @@ TensorPtr op_mse(const TensorPtr& pred, const TensorPtr& target) {
         // The gradient for an incoming gradient of 1 is written in the forward pass; backward() from this loss
         // (its usual place, the root) then has nothing left to compute.
         auto dp1 = make_cuda(pred->shape);
-        check(akr_mse_fwd_grad(pred->data, target->data, out->data, dp1->data, (size_t)pred->size, nullptr));
+        if (feeds_bias_grad(pred)) {
+            // pred = x W + b: the bias gradient is the column sum of this gradient, taken in the same pass
+            const int64_t cols = pred->shape.back();
+            dp1->colsum = make_cuda({cols});
+            check(akr_mse_fwd_grad_colsum(pred->data, target->data, out->data, dp1->data, dp1->colsum->data,
+                                          pred->size / cols, cols, nullptr));
+        } else {
+            check(akr_mse_fwd_grad(pred->data, target->data, out->data, dp1->data, (size_t)pred->size, nullptr));
+        }
         attach(out, "mse", {pred}, [pred, target, dp1](TensorPtr g) {
             if (g.get() == g_unit_root_grad) return std::vector<TensorPtr>{dp1};
             auto dp = make_cuda(pred->shape);

@@ -71,6 +71,10 @@ public:
     TensorPtr grad;
     std::shared_ptr<Node> grad_fn;
     TensorPtr base;  // parent of a view
+    // Column sums of this tensor over all its leading dims (shape [last dim]), attached by the kernel that wrote
+    // it when the consumer is known to want them: a gradient that flows into a Linear layer's output carries
+    // that layer's bias gradient, so no extra pass over the gradient is needed.
+    TensorPtr colsum;
 
     // Fresh contiguous allocation.
     Tensor(std::vector<int64_t> shp, const std::string& dev, int dt = AKR_DTYPE_F32)

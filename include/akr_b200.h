@@ -134,6 +134,16 @@ AKR_API int akr_matmul_bwd(const akr_view* a, const akr_view* b, const akr_view*
 AKR_API int akr_matmul_bwd_tanh(const akr_view* a_tanh_out, const akr_view* b, const akr_view* dc,
                                 akr_view* dz_or_null, akr_view* db_or_null, int mode, void* stream);
 
+/* akr_matmul_bwd (a_is_tanh_output == 0) or akr_matmul_bwd_tanh (!= 0) that also returns the column sums of
+ * the gradient it produces for A: da_colsum[k] = sum over all rows and batch entries of dA[.., k] (K floats).
+ * When A is the output of a Linear layer, x W + b (aakaar/nn.py:14-15), these are that layer's bias gradient -
+ * the reference's broadcast-add backward, src/bindings.cpp:1567-1571 -> reduce_grad_to_shape, :1467-1503 (a full
+ * pass over dA in sum_axis_kernel, src/reduction_kernel.cu:10-26). In TF32 mode the sums are taken per 32-row
+ * block in the GEMM's epilogue and added up by a small second kernel; no pass over dA. Other cases (fp32-accurate
+ * mode, split contractions) fall back to that pass. Deterministic (no atomics). da must not be NULL. */
+AKR_API int akr_matmul_bwd_colsum(const akr_view* a, const akr_view* b, const akr_view* dc, akr_view* da,
+                                  akr_view* db_or_null, float* da_colsum, int a_is_tanh_output, int mode, void* stream);
+
 /* C = alpha * (A @ B) + beta * D in one launch (D: an array of C's shape with any strides, may be NULL when
  * beta == 0). The two products of the Newton-Schulz iteration of the Muon optimizer
  * (aakaar/optim.py:533-542: `B = b * A + c * (A @ A)`, `X = a * X + X @ B`), which the reference runs as a
@@ -280,6 +290,10 @@ AKR_API int akr_mse_fwd(const float* pred, const float* target, float* loss_out,
  * gradient is 1 (a loss at the root of backward()), which saves the backward pass over pred and target. */
 AKR_API int akr_mse_fwd_grad(const float* pred, const float* target, float* loss_out, float* dpred, size_t n,
                              void* stream);
+/* akr_mse_fwd_grad that also returns the column sums of dpred over a dense [rows][cols] layout (the bias gradient
+ * of the Linear layer that produced pred), in the same pass. */
+AKR_API int akr_mse_fwd_grad_colsum(const float* pred, const float* target, float* loss_out, float* dpred,
+                                    float* dpred_colsum, int64_t rows, int64_t cols, void* stream);
 AKR_API int akr_mse_bwd(const float* pred, const float* target, const float* grad_scalar, float* dpred,
                 size_t n, void* stream);
 AKR_API int akr_sgd_step(float* param, const float* grad, float* velocity_or_null, float lr, float momentum,

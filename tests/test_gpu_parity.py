@@ -700,3 +700,36 @@ def test_random_mid_size_shapes_sampled(mode, tol):
         bias = normal((1, N), 4000 + case)
         c3 = cabi.matmul_fwd(Av, Bv, bias=dev(bias), mode=mode).to_numpy()
         assert rel_fro(c3[:, rows], ref + bias) < tol, what
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_bias_gradient_handed_along_by_the_producing_kernel(mode, tol):
+    # db of y = x W + b is the column sum of dy (broadcast-add backward of the reference). The kernel that WRITES
+    # dy returns it: the backward product of the next layer (optionally through tanh'), or the MSE forward pass.
+    rng = np.random.Generator(np.random.PCG64(77))
+    for (M, K, N, batch) in ((1000, 520, 300, ()), (4096, 1024, 512, ()), (130, 96, 260, (3,)), (2500, 2600, 2700, ())):
+        a = np.tanh(rng.standard_normal(batch + (M, K)).astype(np.float32))
+        b = rng.standard_normal((K, N)).astype(np.float32) * np.float32(1 / np.sqrt(K))
+        dc = rng.standard_normal(batch + (M, N)).astype(np.float32)
+        A, B, G = dev(a), dev(b), dev(dc)
+        for through_tanh in (False, True):
+            da, db, cs = cabi.matmul_bwd_colsum(A, B, G, a_is_tanh=through_tanh, mode=mode)
+            want_da, want_db = (cabi.matmul_bwd_tanh if through_tanh else cabi.matmul_bwd)(A, B, G, mode=mode)
+            assert np.array_equal(da.to_numpy(), want_da.to_numpy())      # same product, same epilogue
+            assert np.array_equal(db.to_numpy(), want_db.to_numpy())
+            ref = da.to_numpy().astype(np.float64).reshape(-1, K).sum(axis=0)
+            assert rel_fro(cs.to_numpy(), ref) < 1e-5, (M, K, N, batch, through_tanh)
+            again = cabi.matmul_bwd_colsum(A, B, G, a_is_tanh=through_tanh, mode=mode)[2]
+            assert np.array_equal(cs.to_numpy(), again.to_numpy())        # no atomics: repeatable bit for bit
+    # MSE forward: loss, gradient and the gradient's column sums in one pass (and the odd-width fallback)
+    import ctypes as C
+    lib = cabi.lib()
+    for rows, cols in ((4096, 1024), (37, 132), (50, 30)):
+        p, t = rng.standard_normal((rows, cols)).astype(np.float32), rng.standard_normal((rows, cols)).astype(np.float32)
+        P, T, D, L, S = dev(p), dev(t), DA((rows, cols)), DA((1,)), DA((cols,))
+        cabi.check(lib.akr_mse_fwd_grad_colsum(cabi.fptr(P), cabi.fptr(T), cabi.fptr(L), cabi.fptr(D), cabi.fptr(S),
+                                               rows, cols, None))
+        d64 = p.astype(np.float64) - t.astype(np.float64)
+        assert abs(L.to_numpy()[0] - (d64 ** 2).mean()) < 1e-5 * (d64 ** 2).mean()
+        assert rel_fro(D.to_numpy(), 2 * d64 / d64.size) < 1e-6
+        assert rel_fro(S.to_numpy(), (2 * d64 / d64.size).sum(axis=0)) < 1e-5

@@ -183,8 +183,9 @@ def test_typed_forward_only_matmul(ak):
 
 def test_tanh_backward_folded_into_next_matmul(ak):
     # Linear -> tanh -> Linear -> MSE: with the fusion the tanh node's backward runs inside the epilogue
-    # of the second layer's dA product (TF32 mode: one launch less; the fp32-accurate kernels apply it in a
-    # separate pass, same launch count), gradients unchanged
+    # of the second layer's dA product and both bias gradients are handed along by the kernels that write
+    # the gradients they are column sums of (the MSE forward pass, the dA epilogue): fewer launches in the
+    # backward pass (TF32 mode: 4 instead of 8), gradients unchanged
     from aakaar_b200 import _C
     x, tgt = normal((96, 40), 1), normal((96, 24), 2)
     w1, b1 = uniform((40, 72), 3) * 0.2, uniform((1, 72), 4) * 0.1
@@ -209,7 +210,7 @@ def test_tanh_backward_folded_into_next_matmul(ak):
             _C._set_backward_fusion(True)
             ak.set_tf32(False)
         (g0, n0), (g1, n1) = results[False], results[True]
-        assert n1 == n0 - (1 if tf32 else 0)
+        assert n1 < n0 and (not tf32 or n1 <= n0 - 3), (tf32, n0, n1)
         for got0, got1, key in zip(g0, g1, ("w1", "b1", "w2", "b2")):
             assert rel_fro(got1, ref[key]) < tol, key
             assert rel_fro(got1, got0) < tol, key
