@@ -1081,6 +1081,15 @@ AKR_API int akr_contiguous(const akr_view* src, float* dst, void* stream) {
     AKR_LAUNCH(launch_gather(to_strided(src), dst, (cudaStream_t)stream), "gather launch");
 }
 
+AKR_API int akr_scatter(const float* src, akr_view* dst, void* stream) {
+    int rc = check_view(dst, "scatter destination", 0);
+    if (rc != AKR_OK) return rc;
+    if (!src) return fail(AKR_ERR_INVALID, "scatter: null source");
+    for (int i = 0; i < dst->ndim; ++i)
+        if (dst->shape[i] > 1 && dst->stride[i] == 0) return fail(AKR_ERR_INVALID, "scatter: destination must not be a broadcast view");
+    AKR_LAUNCH(launch_scatter(src, to_strided(dst), (cudaStream_t)stream), "scatter launch");
+}
+
 static int binary_op(const akr_view* a, const akr_view* b, akr_view* out, void* stream, bool multiply);
 AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* stream) {
     return binary_op(a, b, out, stream, false);
@@ -1204,6 +1213,43 @@ AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* g
     if (!grad_col || !grad_x) return fail(AKR_ERR_INVALID, "col2im: null data pointer");
     cudaError_t e = launch_col2im(grad_col, grad_x, g, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "col2im launch");
+    st->launches++;
+    return AKR_OK;
+}
+
+static int window_geom_3d(const akr_window3d* w, WindowGeom* g) {
+    if (!w) return fail(AKR_ERR_INVALID, "im2col_3d: null geometry");
+    if (w->B <= 0 || w->C <= 0 || w->D <= 0 || w->H <= 0 || w->W <= 0 || w->KD <= 0 || w->KH <= 0 || w->KW <= 0 ||
+        w->SD <= 0 || w->SH <= 0 || w->SW <= 0 || w->DD <= 0 || w->DH <= 0 || w->DW <= 0 || w->PD < 0 || w->PH < 0 ||
+        w->PW < 0 || w->OD <= 0 || w->OH <= 0 || w->OW <= 0)
+        return fail(AKR_ERR_INVALID, "im2col_3d: sizes, strides and dilations must be positive, padding non-negative");
+    g->B = w->B; g->C = w->C; g->D = w->D; g->H = w->H; g->W = w->W;
+    g->KD = w->KD; g->KH = w->KH; g->KW = w->KW; g->SD = w->SD; g->SH = w->SH; g->SW = w->SW;
+    g->PD = w->PD; g->PH = w->PH; g->PW = w->PW; g->DD = w->DD; g->DH = w->DH; g->DW = w->DW;
+    g->OD = w->OD; g->OH = w->OH; g->OW = w->OW;
+    return AKR_OK;
+}
+AKR_API int akr_im2col_3d(const float* x, float* col, const akr_window3d* geom, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    WindowGeom g;
+    if ((rc = window_geom_3d(geom, &g)) != AKR_OK) return rc;
+    if (!x || !col) return fail(AKR_ERR_INVALID, "im2col_3d: null data pointer");
+    cudaError_t e = launch_im2col(x, col, g, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "im2col_3d launch");
+    st->launches++;
+    return AKR_OK;
+}
+AKR_API int akr_col2im_3d(const float* grad_col, float* grad_x, const akr_window3d* geom, void* stream) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    WindowGeom g;
+    if ((rc = window_geom_3d(geom, &g)) != AKR_OK) return rc;
+    if (!grad_col || !grad_x) return fail(AKR_ERR_INVALID, "col2im_3d: null data pointer");
+    cudaError_t e = launch_col2im(grad_col, grad_x, g, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "col2im_3d launch");
     st->launches++;
     return AKR_OK;
 }

@@ -228,6 +228,21 @@ __global__ void gather_kernel(const GatherArgs a) {
     }
 }
 
+// The adjoint of the gather: dense source (the view's shape, row-major) written through the view's strides.
+__global__ void scatter_kernel(const GatherArgs a, float* __restrict__ dst_base) {
+    dep_sync();
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
+        int64_t t = i, off = 0;
+        for (int d = a.nd - 1; d >= 0; --d) {
+            const int64_t idx = t % a.shape[d];
+            t /= a.shape[d];
+            off += idx * a.stride[d];
+        }
+        dst_base[off] = __ldg(a.src + i);
+    }
+}
+
 struct AddArgs {
     const float *a, *b;
     float* out;
@@ -630,6 +645,22 @@ cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+cudaError_t launch_scatter(const float* src, const StridedView& dst, cudaStream_t s) {
+    GatherArgs a;
+    a.src = src;
+    a.dst = nullptr;
+    a.nd = dst.nd;
+    a.total = 1;
+    for (int d = 0; d < kMaxDims; ++d) {
+        a.shape[d] = d < dst.nd ? dst.shape[d] : 1;
+        a.stride[d] = d < dst.nd ? dst.stride[d] : 0;
+        a.total *= a.shape[d];
+    }
+    if (a.total == 0) return cudaSuccess;
+    launch_dep(scatter_kernel, grid_for((size_t)a.total, 2), kThreads, s, a, const_cast<float*>(dst.ptr));
+    return cudaGetLastError();
+}
+
 cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
                        const int64_t* shape, cudaStream_t s, bool multiply) {
     AddArgs p;
@@ -909,7 +940,104 @@ __global__ void col2im_kernel(const float* __restrict__ gc, float* __restrict__ 
         else gp[i0] = acc[0];
     }
 }
+// 3-D windows: the same two kernels with a depth index. One block per (b, c, kd, kh, kw) row of `col`, four
+// consecutive (od, oh, ow) positions per thread and store.
+template <bool VEC>
+__global__ void im2col3d_kernel(const float* __restrict__ x, float* __restrict__ col, WindowGeom g) {
+    dep_sync();
+    const unsigned row = blockIdx.x;  // (((b * C + c) * KD + kd) * KH + kh) * KW + kw
+    const int kw = (int)(row % (unsigned)g.KW);
+    const unsigned r1 = row / (unsigned)g.KW;
+    const int kh = (int)(r1 % (unsigned)g.KH);
+    const unsigned r2 = r1 / (unsigned)g.KH;
+    const int kd = (int)(r2 % (unsigned)g.KD);
+    const unsigned plane = r2 / (unsigned)g.KD;  // b * C + c
+    const int OW = (int)g.OW, OH = (int)g.OH, OHW = OH * OW, ODHW = (int)g.OD * OHW;
+    const int D = (int)g.D, H = (int)g.H, W = (int)g.W;
+    const float* xp = x + (size_t)plane * D * H * W;
+    float* cp = col + (size_t)row * ODHW;
+    const int d_off = kd * g.DD - g.PD, h_off = kh * g.DH - g.PH, w_off = kw * g.DW - g.PW;
+    constexpr int V = VEC ? 4 : 1;
+    for (int o0 = (blockIdx.y * blockDim.x + threadIdx.x) * V; o0 < ODHW; o0 += gridDim.y * blockDim.x * V) {
+        float v[V];
+        int od = o0 / OHW;
+        int rem = o0 - od * OHW;
+        int oh = rem / OW, ow = rem - oh * OW;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const int d = od * g.SD + d_off, h = oh * g.SH + h_off, w = ow * g.SW + w_off;
+            v[e] = (d >= 0 && d < D && h >= 0 && h < H && w >= 0 && w < W) ? __ldg(xp + ((size_t)d * H + h) * W + w) : 0.f;
+            if (++ow == OW) {
+                ow = 0;
+                if (++oh == OH) {
+                    oh = 0;
+                    ++od;
+                }
+            }
+        }
+        if (VEC) *reinterpret_cast<float4*>(cp + o0) = make_float4(v[0], v[V > 1 ? 1 : 0], v[V > 2 ? 2 : 0], v[V > 3 ? 3 : 0]);
+        else cp[o0] = v[0];
+    }
+}
+// Fold: one block row per (b, c) volume, one element per thread; each sums, in (kd, kh, kw) order, the window
+// entries that read it.
+__global__ void col2im3d_kernel(const float* __restrict__ gc, float* __restrict__ gx, WindowGeom g) {
+    dep_sync();
+    const unsigned plane = blockIdx.x;  // b * C + c
+    const int OW = (int)g.OW, OH = (int)g.OH, OD = (int)g.OD, OHW = OH * OW;
+    const int D = (int)g.D, H = (int)g.H, W = (int)g.W, HW = H * W;
+    const size_t odhw = (size_t)OD * OHW;
+    const float* base = gc + (size_t)plane * g.KD * g.KH * g.KW * odhw;
+    float* gp = gx + (size_t)plane * D * HW;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < D * HW; i += gridDim.y * blockDim.x) {
+        const int d = i / HW;
+        const int r = i - d * HW;
+        const int h = r / W, w = r - h * W;
+        float acc = 0.f;
+        for (int kd = 0; kd < g.KD; ++kd) {
+            const int nd = d + g.PD - kd * g.DD;
+            const int od = nd / g.SD;
+            if (nd < 0 || od >= OD || od * g.SD != nd) continue;
+            for (int kh = 0; kh < g.KH; ++kh) {
+                const int nh = h + g.PH - kh * g.DH;
+                const int oh = nh / g.SH;
+                if (nh < 0 || oh >= OH || oh * g.SH != nh) continue;
+                for (int kw = 0; kw < g.KW; ++kw) {
+                    const int nw = w + g.PW - kw * g.DW;
+                    const int ow = nw / g.SW;
+                    if (nw < 0 || ow >= OW || ow * g.SW != nw) continue;
+                    acc += __ldg(base + (size_t)((kd * g.KH + kh) * g.KW + kw) * odhw + (size_t)od * OHW + oh * OW + ow);
+                }
+            }
+        }
+        gp[i] = acc;
+    }
+}
+static bool is_3d(const WindowGeom& g) { return g.D != 1 || g.KD != 1 || g.OD != 1 || g.PD != 0; }
+static cudaError_t launch_im2col3d(const float* x, float* col, const WindowGeom& g, cudaStream_t s) {
+    const size_t rows = (size_t)g.B * g.C * g.KD * g.KH * g.KW;
+    const size_t odhw = (size_t)g.OD * g.OH * g.OW;
+    if (rows == 0 || odhw == 0) return cudaSuccess;
+    if (rows > 0x7fffffffull || odhw > 0x7fffffffull || (size_t)g.D * g.H * g.W > 0x7fffffffull) return cudaErrorInvalidValue;
+    const bool vec = (odhw & 3) == 0 && (reinterpret_cast<uintptr_t>(col) & 15u) == 0;
+    const size_t per_block = (size_t)kThreads * (vec ? 4 : 1) * 4;
+    const unsigned gy = (unsigned)std::min<size_t>((odhw + per_block - 1) / per_block, 64);
+    if (vec) launch_dep(im2col3d_kernel<true>, dim3((unsigned)rows, gy), kThreads, s, x, col, g);
+    else launch_dep(im2col3d_kernel<false>, dim3((unsigned)rows, gy), kThreads, s, x, col, g);
+    return cudaGetLastError();
+}
+static cudaError_t launch_col2im3d(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s) {
+    const size_t planes = (size_t)g.B * g.C;
+    const size_t dhw = (size_t)g.D * g.H * g.W;
+    if (planes == 0 || dhw == 0) return cudaSuccess;
+    if (planes > 0x7fffffffull || dhw > 0x7fffffffull || (size_t)g.OD * g.OH * g.OW > 0x7fffffffull) return cudaErrorInvalidValue;
+    const unsigned gy = (unsigned)std::min<size_t>((dhw + kThreads - 1) / kThreads, 256);
+    launch_dep(col2im3d_kernel, dim3((unsigned)planes, gy), kThreads, s, grad_col, grad_x, g);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaStream_t s) {
+    if (is_3d(g)) return launch_im2col3d(x, col, g, s);
     const size_t rows = (size_t)g.B * g.C * g.KH * g.KW;
     const size_t ohw = (size_t)g.OH * g.OW;
     if (rows == 0 || ohw == 0) return cudaSuccess;
@@ -922,6 +1050,7 @@ cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaS
     return cudaGetLastError();
 }
 cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s) {
+    if (is_3d(g)) return launch_col2im3d(grad_col, grad_x, g, s);
     const size_t planes = (size_t)g.B * g.C;
     const size_t hw = (size_t)g.H * g.W;
     if (planes == 0 || hw == 0) return cudaSuccess;

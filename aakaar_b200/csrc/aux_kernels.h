@@ -45,6 +45,9 @@ struct StridedView {
 };
 // dst (contiguous, shape = v.shape) = gather(v)
 cudaError_t launch_gather(const StridedView& v, float* dst, cudaStream_t s);
+// The adjoint: the view `dst` (its ptr is written) receives the dense, row-major `src` of the view's shape.
+// Elements of a view with overlapping strides are written in an unspecified order.
+cudaError_t launch_scatter(const float* src, const StridedView& dst, cudaStream_t s);
 // out[i] = a[bcast(i)] + b[bcast(i)], out contiguous with shape `shape`
 cudaError_t launch_add(const StridedView& a, const StridedView& b, float* out, int nd,
                        const int64_t* shape, cudaStream_t s, bool multiply = false);
@@ -68,12 +71,16 @@ struct EpiApply {
 };
 cudaError_t launch_epi_apply(const EpiApply& a, cudaStream_t s);
 
-// Sliding-window unfold of a contiguous (B, C, H, W) array into (B, C*KH*KW, OH*OW) and its adjoint
+// Sliding-window unfold of a contiguous (B, C, [D,] H, W) array into (B, C*[KD*]KH*KW, [OD*]OH*OW) and its adjoint
 // (gather form: every input element sums the window entries that read it). 1-D is H = KH = OH = 1.
 struct WindowGeom {
     int64_t B = 0, C = 0, H = 0, W = 0;
     int KH = 1, KW = 1, SH = 1, SW = 1, PH = 0, PW = 0, DH = 1, DW = 1;
     int64_t OH = 0, OW = 0;
+    // depth (3-D windows over a (B, C, D, H, W) array); all ones / zero padding for 1-D and 2-D
+    int64_t D = 1;
+    int KD = 1, SD = 1, PD = 0, DD = 1;
+    int64_t OD = 1;
 };
 cudaError_t launch_im2col(const float* x, float* col, const WindowGeom& g, cudaStream_t s);
 cudaError_t launch_col2im(const float* grad_col, float* grad_x, const WindowGeom& g, cudaStream_t s);

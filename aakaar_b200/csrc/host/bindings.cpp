@@ -5,6 +5,7 @@
 // needs. Every computation is a call into the C ABI of include/akr_b200.h; nothing here touches
 // CUDA or PyTorch directly.
 #include <pybind11/numpy.h>
+#include <cmath>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -381,33 +382,67 @@ TensorPtr cpu_matmul_refused(const TensorPtr&, const TensorPtr&) {
 
 // ------------------------------------------------------------------ convolution callers of the matmul path
 
-// im2col_1d / im2col_2d of the reference (dispatch_im2col_1d, src/bindings.cpp:988-1039; dispatch_im2col_2d,
-// :1169-1225): unfold into the (B, C*K, L_out) matrix the convolution fallback multiplies by the flattened
-// weights; the backward of the node is the adjoint fold (col2im).
-TensorPtr op_im2col(const TensorPtr& x_in, akr_window w, const char* what) {
+// im2col_{1,2,3}d and col2im_{1,2,3}d of the reference (dispatch_im2col_1d, src/bindings.cpp:988-1039;
+// dispatch_col2im_1d, :1041-1081; the 2-D and 3-D twins up to :1400): unfold into the (B, C*K, L_out) matrix the
+// convolution fallback multiplies by the flattened weights, and the adjoint fold that is the forward pass of the
+// transposed convolutions. Each is the other's backward. One geometry type (3-D; lower ranks have depth 1).
+TensorPtr op_fold(const TensorPtr& col_in, akr_window3d w, int rank, const char* what);
+
+TensorPtr op_unfold(const TensorPtr& x_in, akr_window3d w, int rank, const char* what) {
     require_cuda(x_in, what);
     require_f32(x_in, what);
     auto x = x_in->is_contiguous() ? x_in : op_contiguous(x_in);
-    auto col = make_cuda({w.B, w.C * w.KH * w.KW, w.OH * w.OW});
-    check(akr_im2col(x->data, col->data, &w, nullptr));
+    auto col = make_cuda({w.B, w.C * w.KD * w.KH * w.KW, w.OD * w.OH * w.OW});
+    check(akr_im2col_3d(x->data, col->data, &w, nullptr));
     if (needs_graph(x)) {
         const auto in_shape = x->shape;
         attach(col, what, {x}, [w, in_shape](TensorPtr g) {
             auto gc = g->is_contiguous() ? g : op_contiguous(g);
             auto gx = make_cuda(in_shape);
-            check(akr_col2im(gc->data, gx->data, &w, nullptr));
+            check(akr_col2im_3d(gc->data, gx->data, &w, nullptr));
             return std::vector<TensorPtr>{gx};
         });
     }
     return col;
 }
 
+// `rank` spatial dims of the result: (B, C, W), (B, C, H, W) or (B, C, D, H, W).
+TensorPtr op_fold(const TensorPtr& col_in, akr_window3d w, int rank, const char* what) {
+    require_cuda(col_in, what);
+    if (col_in->dtype != AKR_DTYPE_F32) throw std::runtime_error(std::string(what) + ": only float32 is currently supported.");
+    auto col = col_in->is_contiguous() ? col_in : op_contiguous(col_in);
+    std::vector<int64_t> out_shape{w.B, w.C};
+    if (rank == 3) out_shape.push_back(w.D);
+    if (rank >= 2) out_shape.push_back(w.H);
+    out_shape.push_back(w.W);
+    auto out = make_cuda(out_shape);
+    check(akr_col2im_3d(col->data, out->data, &w, nullptr));
+    if (needs_graph(col)) {
+        const auto col_shape = col->shape;
+        attach(out, what, {col}, [w, col_shape](TensorPtr g) {
+            // the fold's backward is the unfold with the same geometry
+            auto gg = g->is_contiguous() ? g : op_contiguous(g);
+            auto gc = make_cuda(col_shape);
+            check(akr_im2col_3d(gg->data, gc->data, &w, nullptr));
+            return std::vector<TensorPtr>{gc};
+        });
+    }
+    return out;
+}
+
+akr_window3d window_1d(int64_t B, int64_t C, int64_t L, int K, int S, int P, int D, int64_t L_out) {
+    return akr_window3d{B, C, 1, 1, L, 1, 1, K, 1, 1, S, 0, 0, P, 1, 1, D, 1, 1, L_out};
+}
+akr_window3d window_2d(int64_t B, int64_t C, int64_t H, int64_t W, int KH, int KW, int SH, int SW, int PH, int PW, int DH,
+                       int DW, int64_t OH, int64_t OW) {
+    return akr_window3d{B, C, 1, H, W, 1, KH, KW, 1, SH, SW, 0, PH, PW, 1, DH, DW, 1, OH, OW};
+}
+
 TensorPtr op_im2col_1d(const TensorPtr& x, int K, int S, int P, int D, int64_t L_out) {
     if (x->shape.size() != 3)
         throw std::invalid_argument("im2col_1d: expected input of shape (batch, channels, length), got rank " +
                                     std::to_string(x->shape.size()));
-    akr_window w{x->shape[0], x->shape[1], 1, x->shape[2], 1, K, 1, S, 0, P, 1, D, 1, L_out};
-    return op_im2col(x, w, "im2col_1d");
+    return op_unfold(x, window_1d(x->shape[0], x->shape[1], x->shape[2], K, S, P, D, L_out), 1, "im2col_1d");
 }
 
 TensorPtr op_im2col_2d(const TensorPtr& x, int KH, int KW, int SH, int SW, int PH, int PW, int DH, int DW, int64_t OH,
@@ -415,8 +450,59 @@ TensorPtr op_im2col_2d(const TensorPtr& x, int KH, int KW, int SH, int SW, int P
     if (x->shape.size() != 4)
         throw std::invalid_argument("im2col_2d: expected input of shape (batch, channels, H, W), got rank " +
                                     std::to_string(x->shape.size()));
-    akr_window w{x->shape[0], x->shape[1], x->shape[2], x->shape[3], KH, KW, SH, SW, PH, PW, DH, DW, OH, OW};
-    return op_im2col(x, w, "im2col_2d");
+    return op_unfold(x, window_2d(x->shape[0], x->shape[1], x->shape[2], x->shape[3], KH, KW, SH, SW, PH, PW, DH, DW, OH, OW),
+                     2, "im2col_2d");
+}
+
+TensorPtr op_im2col_3d(const TensorPtr& x, int KD, int KH, int KW, int SD, int SH, int SW, int PD, int PH, int PW, int DD,
+                       int DH, int DW, int64_t OD, int64_t OH, int64_t OW) {
+    if (x->shape.size() != 5)
+        throw std::invalid_argument("im2col_3d: expected input of shape (batch, channels, D, H, W), got rank " +
+                                    std::to_string(x->shape.size()));
+    akr_window3d w{x->shape[0], x->shape[1], x->shape[2], x->shape[3], x->shape[4], KD, KH, KW, SD, SH, SW,
+                   PD, PH, PW, DD, DH, DW, OD, OH, OW};
+    return op_unfold(x, w, 3, "im2col_3d");
+}
+
+// The reference derives the kernel size from the row count and assumes equal sizes per dim
+// (src/bindings.cpp:1094-1099, 1138-1143); explicit sizes (k* > 0) lift that restriction.
+int kernel_from_rows(const TensorPtr& col, int64_t C, int dims, const char* what) {
+    if (col->shape.size() != 3)
+        throw std::invalid_argument(std::string(what) + ": expected input of shape (batch, channels*kernel, positions), got rank " +
+                                    std::to_string(col->shape.size()));
+    const int64_t rows = col->shape[1];
+    if (C <= 0 || rows % C != 0) throw std::invalid_argument(std::string(what) + ": channels*kernel is not divisible by C");
+    const int64_t kk = rows / C;
+    if (dims == 1) return (int)kk;
+    const int k = (int)std::llround(dims == 2 ? std::sqrt((double)kk) : std::cbrt((double)kk));
+    int64_t pw = 1;
+    for (int i = 0; i < dims; ++i) pw *= k;
+    if (pw != kk) throw std::invalid_argument(std::string(what) + ": kernel is not the same size in every dim; pass kernel_size");
+    return k;
+}
+
+TensorPtr op_col2im_1d(const TensorPtr& col, int64_t C, int64_t L_in, int S, int P, int D, int64_t L_out) {
+    const int K = kernel_from_rows(col, C, 1, "col2im_1d");
+    if (col->shape[2] != L_out) throw std::invalid_argument("col2im_1d: column count does not match out_length");
+    return op_fold(col, window_1d(col->shape[0], C, L_in, K, S, P, D, L_out), 1, "col2im_1d");
+}
+
+TensorPtr op_col2im_2d(const TensorPtr& col, int64_t C, int64_t H_in, int64_t W_in, int SH, int SW, int PH, int PW, int DH,
+                       int DW, int64_t OH, int64_t OW, int KH, int KW) {
+    if (KH <= 0 || KW <= 0) KH = KW = kernel_from_rows(col, C, 2, "col2im_2d");
+    if (col->shape.size() != 3 || col->shape[1] != C * KH * KW || col->shape[2] != OH * OW)
+        throw std::invalid_argument("col2im_2d: expected input of shape (batch, channels*KH*KW, OH*OW)");
+    return op_fold(col, window_2d(col->shape[0], C, H_in, W_in, KH, KW, SH, SW, PH, PW, DH, DW, OH, OW), 2, "col2im_2d");
+}
+
+TensorPtr op_col2im_3d(const TensorPtr& col, int64_t C, int64_t D_in, int64_t H_in, int64_t W_in, int SD, int SH, int SW,
+                       int PD, int PH, int PW, int DD, int DH, int DW, int64_t OD, int64_t OH, int64_t OW, int KD, int KH,
+                       int KW) {
+    if (KD <= 0 || KH <= 0 || KW <= 0) KD = KH = KW = kernel_from_rows(col, C, 3, "col2im_3d");
+    if (col->shape.size() != 3 || col->shape[1] != C * KD * KH * KW || col->shape[2] != OD * OH * OW)
+        throw std::invalid_argument("col2im_3d: expected input of shape (batch, channels*KD*KH*KW, OD*OH*OW)");
+    akr_window3d w{col->shape[0], C, D_in, H_in, W_in, KD, KH, KW, SD, SH, SW, PD, PH, PW, DD, DH, DW, OD, OH, OW};
+    return op_fold(col, w, 3, "col2im_3d");
 }
 
 // ------------------------------------------------------------------ losses / optimiser
@@ -672,13 +758,19 @@ TensorPtr to_device(const TensorPtr& t, const std::string& target) {
 
 void copy_into(const TensorPtr& dst, const TensorPtr& src) {
     if (dst->size != src->size) throw std::invalid_argument("copy_: size mismatch");
-    if (!dst->is_contiguous()) throw std::invalid_argument("copy_: destination must be contiguous");
     require_cuda(dst, "copy_");
     require_f32(dst, "copy_");
     bool prev = g_grad_enabled;
     g_grad_enabled = false;
     TensorPtr s = src->is_contiguous() ? src : op_contiguous(src);
     g_grad_enabled = prev;
+    if (!dst->is_contiguous()) {
+        // a view (transposed, sliced): the dense source is written through the view's strides
+        if (s->device != "cuda") throw std::invalid_argument("copy_: a non-contiguous destination takes a CUDA source");
+        akr_view vd = dst->view();
+        check(akr_scatter(s->data, &vd, nullptr));
+        return;
+    }
     if (s->device == "cuda") check(akr_memcpy_d2d(dst->data, s->data, (size_t)dst->size * sizeof(float), nullptr));
     else {
         check(akr_memcpy_h2d(dst->data, s->data, (size_t)dst->size * sizeof(float), nullptr));
@@ -700,12 +792,9 @@ float item(const TensorPtr& t) {
 }
 
 // Basic indexing: ints, slices and tuples of them produce a view (offset + scaled strides), as
-// Tensor.__getitem__ of the reference does (src/bindings.cpp:2613-2732). Gradients do not flow
-// through a slice in this build.
+// Tensor.__getitem__ of the reference does (src/bindings.cpp:2613-2732). The node's backward places the
+// incoming gradient into a zero tensor of the base's shape, at the positions the view covers.
 TensorPtr getitem(const TensorPtr& self, py::object key) {
-    if (needs_graph(self))
-        throw std::runtime_error("__getitem__: autograd through slicing is outside the matmul path of this build; "
-                                 "slice a detached tensor or under no_grad()");
     py::tuple keys = py::isinstance<py::tuple>(key) ? key.cast<py::tuple>() : py::make_tuple(key);
     if (keys.size() > self->shape.size()) throw std::out_of_range("too many indices for tensor");
     std::vector<int64_t> shape, strides;
@@ -739,7 +828,45 @@ TensorPtr getitem(const TensorPtr& self, py::object key) {
         shape.push_back(1);
         strides.push_back(1);
     }
-    return std::make_shared<Tensor>(self, off, shape, strides);
+    auto out = std::make_shared<Tensor>(self, off, shape, strides);
+    if (needs_graph(self)) {
+        require_f32(self, "__getitem__");
+        const auto base_shape = self->shape;
+        // the view's geometry relative to a CONTIGUOUS tensor of the base's shape (the gradient is contiguous)
+        const auto cst = contiguous_strides(self->shape);
+        std::vector<int64_t> gstrides;
+        int64_t goff = 0;
+        {
+            size_t d = 0;
+            for (auto k : keys) {
+                if (py::isinstance<py::slice>(k)) {
+                    py::ssize_t start, stop, step, len;
+                    k.cast<py::slice>().compute(self->shape[d], &start, &stop, &step, &len);
+                    goff += start * cst[d];
+                    gstrides.push_back(cst[d] * step);
+                } else {
+                    int64_t i = k.cast<int64_t>();
+                    if (i < 0) i += self->shape[d];
+                    goff += i * cst[d];
+                }
+                ++d;
+            }
+            for (; d < self->shape.size(); ++d) gstrides.push_back(cst[d]);
+            if (gstrides.empty()) gstrides.push_back(1);
+        }
+        const auto vshape = shape;
+        attach(out, "getitem", {self}, [base_shape, vshape, gstrides, goff](TensorPtr g) {
+            require_cuda(g, "__getitem__ backward");
+            auto gc = g->is_contiguous() ? g : op_contiguous(g);
+            auto gi = make_cuda(base_shape);
+            check(akr_fill(gi->data, 0.0f, (size_t)gi->size, nullptr));
+            Tensor window(gi, goff, vshape, gstrides);
+            akr_view vw = window.view();
+            check(akr_scatter(gc->data, &vw, nullptr));
+            return std::vector<TensorPtr>{gi};
+        });
+    }
+    return out;
 }
 
 std::string repr(const TensorPtr& t) {
@@ -841,6 +968,16 @@ PYBIND11_MODULE(_C, m) {
     m.def("im2col_1d", &op_im2col_1d, py::arg("x"), py::arg("kernel_size"), py::arg("stride"), py::arg("padding"),
           py::arg("dilation"), py::arg("out_length"));
     m.def("im2col_2d", &op_im2col_2d);
+    m.def("im2col_3d", &op_im2col_3d);
+    m.def("col2im_1d", &op_col2im_1d, py::arg("col"), py::arg("C"), py::arg("L_in"), py::arg("stride"), py::arg("padding"),
+          py::arg("dilation"), py::arg("out_length"));
+    m.def("col2im_2d", &op_col2im_2d, py::arg("col"), py::arg("C"), py::arg("H_in"), py::arg("W_in"), py::arg("SH"),
+          py::arg("SW"), py::arg("PH"), py::arg("PW"), py::arg("DH"), py::arg("DW"), py::arg("OH"), py::arg("OW"),
+          py::arg("KH") = 0, py::arg("KW") = 0);
+    m.def("col2im_3d", &op_col2im_3d, py::arg("col"), py::arg("C"), py::arg("D_in"), py::arg("H_in"), py::arg("W_in"),
+          py::arg("SD"), py::arg("SH"), py::arg("SW"), py::arg("PD"), py::arg("PH"), py::arg("PW"), py::arg("DD"),
+          py::arg("DH"), py::arg("DW"), py::arg("OD"), py::arg("OH"), py::arg("OW"), py::arg("KD") = 0, py::arg("KH") = 0,
+          py::arg("KW") = 0);
     m.def("linear", &op_matmul_bias, py::arg("x"), py::arg("weight"), py::arg("bias") = nullptr,
           "x @ weight + bias with the bias add fused into the GEMM epilogue");
     m.def("from_numpy", &from_numpy, py::arg("array"), py::arg("device") = "cuda", py::arg("requires_grad") = false);

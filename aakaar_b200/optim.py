@@ -8,6 +8,18 @@ from __future__ import annotations
 from . import _C, no_grad
 
 
+def _fused_update(p, grad, velocity, lr, momentum, weight_decay, dampening, nesterov, has_momentum, initialized):
+    """The fused update on `p`. A parameter that is a view (transposed, sliced) takes it on a dense copy that
+    is written back through the view's strides - the reference's unfused fallback for such parameters
+    (aakaar/optim.py:24-48: ``p.copy_(p - update * lr)``), same arithmetic."""
+    if p.is_contiguous():
+        _C._sgd_step_fused(p, grad, velocity, lr, momentum, weight_decay, dampening, nesterov, has_momentum, initialized)
+        return
+    dense = p.contiguous()
+    _C._sgd_step_fused(dense, grad, velocity, lr, momentum, weight_decay, dampening, nesterov, has_momentum, initialized)
+    p.copy_(dense)
+
+
 class SGD:
     def __init__(self, parameters, lr=0.01, momentum=0.0, weight_decay=0.0, dampening=0.0, nesterov=False):
         if nesterov and (momentum <= 0 or dampening != 0):
@@ -26,13 +38,11 @@ class SGD:
                 if p.grad is None:
                     continue
                 grad = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
-                if not p.is_contiguous():
-                    raise ValueError("SGD.step: parameters must be contiguous")
                 initialized = self._velocity[i] is not None
                 if self.momentum != 0 and self._velocity[i] is None:
                     self._velocity[i] = grad * 0.0
-                _C._sgd_step_fused(p, grad, self._velocity[i], self.lr, self.momentum, self.weight_decay,
-                                   self.dampening, int(self.nesterov), int(self.momentum != 0), int(initialized))
+                _fused_update(p, grad, self._velocity[i], self.lr, self.momentum, self.weight_decay,
+                              self.dampening, int(self.nesterov), int(self.momentum != 0), int(initialized))
 
     def zero_grad(self):
         for p in self.parameters:
@@ -78,10 +88,8 @@ class Muon:
                     update = self._newton_schulz_orthogonalize(self._buf[i], self.ns_steps)
                 else:
                     update = self._buf[i]
-                if not p.is_contiguous():
-                    raise ValueError("Muon.step: parameters must be contiguous")
                 upd = update if update.is_contiguous() else update.contiguous()
-                _C._sgd_step_fused(p, upd, None, self.lr, 0.0, 0.0, 0.0, 0, 0, 0)   # p -= lr * update
+                _fused_update(p, upd, None, self.lr, 0.0, 0.0, 0.0, 0, 0, 0)        # p -= lr * update
 
     def zero_grad(self):
         for p in self.parameters:

@@ -263,6 +263,10 @@ AKR_API int64_t akr_launch_count(int reset);
  *   mse fwd/bwd   : src/elementwise_kernel.cu:2253-2300
  *   sgd_step      : src/optim_kernels.cu:21-55 (plain / weight decay / momentum) */
 AKR_API int akr_contiguous(const akr_view* src, float* dst, void* stream);
+/* The adjoint of akr_contiguous: the dense, row-major `src` (dst's shape) is written through dst's strides. The
+ * backward of Tensor.__getitem__ (src/bindings.cpp:2670-2727: the incoming gradient placed into a zero tensor
+ * of the base's shape) and of copy_ into a view. */
+AKR_API int akr_scatter(const float* src, akr_view* dst, void* stream);
 AKR_API int akr_add(const akr_view* a, const akr_view* b, akr_view* out, void* stream);
 /* out = a * b elementwise with the broadcasting of akr_add (mul_broadcast_kernel, src/elementwise_kernel.cu). */
 AKR_API int akr_mul(const akr_view* a, const akr_view* b, akr_view* out, void* stream);
@@ -282,6 +286,17 @@ typedef struct akr_window {
 } akr_window;
 AKR_API int akr_im2col(const float* x, float* col, const akr_window* geom, void* stream);
 AKR_API int akr_col2im(const float* grad_col, float* grad_x, const akr_window* geom, void* stream);
+/* The 3-D forms (aakaar/__init__.py:354-363, 451-463; src/conv3d_kernel.cpp and its .cu twin): x contiguous
+ * (B, C, D, H, W); col contiguous (B, C*KD*KH*KW, OD*OH*OW), row (c, kd, kh, kw), column (od, oh, ow). The fold
+ * is also the forward pass of the transposed convolutions (aakaar/__init__.py:398-519), whose backward is the
+ * unfold. */
+typedef struct akr_window3d {
+    int64_t B, C, D, H, W;
+    int32_t KD, KH, KW, SD, SH, SW, PD, PH, PW, DD, DH, DW;
+    int64_t OD, OH, OW;
+} akr_window3d;
+AKR_API int akr_im2col_3d(const float* x, float* col, const akr_window3d* geom, void* stream);
+AKR_API int akr_col2im_3d(const float* grad_col, float* grad_x, const akr_window3d* geom, void* stream);
 
 /* loss_out[0] = sum((pred - target)^2) / n; target == NULL gives the mean of squares of pred (the Frobenius
  * norm the Muon optimizer divides by, aakaar/optim.py:534). */

@@ -299,6 +299,96 @@ def conv2d_forward_backward(x, weight, grad_out, stride=(1, 1), padding=(0, 0), 
     return y, dx, dw_flat.reshape(weight.shape)
 
 
+def im2col_3d(x, K, S, P, D, O):
+    """(B, C, D, H, W) -> (B, C*KD*KH*KW, OD*OH*OW) (run_cpu_im2col_3d, src/conv3d_kernel.cpp): row
+    (c, kd, kh, kw), column (od, oh, ow), zero outside the input. K, S, P, D, O: 3-tuples."""
+    x = np.asarray(x)
+    B, C = x.shape[:2]
+    dims = x.shape[2:]
+    col = np.zeros((B, C) + tuple(K) + tuple(O), dtype=x.dtype)
+    for kd in range(K[0]):
+        for kh in range(K[1]):
+            for kw in range(K[2]):
+                for od in range(O[0]):
+                    d = od * S[0] - P[0] + kd * D[0]
+                    if d < 0 or d >= dims[0]:
+                        continue
+                    for oh in range(O[1]):
+                        h = oh * S[1] - P[1] + kh * D[1]
+                        if h < 0 or h >= dims[1]:
+                            continue
+                        for ow in range(O[2]):
+                            w = ow * S[2] - P[2] + kw * D[2]
+                            if 0 <= w < dims[2]:
+                                col[:, :, kd, kh, kw, od, oh, ow] = x[:, :, d, h, w]
+    return col.reshape(B, C * int(np.prod(K)), int(np.prod(O)))
+
+
+def col2im_3d(gcol, C, dims, K, S, P, D, O):
+    """Adjoint of im2col_3d (run_cpu_col2im_3d): (B, C*KD*KH*KW, OD*OH*OW) summed into (B, C, *dims)."""
+    gcol = np.asarray(gcol)
+    B = gcol.shape[0]
+    g = gcol.reshape((B, C) + tuple(K) + tuple(O))
+    gx = np.zeros((B, C) + tuple(dims), dtype=np.float64)
+    for kd in range(K[0]):
+        for kh in range(K[1]):
+            for kw in range(K[2]):
+                for od in range(O[0]):
+                    d = od * S[0] - P[0] + kd * D[0]
+                    if d < 0 or d >= dims[0]:
+                        continue
+                    for oh in range(O[1]):
+                        h = oh * S[1] - P[1] + kh * D[1]
+                        if h < 0 or h >= dims[1]:
+                            continue
+                        for ow in range(O[2]):
+                            w = ow * S[2] - P[2] + kw * D[2]
+                            if 0 <= w < dims[2]:
+                                gx[:, :, d, h, w] += g[:, :, kd, kh, kw, od, oh, ow]
+    return gx.astype(np.float32)
+
+
+def _pad3(v, fill):
+    v = tuple(v)
+    return (fill,) * (3 - len(v)) + v
+
+
+def conv_nd_forward_backward(x, weight, grad_out, stride, padding, dilation, acc=np.float32):
+    """conv1d / conv2d / conv3d of the reference's fallback (aakaar/__init__.py:289-388) as unfold + matmul,
+    and (dx, dweight) for a given dy. Rank is taken from the weight; lower ranks run as depth-1 volumes."""
+    nd = weight.ndim - 2
+    K, S, P, D = _pad3(weight.shape[2:], 1), _pad3(stride, 1), _pad3(padding, 0), _pad3(dilation, 1)
+    dims = _pad3(x.shape[2:], 1)
+    O = tuple((dims[i] + 2 * P[i] - D[i] * (K[i] - 1) - 1) // S[i] + 1 for i in range(3))
+    B, C_in, C_out = x.shape[0], x.shape[1], weight.shape[0]
+    col = im2col_3d(np.asarray(x).reshape((B, C_in) + dims), K, S, P, D, O)
+    w_flat = np.ascontiguousarray(weight).reshape(1, C_out, C_in * int(np.prod(K)))
+    y = matmul_forward(w_flat, col, acc).reshape((B, C_out) + O[3 - nd:])
+    dw_flat, dcol = matmul_backward(w_flat, col, np.ascontiguousarray(grad_out).reshape(B, C_out, int(np.prod(O))), acc)
+    dx = col2im_3d(dcol, C_in, dims, K, S, P, D, O).reshape(x.shape)
+    return y, dx, dw_flat.reshape(weight.shape)
+
+
+def conv_transpose_nd_forward_backward(x, weight, grad_out, stride, padding, dilation, acc=np.float32):
+    """conv_transpose{1,2,3}d of the reference's fallback (aakaar/__init__.py:398-519): weight
+    (C_in, C_out, *K); col = W_flat^T @ x, then the fold; and (dx, dweight) for a given dy (the fold's
+    backward is the unfold, src/bindings.cpp:1066-1078)."""
+    nd = weight.ndim - 2
+    K, S, P, D = _pad3(weight.shape[2:], 1), _pad3(stride, 1), _pad3(padding, 0), _pad3(dilation, 1)
+    win = _pad3(x.shape[2:], 1)                       # the input positions are the WINDOW positions of the fold
+    out_dims = tuple((win[i] - 1) * S[i] - 2 * P[i] + D[i] * (K[i] - 1) + 1 for i in range(3))
+    B, C_in, C_out = x.shape[0], weight.shape[0], weight.shape[1]
+    kk = int(np.prod(K))
+    w_t = np.ascontiguousarray(np.ascontiguousarray(weight).reshape(C_in, C_out * kk).T)[None]   # (1, C_out*kk, C_in)
+    x_flat = np.ascontiguousarray(x).reshape(B, C_in, int(np.prod(win)))
+    col = matmul_forward(w_t, x_flat, acc)                                                        # (B, C_out*kk, L_in)
+    y = col2im_3d(col, C_out, out_dims, K, S, P, D, win).reshape((B, C_out) + out_dims[3 - nd:])
+    dcol = im2col_3d(np.asarray(grad_out).reshape((B, C_out) + out_dims), K, S, P, D, win)
+    dw_t, dx_flat = matmul_backward(w_t, x_flat, dcol, acc)
+    dw = np.ascontiguousarray(dw_t[0].T).reshape(weight.shape)
+    return y, dx_flat.reshape(x.shape), dw
+
+
 # ---------------------------------------------------------------- Linear training step support
 
 def linear_forward(x, w, bias, acc=np.float32):

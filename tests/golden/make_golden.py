@@ -173,6 +173,45 @@ dy2 = normal(tuple(Y2.shape), 56)
 Y2.backward(T(dy2))
 out["conv2d_y"], out["conv2d_dx"], out["conv2d_dw"] = Y2.to_numpy(), X2.grad.to_numpy(), W2.grad.to_numpy()
 
+# 8g. conv3d and the transposed convolutions (aakaar/__init__.py:365-388, 398-519), composed from the reference's own
+#     im2col_3d / col2im_* + reshape / transpose + matmul ops exactly as its Python fallback composes them
+xc3, wc3 = normal((2, 3, 5, 6, 7), 61), uniform((4, 3, 2, 3, 2), 62)
+X3, W3 = T(xc3, True), T(wc3, True)
+OD3, OH3, OW3 = (5 + 2 * 1 - 1 * (2 - 1) - 1) // 2 + 1, (6 + 2 * 0 - 1 * (3 - 1) - 1) // 1 + 1, (7 + 2 * 1 - 2 * (2 - 1) - 1) // 1 + 1
+col3 = ref.im2col_3d(X3, 2, 3, 2, 2, 1, 1, 1, 0, 1, 1, 1, 2, OD3, OH3, OW3)
+Y3 = ref.cpu_matmul(W3.reshape([4, 36]).reshape([1, 4, 36]), col3).reshape([2, 4, OD3, OH3, OW3])
+dy3 = normal(tuple(Y3.shape), 63)
+Y3.backward(T(dy3))
+out["conv3d_y"], out["conv3d_dx"], out["conv3d_dw"] = Y3.to_numpy(), X3.grad.to_numpy(), W3.grad.to_numpy()
+
+def ref_conv_transpose(x_np, w_np, dims, stride, padding, dilation, seed):
+    """conv_transpose{1,2,3}d of the reference's fallback path; kernels are cubic (its col2im infers the size)."""
+    X, W = T(x_np, True), T(w_np, True)
+    cin, cout = w_np.shape[0], w_np.shape[1]
+    k = w_np.shape[2:]
+    spatial = x_np.shape[2:]
+    outsz = [(spatial[i] - 1) * stride[i] - 2 * padding[i] + dilation[i] * (k[i] - 1) + 1 for i in range(dims)]
+    kk = int(np.prod(k))
+    w_t = W.reshape([cin, cout * kk]).transpose(0, 1).reshape([1, cout * kk, cin])
+    col = ref.cpu_matmul(w_t, X.reshape([x_np.shape[0], cin, int(np.prod(spatial))]))
+    if dims == 1:
+        Y = ref.col2im_1d(col, cout, outsz[0], stride[0], padding[0], dilation[0], spatial[0])
+    elif dims == 2:
+        Y = ref.col2im_2d(col, cout, outsz[0], outsz[1], stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+                          spatial[0], spatial[1])
+    else:
+        Y = ref.col2im_3d(col, cout, outsz[0], outsz[1], outsz[2], *stride, *padding, *dilation, *spatial)
+    dy = normal(tuple(Y.shape), seed)
+    Y.backward(T(dy))
+    return Y.to_numpy(), X.grad.to_numpy(), W.grad.to_numpy()
+
+for name, xs_, ws_, dims, st_, pd_, dl_, seed in (
+        ("convT1d", (3, 4, 9), (4, 5, 3), 1, (2,), (1,), (2,), 64),
+        ("convT2d", (2, 3, 5, 6), (3, 4, 3, 3), 2, (2, 1), (1, 0), (1, 2), 67),
+        ("convT3d", (2, 3, 3, 4, 5), (3, 2, 2, 2, 2), 3, (1, 2, 1), (0, 1, 0), (1, 1, 2), 70)):
+    y_, dx_, dw_ = ref_conv_transpose(normal(xs_, seed + 1), uniform(ws_, seed + 2), dims, st_, pd_, dl_, seed)
+    out[name + "_y"], out[name + "_dx"], out[name + "_dw"] = y_, dx_, dw_
+
 # 8f. the README's training example (README.md:101-137): Linear(1,16) -> tanh -> Linear(16,1) on sin(x), its own
 #     mse (diff * diff).sum() / n, plain SGD lr 0.05, 300 epochs; weights drawn as aakaar/nn.py:5-13 draws them
 np.random.seed(0)

@@ -277,6 +277,71 @@ def test_conv_fallback_callers(ak, tf32, tol):
         ak.set_tf32(False)
 
 
+@pytest.mark.parametrize("tf32,tol", [(False, TOL_FP32), (True, TOL_TF32)])
+def test_conv3d_and_transposed_convolutions(ak, tf32, tol):
+    # conv3d (unfold + one broadcast-batched matmul) and conv_transpose{1,2,3}d (matmul with the weights read as a
+    # transposed view + fold), forward and backward, against the vectors of the reference's own compositions;
+    # then a non-cubic transposed kernel (beyond what the reference's fold accepts) against the oracle
+    G, _ = load_golden()
+    ak.set_tf32(tf32)
+    try:
+        X = ak.from_numpy(normal((2, 3, 5, 6, 7), 61), requires_grad=True)
+        W = ak.from_numpy(uniform((4, 3, 2, 3, 2), 62), requires_grad=True)
+        Y = ak.conv3d(X, W, stride=(2, 1, 1), padding=(1, 0, 1), dilation=(1, 1, 2))
+        assert Y.shape == list(G["conv3d_y"].shape)
+        Y.backward(ak.from_numpy(normal(tuple(Y.shape), 63)))
+        assert rel_fro(Y.to_numpy(), G["conv3d_y"]) < tol
+        assert rel_fro(X.grad.to_numpy(), G["conv3d_dx"]) < tol and rel_fro(W.grad.to_numpy(), G["conv3d_dw"]) < tol
+        for name, fn, xs, ws, st, pd, dl, seed in (
+                ("convT1d", ak.conv_transpose1d, (3, 4, 9), (4, 5, 3), 2, 1, 2, 64),
+                ("convT2d", ak.conv_transpose2d, (2, 3, 5, 6), (3, 4, 3, 3), (2, 1), (1, 0), (1, 2), 67),
+                ("convT3d", ak.conv_transpose3d, (2, 3, 3, 4, 5), (3, 2, 2, 2, 2), (1, 2, 1), (0, 1, 0), (1, 1, 2), 70)):
+            X = ak.from_numpy(normal(xs, seed + 1), requires_grad=True)
+            W = ak.from_numpy(uniform(ws, seed + 2), requires_grad=True)
+            Y = fn(X, W, stride=st, padding=pd, dilation=dl)
+            assert Y.shape == list(G[name + "_y"].shape), name
+            Y.backward(ak.from_numpy(normal(tuple(Y.shape), seed)))
+            assert rel_fro(Y.to_numpy(), G[name + "_y"]) < tol, name
+            assert rel_fro(X.grad.to_numpy(), G[name + "_dx"]) < tol, name
+            assert rel_fro(W.grad.to_numpy(), G[name + "_dw"]) < tol, name
+        x, w = normal((4, 16, 12, 10), 81), uniform((16, 24, 3, 2), 82) * 0.2
+        X, W = ak.from_numpy(x, requires_grad=True), ak.from_numpy(w, requires_grad=True)
+        Y = ak.conv_transpose2d(X, W, stride=(2, 3), padding=(1, 0))
+        dy = normal(tuple(Y.shape), 83)
+        Y.backward(ak.from_numpy(dy))
+        ry, rdx, rdw = mo.conv_transpose_nd_forward_backward(x, w, dy, (2, 3), (1, 0), (1, 1), np.float64)
+        assert rel_fro(Y.to_numpy(), ry) < tol
+        assert rel_fro(X.grad.to_numpy(), rdx) < tol and rel_fro(W.grad.to_numpy(), rdw) < tol
+        with pytest.raises(NotImplementedError):
+            ak.conv_transpose1d(X, W, output_padding=1)
+    finally:
+        ak.set_tf32(False)
+    # modules: parameters drawn as the reference draws them, bias added, its gradient the sum over batch and positions
+    np.random.seed(11)
+    m = ak.nn.ConvTranspose2d(3, 5, 3, stride=2, padding=1)
+    np.random.seed(11)
+    lim = 1.0 / np.sqrt(3 * 9)
+    w = np.random.uniform(-lim, lim, (3, 5, 3, 3)).astype(np.float32)
+    b = np.random.uniform(-lim, lim, (1, 5, 1, 1)).astype(np.float32)
+    np.testing.assert_array_equal(m.weight.to_numpy(), w)
+    np.testing.assert_array_equal(m.bias.to_numpy(), b)
+    x = normal((2, 3, 6, 7), 84)
+    X = ak.from_numpy(x, requires_grad=True)
+    y = m(X)
+    dy = normal(tuple(y.shape), 85)
+    y.backward(ak.from_numpy(dy))
+    ry, rdx, rdw = mo.conv_transpose_nd_forward_backward(x, w, dy, (2, 2), (1, 1), (1, 1), np.float64)
+    assert rel_fro(y.to_numpy(), ry + b) < TOL_FP32
+    assert rel_fro(X.grad.to_numpy(), rdx) < TOL_FP32 and rel_fro(m.weight.grad.to_numpy(), rdw) < TOL_FP32
+    assert rel_fro(m.bias.grad.to_numpy(), dy.sum(axis=(0, 2, 3), keepdims=True)) < TOL_FP32
+    c3 = ak.nn.Conv3d(2, 3, (2, 1, 2), padding=(1, 0, 0))
+    x3 = normal((2, 2, 4, 3, 5), 86)
+    y3 = c3(ak.from_numpy(x3))
+    ry3, _, _ = mo.conv_nd_forward_backward(x3, c3.weight.to_numpy(), np.zeros(tuple(y3.shape), np.float32), (1, 1, 1),
+                                            (1, 0, 0), (1, 1, 1), np.float64)
+    assert rel_fro(y3.to_numpy(), ry3 + c3.bias.to_numpy()) < TOL_FP32
+
+
 def test_conv_modules_with_bias(ak):
     np.random.seed(7)
     conv = ak.nn.Conv2d(3, 5, (3, 2), stride=(2, 1), padding=(1, 0), dilation=(1, 2))
@@ -332,3 +397,55 @@ def test_readme_training_example(ak):
     np.testing.assert_allclose(got[:3], G["readme_losses"][:3], rtol=1e-5)
     np.testing.assert_allclose(got[3:], G["readme_losses"][3:], rtol=2e-3)   # 100 - 300 chained fp32 steps
     assert got[-1] < 0.05 * got[0]
+
+
+def test_autograd_through_getitem_views(ak):
+    # Tensor.__getitem__ records a node (src/bindings.cpp:2670-2727): the incoming gradient lands in a zero
+    # tensor of the base's shape at the positions the view covers. Slices feed the strided matmul path.
+    a = uniform((6, 10, 12), 91)
+    b = uniform((12, 7), 92)
+    A = ak.from_numpy(a, requires_grad=True)
+    B = ak.from_numpy(b, requires_grad=True)
+    sub = A[1:5, 2:10:2]                      # [4, 4, 12] with a stepped middle dim
+    assert sub.requires_grad and sub.shape == [4, 4, 12]
+    out = ak.matmul(sub, B)
+    dy = normal((4, 4, 7), 93)
+    out.backward(ak.from_numpy(dy))
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    ref_da = np.zeros_like(a64)
+    ref_da[1:5, 2:10:2] = dy.astype(np.float64) @ b64.T
+    ref_db = np.einsum("ijk,ijn->kn", a64[1:5, 2:10:2], dy.astype(np.float64))
+    assert rel_fro(A.grad.to_numpy(), ref_da) < TOL_FP32
+    assert rel_fro(B.grad.to_numpy(), ref_db) < TOL_FP32
+    # an integer index drops a dim; two views of one base accumulate into its gradient
+    W = ak.from_numpy(uniform((5, 8, 8), 94), requires_grad=True)
+    x = ak.from_numpy(uniform((3, 8), 95))
+    y = ak.matmul(x, W[2]) + ak.matmul(x, W[-1])
+    y.sum().backward()
+    ref = np.zeros((5, 8, 8))
+    ref[2] = ref[4] = uniform((3, 8), 95).astype(np.float64).T @ np.ones((3, 8))
+    assert rel_fro(W.grad.to_numpy(), ref) < TOL_FP32
+    with pytest.raises(IndexError):
+        W[7]
+
+
+def test_optimizers_step_view_parameters(ak):
+    # a parameter that is a transposed view takes the same update as its dense twin (the reference's unfused
+    # fallback, aakaar/optim.py:24-48), written back through the view's strides
+    base = uniform((6, 4), 96)
+    g = normal((4, 6), 97)
+    P = ak.from_numpy(base).transpose(0, 1)        # [4, 6], non-contiguous
+    P.requires_grad = True
+    P.grad = ak.from_numpy(g)
+    opt = ak.optim.SGD([P], lr=0.1, momentum=0.9, weight_decay=0.01)
+    opt.step()
+    opt.step()
+    p = base.T.astype(np.float64).copy()
+    g64 = g.astype(np.float64)
+    v = None
+    for _ in range(2):
+        gg = g64 + 0.01 * p
+        v = gg if v is None else 0.9 * v + gg
+        p = p - 0.1 * v
+    assert not P.is_contiguous()
+    assert rel_fro(P.contiguous().to_numpy(), p) < TOL_FP32

@@ -150,3 +150,24 @@ def test_conv_fallback_matches_reference():
     y2, dx2, dw2 = mo.conv2d_forward_backward(x2, w2, normal(G["conv2d_y"].shape, 56), (2, 1), (1, 0), (1, 2))
     assert rel_fro(y2, G["conv2d_y"]) < 2e-6
     assert rel_fro(dx2, G["conv2d_dx"]) < 2e-6 and rel_fro(dw2, G["conv2d_dw"]) < 2e-6
+
+
+def test_conv3d_and_transposed_convolutions_match_reference():
+    # vectors of the reference's own im2col_3d / col2im_* + matmul compositions (tests/golden/make_golden.py 8g)
+    G, _ = load_golden()
+    x, w = normal((2, 3, 5, 6, 7), 61), uniform((4, 3, 2, 3, 2), 62)
+    y, dx, dw = mo.conv_nd_forward_backward(x, w, normal(G["conv3d_y"].shape, 63), (2, 1, 1), (1, 0, 1), (1, 1, 2))
+    assert rel_fro(y, G["conv3d_y"]) < 2e-6
+    assert rel_fro(dx, G["conv3d_dx"]) < 2e-6 and rel_fro(dw, G["conv3d_dw"]) < 2e-6
+    for name, xs, ws, st, pd, dl, seed in (("convT1d", (3, 4, 9), (4, 5, 3), (2,), (1,), (2,), 64),
+                                           ("convT2d", (2, 3, 5, 6), (3, 4, 3, 3), (2, 1), (1, 0), (1, 2), 67),
+                                           ("convT3d", (2, 3, 3, 4, 5), (3, 2, 2, 2, 2), (1, 2, 1), (0, 1, 0), (1, 1, 2), 70)):
+        x, w = normal(xs, seed + 1), uniform(ws, seed + 2)
+        y, dx, dw = mo.conv_transpose_nd_forward_backward(x, w, normal(G[name + "_y"].shape, seed), st, pd, dl)
+        assert y.shape == G[name + "_y"].shape
+        assert rel_fro(y, G[name + "_y"]) < 2e-6, name
+        assert rel_fro(dx, G[name + "_dx"]) < 2e-6 and rel_fro(dw, G[name + "_dw"]) < 2e-6, name
+    # the 2-D case through the N-D oracle agrees with the 2-D one
+    x2, w2 = normal((2, 3, 9, 11), 54), uniform((4, 3, 3, 2), 55)
+    y2, dx2, dw2 = mo.conv_nd_forward_backward(x2, w2, normal(G["conv2d_y"].shape, 56), (2, 1), (1, 0), (1, 2))
+    assert rel_fro(y2, G["conv2d_y"]) < 2e-6 and rel_fro(dx2, G["conv2d_dx"]) < 2e-6 and rel_fro(dw2, G["conv2d_dw"]) < 2e-6
