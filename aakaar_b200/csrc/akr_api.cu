@@ -31,7 +31,7 @@ int cuda_fail(cudaError_t e, const char* what) {
     return fail(AKR_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-enum WsSlot { WS_A_HI = 0, WS_A_LO, WS_B_HI, WS_B_LO, WS_PARTIALS, WS_COUNTERS, WS_MISC, WS_COLPART, WS_COUNT };
+enum WsSlot { WS_A_PACK = 0, WS_B_PACK, WS_PARTIALS, WS_COUNTERS, WS_MISC, WS_COLPART, WS_COUNT };
 
 struct Region {
     void* ptr = nullptr;
@@ -220,10 +220,9 @@ struct Prepared {
 };
 
 // Decides how the GEMM kernel reads one operand: in place through TMA when its layout allows it,
-// else from a packed copy; with `split` from freshly split hi / lo arrays (large fp32-accurate products).
+// else from a packed copy.
 int prepare_operand(DeviceState* st, const Operand& src, int64_t mn, int64_t k,
-                    const std::vector<Dim>& dims, bool is_a, bool split, cudaStream_t stream,
-                    Prepared* out) {
+                    const std::vector<Dim>& dims, bool is_a, cudaStream_t stream, Prepared* out) {
     const size_t nd = dims.size();
     std::vector<int64_t> bs(nd);
     for (size_t i = 0; i < nd; ++i) bs[i] = is_a ? dims[i].a : dims[i].b;
@@ -236,9 +235,8 @@ int prepare_operand(DeviceState* st, const Operand& src, int64_t mn, int64_t k,
     const bool k_major_ok = (k == 1 || src.s_k == 1) && (mn == 1 || (src.s_mn > 0 && (src.s_mn & 3) == 0));
     const bool mn_major_ok = (mn == 1 || src.s_mn == 1) && (k == 1 || (src.s_k > 0 && (src.s_k & 3) == 0));
 
-    if (!split && strides_ok() && (k_major_ok || mn_major_ok)) {
+    if (strides_ok() && (k_major_ok || mn_major_ok)) {
         out->op.ptr = src.ptr;
-        out->op.lo = nullptr;
         out->op.mn_major = k_major_ok ? 0 : 1;
         out->op.ld = k_major_ok ? src.s_mn : src.s_k;
         out->bs = bs;
@@ -268,18 +266,13 @@ int prepare_operand(DeviceState* st, const Operand& src, int64_t mn, int64_t k,
     int64_t nbatch = 1;
     for (int i = 0; i < ps.nb; ++i) nbatch *= ps.bshape[i];
     const size_t bytes = (size_t)nbatch * ps.rows * ld * sizeof(float);
-    void *hi = nullptr, *lo = nullptr;
-    int rc = ws_get(st, is_a ? WS_A_HI : WS_B_HI, bytes, &hi);
+    void* packed = nullptr;
+    int rc = ws_get(st, is_a ? WS_A_PACK : WS_B_PACK, bytes, &packed);
     if (rc != AKR_OK) return rc;
-    if (split) {
-        rc = ws_get(st, is_a ? WS_A_LO : WS_B_LO, bytes, &lo);
-        if (rc != AKR_OK) return rc;
-    }
-    cudaError_t e = launch_pack_split(ps, (float*)hi, (float*)lo, ld, stream);
-    if (e != cudaSuccess) return cuda_fail(e, "pack/split launch");
+    cudaError_t e = launch_pack(ps, (float*)packed, ld, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "pack launch");
     st->launches++;
-    out->op.ptr = (const float*)hi;
-    out->op.lo = (const float*)lo;
+    out->op.ptr = (const float*)packed;
     out->op.mn_major = keep_mn ? 1 : 0;
     out->op.ld = ld;
     out->bs.assign(nd, 0);
@@ -313,24 +306,10 @@ int run_problem(const Problem& p, cudaStream_t stream) {
     for (const Dim& d : all)
         if (d.e > 0x7fffffff) return fail(AKR_ERR_INVALID, "matmul: batch extent exceeds 2^31-1");
 
-    // fp32-accurate mode: the kernel derives the low parts of its operands in shared memory, which
-    // costs shared-memory bandwidth. Large compute-bound products are faster when hi / lo are split
-    // once up front (an extra HBM pass over the operands) and both fetched by TMA.
-    bool split = false;
-    if (p.mode == AKR_MODE_FP32 && redd.empty() && outd.size() <= 2) {
-        GemmDesc shape;
-        shape.M = (int)p.M;
-        shape.N = (int)p.N;
-        shape.K = (int)p.K;
-        shape.terms = 3;
-        if (outd.size() >= 1) shape.o1 = (int)outd.back().e;
-        if (outd.size() == 2) shape.o0 = (int)outd[0].e;
-        split = gemm_sm100_presplit_pays(shape);
-    }
     Prepared A, B;
-    rc = prepare_operand(st, p.A, p.M, p.K, all, true, split, stream, &A);
+    rc = prepare_operand(st, p.A, p.M, p.K, all, true, stream, &A);
     if (rc != AKR_OK) return rc;
-    rc = prepare_operand(st, p.B, p.N, p.K, all, false, split, stream, &B);
+    rc = prepare_operand(st, p.B, p.N, p.K, all, false, stream, &B);
     if (rc != AKR_OK) return rc;
 
     int* status = nullptr;
@@ -430,8 +409,6 @@ int run_problem(const Problem& p, cudaStream_t stream) {
             GemmDesc gi = g;
             gi.A.ptr = g.A.ptr + ao + ar;
             gi.B.ptr = g.B.ptr + bo + br;
-            if (g.A.lo) gi.A.lo = g.A.lo + ao + ar;
-            if (g.B.lo) gi.B.lo = g.B.lo + bo + br;
             gi.C = p.C + co;
             gi.accumulate = ir > 0 ? 1 : 0;
             // bias and the second epilogue operand apply once, to the complete sum: on the last launch

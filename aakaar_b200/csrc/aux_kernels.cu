@@ -54,17 +54,9 @@ int grid_for(size_t n, int per_thread = 4) {
     return (int)blocks;
 }
 
-// Round-to-nearest (ties away from zero) to 10 explicit mantissa bits; the value stays an fp32.
-__device__ __forceinline__ float to_tf32_rna(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
-}
-
 struct PackArgs {
     const float* src;
-    float* hi;
-    float* lo;
+    float* dst;
     int nb;
     int64_t bshape[kMaxDims];
     int64_t bstride[kMaxDims];
@@ -73,7 +65,7 @@ struct PackArgs {
     int64_t total;  // batch * rows * ld
 };
 
-__global__ void pack_split_kernel(const PackArgs a) {
+__global__ void pack_kernel(const PackArgs a) {
     dep_sync();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.total; i += stride) {
@@ -91,48 +83,10 @@ __global__ void pack_split_kernel(const PackArgs a) {
             }
             v = __ldg(a.src + off);
         }
-        if (a.lo != nullptr) {
-            const float h = to_tf32_rna(v);
-            a.hi[i] = h;
-            a.lo[i] = v - h;
-        } else {
-            a.hi[i] = v;
-        }
+        a.dst[i] = v;
     }
 }
 
-// Contiguous-source fast path of the split: no index decode, four independent 16-byte loads in
-// flight per thread before the first use (the pass is HBM-bound; memory-level parallelism decides).
-__device__ __forceinline__ void split4(const float4 v, float4& h, float4& l) {
-    h.x = to_tf32_rna(v.x); l.x = v.x - h.x;
-    h.y = to_tf32_rna(v.y); l.y = v.y - h.y;
-    h.z = to_tf32_rna(v.z); l.z = v.z - h.z;
-    h.w = to_tf32_rna(v.w); l.w = v.w - h.w;
-}
-
-__global__ void split_vec4_kernel(const float4* __restrict__ src, float4* __restrict__ hi,
-                                  float4* __restrict__ lo, int64_t n4) {
-    dep_sync();
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < n4; i += 4 * stride) {
-        float4 v[4], h, l;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = __ldcs(src + i + u * stride);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            split4(v[u], h, l);
-            hi[i + u * stride] = h;
-            lo[i + u * stride] = l;
-        }
-    }
-    for (; i < n4; i += stride) {
-        float4 h, l;
-        split4(__ldcs(src + i), h, l);
-        hi[i] = h;
-        lo[i] = l;
-    }
-}
 
 constexpr int ST = 16;  // SIMT reference GEMM tile
 
@@ -563,32 +517,14 @@ __global__ void sgd_kernel(float* __restrict__ p, const float* __restrict__ grad
 
 }  // namespace
 
-cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t ld, cudaStream_t s) {
+cudaError_t launch_pack(const PackSrc& src, float* dst, int64_t ld, cudaStream_t s) {
     int64_t batch = 1;
     for (int d = 0; d < src.nb; ++d) batch *= src.bshape[d];
     const int64_t total = batch * src.rows * ld;
     if (total == 0) return cudaSuccess;
-    // Dense source with the same leading dimension: plain vectorised split.
-    bool dense = lo != nullptr && src.col_stride == 1 && src.row_stride == ld && ld == src.cols &&
-                 (ld & 3) == 0 && ((uintptr_t)src.ptr & 15u) == 0;
-    if (dense) {
-        int64_t expect = src.rows * ld;
-        for (int d = src.nb - 1; d >= 0 && dense; --d) {
-            if (src.bshape[d] != 1 && src.bstride[d] != expect) dense = false;
-            expect *= src.bshape[d];
-        }
-    }
-    if (dense) {
-        const int64_t n4 = total / 4;
-        launch_dep(split_vec4_kernel, grid_for((size_t)n4, 2), kThreads, s, 
-            reinterpret_cast<const float4*>(src.ptr), reinterpret_cast<float4*>(hi),
-            reinterpret_cast<float4*>(lo), n4);
-        return cudaGetLastError();
-    }
     PackArgs a;
     a.src = src.ptr;
-    a.hi = hi;
-    a.lo = lo;
+    a.dst = dst;
     a.nb = src.nb;
     for (int d = 0; d < kMaxDims; ++d) {
         a.bshape[d] = d < src.nb ? src.bshape[d] : 1;
@@ -600,7 +536,7 @@ cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t 
     a.row_stride = src.row_stride;
     a.col_stride = src.col_stride;
     a.total = total;
-    launch_dep(pack_split_kernel, grid_for((size_t)total, 2), kThreads, s, a);
+    launch_dep(pack_kernel, grid_for((size_t)total, 2), kThreads, s, a);
     return cudaGetLastError();
 }
 

@@ -1,4 +1,4 @@
-// Bandwidth-bound helper kernels around the GEMM: operand packing / TF32 splitting, a plain-FMA
+// Bandwidth-bound helper kernels around the GEMM: operand packing, a plain-FMA
 // reference matmul, and the elementwise / reduction ops of the Linear training step.
 #pragma once
 #include <cstddef>
@@ -19,10 +19,9 @@ struct PackSrc {
     int64_t row_stride, col_stride;
 };
 
-// Gathers `src` into dense [batch][rows][ld] arrays. hi receives the value rounded to TF32
-// (round-to-nearest, ties away) when `lo` is given, else the value itself; lo receives value - hi.
-// Padding columns [cols, ld) are zeroed.
-cudaError_t launch_pack_split(const PackSrc& src, float* hi, float* lo, int64_t ld, cudaStream_t s);
+// Gathers `src` into a dense [batch][rows][ld] array (a view TMA cannot read in place). Padding columns
+// [cols, ld) are zeroed.
+cudaError_t launch_pack(const PackSrc& src, float* dst, int64_t ld, cudaStream_t s);
 
 struct SimtGemm {
     const float *A, *B;

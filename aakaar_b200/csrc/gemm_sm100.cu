@@ -13,8 +13,8 @@
 // Operand layouts: each operand may be K-major or M/N-major in global memory; the tile is staged
 // the way it lies and the UMMA descriptors carry the major-ness, so transposed views need no copy.
 // TF32 mode issues one MMA per 8-deep k-slice; 3xTF32 mode issues three (lo*hi, hi*lo, hi*hi), the
-// low parts either derived in shared memory by two converter warps or, for large compute-bound
-// products, split once up front and fetched by TMA; both give fp32-level accuracy.
+// low parts derived in shared memory by two converter warps (the tensor core truncates fp32 operands to TF32, so the
+// raw tile is the high part): fp32-level accuracy with operands still read in place.
 #include "gemm_sm100.h"
 #include "sm100_ptx.cuh"
 
@@ -49,8 +49,6 @@ struct KernelParams {
     CUtensorMap tmA, tmB;
     CUtensorMap tmC;           // output map for the TMA-store epilogue (valid when c_tma != 0)
     int c_tma;                 // 1: epilogue stores through TMA (aligned output, no accumulate, no split)
-    CUtensorMap tmAlo, tmBlo;  // pre-split low parts (fp32-accurate mode of large products)
-    int presplit;              // 1: low parts come from tmAlo / tmBlo, 0: derived in shared memory
     float* C;
     const float* bias;
     // Second epilogue operand, an array of the output's shape with its own strides (aux_op != 0):
@@ -375,12 +373,19 @@ __device__ __forceinline__ void store_block_tma_warp(float (&v)[32], float4* my_
 // (64-byte swizzle), used by the fp32-accurate mode to have four finer stages in flight instead of
 // two coarse ones (its stages carry hi and lo parts and are twice as large per k).
 // Staging tiles per slab of the general kernel: two when shared memory has room for them.
-template <int BN, int TERMS, int STAGES, int BKT>
+template <int BN, int TERMS, int STAGES, int BKT, int LO = 0>
 struct EpiBufs {
     static constexpr int value =
-        (TERMS == 1 && STAGES * SmemLayout<BN, TERMS, BKT>::STAGE_BYTES + 2 * slabs_of(BN) * 4 * EPI_STAGE_BYTES + 2048 <= 232448)
+        ((STAGES + LO) * SmemLayout<BN, TERMS, BKT>::STAGE_BYTES + 2 * slabs_of(BN) * 4 * EPI_STAGE_BYTES + 2048 <= 232448)
             ? 2
             : 1;
+};
+// Instantiations for short, write-heavy contractions (few stages, two staging sets): every epilogue warp sends
+// its own 32-row boxes, without a barrier between warps.
+template <int BN, int TERMS, int STAGES, int BKT, int LO>
+struct WarpStore {
+    static constexpr bool value = EpiBufs<BN, TERMS, STAGES, BKT, LO>::value == 2 && BN == 256 &&
+                                  ((TERMS == 1 && STAGES == 3) || (TERMS == 3 && STAGES == 4));
 };
 
 // LO: slots of the low-part ring (fp32-accurate mode; 0 in TF32 mode).
@@ -406,7 +411,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     // [stages][epilogue staging: one 16 KB tile per 128-column slab (two where they fit: the TMA-store
     // epilogue then alternates between them), 1024-byte aligned][barriers]
     // [raw stages][low-part slots][epilogue staging ...][barriers]
-    constexpr int EPI_BUFS = EpiBufs<BN, TERMS, STAGES, BKT>::value;
+    constexpr int EPI_BUFS = EpiBufs<BN, TERMS, STAGES, BKT, LO>::value;
     constexpr int EPI_BYTES = EPI_BUFS * SLABS * 4 * EPI_STAGE_BYTES;
     constexpr int TILE_BYTES = (STAGES + LO) * L::STAGE_BYTES;
     constexpr int LO_BASE = STAGES * L::STAGE_BYTES;
@@ -707,7 +712,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         constexpr int EPI_ALT = SLABS * 4 * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
         int epi_buf = 0;                                           // which set the next TMA-store block uses
         // three-stage instantiation (short, write-heavy contractions): every warp sends its own 32-row boxes
-        constexpr bool WARP_STORE = EPI_BUFS == 2 && STAGES == 3;
+        constexpr bool WARP_STORE = WarpStore<BN, TERMS, STAGES, BKT, LO>::value;
         const uint32_t my_stage_addr = smem_base + TILE_BYTES + (slab * 4 + q) * EPI_STAGE_BYTES;
         const bool use_tma = p.c_tma != 0 && !split_mode;  // kernel-uniform
         int handoff = 0;
@@ -795,7 +800,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ACC_N > 1 ? ch * 32 + j : 0];
-                        if (use_tma) {
+                        if (use_tma && WARP_STORE) {
+                            store_block_tma_warp(f, my_stage + epi_buf * (EPI_ALT / 16), my_stage_addr + epi_buf * EPI_ALT,
+                                                 &p.tmC, col0, row0, c.i1, c.i0, p.N, bias, lane);
+                            epi_buf ^= 1;
+                        } else if (use_tma) {
                             store_block_tma<EPI_BUFS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
                                                       &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane, q == 0 && lane == 0,
                                                       2 + slab);
@@ -898,7 +907,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 
     // the threads that issued bulk stores wait for them before the CTA winds down
     if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && lane == 0 &&
-        ((EpiBufs<BN, TERMS, STAGES, BKT>::value == 2 && STAGES == 3) || (hw_warp & 3) == 0))
+        (WarpStore<BN, TERMS, STAGES, BKT, LO>::value || (hw_warp & 3) == 0))
         ptx::bulk_wait_all();
 
     // ------------------------------------------------------------ teardown (all paths)
@@ -1176,11 +1185,18 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
 //   leader = cluster rank 0: issues the MMAs and owns the barriers the pair synchronises on.
 //   per CTA: warp 0 TMA producer (local barriers), warp 1 MMA (leader) + TMEM, warps 2..9 epilogue
 //   with fp32 promotion of 64-deep chains, warps 10..11 low-part converters that also tell the leader
-//   when this CTA's stage is ready.
-constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 16, PAIR_STAGES = 6, PAIR_KC = 4;
+//   when this CTA's low parts are written (the peer with a relaxed arrive on the leader's barrier: its
+//   payload never crosses the cluster through memory - each CTA's tensor core reads its own tiles, made
+//   visible to it by the converter's fence.proxy.async - and an arrive with release semantics at cluster
+//   scope cost several microseconds per k-block).
+constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 16, PAIR_KC = 4;
 constexpr int PAIR_A_BYTES = 128 * PAIR_BK * 4, PAIR_B_BYTES = 128 * PAIR_BK * 4;
 constexpr int PAIR_RAW_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
-constexpr int PAIR_STAGE_BYTES = 2 * PAIR_RAW_BYTES;  // raw (high parts) + low parts
+// The tiles are laid out as PAIR_RAW_STAGES raw stages followed by PAIR_LO_SLOTS low-part slots (16 KB each): a
+// low-part tile only lives from its conversion to the end of its MMAs. Six slots, not fewer: a slot's round trip
+// crosses the cluster twice (the peer's "written" arrive, the leader's commit back) and takes several microseconds.
+constexpr int PAIR_RAW_STAGES = 6, PAIR_LO_SLOTS = 6;
+constexpr int PAIR_BAR_BYTES = 512;  // 32 mbarriers + TMEM slot + flags
 constexpr int PAIR_THREADS = 64 + 256 + 64;
 constexpr int PAIR_EPI_WARPS = 8, PAIR_CONV_WARPS = 2;
 
@@ -1192,18 +1208,23 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    constexpr int S = PAIR_STAGES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * PAIR_STAGE_BYTES);
-    const uint32_t bar_base = smem_base + S * PAIR_STAGE_BYTES;
-    auto landed_bar = [&](int s) { return bar_base + 8u * s; };          // local: this CTA's TMA tiles arrived
-    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };     // local: stage may be refilled
-    auto ready_bar = [&](int s) { return bar_base + 8u * (2 * S + s); }; // leader: both CTAs' stage complete
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };   // local: accumulator chain done
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };  // leader: both epilogues drained
-    auto done_bar = [&](int s) { return bar_base + 8u * (3 * S + 4 + s); };   // peer: its stage is complete (local)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * S + 4);
+    constexpr int S = PAIR_RAW_STAGES;   // raw stages
+    constexpr int LS = PAIR_LO_SLOTS;    // low-part slots
+    constexpr int TILE_BYTES = (S + LS) * PAIR_RAW_BYTES;
+    constexpr int LO_BASE = S * PAIR_RAW_BYTES;
+    constexpr int stage_bytes = PAIR_RAW_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TILE_BYTES);
+    const uint32_t bar_base = smem_base + TILE_BYTES;
+    auto landed_bar = [&](int s) { return bar_base + 8u * s; };            // local: this CTA's TMA tiles arrived (0..7)
+    auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };       // local: stage may be refilled (8..15)
+    // leader: the low parts of both CTAs are written, per low-part slot (16..21)
+    auto ready_bar = [&](int s) { return bar_base + 8u * (16 + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (22 + b); };      // local: accumulator chain done
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (24 + b); };     // leader: both epilogues drained
+    auto lofree_bar = [&](int l) { return bar_base + 8u * (26 + l); };     // local: low-part slot may be rewritten (26..31)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* epi_stage_base = smem + S * PAIR_STAGE_BYTES + 256;
+    uint8_t* epi_stage_base = smem + TILE_BYTES + PAIR_BAR_BYTES;
 
     // Roles by hardware warp: 0..7 epilogue, 8 producer, 9 MMA, 10..11 converters, so that the two epilogue
     // warpgroups can take the registers the third one gives back. `warp` is the role index used below
@@ -1217,14 +1238,13 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     const int num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
+        for (int s = 0; s < 8; ++s) {
             ptx::mbar_init(landed_bar(s), 1);
             ptx::mbar_init(empty_bar(s), 1);
-            // in-kernel low parts: leader's converter warps + the peer's relay; pre-split operands: the
-            // leader's expect-tx arrive, completed by the TMA bytes of both CTAs
-            ptx::mbar_init(ready_bar(s), p.presplit ? 1 : PAIR_CONV_WARPS + 1);
-            ptx::mbar_init(done_bar(s), PAIR_CONV_WARPS);
         }
+        // the converter warps of both CTAs arrive here (the peer's directly on the leader's barrier)
+        for (int s = 0; s < 6; ++s) ptx::mbar_init(ready_bar(s), 2 * PAIR_CONV_WARPS);
+        for (int l = 0; l < LS; ++l) ptx::mbar_init(lofree_bar(l), 1);
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(tfull_bar(b), 1);
             ptx::mbar_init(tempty_bar(b), 2 * PAIR_EPI_WARPS);
@@ -1248,7 +1268,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
     const int total_iters = p.red * p.nkb;
-    const bool presplit = p.presplit != 0;
     const int kc = (AKR_DIAG(p.debug, 64)) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
 
     // 128 promotion accumulators per epilogue thread do not fit the uniform 168 registers of a 12-warp CTA (they
@@ -1285,46 +1304,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         }
                         continue;
                     }
-                    const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                    const uint32_t sa = smem_base + stage * stage_bytes;
                     const uint32_t sb = sa + PAIR_A_BYTES;
-                    if (presplit) {
-                        // hi and lo tiles of both CTAs land on the LEADER's ready barrier: no relay hop
-                        const uint32_t lb = ptx::map_to_cta(ready_bar(stage), 0);
-                        if (leader) ptx::mbar_arrive_expect_tx(ready_bar(stage), 2 * PAIR_STAGE_BYTES);
-                        const int bcv[4] = {c.i1, c.i0, r, 0};
-                        const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
-                        const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-                        for (int term = 0; term < 2; ++term) {
-                            const CUtensorMap* ma = term ? &p.tmAlo : &p.tmA;
-                            const CUtensorMap* mb = term ? &p.tmBlo : &p.tmB;
-                            const uint32_t da = sa + term * PAIR_RAW_BYTES;
-                            const uint32_t db = sb + term * PAIR_RAW_BYTES;
-                            if (MAJA == 0) {
-                                ptx::tma_load_5d_pair(da, ma, lb, k0, m_row0, a0, a1, a2);
-                            } else if (p.a_fold) {
-                                ptx::tma_load_5d_pair(da, ma, lb, 0, k0, m_row0 / CHUNK, a0, a1);
-                            } else {
-#pragma unroll
-                                for (int ch = 0; ch < 128 / CHUNK; ++ch)
-                                    ptx::tma_load_5d_pair(da + ch * (PAIR_BK * 128), ma, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
-                            }
-                            if (MAJB == 0) {
-                                ptx::tma_load_5d_pair(db, mb, lb, k0, n_col0, b0, b1, b2);
-                            } else if (p.b_fold) {
-                                ptx::tma_load_5d_pair(db, mb, lb, 0, k0, n_col0 / CHUNK, b0, b1);
-                            } else {
-#pragma unroll
-                                for (int ch = 0; ch < 128 / CHUNK; ++ch)
-                                    ptx::tma_load_5d_pair(db + ch * (PAIR_BK * 128), mb, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
-                            }
-                        }
-                        ++issued;
-                        if (++stage == S) {
-                            stage = 0;
-                            phase ^= 1u;
-                        }
-                        continue;
-                    }
                     ptx::mbar_arrive_expect_tx(fb, PAIR_RAW_BYTES);
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
@@ -1360,11 +1341,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                     }
                 }
             }
-            if ((!ok || *abort_flag) && presplit) {
-                const uint64_t t0 = ptx::globaltimer_ns();  // let copies in flight land (they signal the leader)
-                while (ptx::globaltimer_ns() - t0 < 200000ull) {
-                }
-            } else if (!ok || *abort_flag) {
+            if (!ok || *abort_flag) {
                 int s2 = stage;
                 uint32_t ph = phase;
                 const int n = issued < S ? (int)issued : S;
@@ -1382,26 +1359,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && !leader && !presplit) {
-            // Peer CTA: this otherwise idle thread tells the leader when a stage of this CTA is complete.
-            // The cross-CTA arrive is slow; keeping it off the converter warps keeps their loop short.
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
-                for (int it = 0; it < total_iters; ++it) {
-                    if (!ptx::mbar_wait(done_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
-                        ok = false;
-                        break;
-                    }
-                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
-                    if (++stage == S) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                }
-            }
-        }
         if (lane == 0 && leader) {
             constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
             constexpr uint32_t K_SBO = 8 * PAIR_BK * 4;
@@ -1409,8 +1366,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
             constexpr uint32_t a_lbo = MAJA == 0 ? 16 : PAIR_BK * 128, b_lbo = MAJB == 0 ? 16 : PAIR_BK * 128;
             constexpr uint32_t a_sbo = MAJA == 0 ? K_SBO : 512, b_sbo = MAJB == 0 ? K_SBO : 512;
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, slot = 0;
+            uint32_t phase = 0, slot_phase = 0;
             int handoff = 0;
             bool ok = true;
             for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
@@ -1425,21 +1382,23 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                     ptx::tc_fence_after();
                     const uint32_t d_tmem = tmem_base + buf * PAIR_BN;
                     for (int it = cs; it < ce; ++it) {
-                        if (!ptx::mbar_wait(ready_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
+                        if (!ptx::mbar_wait(ready_bar(slot), slot_phase, abort_flag, p.wait_limit_ns)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
-                        const uint32_t sa = smem_base + stage * PAIR_STAGE_BYTES;
+                        const uint32_t sa = smem_base + stage * stage_bytes;
                         const uint32_t sb = sa + PAIR_A_BYTES;
+                        const uint32_t sa_lo = smem_base + LO_BASE + slot * PAIR_RAW_BYTES;
+                        const uint32_t sb_lo = sa_lo + PAIR_A_BYTES;
 #pragma unroll
                         for (int k8 = 0; k8 < PAIR_BK / UMMA_K; ++k8) {
                             const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
                             const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
                             const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
-                            const uint64_t da_lo = ptx::smem_desc(sa + PAIR_RAW_BYTES + a_off, a_lbo, a_sbo, a_lay);
-                            const uint64_t db_lo = ptx::smem_desc(sb + PAIR_RAW_BYTES + b_off, b_lbo, b_sbo, b_lay);
+                            const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
                             if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
                                 if (first == 0u) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
@@ -1455,6 +1414,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                             stage = 0;
                             phase ^= 1u;
                         }
+                        ptx::mma_commit_pair(lofree_bar(slot));  // and rewrite this low-part slot
+                        if (++slot == LS) {
+                            slot = 0;
+                            slot_phase ^= 1u;
+                        }
                     }
                     if (ok) {  // this chain's accumulator is complete in both CTAs' tensor memory
                         ptx::mma_commit_pair(tfull_bar(buf));
@@ -1464,21 +1428,23 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             }
         }
     } else if (warp >= 2 + PAIR_EPI_WARPS) {
-        // ------------------------------------------------------------ low-part converter / stage relay
+        // ------------------------------------------------------------ low-part converter
         const int ct = (warp - 2 - PAIR_EPI_WARPS) * 32 + lane;
-        int stage = 0;
-        uint32_t phase = 0;
+        int stage = 0, slot = 0;
+        uint32_t phase = 0, slot_phase = 0;
         bool ok = true;
-        // pre-split operands arrive complete by TMA on the leader's barrier: nothing to do here
-        for (int t = pair_id; t < p.total_tiles && ok && !presplit; t += num_pairs) {
+        const uint32_t leader_ready0 = ptx::map_to_cta(ready_bar(0), 0);  // the leader's ready barriers, seen from here
+        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
             for (int it = 0; it < total_iters; ++it) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(landed_bar(stage), phase, abort_flag, p.wait_limit_ns))) {
+                // the raw tiles have landed, and the MMAs that read this low-part slot last have finished
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(landed_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
+                    !__all_sync(0xffffffffu, ptx::mbar_wait(lofree_bar(slot), slot_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
                 {
-                    const float4* src = reinterpret_cast<const float4*>(smem + stage * PAIR_STAGE_BYTES);
-                    float4* dst = reinterpret_cast<float4*>(smem + stage * PAIR_STAGE_BYTES + PAIR_RAW_BYTES);
+                    const float4* src = reinterpret_cast<const float4*>(smem + stage * PAIR_RAW_BYTES);
+                    float4* dst = reinterpret_cast<float4*>(smem + LO_BASE + slot * PAIR_RAW_BYTES);
                     constexpr int PER_THREAD = PAIR_RAW_BYTES / 16 / (PAIR_CONV_WARPS * 32);
                     constexpr int BATCH = 8;
                     static_assert(PER_THREAD % BATCH == 0, "converter work must divide evenly");
@@ -1499,11 +1465,18 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                     ptx::fence_proxy_async_smem();
                 }
                 __syncwarp();
-                // cheap local arrive; the peer's stage is announced to the leader by its relay thread
-                if (lane == 0) ptx::mbar_arrive(leader ? ready_bar(stage) : done_bar(stage));
+                // both CTAs' converter warps arrive on the LEADER's barrier of this slot (a remote arrive for the peer)
+                if (lane == 0) {
+                    if (leader) ptx::mbar_arrive(ready_bar(slot));
+                    else ptx::mbar_arrive_cluster_relaxed(leader_ready0 + 8u * slot);
+                }
                 if (++stage == S) {
                     stage = 0;
                     phase ^= 1u;
+                }
+                if (++slot == LS) {
+                    slot = 0;
+                    slot_phase ^= 1u;
                 }
             }
         }
@@ -2028,7 +2001,7 @@ template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT, in
 int launch_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     using L = SmemLayout<BN, TERMS, BKT>;
     constexpr int smem = (STAGES + LO) * L::STAGE_BYTES + 1024 + BAR_BYTES +
-                         EpiBufs<BN, TERMS, STAGES, BKT>::value * slabs_of(BN) * 4 * EPI_STAGE_BYTES;
+                         EpiBufs<BN, TERMS, STAGES, BKT, LO>::value * slabs_of(BN) * 4 * EPI_STAGE_BYTES;
     static_assert(smem <= 232448, "more shared memory than one CTA may have");
     auto kern = gemm_tf32_kernel<BN, MAJA, MAJB, TERMS, STAGES, KC, BKT, LO>;
     static bool attr_done_dev[kMaxDev] = {};  // per instantiation and device
@@ -2089,7 +2062,7 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
 template <bool DUO, int MAJA, int MAJB>
 int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     constexpr int smem = DUO ? DUO_SMEM
-                             : PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
+                             : (PAIR_RAW_STAGES + PAIR_LO_SLOTS) * PAIR_RAW_BYTES + 1024 + PAIR_BAR_BYTES + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
     constexpr int threads = DUO ? DUO_THREADS : PAIR_THREADS;
     auto kern = DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>;
     static bool attr_done_dev[kMaxDev] = {};
@@ -2137,18 +2110,18 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
     return 0;
 }
 
-// CTA pairs serve the fp32-accurate mode of large products whose operands were split up front: there
-// both CTAs' tiles land on the leader's barrier by TMA and the pair runs 4.07 ms against 4.34 ms for
-// one CTA per tile at 8192^3. With in-kernel low parts the pair is still slower (5.3 ms against 4.9 ms:
-// the peer's "stage ready" has to be relayed to the leader, which puts about 5 us into the round trip
-// of a stage while shared memory holds about 3 us of look-ahead), so that combination is opt-in
-// (debug bit 5).
+// CTA pairs serve the fp32-accurate mode wherever 256 x 256 tiles fill a good part of the machine and the
+// contraction is long enough to amortise the pair's hand-shakes: each CTA reads only half of B per MMA and converts
+// only its own share, which is what this shared-memory-bound mode needs (2560^3: 0.253 -> 0.183 ms, 4096 x 1024 x
+// 4096: 0.185 -> 0.147 ms, 64 x (512 x 512 x 2048): 0.369 -> 0.312 ms against one CTA per 128 x 256 tile). Short
+// contractions stay with the general kernel (K = 256 equal, K = 128 8 % slower on pairs). Debug bit 5 routes every
+// eligible shape here.
 bool use_pairs(const GemmDesc& g) {
     if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
-    const bool presplit = g.A.lo != nullptr && g.B.lo != nullptr;
-    if (!presplit && !(g.debug & 32)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
-    return tiles * 4 >= gemm_sm100_num_ctas();
+    if (tiles * 4 < gemm_sm100_num_ctas()) return false;
+    const long long iters = (long long)g.red * ((g.K + PAIR_BK - 1) / PAIR_BK);
+    return iters >= 20 || (g.debug & 32);
 }
 
 // TF32 mode on CTA pairs: long contractions whose 256 x 256 tiles give most pairs one tile but do not
@@ -2229,26 +2202,12 @@ int gemm_sm100_num_ctas() {
 
 bool gemm_sm100_operand_ok(const GemmOperand& op, int mn, int k, const int batch[3]) {
     if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0) return false;
-    if (op.lo && (reinterpret_cast<uintptr_t>(op.lo) & 15u) != 0) return false;
     const int other = op.mn_major ? k : mn;
     if (other > 1 && (op.ld <= 0 || (op.ld & 3) != 0)) return false;
     for (int i = 0; i < 3; ++i) {
         if (batch[i] > 1 && op.bs[i] != 0 && ((op.bs[i] & 3) != 0 || op.bs[i] < 0)) return false;
     }
     return true;
-}
-
-// Large compute-bound fp32-accurate products run fastest with their operands split into high and low parts
-// up front (an extra pass over the operands) and both fetched by TMA; only the CTA-pair kernel reads such
-// operands, so the shapes are the ones that kernel takes.
-bool gemm_sm100_presplit_pays(const GemmDesc& g) {
-    if (g.terms != 3) return false;
-    const double flop = 2.0 * (double)g.M * (double)g.N * (double)g.K;
-    const double bytes = 4.0 * ((double)g.M * g.K + (double)g.K * g.N + (double)g.M * g.N);
-    if (flop / bytes < 512.0) return false;
-    if (g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug | g_debug_flags, 512)) return false;
-    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
-    return tiles * 4 >= gemm_sm100_num_ctas();
 }
 
 int gemm_sm100_pick_splits(const GemmDesc& g) {
@@ -2314,26 +2273,18 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     std::memset(&kp, 0, sizeof(kp));
     MapPlan pa = plan_map(g.A, g.M, batch, !AKR_DIAG(g.debug, 4));
     MapPlan pb = plan_map(g.B, g.N, batch, !AKR_DIAG(g.debug, 4));
-    const bool presplit = g.terms == 3 && g.A.lo != nullptr && g.B.lo != nullptr;
-    if (presplit && !pairs) {
-        seterr(err, errlen, "gemm_sm100: pre-split operands are read by the CTA-pair kernel only (see gemm_sm100_presplit_pays)");
-        return -1;
-    }
-    auto build = [&](CUtensorMap* hi, CUtensorMap* lo, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
-        bool ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
+    auto build = [&](CUtensorMap* map, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
+        bool ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, bk);
         if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
             mp.fold = false;
-            ok = make_map(hi, op.ptr, op, mp, mn, g.K, tile, bk);
+            ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, bk);
         }
-        if (ok && presplit) ok = make_map(lo, op.lo, op, mp, mn, g.K, tile, bk);
         return ok;
     };
-    if (!build(&kp.tmA, &kp.tmAlo, g.A, pa, g.M, pairs ? 128 : bm) ||
-        !build(&kp.tmB, &kp.tmBlo, g.B, pb, g.N, pairs ? 128 : bn)) {
+    if (!build(&kp.tmA, g.A, pa, g.M, pairs ? 128 : bm) || !build(&kp.tmB, g.B, pb, g.N, pairs ? 128 : bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
-    kp.presplit = presplit ? 1 : 0;
     kp.a_fold = pa.fold ? 1 : 0;
     kp.b_fold = pb.fold ? 1 : 0;
     for (int i = 0; i < 3; ++i) {
@@ -2387,7 +2338,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         cuuint64_t strides[3] = {ldc_b, (cuuint64_t)(g.o1 > 1 ? g.c_bs1 * 4 : (long long)ldc_b),
                                  (cuuint64_t)(g.o0 > 1 ? g.c_bs0 * 4 : (long long)ldc_b)};
         // the three-stage instantiation for short contractions sends one box per warp (32 rows)
-        const bool warp_boxes = g.terms == 1 && !big && !pairs && bn == 256 && (long long)g.red * ((g.K + bk - 1) / bk) <= 8;
+        const bool warp_boxes = !big && !pairs && bn == 256 && (long long)g.red * ((g.K + bk - 1) / bk) <= 8;
         cuuint32_t box[4] = {32u, warp_boxes ? 32u : 128u, 1u, 1u};
         cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
         if (enc && enc(&kp.tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, g.C, dims, strides, box, estr,
@@ -2443,9 +2394,13 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     int rc;
     if (g.terms == 3) {
         // raw stages x 24 / 16 / 12 KB in flight from HBM + a short ring of low-part tiles
-        rc = bn == 256 ? launch_major<256, 3, 6, 4, 16, 2>(g, kp, grid, stream, err, errlen)
-             : bn == 128 ? launch_major<128, 3, 10, 4, 16, 3>(g, kp, grid, stream, err, errlen)
-                         : launch_major<64, 3, 12, 4, 16, 3>(g, kp, grid, stream, err, errlen);
+        // A low-part slot is busy from its conversion until its MMAs have finished and the commit has arrived:
+        // the narrower the tile, the shorter that work and the more slots it takes to cover the hand-over latency.
+        const bool short_k = (long long)kp.red * kp.nkb <= 8 && kp.splits == 1;
+        rc = bn == 256 ? (short_k ? launch_major<256, 3, 4, 4, 16, 2>(g, kp, grid, stream, err, errlen)
+                                  : launch_major<256, 3, 5, 4, 16, 3>(g, kp, grid, stream, err, errlen))
+             : bn == 128 ? launch_major<128, 3, 8, 4, 16, 4>(g, kp, grid, stream, err, errlen)
+                         : launch_major<64, 3, 12, 4, 16, 4>(g, kp, grid, stream, err, errlen);
     } else if (bn == 64) {
         rc = launch_major<64, 1, 8, 0, 32>(g, kp, grid, stream, err, errlen);
     } else {

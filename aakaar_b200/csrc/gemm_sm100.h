@@ -15,7 +15,6 @@ namespace akr {
 
 struct GemmOperand {
     const float* ptr = nullptr;  // first element of the view
-    const float* lo = nullptr;   // optional pre-split low parts (same geometry); then ptr holds the high parts
     int mn_major = 0;            // 1: the M (for A) / N (for B) index is unit stride; 0: K is
     int64_t ld = 0;              // element stride of the other matrix dim
     int64_t bs[3] = {0, 0, 0};   // element strides along o0, o1, r (0 = broadcast)
@@ -39,8 +38,7 @@ struct GemmDesc {
     // Optional by-product: column sums of the stored output per 32-row block, `colpart` = [o0 * o1 * ceil(M / 32)][N]
     // floats (every entry is written). TF32 mode without a split contraction only.
     float* colpart = nullptr;
-    int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate). With terms == 3 the low parts are
-                                  // derived in the kernel unless BOTH operands carry pre-split `lo` arrays
+    int terms = 1;                // 1 = TF32, 3 = 3xTF32 (fp32-accurate; the low parts are derived in the kernel)
     // Split of the contraction across CTAs (weight gradients with few output tiles):
     // splits > 1 writes fp32 partials to `partials` ([splits][o0*o1][M][N]); they are added up in split
     // order (deterministic) by a second, GPU-wide kernel launched right behind the GEMM - or, when the
@@ -81,9 +79,5 @@ void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* 
 
 // Picks a split factor for `g` (1 when the output already fills the GPU).
 int gemm_sm100_pick_splits(const GemmDesc& g);
-
-// True when an fp32-accurate product of this shape (M, N, K, o0, o1, terms set; operands not needed) should be
-// given pre-split operands (GemmOperand::lo): large compute-bound products that the CTA-pair kernel takes.
-bool gemm_sm100_presplit_pays(const GemmDesc& g);
 
 }  // namespace akr

@@ -793,6 +793,8 @@ def run_config(args):
 
     out = {"config": args.config, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
     results = {}
+    both_modes = [(n, m) for n, m in (("tf32", cabi.MODE_TF32), ("fp32_3xtf32", cabi.MODE_FP32))
+                  if args.only_mode in ("", n.split("_")[0])]
     if args.config == "c3":
         base = cabi.DeviceArray.from_numpy(uniform((64, 8, 64, 512), 301))
         B = cabi.DeviceArray.from_numpy(uniform((1, 8, 64, 512), 302))
@@ -801,15 +803,16 @@ def run_config(args):
         Cd, DAd, DBd = cabi.DeviceArray((64, 8, 512, 512)), cabi.DeviceArray((64, 8, 512, 64)), cabi.DeviceArray((1, 8, 64, 512))
         bytes_step = 1731 * 2 ** 20           # each operand read once, each result written once (fwd + dA + dB)
         flop_step = 3 * 2 * 64 * 8 * 512 * 64 * 512
-        for name, mode in (("tf32", cabi.MODE_TF32), ("fp32_3xtf32", cabi.MODE_FP32)):
+        for name, mode in both_modes:
             def step(mode=mode):
                 cabi.matmul_fwd(A, B, mode=mode, out=Cd)
                 cabi.matmul_bwd(A, B, DC, mode=mode, da=DAd, db=DBd)
             ms, launches = timed(step, args.steps, args.warmup)
             parts = {}
-            for pname, fn in (("fwd", lambda m=mode: cabi.matmul_fwd(A, B, mode=m, out=Cd)),
-                              ("dA", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_db=False, da=DAd)),
-                              ("dB", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_da=False, db=DBd))):
+            for pname, fn in (() if args.only_mode else
+                              (("fwd", lambda m=mode: cabi.matmul_fwd(A, B, mode=m, out=Cd)),
+                               ("dA", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_db=False, da=DAd)),
+                               ("dB", lambda m=mode: cabi.matmul_bwd(A, B, DC, mode=m, need_da=False, db=DBd)))):
                 parts[pname] = timed(fn, args.steps, 2)[0]
             results[name] = {"ms_per_step": ms, "gbs": bytes_step / ms / 1e6, "tflops": flop_step / ms / 1e9,
                              "frac_of_hbm": bytes_step / ms / 1e6 / peaks["hbm_gbs"], "gpu_launches_per_step": launches / args.steps,
@@ -828,7 +831,7 @@ def run_config(args):
         Cd, DAd, DBd = cabi.DeviceArray((nb, 256, 256)), cabi.DeviceArray((nb, 256, 256)), cabi.DeviceArray((nb, 256, 256))
         bytes_step = 9 * total * 256 * 256 * 4     # whole job: 3 GEMMs x (2 operands + 1 result)
         flop_step = 3 * 2 * total * 256 ** 3
-        for name, mode in (("tf32", cabi.MODE_TF32), ("fp32_3xtf32", cabi.MODE_FP32)):
+        for name, mode in both_modes:
             def step(mode=mode):
                 cabi.matmul_fwd(A, B, mode=mode, out=Cd)
                 cabi.matmul_bwd(A, B, DC, mode=mode, da=DAd, db=DBd)
@@ -875,8 +878,9 @@ def run_config(args):
         flop_step = 5 * 2 * 4096 * 1024 * 4096
         # *_unfused: the tanh node's backward as its own elementwise pass (the reference's graph);
         # default: folded into the epilogue of the second layer's dA product
-        for name, tf32, fused in (("tf32", True, True), ("fp32_3xtf32", False, True),
-                                  ("tf32_unfused", True, False), ("fp32_3xtf32_unfused", False, False)):
+        for name, tf32, fused in [c for c in (("tf32", True, True), ("fp32_3xtf32", False, True),
+                                              ("tf32_unfused", True, False), ("fp32_3xtf32_unfused", False, False))
+                                  if not args.only_mode or (c[0] == {"tf32": "tf32", "fp32": "fp32_3xtf32"}[args.only_mode])]:
             ak.set_tf32(tf32)
             ak._C._set_backward_fusion(fused)
             np.random.seed(203)
@@ -918,6 +922,8 @@ def main():
     ap.add_argument("--size", type=int, default=8192, help="square size (profiling only; the benchmark is 8192)")
     ap.add_argument("--profile", default="", choices=["", "tf32", "fp32"],
                     help="profiler capture run: one device phase only, warm-up not forced to 3")
+    ap.add_argument("--only-mode", default="", choices=["", "tf32", "fp32"],
+                    help="secondary configurations: run one arithmetic mode only (profiler captures)")
     ap.add_argument("--_cpu-child", dest="cpu_child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if not args.profile:

@@ -242,8 +242,8 @@ AKR_API int akr_event_destroy(void* event);
  *    1  the GEMM kernels skip their TMA loads and multiply whatever shared memory holds: times the
  *       tcgen05.mma issue rate alone (the measured tensor-pipe ceiling a benchmark divides by); results invalid
  *   16  the load warp never signals its stages, so that every waiter gives up (failure-path test)
- *   32  fp32-accurate products run on the CTA-pair (cta_group::2) kernel even with in-kernel low parts
- *       (by default only large pre-split products use it)
+ *   32  fp32-accurate products run on the CTA-pair (cta_group::2) kernel wherever its tiles apply
+ *       (by default contractions of at least 320 and enough 256 x 256 tiles to fill a quarter of the GPU)
  * 2048  TF32 products run on the CTA-pair kernel wherever it applies (by default a band of shapes)
  * akr_debug_configure(0, 0) restores normal operation. Further timing switches exist only in builds
  * compiled with -DAKR_B200_DIAG. */

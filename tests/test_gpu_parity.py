@@ -353,7 +353,7 @@ def test_config5a_full_batch(mode, tol):
 
 def test_largest_benchmark_square_16384_sampled_rows():
     # the largest size of the benchmark sweep (16384^3, 1 GiB per matrix): sampled rows of C, dA and dB against
-    # float64, TF32 mode and the fp32-accurate mode (the latter splits its operands up front at this size)
+    # float64, TF32 mode and the fp32-accurate mode (CTA pairs, low parts derived in the kernel)
     n = 16384
     g = np.random.Generator(np.random.PCG64(404))
     s = np.float32(1.0 / np.sqrt(n))
@@ -474,7 +474,8 @@ def test_bounded_wait_abort_is_reported_and_recoverable():
 
 
 def test_experimental_cta_pair_kernel_parity():
-    # The opt-in cta_group::2 kernel of the fp32-accurate mode (two CTAs share one 256 x 256 tile).
+    # The cta_group::2 kernel of the fp32-accurate mode (two CTAs share one 256 x 256 tile), forced onto shapes
+    # below its default threshold (short contraction) and on its default territory.
     lib = cabi.lib()
     a, b = uniform((1500, 200), 71), uniform((200, 1700), 72)
     bias = normal((1, 1700), 73)
@@ -487,8 +488,7 @@ def test_experimental_cta_pair_kernel_parity():
         at, bt = dev(np.ascontiguousarray(a.T)), dev(np.ascontiguousarray(b.T))
         c = cabi.matmul_fwd(at.transpose(0, 1), bt.transpose(0, 1), mode=MODE_FP32).to_numpy()
         assert rel_fro(c, ref) < TOL_FP32
-        # large compute-bound product: operands are split up front and both CTAs' tiles land on the
-        # leader's barrier directly
+        # a large compute-bound product (the kernel's default territory): 256 pair tiles, 256 k-blocks
         n = 4096
         s_ = 1.0 / np.sqrt(n)
         a2, b2 = normal((n, n), 401, s_), normal((n, n), 402, s_)
