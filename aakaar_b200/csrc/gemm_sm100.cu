@@ -1185,10 +1185,9 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
 //   leader = cluster rank 0: issues the MMAs and owns the barriers the pair synchronises on.
 //   per CTA: warp 0 TMA producer (local barriers), warp 1 MMA (leader) + TMEM, warps 2..9 epilogue
 //   with fp32 promotion of 64-deep chains, warps 10..11 low-part converters that also tell the leader
-//   when this CTA's low parts are written (the peer with a relaxed arrive on the leader's barrier: its
-//   payload never crosses the cluster through memory - each CTA's tensor core reads its own tiles, made
-//   visible to it by the converter's fence.proxy.async - and an arrive with release semantics at cluster
-//   scope cost several microseconds per k-block).
+//   when this CTA's low parts are written (the peer with an arrive on the leader's barrier whose release is
+//   CTA-scoped: its payload never crosses the cluster through memory - each CTA's tensor core reads its own
+//   tiles, made visible to it by the converter's fence.proxy.async).
 constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 16, PAIR_KC = 4;
 constexpr int PAIR_A_BYTES = 128 * PAIR_BK * 4, PAIR_B_BYTES = 128 * PAIR_BK * 4;
 constexpr int PAIR_RAW_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
@@ -1468,7 +1467,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                 // both CTAs' converter warps arrive on the LEADER's barrier of this slot (a remote arrive for the peer)
                 if (lane == 0) {
                     if (leader) ptx::mbar_arrive(ready_bar(slot));
-                    else ptx::mbar_arrive_cluster_relaxed(leader_ready0 + 8u * slot);
+                    else ptx::mbar_arrive_cluster(leader_ready0 + 8u * slot);
                 }
                 if (++stage == S) {
                     stage = 0;

@@ -262,14 +262,13 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap
         "r"(c4)
         : "memory");
 }
-// Arrive on an mbarrier given by its shared::cluster address (own or peer CTA).
+// Arrive on an mbarrier given by its shared::cluster address (own or peer CTA). Release semantics at CTA scope
+// (the instruction's default): what such a signal orders - tensor-memory reads finished, a CTA's own shared-memory
+// tiles written for its own tensor core - never travels through memory to the other CTA. The same arrive with
+// release at CLUSTER scope cost several microseconds per signal (measured: 2.6 against 1.6 ms on 8192 batched
+// 256^3 products when the converter warps of a CTA pair signalled the leader that way).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// The same without release semantics: for a signal whose payload the receiver does not read through memory (the
-// sender made its own shared-memory writes visible to its own tensor core with fence.proxy.async beforehand).
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
