@@ -77,6 +77,11 @@ def load():
         "akr_mse_fwd": [fp, fp, fp, sz, vp],
         "akr_mse_bwd": [fp, fp, fp, fp, sz, vp],
         "akr_sgd_step": [fp, fp, fp, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, sz, vp],
+        "akr_sgd_step_multi": [C.c_int, C.POINTER(fp), C.POINTER(fp), C.POINTER(fp), C.POINTER(sz), C.POINTER(C.c_int),
+                               C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int, vp],
+        "akr_scatter": [fp, V, vp],
+        "akr_im2col_3d": [fp, fp, vp, vp],
+        "akr_col2im_3d": [fp, fp, vp, vp],
         "akr_set_tf32": [C.c_int],
         "akr_set_cudnn_tf32": [C.c_int],
         "akr_set_device": [C.c_int],

@@ -1302,4 +1302,34 @@ AKR_API int akr_sgd_step(float* param, const float* grad, float* velocity, float
                "sgd launch");
 }
 
+AKR_API int akr_sgd_step_multi(int count, float* const* params, const float* const* grads, float* const* velocities,
+                               const size_t* sizes, const int* velocity_initialized, float lr, float momentum,
+                               float weight_decay, float dampening, int nesterov, int has_momentum, void* stream) {
+    if (count < 0 || (count > 0 && (!params || !grads || !sizes)))
+        return fail(AKR_ERR_INVALID, "sgd_step_multi: null argument");
+    if (has_momentum && !velocities) return fail(AKR_ERR_INVALID, "sgd_step_multi: momentum needs velocity buffers");
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    for (int first = 0; first < count; first += kSgdMultiMax) {   // 48 tensors per launch
+        SgdMulti m;
+        m.count = std::min(kSgdMultiMax, count - first);
+        for (int i = 0; i < m.count; ++i) {
+            const int j = first + i;
+            if (!params[j] || !grads[j] || (has_momentum && !velocities[j]))
+                return fail(AKR_ERR_INVALID, "sgd_step_multi: null tensor");
+            m.param[i] = params[j];
+            m.grad[i] = grads[j];
+            m.vel[i] = has_momentum ? velocities[j] : nullptr;
+            m.n[i] = sizes[j];
+            m.vel_init[i] = velocity_initialized ? velocity_initialized[j] : 0;
+        }
+        cudaError_t e = launch_sgd_multi(m, lr, momentum, weight_decay, dampening, nesterov, has_momentum,
+                                         (cudaStream_t)stream);
+        if (e != cudaSuccess) return cuda_fail(e, "sgd launch");
+        st->launches++;
+    }
+    return AKR_OK;
+}
+
 }  // extern "C"

@@ -379,6 +379,48 @@ __global__ void sgd_plain_vec_kernel(float4* __restrict__ p, const float4* __res
         p[i] = w;
     }
 }
+// The update of several parameter tensors in ONE launch (an optimizer step over a model's parameter list): the
+// tensors are cut into chunks of 4096 elements, blocks stride over the chunks of all of them.
+__global__ void sgd_multi_kernel(const SgdMulti m, float lr, float momentum, float wd, float dampening, int nesterov,
+                                 int has_momentum) {
+    dep_sync();
+    constexpr int CHUNK = 4096;
+    for (long long c = blockIdx.x; c < m.total_chunks; c += gridDim.x) {
+        int t = 0;
+        while (t + 1 < m.count && c >= m.chunk_start[t + 1]) ++t;
+        const size_t n = m.n[t];
+        const size_t base = (size_t)(c - m.chunk_start[t]) * CHUNK;
+        float* __restrict__ p = m.param[t];
+        const float* __restrict__ g = m.grad[t];
+        float* __restrict__ v = m.vel[t];
+        const int vel_init = m.vel_init[t];
+        const size_t end = base + CHUNK < n ? base + CHUNK : n;
+        const bool vec = (n & 3) == 0 && (((uintptr_t)p | (uintptr_t)g | (uintptr_t)v) & 15u) == 0;
+        if (vec && !has_momentum) {
+            for (size_t i = base / 4 + threadIdx.x; i < end / 4; i += blockDim.x) {
+                float4 w = reinterpret_cast<float4*>(p)[i];
+                float4 gg = reinterpret_cast<const float4*>(g)[i];
+                if (wd != 0.0f) {
+                    gg.x += w.x * wd; gg.y += w.y * wd; gg.z += w.z * wd; gg.w += w.w * wd;
+                }
+                w.x -= gg.x * lr; w.y -= gg.y * lr; w.z -= gg.z * lr; w.w -= gg.w * lr;
+                reinterpret_cast<float4*>(p)[i] = w;
+            }
+        } else {
+            for (size_t i = base + threadIdx.x; i < end; i += blockDim.x) {
+                float gg = g[i];
+                if (wd != 0.0f) gg += p[i] * wd;
+                float update = gg;
+                if (has_momentum) {
+                    const float vv = vel_init ? (v[i] * momentum + gg * (1.0f - dampening)) : gg;
+                    v[i] = vv;
+                    update = nesterov ? (gg + vv * momentum) : vv;
+                }
+                p[i] = p[i] - update * lr;
+            }
+        }
+    }
+}
 __global__ void tanh_bwd_kernel(const float* __restrict__ g, const float* __restrict__ y,
                                 float* __restrict__ dx, size_t n) {
     dep_sync();
@@ -1019,6 +1061,21 @@ cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float mom
     }
     launch_dep(sgd_kernel, grid_for(n), kThreads, s, p, g, vel, lr, momentum, wd, dampening, nesterov,
                                                  has_momentum, vel_init, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sgd_multi(SgdMulti& m, float lr, float momentum, float wd, float dampening, int nesterov,
+                             int has_momentum, cudaStream_t s) {
+    long long chunks = 0;
+    for (int t = 0; t < m.count; ++t) {
+        m.chunk_start[t] = chunks;
+        chunks += (long long)((m.n[t] + 4095) / 4096);
+    }
+    m.total_chunks = chunks;
+    if (chunks == 0) return cudaSuccess;
+    const long long cap = (long long)grid_for((size_t)chunks * 4096, 4);
+    launch_dep(sgd_multi_kernel, (unsigned)(chunks < cap ? chunks : cap), kThreads, s, m, lr, momentum, wd, dampening,
+               nesterov, has_momentum);
     return cudaGetLastError();
 }
 

@@ -106,4 +106,20 @@ cudaError_t launch_sgd(float* p, const float* g, float* vel, float lr, float mom
                        float dampening, int nesterov, int has_momentum, int vel_init, size_t n,
                        cudaStream_t s);
 
+// The same update for up to kSgdMultiMax tensors in one launch (chunk_start / total_chunks are filled in by the
+// launcher).
+constexpr int kSgdMultiMax = 48;
+struct SgdMulti {
+    int count = 0;
+    float* param[kSgdMultiMax];
+    const float* grad[kSgdMultiMax];
+    float* vel[kSgdMultiMax];       // null without momentum
+    size_t n[kSgdMultiMax];
+    int vel_init[kSgdMultiMax];
+    long long chunk_start[kSgdMultiMax];
+    long long total_chunks = 0;
+};
+cudaError_t launch_sgd_multi(SgdMulti& m, float lr, float momentum, float wd, float dampening, int nesterov,
+                             int has_momentum, cudaStream_t s);
+
 }  // namespace akr

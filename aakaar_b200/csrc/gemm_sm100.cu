@@ -80,7 +80,7 @@ struct Tile {
     int split, batch, i0, i1, m0, n0;
 };
 
-__device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn, int bm = BM) {
+__device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn, int bm = BM, int group_m = GROUP_M) {
     Tile c;
     c.split = t % p.splits;
     t /= p.splits;
@@ -89,10 +89,10 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     const int r = t - c.batch * per_batch;
     c.i0 = c.batch / p.o1;
     c.i1 = c.batch - c.i0 * p.o1;
-    const int group_sz = GROUP_M * p.nt;
+    const int group_sz = group_m * p.nt;
     const int g = r / group_sz;
-    const int first_m = g * GROUP_M;
-    const int gm = min(p.mt - first_m, GROUP_M);
+    const int first_m = g * group_m;
+    const int gm = min(p.mt - first_m, group_m);
     const int in = r - g * group_sz;
     const int n_t = in / gm;
     const int m_t = first_m + (in - n_t * gm);
@@ -662,8 +662,8 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             for (int it = it0; it < it1; ++it) {
                 // the raw tiles have landed, and the MMAs that read this low-part slot last have finished
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
-                    !__all_sync(0xffffffffu, ptx::mbar_wait(lofree_bar(lo_slot), lo_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_warp(full_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
+                    !__all_sync(0xffffffffu, ptx::mbar_wait_warp(lofree_bar(lo_slot), lo_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
@@ -744,7 +744,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             for (int cs = it0; cs < it1 && ok; cs = (it1 - cs > CHUNK_ITERS) ? cs + CHUNK_ITERS : it1) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
-                bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
+                bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
                 // the slab-wide TMA-store path synchronises the four warps of a slab: they must leave together
                 if (use_tma && !WARP_STORE) got = ptx::named_barrier_and(2 + slab, 128, got);
                 if (!got) {
@@ -922,6 +922,26 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 }
 
 
+#ifdef AKR_B200_DIAG
+// Diagnostic builds: SM cycles and nanoseconds one thread of every CTA spent inside the kernel (debug bit 15),
+// i.e. the SM clock the kernel really ran at.
+__device__ unsigned long long g_diag_clk[2 * 256];
+#define AKR_DIAG_CLK_BEGIN                                                        \
+    unsigned long long diag_c0 = 0, diag_t0 = 0;                                  \
+    if ((p.debug & 32768) && threadIdx.x == 0) {                                  \
+        diag_c0 = clock64();                                                      \
+        diag_t0 = ptx::globaltimer_ns();                                          \
+    }
+#define AKR_DIAG_CLK_END                                                          \
+    if ((p.debug & 32768) && threadIdx.x == 0 && blockIdx.x < 256) {              \
+        g_diag_clk[2 * blockIdx.x] = clock64() - diag_c0;                         \
+        g_diag_clk[2 * blockIdx.x + 1] = ptx::globaltimer_ns() - diag_t0;         \
+    }
+#else
+#define AKR_DIAG_CLK_BEGIN
+#define AKR_DIAG_CLK_END
+#endif
+
 // ---------------------------------------------------------------------------------- 256 x 256 tiles
 // TF32 kernel for large products: one CTA computes a 256 x 256 tile as two 128 x 256 accumulators
 // that share the B tile in shared memory. Per flop it pulls one third fewer bytes from L2 than the
@@ -929,14 +949,20 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 // Both accumulators fill all 512 TMEM columns, so a tile's MMAs may only start on an accumulator
 // once the epilogue has drained it: one short stall per tile, amortised over a long contraction.
 // No split-K and no fp32 promotion here; those stay with the general kernel.
-constexpr int BIG_BM = 256, BIG_BN = 256, BIG_STAGES = 3;
-constexpr int BIG_A_BYTES = BIG_BM * BK * 4, BIG_B_BYTES = BIG_BN * BK * 4;
-constexpr int BIG_STAGE_BYTES = BIG_A_BYTES + BIG_B_BYTES;
+// BKT = fp32 per k-block: 192 KB of load stages either way, as 3 x 64 KB (BKT = 32, the shipped form) or 6 x 32 KB
+// (BKT = 16, diagnostic builds: twice as many stage hand-overs made 8192^3 16 % slower, 1.60 against 1.38 ms).
+constexpr int BIG_BM = 256, BIG_BN = 256;
+constexpr int BIG_RING_BYTES = 192 * 1024;
 constexpr int BIG_THREADS = 64 + 256;
+constexpr int BIG_SMEM = BIG_RING_BYTES + 1024 + 256 + 8 * EPI_STAGE_BYTES;
 
-template <int MAJA, int MAJB>
+template <int MAJA, int MAJB, int BKT>
 __global__ void __launch_bounds__(BIG_THREADS, 1)
 gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
+    constexpr int BIG_A_BYTES = BIG_BM * BKT * 4, BIG_B_BYTES = BIG_BN * BKT * 4;
+    constexpr int BIG_STAGE_BYTES = BIG_A_BYTES + BIG_B_BYTES;
+    constexpr int BIG_STAGES = BIG_RING_BYTES / BIG_STAGE_BYTES;
+    static_assert((2 * BIG_STAGES + 3) * 8 + 8 <= 256, "barrier area");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -980,6 +1006,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
+    AKR_DIAG_CLK_BEGIN
     const int total_iters = p.red * p.nkb;
 
     if (warp == 0) {
@@ -993,7 +1020,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                 const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
                 for (int it = 0; it < total_iters; ++it) {
                     const int r = it / p.nkb;
-                    const int k0 = (it - r * p.nkb) * BK;
+                    const int k0 = (it - r * p.nkb) * BKT;
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
@@ -1022,7 +1049,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                     } else {
 #pragma unroll
                         for (int ch = 0; ch < BIG_BM / CHUNK; ++ch)
-                            ptx::tma_load_5d(da + ch * (BK * 128), &p.tmA, fb, c.m0 + ch * CHUNK, k0, a0, a1, a2);
+                            ptx::tma_load_5d(da + ch * (BKT * 128), &p.tmA, fb, c.m0 + ch * CHUNK, k0, a0, a1, a2);
                     }
                     if (MAJB == 0) {
                         ptx::tma_load_5d(db, &p.tmB, fb, k0, c.n0, b0, b1, b2);
@@ -1031,7 +1058,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                     } else {
 #pragma unroll
                         for (int ch = 0; ch < BIG_BN / CHUNK; ++ch)
-                            ptx::tma_load_5d(db + ch * (BK * 128), &p.tmB, fb, c.n0 + ch * CHUNK, k0, b0, b1, b2);
+                            ptx::tma_load_5d(db + ch * (BKT * 128), &p.tmB, fb, c.n0 + ch * CHUNK, k0, b0, b1, b2);
                     }
                     ++issued;
                     if (++stage == BIG_STAGES) {
@@ -1061,10 +1088,12 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BIG_BN, MAJA, MAJB);
-            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
-            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
-            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : BK * 128, b_lbo = MAJB == 0 ? 16 : BK * 128;
-            constexpr uint32_t a_sbo = MAJA == 0 ? 1024 : 512, b_sbo = MAJB == 0 ? 1024 : 512;
+            // K-major rows are BKT * 4 bytes (128- or 64-byte swizzle), 8 rows per group
+            constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
+            constexpr uint32_t a_lay = MAJA == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : BKT * 128, b_lbo = MAJB == 0 ? 16 : BKT * 128;
+            constexpr uint32_t a_sbo = MAJA == 0 ? 8 * BKT * 4 : 512, b_sbo = MAJB == 0 ? 8 * BKT * 4 : 512;
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
@@ -1090,14 +1119,18 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                             ptx::tc_fence_after();
                         }
                         // rows h*128.. of the A tile: 128 rows x 128 B (K-major) or 4 chunks x 4 KB
-                        const uint32_t sa_h = sa + h * (BM * BK * 4);
+                        const uint32_t sa_h = sa + h * (BM * BKT * 4);
                         const uint32_t d_tmem = tmem_base + h * BIG_BN;
 #pragma unroll
-                        for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                        for (int k8 = 0; k8 < BKT / UMMA_K; ++k8) {
                             const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
                             const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
                             const uint64_t da = ptx::smem_desc(sa_h + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                            if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
+                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 0u);
+                                continue;
+                            }
                             ptx::mma_tf32_ss(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
                         }
                     }
@@ -1124,7 +1157,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
             const Epi epi = tile_epi(p, c);
-            bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
+            bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
             if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
             if (!got) {
                 ok = false;
@@ -1172,6 +1205,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<512>(tmem_base);
     }
+    AKR_DIAG_CLK_END
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
@@ -1436,8 +1470,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
             for (int it = 0; it < total_iters; ++it) {
                 // the raw tiles have landed, and the MMAs that read this low-part slot last have finished
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(landed_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
-                    !__all_sync(0xffffffffu, ptx::mbar_wait(lofree_bar(slot), slot_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_warp(landed_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
+                    !__all_sync(0xffffffffu, ptx::mbar_wait_warp(lofree_bar(slot), slot_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
@@ -1500,7 +1534,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             for (int cs = 0; cs < total_iters && ok; cs = (total_iters - cs > kc) ? cs + kc : total_iters) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
                     ok = false;
                     break;
                 }
@@ -1599,7 +1633,9 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SM; ++s) {
-            ptx::mbar_init(ready_bar(s), 1);  // the leader's expect-tx arrive, completed by both CTAs' bytes
+            // the leader's expect-tx arrive, completed by both CTAs' bytes (MMA-only timing: one arrive per CTA instead,
+            // so that the peer's producer still cannot be lapped)
+            ptx::mbar_init(ready_bar(s), (p.debug & 1) ? 2 : 1);
             ptx::mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -1647,7 +1683,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                     if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
                     const uint32_t lb = ptx::map_to_cta(ready_bar(stage), 0);
                     if (p.debug & 1) {  // timing experiment: no loads, stale shared memory
-                        if (leader) ptx::mbar_arrive(ready_bar(stage));
+                        ptx::mbar_arrive_cluster(lb);
                         if (++stage == S) {
                             stage = 0;
                             phase ^= 1u;
@@ -1755,7 +1791,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
             const Epi epi = tile_epi(p, c);
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1u;
-            bool got = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
+            bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
             if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
             if (!got) {
                 ok = false;
@@ -1804,6 +1840,275 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc_pair<512>(tmem_base);
     }
+    if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
+}
+
+// ---------------------------------------------------------------------------------- 512 x 256 tiles on CTA pairs
+// Large TF32 products are limited by the rate at which operand tiles reach shared memory, not by the
+// MMA pipe. Here a CTA pair computes a 512 x 256 tile: each CTA holds 256 rows of A (two 128-row halves)
+// and 128 columns of B per k-block, and the pair's MMAs (M = 256: one 128-row half from each CTA) fill
+// both of its 128 x 256 accumulators from the same B tile. Per flop that is a quarter fewer bytes into
+// shared memory than a 256 x 256 tile on one CTA (384 operand rows per k-block for 256 x 256 outputs
+// instead of 512), and each MMA reads only half of B in each CTA. Like the single-CTA 256 x 256 kernel
+// it fills all 512 TMEM columns: a tile's MMAs start on an accumulator once the epilogue has drained it.
+//   both CTAs: warp 0 loads its own tiles, completion bytes counted on the LEADER's barrier
+//   (cp.async.bulk.tensor ... .cta_group::2, one destination CTA per copy, no multicast);
+//   leader: warp 1 issues the MMAs; tcgen05.commit signals both CTAs; warps 2..9 of each CTA drain its 256 rows.
+constexpr int QUAD_BM = 512, QUAD_BN = 256;
+constexpr int QUAD_RING_BYTES = 192 * 1024;  // 4 stages of 48 KB (32-deep k-blocks) or 8 of 24 KB (16-deep)
+constexpr int QUAD_THREADS = 64 + 256;
+constexpr int QUAD_EPI_WARPS = 8;
+constexpr int QUAD_SMEM = QUAD_RING_BYTES + QUAD_EPI_WARPS * EPI_STAGE_BYTES + 256 + 1024;
+
+template <int MAJA, int MAJB, int BKT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(QUAD_THREADS, 1)
+gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
+    constexpr int QUAD_A_BYTES = 256 * BKT * 4, QUAD_B_BYTES = 128 * BKT * 4;
+    constexpr int QUAD_STAGE_BYTES = QUAD_A_BYTES + QUAD_B_BYTES;
+    constexpr int QUAD_STAGES = QUAD_RING_BYTES / QUAD_STAGE_BYTES;
+    static_assert((2 * QUAD_STAGES + 3) * 8 + 8 <= 256, "barrier area");
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t* smem = smem_raw + pad;
+    const uint32_t smem_base = raw_addr + pad;
+    constexpr int S = QUAD_STAGES;
+    constexpr int EPI_BYTES = QUAD_EPI_WARPS * EPI_STAGE_BYTES;
+    // [4 stages][staging area][barriers]
+    uint8_t* epi_stage_base = smem + S * QUAD_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * QUAD_STAGE_BYTES + EPI_BYTES);
+    const uint32_t bar_base = smem_base + S * QUAD_STAGE_BYTES + EPI_BYTES;
+    auto ready_bar = [&](int s) { return bar_base + 8u * s; };                 // leader: both CTAs' tiles landed
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };           // local: stage may be refilled
+    const uint32_t tfull_bar = bar_base + 8u * (2 * S);                        // local: both accumulators complete
+    auto tempty_bar = [&](int h) { return bar_base + 8u * (2 * S + 1 + h); };  // leader: both CTAs drained half h
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 3);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            // the leader's expect-tx arrive, completed by both CTAs' bytes (MMA-only timing: one arrive per CTA instead,
+            // so that the peer's producer still cannot be lapped)
+            ptx::mbar_init(ready_bar(s), (p.debug & 1) ? 2 : 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(tfull_bar, 1);
+        ptx::mbar_init(tempty_bar(0), 2 * QUAD_EPI_WARPS);
+        ptx::mbar_init(tempty_bar(1), 2 * QUAD_EPI_WARPS);
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+        if (p.c_tma) ptx::prefetch_tensormap(&p.tmC);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair<512>(ptx::smem_u32(tmem_slot));
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    ptx::grid_dep_launch();
+    ptx::grid_dep_wait();
+    AKR_DIAG_CLK_BEGIN
+    const int total_iters = p.red * p.nkb;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (own tiles, leader's barrier)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
+                const Tile c = decode_tile(t, p, QUAD_BN, QUAD_BM, 8);
+                const int m_row0 = c.m0 + 256 * (int)rank;  // this CTA's rows of A
+                const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
+                for (int it = 0; it < total_iters; ++it) {
+                    const int r = it / p.nkb;
+                    const int k0 = (it - r * p.nkb) * BKT;
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    if (p.debug & 16) continue;  // test hook: nothing ever arrives, every waiter must give up
+                    const uint32_t lb = ptx::map_to_cta(ready_bar(stage), 0);
+                    if (p.debug & 1) {  // timing experiment: no loads, stale shared memory
+                        ptx::mbar_arrive_cluster(lb);
+                        if (++stage == S) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
+                    if (leader) ptx::mbar_arrive_expect_tx(ready_bar(stage), 2 * QUAD_STAGE_BYTES);
+                    const uint32_t da = smem_base + stage * QUAD_STAGE_BYTES;
+                    const uint32_t db = da + QUAD_A_BYTES;
+                    const int bcv[4] = {c.i1, c.i0, r, 0};
+                    const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
+                    const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
+                    if (MAJA == 0) {
+                        ptx::tma_load_5d_pair(da, &p.tmA, lb, k0, m_row0, a0, a1, a2);
+                    } else if (p.a_fold) {
+                        ptx::tma_load_5d_pair(da, &p.tmA, lb, 0, k0, m_row0 / CHUNK, a0, a1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 256 / CHUNK; ++ch)
+                            ptx::tma_load_5d_pair(da + ch * (BKT * 128), &p.tmA, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
+                    }
+                    if (MAJB == 0) {
+                        ptx::tma_load_5d_pair(db, &p.tmB, lb, k0, n_col0, b0, b1, b2);
+                    } else if (p.b_fold) {
+                        ptx::tma_load_5d_pair(db, &p.tmB, lb, 0, k0, n_col0 / CHUNK, b0, b1);
+                    } else {
+#pragma unroll
+                        for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                            ptx::tma_load_5d_pair(db + ch * (BKT * 128), &p.tmB, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                    }
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok || *abort_flag) {
+                const uint64_t t0 = ptx::globaltimer_ns();  // let copies in flight land (they signal the leader)
+                while (ptx::globaltimer_ns() - t0 < 200000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t IDESC = ptx::idesc_tf32(256, QUAD_BN, MAJA, MAJB);
+            constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
+            constexpr uint32_t a_lay = MAJA == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t a_lbo = MAJA == 0 ? 16 : BKT * 128, b_lbo = MAJB == 0 ? 16 : BKT * 128;
+            constexpr uint32_t a_sbo = MAJA == 0 ? 8 * BKT * 4 : 512, b_sbo = MAJB == 0 ? 8 * BKT * 4 : 512;
+            int stage = 0;
+            uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
+                const uint32_t tile_par = local & 1u;
+                for (int it = 0; it < total_iters && ok; ++it) {
+                    if (!ptx::mbar_wait(ready_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_base + stage * QUAD_STAGE_BYTES;
+                    const uint32_t sb = sa + QUAD_A_BYTES;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        if (it == 0) {
+                            // accumulator h must have been drained by both CTAs' epilogues of the previous tile
+                            if (!ptx::mbar_wait(tempty_bar(h), tile_par ^ 1u, abort_flag, p.wait_limit_ns)) {
+                                ok = false;
+                                break;
+                            }
+                            ptx::tc_fence_after();
+                        }
+                        // rows h*128.. of each CTA's A tile: 128 rows x 128 B (K-major) or 4 chunks x 4 KB
+                        const uint32_t sa_h = sa + h * (BM * BKT * 4);
+                        const uint32_t d_tmem = tmem_base + h * QUAD_BN;
+#pragma unroll
+                        for (int k8 = 0; k8 < BKT / UMMA_K; ++k8) {
+                            const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
+                            const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
+                            const uint64_t da = ptx::smem_desc(sa_h + a_off, a_lbo, a_sbo, a_lay);
+                            const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
+                            if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
+                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                                continue;
+                            }
+                            ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::mma_commit_pair(empty_bar(stage));  // both CTAs may refill this stage
+                    if (++stage == S) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::mma_commit_pair(tfull_bar);  // both accumulators complete in both CTAs' tensor memory
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..9): this CTA's 256 rows
+        const int q = warp & 3;
+        const int slab = (warp - 2) >> 2;
+        const bool vec = p.vec_ok != 0;
+        const bool use_tma = p.c_tma != 0;
+        float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
+        const uint32_t slab_tile_addr = smem_base + S * QUAD_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        int local = 0;
+        bool ok = true;
+        for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
+            const Tile c = decode_tile(t, p, QUAD_BN, QUAD_BM, 8);
+            const Epi epi = tile_epi(p, c);
+            bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
+            if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
+            if (!got) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            const int slab_col0 = c.n0 + slab * 128;
+            float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const int row_base = c.m0 + 256 * (int)rank + h * 128;
+                const int row0 = row_base + q * 32;
+                const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + h * QUAD_BN + slab * 128;
+                if (row_base < p.M) {  // warp-uniform: skip a half that lies below the matrix
+#pragma unroll 1
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const int col0 = slab_col0 + ch * 32;
+                        if (col0 < p.N) {
+                            __syncwarp();
+                            uint32_t v[32];
+                            ptx::tmem_ld_32x32(t_row + ch * 32, v);
+                            ptx::tmem_ld_wait();
+                            float f[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                            if (use_tma)
+                                store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
+                                                lane, q == 0 && lane == 0, 2 + slab);
+                            else
+                                store_block_warp<true>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
+                        }
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(h), 0));
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown (all paths)
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair<512>(tmem_base);
+    }
+    AKR_DIAG_CLK_END
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
@@ -2034,10 +2339,10 @@ int launch_major(const GemmDesc& g, const KernelParams& kp, int grid, cudaStream
     }
 }
 
-template <int MAJA, int MAJB>
+template <int MAJA, int MAJB, int BKT>
 int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
-    constexpr int smem = BIG_STAGES * BIG_STAGE_BYTES + 1024 + 256 + 8 * EPI_STAGE_BYTES;
-    auto kern = gemm_tf32_big_kernel<MAJA, MAJB>;
+    constexpr int smem = BIG_SMEM;
+    auto kern = gemm_tf32_big_kernel<MAJA, MAJB, BKT>;
     static bool attr_done_dev[kMaxDev] = {};
     bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
@@ -2057,13 +2362,17 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
     return 0;
 }
 
-// DUO = false: fp32-accurate pair kernel, true: TF32 pair kernel.
-template <bool DUO, int MAJA, int MAJB>
+// The three kernels on CTA pairs: the fp32-accurate one, TF32 with 256 x 256 tiles, TF32 with 512 x 256 tiles.
+enum PairKind { PAIR_FP32 = 0, PAIR_DUO = 1, PAIR_QUAD = 2 };
+template <int KIND, int MAJA, int MAJB, int BKT = BK>
 int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
-    constexpr int smem = DUO ? DUO_SMEM
+    constexpr int smem = KIND == PAIR_QUAD ? QUAD_SMEM
+                         : KIND == PAIR_DUO
+                             ? DUO_SMEM
                              : (PAIR_RAW_STAGES + PAIR_LO_SLOTS) * PAIR_RAW_BYTES + 1024 + PAIR_BAR_BYTES + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
-    constexpr int threads = DUO ? DUO_THREADS : PAIR_THREADS;
-    auto kern = DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>;
+    constexpr int threads = KIND == PAIR_QUAD ? QUAD_THREADS : (KIND == PAIR_DUO ? DUO_THREADS : PAIR_THREADS);
+    auto kern = KIND == PAIR_QUAD ? gemm_tf32_quad_kernel<MAJA, MAJB, BKT>
+                                  : (KIND == PAIR_DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>);
     static bool attr_done_dev[kMaxDev] = {};
     bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
@@ -2096,7 +2405,7 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
         }
         max_pairs = n;
 #ifdef AKR_B200_DIAG
-        if (std::getenv("AKR_B200_VERBOSE")) std::fprintf(stderr, "akr_b200: %d CTA pairs resident (%s kernel)\n", n, DUO ? "tf32 pair" : "fp32 pair");
+        if (std::getenv("AKR_B200_VERBOSE")) std::fprintf(stderr, "akr_b200: %d CTA pairs resident (%s kernel)\n", n, KIND == PAIR_QUAD ? "tf32 512x256 pair" : (KIND == PAIR_DUO ? "tf32 pair" : "fp32 pair"));
 #endif
     }
     if (grid > 2 * max_pairs) grid = 2 * max_pairs;
@@ -2146,6 +2455,15 @@ bool use_big_tiles(const GemmDesc& g) {
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + BIG_BM - 1) / BIG_BM) * ((g.N + BIG_BN - 1) / BIG_BN);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
     return tiles >= gemm_sm100_num_ctas() && iters >= 32;
+}
+
+// 512 x 256 tiles on CTA pairs wherever 256 x 256 tiles on single CTAs would be chosen and the taller tiles
+// still give every pair one: a quarter fewer operand bytes into shared memory per flop. Debug bit 13 keeps the
+// single-CTA kernel (diagnostic builds).
+bool use_quad(const GemmDesc& g) {
+    if (!use_big_tiles(g) || AKR_DIAG(g.debug, 8192)) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + QUAD_BM - 1) / QUAD_BM) * ((g.N + QUAD_BN - 1) / QUAD_BN);
+    return tiles * 2 >= gemm_sm100_num_ctas();
 }
 
 int pick_bn(const GemmDesc& g) {
@@ -2262,11 +2580,15 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     GemmDesc gd = g;
     gd.debug |= g_debug_flags;
     const bool duo = use_duo(gd);
-    const bool big = !duo && use_big_tiles(gd);
-    const bool pairs = duo || use_pairs(gd);
-    const int bn = big ? BIG_BN : (pairs ? PAIR_BN : pick_bn(g));
-    const int bm = big ? BIG_BM : (pairs ? PAIR_BM : BM);
-    const int bk = g.terms == 3 ? 16 : BK;  // finer stages for the hi+lo mode
+    const bool quad = !duo && use_quad(gd);
+    const bool big = !duo && !quad && use_big_tiles(gd);
+    const bool pairs = duo || quad || use_pairs(gd);
+    const int bn = big ? BIG_BN : (quad ? QUAD_BN : (pairs ? PAIR_BN : pick_bn(g)));
+    const int bm = big ? BIG_BM : (quad ? QUAD_BM : (pairs ? PAIR_BM : BM));
+    // 16-deep k-blocks: finer stages for the hi+lo mode. The large-tile TF32 kernels keep 32-deep ones: twice as
+    // many stage hand-overs cost them 16 % at 8192^3 (debug bit 14 selects the finer ring in diagnostic builds).
+    const bool fine = (big || quad) && AKR_DIAG(gd.debug, 16384);
+    const int bk = (g.terms == 3 || fine) ? 16 : BK;
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
@@ -2280,7 +2602,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         }
         return ok;
     };
-    if (!build(&kp.tmA, g.A, pa, g.M, pairs ? 128 : bm) || !build(&kp.tmB, g.B, pb, g.N, pairs ? 128 : bn)) {
+    // rows of A / columns of B one TMA box brings: a CTA of a pair loads its own share of the pair's tile
+    if (!build(&kp.tmA, g.A, pa, g.M, quad ? 256 : (pairs ? 128 : bm)) || !build(&kp.tmB, g.B, pb, g.N, pairs ? 128 : bn)) {
         seterr(err, errlen, "gemm_sm100: cuTensorMapEncodeTiled failed");
         return -2;
     }
@@ -2329,7 +2652,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: column sums of the output are produced by the TF32 kernels without a split contraction only");
         return -1;
     }
-    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo) && g.colpart == nullptr &&
+    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo || quad) && g.colpart == nullptr &&
         !AKR_DIAG(g.debug | g_debug_flags, 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
@@ -2366,27 +2689,51 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     if (pairs) {
         const int npairs = (int)std::min<long long>(total, ctas / 2);
         const int sel = g.A.mn_major * 2 + g.B.mn_major;
+        if (quad) {
+            switch (sel + (fine ? 4 : 0)) {
+                case 0: return launch_pair_variant<PAIR_QUAD, 0, 0, 32>(kp, 2 * npairs, stream, err, errlen);
+                case 1: return launch_pair_variant<PAIR_QUAD, 0, 1, 32>(kp, 2 * npairs, stream, err, errlen);
+                case 2: return launch_pair_variant<PAIR_QUAD, 1, 0, 32>(kp, 2 * npairs, stream, err, errlen);
+                case 3: return launch_pair_variant<PAIR_QUAD, 1, 1, 32>(kp, 2 * npairs, stream, err, errlen);
+#ifdef AKR_B200_DIAG
+                case 4: return launch_pair_variant<PAIR_QUAD, 0, 0, 16>(kp, 2 * npairs, stream, err, errlen);
+                case 5: return launch_pair_variant<PAIR_QUAD, 0, 1, 16>(kp, 2 * npairs, stream, err, errlen);
+                case 6: return launch_pair_variant<PAIR_QUAD, 1, 0, 16>(kp, 2 * npairs, stream, err, errlen);
+                default: return launch_pair_variant<PAIR_QUAD, 1, 1, 16>(kp, 2 * npairs, stream, err, errlen);
+#else
+                default: return -1;
+#endif
+            }
+        }
         if (duo) {
             switch (sel) {
-                case 0: return launch_pair_variant<true, 0, 0>(kp, 2 * npairs, stream, err, errlen);
-                case 1: return launch_pair_variant<true, 0, 1>(kp, 2 * npairs, stream, err, errlen);
-                case 2: return launch_pair_variant<true, 1, 0>(kp, 2 * npairs, stream, err, errlen);
-                default: return launch_pair_variant<true, 1, 1>(kp, 2 * npairs, stream, err, errlen);
+                case 0: return launch_pair_variant<PAIR_DUO, 0, 0>(kp, 2 * npairs, stream, err, errlen);
+                case 1: return launch_pair_variant<PAIR_DUO, 0, 1>(kp, 2 * npairs, stream, err, errlen);
+                case 2: return launch_pair_variant<PAIR_DUO, 1, 0>(kp, 2 * npairs, stream, err, errlen);
+                default: return launch_pair_variant<PAIR_DUO, 1, 1>(kp, 2 * npairs, stream, err, errlen);
             }
         }
         switch (sel) {
-            case 0: return launch_pair_variant<false, 0, 0>(kp, 2 * npairs, stream, err, errlen);
-            case 1: return launch_pair_variant<false, 0, 1>(kp, 2 * npairs, stream, err, errlen);
-            case 2: return launch_pair_variant<false, 1, 0>(kp, 2 * npairs, stream, err, errlen);
-            default: return launch_pair_variant<false, 1, 1>(kp, 2 * npairs, stream, err, errlen);
+            case 0: return launch_pair_variant<PAIR_FP32, 0, 0>(kp, 2 * npairs, stream, err, errlen);
+            case 1: return launch_pair_variant<PAIR_FP32, 0, 1>(kp, 2 * npairs, stream, err, errlen);
+            case 2: return launch_pair_variant<PAIR_FP32, 1, 0>(kp, 2 * npairs, stream, err, errlen);
+            default: return launch_pair_variant<PAIR_FP32, 1, 1>(kp, 2 * npairs, stream, err, errlen);
         }
     }
     if (big) {
-        switch (g.A.mn_major * 2 + g.B.mn_major) {
-            case 0: return launch_big_variant<0, 0>(kp, grid, stream, err, errlen);
-            case 1: return launch_big_variant<0, 1>(kp, grid, stream, err, errlen);
-            case 2: return launch_big_variant<1, 0>(kp, grid, stream, err, errlen);
-            default: return launch_big_variant<1, 1>(kp, grid, stream, err, errlen);
+        switch (g.A.mn_major * 2 + g.B.mn_major + (fine ? 4 : 0)) {
+            case 0: return launch_big_variant<0, 0, 32>(kp, grid, stream, err, errlen);
+            case 1: return launch_big_variant<0, 1, 32>(kp, grid, stream, err, errlen);
+            case 2: return launch_big_variant<1, 0, 32>(kp, grid, stream, err, errlen);
+            case 3: return launch_big_variant<1, 1, 32>(kp, grid, stream, err, errlen);
+#ifdef AKR_B200_DIAG
+            case 4: return launch_big_variant<0, 0, 16>(kp, grid, stream, err, errlen);
+            case 5: return launch_big_variant<0, 1, 16>(kp, grid, stream, err, errlen);
+            case 6: return launch_big_variant<1, 0, 16>(kp, grid, stream, err, errlen);
+            default: return launch_big_variant<1, 1, 16>(kp, grid, stream, err, errlen);
+#else
+            default: return -1;
+#endif
         }
     }
     // fp32-accurate mode: 16-deep k-blocks, chains of 4 of them (64 deep) inside the tensor core.
@@ -2447,5 +2794,24 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     }
     return 0;
 }
+
+#ifdef AKR_B200_DIAG
+extern "C" __attribute__((visibility("default"))) int akr_diag_kernel_clock(int ctas, double* mhz_mean, double* mhz_min, double* us_max) {
+    static unsigned long long h[2 * 256];
+    if (ctas > 256) ctas = 256;
+    if (cudaMemcpyFromSymbol(h, g_diag_clk, sizeof(h)) != cudaSuccess) return -1;
+    double sum = 0, mn = 1e30, um = 0;
+    for (int i = 0; i < ctas; ++i) {
+        const double mhz = h[2 * i + 1] ? 1e3 * (double)h[2 * i] / (double)h[2 * i + 1] : 0.0;
+        sum += mhz;
+        if (mhz < mn) mn = mhz;
+        if ((double)h[2 * i + 1] * 1e-3 > um) um = (double)h[2 * i + 1] * 1e-3;
+    }
+    *mhz_mean = sum / ctas;
+    *mhz_min = mn;
+    *us_max = um;
+    return 0;
+}
+#endif
 
 }  // namespace akr

@@ -556,6 +556,32 @@ void op_sgd_step(const TensorPtr& p, const TensorPtr& grad, const TensorPtr& vel
                        dampening, nesterov, has_momentum, velocity_initialized, (size_t)p->size, nullptr));
 }
 
+// SGD.step over a parameter list in one launch (contiguous float32 CUDA tensors; the caller filters).
+void op_sgd_step_multi(const std::vector<TensorPtr>& params, const std::vector<TensorPtr>& grads,
+                       const std::vector<TensorPtr>& velocities, const std::vector<int>& vel_init, float lr,
+                       float momentum, float weight_decay, float dampening, int nesterov, int has_momentum) {
+    const size_t n = params.size();
+    if (grads.size() != n || vel_init.size() != n || (has_momentum && velocities.size() != n))
+        throw std::invalid_argument("sgd_step_multi: list lengths differ");
+    std::vector<float*> pp(n), vv(n);
+    std::vector<const float*> gg(n);
+    std::vector<size_t> sz(n);
+    for (size_t i = 0; i < n; ++i) {
+        require_cuda(params[i], "sgd_step");
+        require_f32(params[i], "sgd_step");
+        require_cuda(grads[i], "sgd_step");
+        if (!params[i]->is_contiguous() || !grads[i]->is_contiguous())
+            throw std::invalid_argument("sgd_step requires contiguous tensors");
+        if (params[i]->size != grads[i]->size) throw std::invalid_argument("sgd_step: parameter and gradient sizes differ");
+        pp[i] = params[i]->data;
+        gg[i] = grads[i]->data;
+        vv[i] = has_momentum ? velocities[i]->data : nullptr;
+        sz[i] = (size_t)params[i]->size;
+    }
+    check(akr_sgd_step_multi((int)n, pp.data(), gg.data(), has_momentum ? vv.data() : nullptr, sz.data(), vel_init.data(),
+                             lr, momentum, weight_decay, dampening, nesterov, has_momentum, nullptr));
+}
+
 // ------------------------------------------------------------------ backward driver
 // tensor_backward of the reference (src/bindings.cpp:810-877): reverse topological walk, leaf
 // gradients accumulate with add, a graph can be walked once unless retain_graph is set.
@@ -1005,6 +1031,11 @@ PYBIND11_MODULE(_C, m) {
     m.def("_launch_count", [](bool reset) { return akr_launch_count(reset ? 1 : 0); }, py::arg("reset") = false);
     m.def("_mse_fused", &op_mse, py::arg("pred"), py::arg("target"));
     m.def("_sgd_step_fused", &op_sgd_step);
+    m.def("_sgd_step_multi", &op_sgd_step_multi);
+    m.def("_empty_like", [](const TensorPtr& t) {
+        require_cuda(t, "empty_like");
+        return make_cuda(t->shape);
+    }, "an uninitialised device tensor of the same shape (no launch): optimizer state that its first step overwrites");
     m.def("_set_matmul_mode", [](int mode) { g_matmul_mode_override = mode; },
           "per-process override of the arithmetic mode: -1 follow set_tf32, 0 fp32-accurate, 1 TF32");
     m.attr("HAS_CUDA") = true;

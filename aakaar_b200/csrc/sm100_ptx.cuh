@@ -46,23 +46,74 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait. Returns false when the barrier did not flip within `limit_ns`, or when another
-// role of this CTA already gave up (abort flag set); the caller then leaves its loop.
+// Bounded waits. Both return false when the barrier did not flip within `limit_ns`, or when another role of this
+// CTA already gave up (abort flag set); the caller then leaves its loop. Neither reads the clock before a few
+// hundred polls have failed, and both pause between polls:
+//  * a read of %globaltimer holds the thread for hundreds of cycles. With one such read after the first failed
+//    poll, the MMA issuer (normally a little ahead of its data) woke up late every k-block and the tensor pipe's
+//    short queue (about four MMAs) ran dry: 733 -> 575 kilocycles for two 256 x 256 x 8192 tiles without it
+//    (524 is the MMA work itself);
+//  * a poll is a shared-memory access to the barrier word the TMA unit is counting bytes on. Polling without any
+//    pause cost the CTA-pair TF32 kernel 7 % (its leader polls a barrier that both CTAs' copies complete on), and a
+//    dozen warps polling that way cost the shared-memory-bound fp32-accurate kernels 6 %.
+// mbar_wait: for the single threads on the critical path of the stage ring (MMA issuer, TMA producer): 100 ns pause.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;
     uint32_t spins = 0;
     while (true) {
+        asm volatile("nanosleep.u32 100;" ::: "memory");
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0u) {
+        if ((++spins & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+
+// mbar_wait_warp: for whole warps (epilogue warps waiting for an accumulator, converter warps waiting for a tile):
+// the pause doubles from 32 to 256 ns, short against the microseconds such a wait lasts.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint32_t ns = 32;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+        asm volatile("nanosleep.u32 %0;" ::"r"(ns) : "memory");
+        if (mbar_try_wait(bar, parity)) return true;
+        if (ns < 256) ns <<= 1;
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Non-suspending test of a barrier phase (micro-benchmarks).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
 }
 
 // ---------------------------------------------------------------- programmatic dependent launch

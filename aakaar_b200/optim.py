@@ -33,16 +33,29 @@ class SGD:
         self._velocity = [None] * len(self.parameters)
 
     def step(self):
+        """One update of every parameter that has a gradient: the contiguous ones in ONE launch
+        (the reference launches its kernel once per parameter), views through the dense-copy fallback."""
         with no_grad():
+            ps, gs, vs, inits = [], [], [], []
             for i, p in enumerate(self.parameters):
                 if p.grad is None:
                     continue
                 grad = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
                 initialized = self._velocity[i] is not None
                 if self.momentum != 0 and self._velocity[i] is None:
-                    self._velocity[i] = grad * 0.0
-                _fused_update(p, grad, self._velocity[i], self.lr, self.momentum, self.weight_decay,
-                              self.dampening, int(self.nesterov), int(self.momentum != 0), int(initialized))
+                    # the first step writes v = g without reading it (vel_init = 0): no fill needed
+                    self._velocity[i] = _C._empty_like(grad)
+                if p.is_contiguous():
+                    ps.append(p)
+                    gs.append(grad)
+                    vs.append(self._velocity[i])
+                    inits.append(int(initialized))
+                else:
+                    _fused_update(p, grad, self._velocity[i], self.lr, self.momentum, self.weight_decay,
+                                  self.dampening, int(self.nesterov), int(self.momentum != 0), int(initialized))
+            if ps:
+                _C._sgd_step_multi(ps, gs, vs if self.momentum != 0 else [], inits, self.lr, self.momentum,
+                                   self.weight_decay, self.dampening, int(self.nesterov), int(self.momentum != 0))
 
     def zero_grad(self):
         for p in self.parameters:

@@ -314,6 +314,12 @@ AKR_API int akr_mse_bwd(const float* pred, const float* target, const float* gra
 AKR_API int akr_sgd_step(float* param, const float* grad, float* velocity_or_null, float lr, float momentum,
                  float weight_decay, float dampening, int nesterov, int has_momentum,
                  int velocity_initialized, size_t n, void* stream);
+/* The same update for `count` parameter tensors in one launch (per 48 tensors): what SGD.step of the reference does
+ * with one kernel per parameter (aakaar/optim.py:24-48 -> src/optim_kernels.cu:21-55). velocities may be NULL
+ * without momentum; velocity_initialized[i] != 0 once tensor i has taken a step. */
+AKR_API int akr_sgd_step_multi(int count, float* const* params, const float* const* grads, float* const* velocities,
+                               const size_t* sizes, const int* velocity_initialized, float lr, float momentum,
+                               float weight_decay, float dampening, int nesterov, int has_momentum, void* stream);
 AKR_API int akr_fill(float* x, float value, size_t n, void* stream);
 
 #ifdef __cplusplus

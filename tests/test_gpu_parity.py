@@ -533,6 +533,44 @@ def test_tf32_cta_pair_kernel_parity():
         cabi.check(lib.akr_debug_configure(0, 0))
 
 
+def test_tf32_tall_pair_tile_kernel_parity():
+    # Large TF32 products run 512 x 256 tiles on CTA pairs (each CTA 256 rows of A and 128 columns of B per k-block,
+    # two accumulators per CTA). Shapes big enough for that routing: ragged edges in M, N and K, the four operand
+    # layouts, a last tile whose second CTA has no rows at all, batches, bias, and the backward products; sampled
+    # rows against float64.
+    rng = np.random.default_rng(91)
+    def check(bt, M, N, K, ta, tb, with_bias=False):
+        a = uniform(bt + ((K, M) if ta else (M, K)), int(rng.integers(1 << 30)))
+        b = uniform(bt + ((N, K) if tb else (K, N)), int(rng.integers(1 << 30)))
+        A, B = dev(a), dev(b)
+        nd = len(bt) + 2
+        Av = A.transpose(nd - 2, nd - 1) if ta else A
+        Bv = B.transpose(nd - 2, nd - 1) if tb else B
+        bias = normal((1, N), 92) if with_bias else None
+        c = cabi.matmul_fwd(Av, Bv, bias=dev(bias) if with_bias else None, mode=MODE_TF32).to_numpy()
+        rows = np.unique(np.concatenate([np.arange(4), np.array([127, 128, 255, 256, 257, 383, 384, 511, 512, 513]),
+                                         rng.integers(0, M, 12), np.arange(M - 3, M)]))
+        an = np.swapaxes(a, -1, -2) if ta else a
+        bn = np.swapaxes(b, -1, -2) if tb else b
+        ref = np.matmul(an[..., rows, :].astype(np.float64), bn.astype(np.float64))
+        if with_bias:
+            ref = ref + bias
+        assert rel_fro(c[..., rows, :], ref) < TOL_TF32, (bt, M, N, K, ta, tb)
+    for ta in (0, 1):
+        for tb in (0, 1):
+            check((), 4100, 4100, 1030, ta, tb)
+    check((), 4352, 4096, 1024, 0, 0, with_bias=True)   # 8.5 tiles of 512 rows: the last pair's second CTA is empty
+    check((3,), 2048, 2048, 1056, 0, 0)
+    # backward at a size that routes dA (K-major x K-major) and dB (M-major x N-major) there too
+    M, K, N = 4096, 4224, 4100
+    a, b, dc = uniform((M, K), 93), uniform((K, N), 94), uniform((M, N), 95)
+    da, db = cabi.matmul_bwd(dev(a), dev(b), dev(dc), mode=MODE_TF32)
+    rows = np.array([0, 1, 255, 256, 511, 512, 2047, 4095])
+    assert rel_fro(da.to_numpy()[rows], dc[rows].astype(np.float64) @ b.astype(np.float64).T) < TOL_TF32
+    krows = np.array([0, 1, 255, 256, 511, 512, 2047, 4223])
+    assert rel_fro(db.to_numpy()[krows], a[:, krows].astype(np.float64).T @ dc.astype(np.float64)) < TOL_TF32
+
+
 def _random_case(rng):
     """A random product: batch broadcasting, operand layouts (transposed / sliced views), ragged sizes."""
     nb = int(rng.integers(0, 4))

@@ -449,3 +449,36 @@ def test_optimizers_step_view_parameters(ak):
         p = p - 0.1 * v
     assert not P.is_contiguous()
     assert rel_fro(P.contiguous().to_numpy(), p) < TOL_FP32
+
+
+@pytest.mark.parametrize("momentum,nesterov,dampening,wd", [(0.0, False, 0.0, 0.0), (0.0, False, 0.0, 0.05),
+                                                             (0.9, False, 0.1, 0.01), (0.8, True, 0.0, 0.0)])
+def test_sgd_steps_a_parameter_list_in_one_launch(ak, momentum, nesterov, dampening, wd):
+    # SGD.step (aakaar/optim.py:24-48 -> src/optim_kernels.cu:21-55) over several tensors of odd sizes: one
+    # launch for the whole list, same arithmetic as one launch per tensor
+    from aakaar_b200 import _C
+    shapes = [(300, 40), (1, 40), (5000,), (3,), (64, 64)]
+    ps = [uniform(s, 100 + i) for i, s in enumerate(shapes)]
+    gs = [[normal(s, 200 + 10 * step + i) for i, s in enumerate(shapes)] for step in range(3)]
+    P = [ak.from_numpy(p, requires_grad=True) for p in ps]
+    opt = ak.optim.SGD(P, lr=0.05, momentum=momentum, weight_decay=wd, dampening=dampening, nesterov=nesterov)
+    ref = [p.astype(np.float64) for p in ps]
+    vel = [None] * len(ps)
+    for step in range(3):
+        for t, g in zip(P, gs[step]):
+            t.grad = ak.from_numpy(g)
+        ak.synchronize()
+        _C._launch_count(True)
+        opt.step()
+        ak.synchronize()
+        assert _C._launch_count(True) == 1
+        for i, g in enumerate(gs[step]):
+            gg = g.astype(np.float64) + wd * ref[i]
+            if momentum != 0:
+                vel[i] = gg if vel[i] is None else momentum * vel[i] + (1 - dampening) * gg
+                upd = gg + momentum * vel[i] if nesterov else vel[i]
+            else:
+                upd = gg
+            ref[i] = ref[i] - 0.05 * upd
+    for t, r in zip(P, ref):
+        assert rel_fro(t.to_numpy(), r) < TOL_FP32
