@@ -101,6 +101,27 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     return c;
 }
 
+#ifdef AKR_B200_DIAG
+// Diagnostic builds: SM cycles and nanoseconds one thread of every CTA spent inside the kernel (debug bit 15),
+// i.e. the SM clock the kernel really ran at.
+__device__ unsigned long long g_diag_clk[2 * 256];
+__device__ unsigned long long g_diag_iss[4];  // MMA issuer of CTA 0: cycles in waits, MMA issue, commits; stages
+#define AKR_DIAG_CLK_BEGIN                                                        \
+    unsigned long long diag_c0 = 0, diag_t0 = 0;                                  \
+    if ((p.debug & 32768) && threadIdx.x == 0) {                                  \
+        diag_c0 = clock64();                                                      \
+        diag_t0 = ptx::globaltimer_ns();                                          \
+    }
+#define AKR_DIAG_CLK_END                                                          \
+    if ((p.debug & 32768) && threadIdx.x == 0 && blockIdx.x < 256) {              \
+        g_diag_clk[2 * blockIdx.x] = clock64() - diag_c0;                         \
+        g_diag_clk[2 * blockIdx.x + 1] = ptx::globaltimer_ns() - diag_t0;         \
+    }
+#else
+#define AKR_DIAG_CLK_BEGIN
+#define AKR_DIAG_CLK_END
+#endif
+
 // One load stage holds the raw fp32 tiles of A and B as TMA delivers them, in every mode. The
 // fp32-accurate mode keeps the derived low parts in a second, shorter ring of the same tile size (LO
 // slots): a low-part tile only lives from its conversion to the end of its MMAs, so shared memory goes
@@ -340,6 +361,27 @@ __device__ __forceinline__ void store_block_tma(float (&v)[32], float4* my_tile,
     ptx::named_barrier_sync(bar_id, 128);  // the (other) tile may be overwritten
 }
 
+// The same block into a staging tile that nothing else will use (the idle load stages behind a CTA's last tile):
+// no wait for the store to have read it, no second barrier; the issuing thread waits for all its stores at the end.
+__device__ __forceinline__ void store_block_tma_once(float (&v)[32], float4* my_tile, uint32_t slab_tile_addr,
+                                                     const CUtensorMap* tmC, int col0, int row_base, int i1, int i0,
+                                                     int N, const float* bias, int lane, bool issuer, int bar_id) {
+    if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) v[j] += __ldg(bias + col0 + j);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        my_tile[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    ptx::fence_proxy_async_smem();
+    ptx::named_barrier_sync(bar_id, 128);
+    if (issuer) {
+        ptx::tma_store_4d(tmC, slab_tile_addr, col0, row_base, i1, i0);
+        ptx::bulk_commit_group();
+    }
+}
+
 // Per-warp variant for write-heavy short contractions: every epilogue warp stages its own 32 x 32 block
 // (4 KB, same swizzle) and its lane 0 sends it as a box of 32 rows; no barrier between warps at all. The
 // caller alternates between two staging tiles per warp; the lane waits for the box before the one it just
@@ -435,7 +477,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     // third warpgroup gives back: there hardware warps 0..7 are the epilogue, 8 the producer, 9 the MMA warp,
     // 10..11 the converters.
     constexpr bool REMAP = TERMS == 3 && BN == 256;
-    const int hw_warp = threadIdx.x >> 5;
+    const int hw_warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
     const int warp = !REMAP ? hw_warp : (hw_warp < 8 ? hw_warp + 2 : (hw_warp < 10 ? hw_warp - 8 : hw_warp));
     const int lane = threadIdx.x & 31;
 
@@ -470,6 +512,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
+    AKR_DIAG_CLK_BEGIN
 
     const int total_iters = p.red * p.nkb;  // contraction steps of one output tile
 
@@ -562,7 +605,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // All 32 lanes run the loop (waits included); one elected lane issues the MMAs and commits. With a single
+        // lane inside a divergent branch every operand of every tcgen05.mma is moved into uniform registers one by
+        // one: 87 cycles of issue per MMA, more than a 128 x 128 x 8 MMA takes to execute.
+        {
+            const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BN, MAJA, MAJB);
             int stage = 0;
             uint32_t phase = 0;
@@ -587,12 +634,18 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     for (int it = cs; it < ce; ++it) {
                         // fp32-accurate mode: the stage is ready once the converter warps wrote its low parts
                         // (they waited for the raw tiles themselves)
+#ifdef AKR_B200_DIAG
+                        const long long dq0 = clock64();
+#endif
                         if (!ptx::mbar_wait(TERMS == 3 ? conv_bar(lo_slot) : full_bar(stage), TERMS == 3 ? lo_phase : phase,
                                             abort_flag, p.wait_limit_ns)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
+#ifdef AKR_B200_DIAG
+                        const long long dq1 = clock64();
+#endif
                         const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                         const uint32_t sb = sa + L::A_BYTES;
                         const uint32_t sa_lo = smem_base + LO_BASE + lo_slot * L::STAGE_BYTES;
@@ -616,31 +669,43 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
                             if (AKR_DIAG(p.debug, 2)) {
-                                if (k8 == 0 && it == cs) ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 0u);
+                                if (k8 == 0 && it == cs) ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, 0u);
                             } else if (TERMS == 3) {
                                 const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
                                 const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
-                                ptx::mma_tf32_ss(d_tmem, da_lo, db, IDESC, first);
-                                ptx::mma_tf32_ss(d_tmem, da, db_lo, IDESC, 1u);
-                                ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 1u);
+                                ptx::mma_tf32_ss_elected(issuer, d_tmem, da_lo, db, IDESC, first);
+                                ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db_lo, IDESC, 1u);
+                                ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, 1u);
                             } else {
-                                ptx::mma_tf32_ss(d_tmem, da, db, IDESC, first);
+                                ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, first);
                             }
                         }
-                        ptx::mma_commit(empty_bar(stage));  // stage reusable once these MMAs finish
+#ifdef AKR_B200_DIAG
+                        const long long dq2 = clock64();
+#endif
+                        ptx::mma_commit_elected(issuer, empty_bar(stage));  // stage reusable once these MMAs finish
+#ifdef AKR_B200_DIAG
+                        if ((p.debug & 32768) && blockIdx.x == 0) {
+                            const long long dq3 = clock64();
+                            g_diag_iss[0] += dq1 - dq0;
+                            g_diag_iss[1] += dq2 - dq1;
+                            g_diag_iss[2] += dq3 - dq2;
+                            g_diag_iss[3] += 1;
+                        }
+#endif
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1u;
                         }
                         if (TERMS == 3) {
-                            ptx::mma_commit(lofree_bar(lo_slot));  // and so is the low-part slot
+                            ptx::mma_commit_elected(issuer, lofree_bar(lo_slot));  // and so is the low-part slot
                             if (++lo_slot == LO) {
                                 lo_slot = 0;
                                 lo_phase ^= 1u;
                             }
                         }
                     }
-                    if (ok) ptx::mma_commit(tfull_bar(buf));  // this chunk's accumulator is complete
+                    if (ok) ptx::mma_commit_elected(issuer, tfull_bar(buf));  // this chunk's accumulator is complete
                     ++handoff;
                 }
             }
@@ -722,6 +787,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
             const int it0 = (int)((long long)total_iters * c.split / p.splits);
             const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
             const int row0 = c.m0 + q * 32;   // first row of this warp's 32-row band
+            // Behind a CTA's last tile the load stages are idle (no later tile to prefetch, every MMA that read them
+            // has completed once the accumulator is): each 32-column block of the tile gets a staging tile of its
+            // own there, and the epilogue no longer waits block by block for a store to have read the one tile per
+            // slab (7.7 of the 55 kilocycles of a 2048^3 product, one tile per CTA, were that chain).
+            const bool ring_free = TERMS == 1 && !WARP_STORE && t + (int)gridDim.x >= p.total_tiles &&
+                                   SLABS * (SLAB_W / 32) * 4 * EPI_STAGE_BYTES <= TILE_BYTES;
             float* out_base;
             long long out_ld;
             bool vec;
@@ -774,6 +845,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                                 store_block_tma_warp(f, my_stage + epi_buf * (EPI_ALT / 16), my_stage_addr + epi_buf * EPI_ALT,
                                                      &p.tmC, col0, row0, c.i1, c.i0, p.N, bias, lane);
                                 epi_buf ^= 1;
+                            } else if (use_tma && ring_free) {
+                                // one staging tile of its own per 32-column block, in the load stages
+                                const uint32_t off = (uint32_t)((slab * (SLAB_W / 32) + ch) * 4 * EPI_STAGE_BYTES);
+                                store_block_tma_once(f, reinterpret_cast<float4*>(smem + off + q * EPI_STAGE_BYTES), smem_base + off,
+                                                     &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane, q == 0 && lane == 0, 2 + slab);
                             } else if (use_tma) {
                                 store_block_tma<EPI_BUFS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
                                                           &p.tmC, col0, c.m0, c.i1, c.i0, p.N, bias, lane,
@@ -918,29 +994,10 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<TMEM_COLS>(tmem_base);
     }
+    AKR_DIAG_CLK_END
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
-
-#ifdef AKR_B200_DIAG
-// Diagnostic builds: SM cycles and nanoseconds one thread of every CTA spent inside the kernel (debug bit 15),
-// i.e. the SM clock the kernel really ran at.
-__device__ unsigned long long g_diag_clk[2 * 256];
-#define AKR_DIAG_CLK_BEGIN                                                        \
-    unsigned long long diag_c0 = 0, diag_t0 = 0;                                  \
-    if ((p.debug & 32768) && threadIdx.x == 0) {                                  \
-        diag_c0 = clock64();                                                      \
-        diag_t0 = ptx::globaltimer_ns();                                          \
-    }
-#define AKR_DIAG_CLK_END                                                          \
-    if ((p.debug & 32768) && threadIdx.x == 0 && blockIdx.x < 256) {              \
-        g_diag_clk[2 * blockIdx.x] = clock64() - diag_c0;                         \
-        g_diag_clk[2 * blockIdx.x + 1] = ptx::globaltimer_ns() - diag_t0;         \
-    }
-#else
-#define AKR_DIAG_CLK_BEGIN
-#define AKR_DIAG_CLK_END
-#endif
 
 // ---------------------------------------------------------------------------------- 256 x 256 tiles
 // TF32 kernel for large products: one CTA computes a 256 x 256 tile as two 128 x 256 accumulators
@@ -979,7 +1036,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * BIG_STAGES + 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
     const int lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < BIG_STAGES; ++s) {
@@ -1086,7 +1143,8 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {  // all 32 lanes run the loop, one elected lane issues (see the general kernel)
+            const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(BM, BIG_BN, MAJA, MAJB);
             // K-major rows are BKT * 4 bytes (128- or 64-byte swizzle), 8 rows per group
             constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
@@ -1128,20 +1186,20 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t da = ptx::smem_desc(sa_h + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss(d_tmem, da, db, IDESC, 0u);
+                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, 0u);
                                 continue;
                             }
-                            ptx::mma_tf32_ss(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                            ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
                         }
                     }
                     if (!ok) break;
-                    ptx::mma_commit(empty_bar(stage));
+                    ptx::mma_commit_elected(issuer, empty_bar(stage));
                     if (++stage == BIG_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) ptx::mma_commit(tfull_bar);  // both accumulators complete
+                if (ok) ptx::mma_commit_elected(issuer, tfull_bar);  // both accumulators complete
             }
         }
     } else {
@@ -1157,6 +1215,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++local) {
             const Tile c = decode_tile(t, p, BIG_BN, BIG_BM);
             const Epi epi = tile_epi(p, c);
+            const bool ring_free = t + (int)gridDim.x >= p.total_tiles;  // no later tile of this CTA is being prefetched
             bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
             if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
             if (!got) {
@@ -1182,7 +1241,14 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            if (use_tma)
+                            if (use_tma && ring_free && h * 4 + ch < 6) {
+                                // behind the CTA's last tile the load stages are idle: six of a slab's eight blocks
+                                // get a staging tile of their own there and are stored without waiting in between
+                                const uint32_t off = (uint32_t)((slab * 6 + h * 4 + ch) * 4 * EPI_STAGE_BYTES);
+                                store_block_tma_once(f, reinterpret_cast<float4*>(smem + off + q * EPI_STAGE_BYTES), smem_base + off,
+                                                     &p.tmC, col0, c.m0 + h * 128, c.i1, c.i0, p.N, p.bias, lane,
+                                                     q == 0 && lane == 0, 2 + slab);
+                            } else if (use_tma)
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, c.m0 + h * 128, c.i1, c.i0, p.N,
                                                 p.bias, lane, q == 0 && lane == 0, 2 + slab);
                             else
@@ -1262,7 +1328,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     // Roles by hardware warp: 0..7 epilogue, 8 producer, 9 MMA, 10..11 converters, so that the two epilogue
     // warpgroups can take the registers the third one gives back. `warp` is the role index used below
     // (0 producer, 1 MMA, 2..9 epilogue, 10..11 converters).
-    const int hw_warp = threadIdx.x >> 5;
+    const int hw_warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
     const int warp = hw_warp < 8 ? hw_warp + 2 : (hw_warp < 10 ? hw_warp - 8 : hw_warp);
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
@@ -1300,6 +1366,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
+    AKR_DIAG_CLK_BEGIN
     const int total_iters = p.red * p.nkb;
     const int kc = (AKR_DIAG(p.debug, 64)) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
 
@@ -1392,7 +1459,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && leader) {
+        if (leader) {  // all 32 lanes run the loop, one elected lane issues (see the general kernel)
+            const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
             constexpr uint32_t K_SBO = 8 * PAIR_BK * 4;
             constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
@@ -1434,27 +1502,27 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
                             const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
                             if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                                if (first == 0u) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                                if (first == 0u) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
                                 continue;
                             }
-                            ptx::mma_tf32_ss_pair(d_tmem, da_lo, db, IDESC, first);
-                            ptx::mma_tf32_ss_pair(d_tmem, da, db_lo, IDESC, 1u);
-                            ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 1u);
+                            ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da_lo, db, IDESC, first);
+                            ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db_lo, IDESC, 1u);
+                            ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 1u);
                         }
                         // both CTAs may refill this stage once these MMAs have read it
-                        ptx::mma_commit_pair(empty_bar(stage));
+                        ptx::mma_commit_pair_elected(issuer, empty_bar(stage));
                         if (++stage == S) {
                             stage = 0;
                             phase ^= 1u;
                         }
-                        ptx::mma_commit_pair(lofree_bar(slot));  // and rewrite this low-part slot
+                        ptx::mma_commit_pair_elected(issuer, lofree_bar(slot));  // and rewrite this low-part slot
                         if (++slot == LS) {
                             slot = 0;
                             slot_phase ^= 1u;
                         }
                     }
                     if (ok) {  // this chain's accumulator is complete in both CTAs' tensor memory
-                        ptx::mma_commit_pair(tfull_bar(buf));
+                        ptx::mma_commit_pair_elected(issuer, tfull_bar(buf));
                     }
                     ++handoff;
                 }
@@ -1580,6 +1648,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc_pair<512>(tmem_base);
     }
+    AKR_DIAG_CLK_END
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
@@ -1623,7 +1692,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SM + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
     const bool leader = rank == 0;
@@ -1661,6 +1730,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     // set-up on SMs this grid leaves, and do not touch global memory before the previous kernel has finished.
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
+    AKR_DIAG_CLK_BEGIN
     const int total_iters = p.red * p.nkb;
 
     if (warp == 0) {
@@ -1728,7 +1798,8 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && leader) {
+        if (leader) {  // all 32 lanes run the loop, one elected lane issues (see the general kernel)
+            const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
             constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
             constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW128_ATOM32B;
@@ -1762,18 +1833,18 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                         const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                         if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                            if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                            if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
                             continue;
                         }
-                        ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                        ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
                     }
-                    ptx::mma_commit_pair(empty_bar(stage));  // both CTAs may refill this stage
+                    ptx::mma_commit_pair_elected(issuer, empty_bar(stage));  // both CTAs may refill this stage
                     if (++stage == S) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) ptx::mma_commit_pair(tfull_bar(buf));  // accumulator complete in both CTAs' tensor memory
+                if (ok) ptx::mma_commit_pair_elected(issuer, tfull_bar(buf));  // accumulator complete in both CTAs' tensor memory
             }
         }
     } else {
@@ -1840,6 +1911,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc_pair<512>(tmem_base);
     }
+    AKR_DIAG_CLK_END
     if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, 1);
 }
 
@@ -1885,7 +1957,7 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 3);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
     const bool leader = rank == 0;
@@ -1987,7 +2059,8 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
-        if (lane == 0 && leader) {
+        if (leader) {  // all 32 lanes run the loop, one elected lane issues (see the general kernel)
+            const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(256, QUAD_BN, MAJA, MAJB);
             constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
             constexpr uint32_t a_lay = MAJA == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
@@ -2028,20 +2101,20 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
                             const uint64_t da = ptx::smem_desc(sa_h + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                             if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, 0u);
+                                if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
                                 continue;
                             }
-                            ptx::mma_tf32_ss_pair(d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                            ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
                         }
                     }
                     if (!ok) break;
-                    ptx::mma_commit_pair(empty_bar(stage));  // both CTAs may refill this stage
+                    ptx::mma_commit_pair_elected(issuer, empty_bar(stage));  // both CTAs may refill this stage
                     if (++stage == S) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) ptx::mma_commit_pair(tfull_bar);  // both accumulators complete in both CTAs' tensor memory
+                if (ok) ptx::mma_commit_pair_elected(issuer, tfull_bar);  // both accumulators complete in both CTAs' tensor memory
             }
         }
     } else {
@@ -2057,6 +2130,7 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
             const Tile c = decode_tile(t, p, QUAD_BN, QUAD_BM, 8);
             const Epi epi = tile_epi(p, c);
+            const bool ring_free = t + num_pairs >= p.total_tiles;  // no later tile of this pair is being prefetched
             bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar, local & 1u, abort_flag, p.wait_limit_ns));
             if (use_tma) got = ptx::named_barrier_and(2 + slab, 128, got);  // a slab's four warps leave together
             if (!got) {
@@ -2083,7 +2157,13 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
                             float f[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                            if (use_tma)
+                            if (use_tma && ring_free && h * 4 + ch < 6) {
+                                // behind the pair's last tile the load stages are idle (see the single-CTA kernel)
+                                const uint32_t off = (uint32_t)((slab * 6 + h * 4 + ch) * 4 * EPI_STAGE_BYTES);
+                                store_block_tma_once(f, reinterpret_cast<float4*>(smem + off + q * EPI_STAGE_BYTES), smem_base + off,
+                                                     &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias, lane,
+                                                     q == 0 && lane == 0, 2 + slab);
+                            } else if (use_tma)
                                 store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                                 lane, q == 0 && lane == 0, 2 + slab);
                             else
@@ -2796,6 +2876,16 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
 }
 
 #ifdef AKR_B200_DIAG
+extern "C" __attribute__((visibility("default"))) int akr_diag_issuer(double* out4, int reset) {
+    unsigned long long h[4] = {0, 0, 0, 0};
+    if (cudaMemcpyFromSymbol(h, g_diag_iss, sizeof(h)) != cudaSuccess) return -1;
+    for (int i = 0; i < 4; ++i) out4[i] = (double)h[i];
+    if (reset) {
+        unsigned long long z[4] = {0, 0, 0, 0};
+        cudaMemcpyToSymbol(g_diag_iss, z, sizeof(z));
+    }
+    return 0;
+}
 extern "C" __attribute__((visibility("default"))) int akr_diag_kernel_clock(int ctas, double* mhz_mean, double* mhz_min, double* us_max) {
     static unsigned long long h[2 * 256];
     if (ctas > 256) ctas = 256;

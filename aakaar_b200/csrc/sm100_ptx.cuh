@@ -230,6 +230,43 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                  : "memory");
 }
 
+// The same two instructions for a warp that runs its issue loop with all 32 lanes (uniform control flow, so
+// that descriptors and addresses live in uniform registers): `leader` is nonzero in the one lane that issues.
+// The lane is chosen once (elect_one) and must stay the same: a commit tracks the MMAs of the thread that executes it.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t is_leader;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, e;\n\t"
+        "}\n"
+        : "=r"(is_leader));
+    return is_leader;
+}
+__device__ __forceinline__ void mma_tf32_ss_elected(uint32_t leader, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                    uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "setp.ne.b32 e, %5, 0;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit_elected(uint32_t leader, uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "setp.ne.b32 e, %1, 0;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n"
+        ::"r"(bar), "r"(leader)
+        : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -347,6 +384,30 @@ __device__ __forceinline__ void mma_tf32_ss_pair(uint32_t d_tmem, uint64_t adesc
         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The pair forms for an issuing warp that runs with all lanes (see mma_tf32_ss_elected).
+__device__ __forceinline__ void mma_tf32_ss_pair_elected(uint32_t leader, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, e;\n\t"
+        "setp.ne.b32 e, %5, 0;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit_pair_elected(uint32_t leader, uint32_t bar) {
+    const uint16_t both = 0x3;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "setp.ne.b32 e, %2, 0;\n\t"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t"
+        "}\n"
+        ::"r"(bar), "h"(both), "r"(leader)
         : "memory");
 }
 // When the pair MMAs issued so far have finished, arrive once on the mbarrier at shared-memory
