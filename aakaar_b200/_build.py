@@ -92,8 +92,19 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
+def build_microbench(force: bool = False, verbose: bool = False) -> Path:
+    """The stand-alone micro-benchmark of the tcgen05.mma instruction stream (csrc/microbench/mma_stream.cu)."""
+    LIBDIR.mkdir(exist_ok=True)
+    src = CSRC / "microbench" / "mma_stream.cu"
+    out = LIBDIR / "mma_stream_bench"
+    if force or not _newer(out, [src, CSRC / "sm100_ptx.cuh"]):
+        _run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-cudart", "static",
+              src, "-o", out], verbose)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return build_cuda(force, verbose), build_host(force, verbose)
+    return build_cuda(force, verbose), build_host(force, verbose), build_microbench(force, verbose)
 
 
 if __name__ == "__main__":

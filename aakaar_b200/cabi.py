@@ -87,6 +87,7 @@ def load():
         "akr_set_device": [C.c_int],
         "akr_set_gemm_cta_limit": [C.c_int],
         "akr_debug_configure": [C.c_int, C.c_uint],
+        "akr_gemm_clock_read": [C.c_int] + [C.POINTER(C.c_double)] * 4,
         "akr_stream_create": [C.POINTER(vp)],
         "akr_stream_destroy": [vp],
         "akr_stream_wait_event": [vp, vp],
@@ -391,6 +392,14 @@ def h2d(dst: DeviceArray, src_np, stream=None, dst_offset_elems=0):
 
 def d2h(dst_np, src: DeviceArray, stream=None, src_offset_elems=0):
     check(lib().akr_memcpy_d2h(dst_np.ctypes.data, src.ptr + 4 * src_offset_elems, dst_np.nbytes, _sh(stream)))
+
+
+def gemm_clock_read(ctas=148):
+    """What the clock probe (akr_debug_configure(32768, 0)) recorded for the last GEMM launch: a dict with the SM
+    clock in MHz (mean, min over the CTAs), the longest CTA in cycles and in microseconds. Synchronize first."""
+    a, b, c, d = C.c_double(), C.c_double(), C.c_double(), C.c_double()
+    check(lib().akr_gemm_clock_read(ctas, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+    return {"sm_mhz": a.value, "sm_mhz_min": b.value, "cycles": c.value, "us": d.value}
 
 
 def synchronize():

@@ -959,6 +959,16 @@ AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms) {
     return AKR_OK;
 }
 
+AKR_API int akr_gemm_clock_read(int ctas, double* sm_mhz_mean, double* sm_mhz_min, double* cycles_max, double* us_max) {
+    DeviceState* st = nullptr;
+    int rc = need_gpu(&st);
+    if (rc != AKR_OK) return rc;
+    const int r = gemm_sm100_clock_read(ctas, sm_mhz_mean, sm_mhz_min, cycles_max, us_max);
+    if (r == -2) return fail(AKR_ERR_INVALID, "akr_gemm_clock_read: no launch recorded (akr_debug_configure(32768, 0) first)");
+    if (r != 0) return fail(AKR_ERR_CUDA, "akr_gemm_clock_read: cannot read the probe");
+    return AKR_OK;
+}
+
 AKR_API int akr_set_gemm_cta_limit(int ctas) {
     gemm_sm100_set_cta_limit(ctas);
     return AKR_OK;

@@ -101,11 +101,11 @@ __device__ __forceinline__ Tile decode_tile(int t, const KernelParams& p, int bn
     return c;
 }
 
-#ifdef AKR_B200_DIAG
-// Diagnostic builds: SM cycles and nanoseconds one thread of every CTA spent inside the kernel (debug bit 15),
-// i.e. the SM clock the kernel really ran at.
-__device__ unsigned long long g_diag_clk[2 * 256];
-__device__ unsigned long long g_diag_iss[4];  // MMA issuer of CTA 0: cycles in waits, MMA issue, commits; stages
+// Clock probe (debug bit 15): thread 0 of every CTA records the SM cycles (clock64) and the nanoseconds (%globaltimer)
+// it spent between the end of the kernel's set-up and its teardown. Their ratio is the SM clock the kernel really ran
+// at - under the power cap that, not the cycle count, decides how long a large product takes - and the cycle count
+// can be set against the cycles the MMAs alone need. One predicate per CTA when the probe is off.
+__device__ unsigned long long g_clock_probe[2 * 256];
 #define AKR_DIAG_CLK_BEGIN                                                        \
     unsigned long long diag_c0 = 0, diag_t0 = 0;                                  \
     if ((p.debug & 32768) && threadIdx.x == 0) {                                  \
@@ -114,13 +114,9 @@ __device__ unsigned long long g_diag_iss[4];  // MMA issuer of CTA 0: cycles in 
     }
 #define AKR_DIAG_CLK_END                                                          \
     if ((p.debug & 32768) && threadIdx.x == 0 && blockIdx.x < 256) {              \
-        g_diag_clk[2 * blockIdx.x] = clock64() - diag_c0;                         \
-        g_diag_clk[2 * blockIdx.x + 1] = ptx::globaltimer_ns() - diag_t0;         \
+        g_clock_probe[2 * blockIdx.x] = clock64() - diag_c0;                      \
+        g_clock_probe[2 * blockIdx.x + 1] = ptx::globaltimer_ns() - diag_t0;      \
     }
-#else
-#define AKR_DIAG_CLK_BEGIN
-#define AKR_DIAG_CLK_END
-#endif
 
 // One load stage holds the raw fp32 tiles of A and B as TMA delivers them, in every mode. The
 // fp32-accurate mode keeps the derived low parts in a second, shorter ring of the same tile size (LO
@@ -634,18 +630,12 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     for (int it = cs; it < ce; ++it) {
                         // fp32-accurate mode: the stage is ready once the converter warps wrote its low parts
                         // (they waited for the raw tiles themselves)
-#ifdef AKR_B200_DIAG
-                        const long long dq0 = clock64();
-#endif
                         if (!ptx::mbar_wait(TERMS == 3 ? conv_bar(lo_slot) : full_bar(stage), TERMS == 3 ? lo_phase : phase,
                                             abort_flag, p.wait_limit_ns)) {
                             ok = false;
                             break;
                         }
                         ptx::tc_fence_after();
-#ifdef AKR_B200_DIAG
-                        const long long dq1 = clock64();
-#endif
                         const uint32_t sa = smem_base + stage * L::STAGE_BYTES;
                         const uint32_t sb = sa + L::A_BYTES;
                         const uint32_t sa_lo = smem_base + LO_BASE + lo_slot * L::STAGE_BYTES;
@@ -680,19 +670,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                                 ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, first);
                             }
                         }
-#ifdef AKR_B200_DIAG
-                        const long long dq2 = clock64();
-#endif
                         ptx::mma_commit_elected(issuer, empty_bar(stage));  // stage reusable once these MMAs finish
-#ifdef AKR_B200_DIAG
-                        if ((p.debug & 32768) && blockIdx.x == 0) {
-                            const long long dq3 = clock64();
-                            g_diag_iss[0] += dq1 - dq0;
-                            g_diag_iss[1] += dq2 - dq1;
-                            g_diag_iss[2] += dq3 - dq2;
-                            g_diag_iss[3] += 1;
-                        }
-#endif
                         if (++stage == STAGES) {
                             stage = 0;
                             phase ^= 1u;
@@ -2875,33 +2853,32 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     return 0;
 }
 
-#ifdef AKR_B200_DIAG
-extern "C" __attribute__((visibility("default"))) int akr_diag_issuer(double* out4, int reset) {
-    unsigned long long h[4] = {0, 0, 0, 0};
-    if (cudaMemcpyFromSymbol(h, g_diag_iss, sizeof(h)) != cudaSuccess) return -1;
-    for (int i = 0; i < 4; ++i) out4[i] = (double)h[i];
-    if (reset) {
-        unsigned long long z[4] = {0, 0, 0, 0};
-        cudaMemcpyToSymbol(g_diag_iss, z, sizeof(z));
-    }
-    return 0;
-}
-extern "C" __attribute__((visibility("default"))) int akr_diag_kernel_clock(int ctas, double* mhz_mean, double* mhz_min, double* us_max) {
+// What the clock probe recorded for the last GEMM launch of the current device: per-CTA cycles and nanoseconds.
+int gemm_sm100_clock_read(int ctas, double* mhz_mean, double* mhz_min, double* cycles_max, double* us_max) {
     static unsigned long long h[2 * 256];
+    if (ctas < 1) ctas = 1;
     if (ctas > 256) ctas = 256;
-    if (cudaMemcpyFromSymbol(h, g_diag_clk, sizeof(h)) != cudaSuccess) return -1;
-    double sum = 0, mn = 1e30, um = 0;
+    if (cudaMemcpyFromSymbol(h, g_clock_probe, sizeof(h)) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    double sum = 0, mn = 1e30, um = 0, cm = 0;
+    int n = 0;
     for (int i = 0; i < ctas; ++i) {
-        const double mhz = h[2 * i + 1] ? 1e3 * (double)h[2 * i] / (double)h[2 * i + 1] : 0.0;
+        if (h[2 * i + 1] == 0) continue;
+        const double mhz = 1e3 * (double)h[2 * i] / (double)h[2 * i + 1];
         sum += mhz;
+        ++n;
         if (mhz < mn) mn = mhz;
         if ((double)h[2 * i + 1] * 1e-3 > um) um = (double)h[2 * i + 1] * 1e-3;
+        if ((double)h[2 * i] > cm) cm = (double)h[2 * i];
     }
-    *mhz_mean = sum / ctas;
-    *mhz_min = mn;
-    *us_max = um;
+    if (n == 0) return -2;
+    if (mhz_mean) *mhz_mean = sum / n;
+    if (mhz_min) *mhz_min = mn;
+    if (cycles_max) *cycles_max = cm;
+    if (us_max) *us_max = um;
     return 0;
 }
-#endif
 
 }  // namespace akr

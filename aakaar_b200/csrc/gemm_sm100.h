@@ -73,6 +73,9 @@ void gemm_sm100_set_cta_limit(int ctas);
 // Test hooks: extra GemmDesc::debug bits for every launch, and the bound of every in-kernel wait
 // (0 = default, 4 s).
 void gemm_sm100_debug_configure(int flags, unsigned wait_limit_ms);
+// Clock probe (debug bit 15): SM clock (mean / min over the first `ctas` CTAs, MHz), longest CTA in cycles and in
+// microseconds, of the last GEMM launch on the current device. -1: read failed, -2: nothing recorded.
+int gemm_sm100_clock_read(int ctas, double* mhz_mean, double* mhz_min, double* cycles_max, double* us_max);
 
 // Bytes of `partials` and number of `counters` entries a split launch needs.
 void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* counter_count);

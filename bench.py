@@ -534,6 +534,30 @@ def run_gpu_arm(args):
     ms_mma_only = mma_only_ms()
     t_m1 = time.time()
 
+    # ---- the SM clock and the cycle count inside the forward kernel under the same sustained load (clock probe of the
+    #      library: per-CTA clock64 / %globaltimer): the duration of a power-capped product is cycles / clock, and the
+    #      cycles can be set against those its MMAs alone need. Outside every timed region.
+    def clock_probe(steps=12):
+        cabi.check(lib.akr_debug_configure(32768, 0))
+        try:
+            for _ in range(steps):
+                cabi.matmul_fwd(A, B, mode=cabi.MODE_TF32, out=Cd)
+                cabi.matmul_bwd(A, B, DC, mode=cabi.MODE_TF32, need_db=False, da=DAd)
+                cabi.matmul_bwd(A, B, DC, mode=cabi.MODE_TF32, need_da=False, db=DBd)
+            cabi.matmul_fwd(A, B, mode=cabi.MODE_TF32, out=Cd)
+            cabi.synchronize()
+            r = cabi.gemm_clock_read(148)
+        finally:
+            cabi.check(lib.akr_debug_configure(0, 0))
+        sms = 148
+        mma_cycles = 2.0 * N_SQ * N_SQ * N_SQ / (sms * 4096.0)   # 128 x 256 x 8 per 128 cycles per SM
+        return {"kernel": "fwd C=A.B", "sm_mhz": r["sm_mhz"], "sm_mhz_min": r["sm_mhz_min"], "kcycles": r["cycles"] / 1e3,
+                "us": r["us"], "mma_kcycles_perfectly_balanced": mma_cycles / 1e3,
+                "mma_cycle_share": mma_cycles / r["cycles"],
+                "how": "clock64 and %globaltimer of thread 0 of every CTA between set-up and teardown "
+                       "(akr_debug_configure(32768) / akr_gemm_clock_read), forward launch after 12 back-to-back steps"}
+    in_kernel = clock_probe()
+
     c5a = c5a_phase(cabi, lib, dist, rank, n_gpus, max_over_ranks, barrier)
 
     # ---- end to end through the Python API, host buffers in, host buffers out
@@ -697,6 +721,7 @@ def run_gpu_arm(args):
                                        "sm_mhz": mma_clk.get("sm_mhz"), "frac": achieved / mma_only_tf,
                                        "how": "the forward kernel of this workload with its TMA loads switched off "
                                               "(tcgen05.mma kind::tf32 issued back to back), CUDA events, 10 launches"},
+                "in_kernel": in_kernel,
                 "traffic": NCU_TRAFFIC_BYTES, "traffic_over_algorithmic": NCU_TRAFFIC_BYTES / (3 * N_SQ * N_SQ * 4.0),
                 "by_kernel": [{"kernel": names[j], "ms": kern_tf32[j],
                                "tflops": per_launch_flop / (kern_tf32[j] * 1e-3) / 1e12 if n_gpus == 1 else None}

@@ -245,9 +245,18 @@ AKR_API int akr_event_destroy(void* event);
  *   32  fp32-accurate products run on the CTA-pair (cta_group::2) kernel wherever its tiles apply
  *       (by default contractions of at least 320 and enough 256 x 256 tiles to fill a quarter of the GPU)
  * 2048  TF32 products run on the CTA-pair kernel wherever it applies (by default a band of shapes)
+ * 32768 clock probe: every CTA of a GEMM launch records the SM cycles and the nanoseconds it ran for
+ *       (read with akr_gemm_clock_read)
  * akr_debug_configure(0, 0) restores normal operation. Further timing switches exist only in builds
  * compiled with -DAKR_B200_DIAG. */
 AKR_API int akr_debug_configure(int flags, unsigned wait_limit_ms);
+
+/* What the clock probe (flag 32768) recorded for the last GEMM launch of the current device, after a
+ * synchronize: SM clock in MHz as cycles / nanoseconds per CTA (mean and minimum over the first `ctas`
+ * CTAs of the grid), and the longest CTA in cycles and in microseconds. The clock is what a power-capped
+ * product's duration depends on; the cycles can be set against those the MMAs alone need. Any pointer may
+ * be null. No counterpart in the reference. */
+AKR_API int akr_gemm_clock_read(int ctas, double* sm_mhz_mean, double* sm_mhz_min, double* cycles_max, double* us_max);
 
 /* Bytes of scratch the library currently holds on this device (operand splits, split-K partials). */
 AKR_API int akr_workspace_bytes(size_t* bytes);

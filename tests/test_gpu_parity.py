@@ -571,6 +571,25 @@ def test_tf32_tall_pair_tile_kernel_parity():
     assert rel_fro(db.to_numpy()[krows], a[:, krows].astype(np.float64).T @ dc.astype(np.float64)) < TOL_TF32
 
 
+def test_clock_probe_reports_the_sm_clock_of_a_launch():
+    # akr_debug_configure(32768): every CTA records cycles and nanoseconds; the ratio is the SM clock the kernel ran
+    # at (B200: at most 1965 MHz), the cycle count is at least what the MMAs alone need; the product stays correct.
+    lib = cabi.lib()
+    a, b = uniform((2048, 2048), 71), uniform((2048, 2048), 72)
+    A, B = dev(a), dev(b)
+    try:
+        cabi.check(lib.akr_debug_configure(32768, 0))
+        c = cabi.matmul_fwd(A, B, mode=MODE_TF32)
+        cabi.synchronize()
+        r = cabi.gemm_clock_read(148)
+    finally:
+        cabi.check(lib.akr_debug_configure(0, 0))
+    assert 300.0 < r["sm_mhz_min"] <= r["sm_mhz"] < 2100.0, r
+    assert r["cycles"] >= 64 * 512 and r["us"] > 0, r      # one 128 x 256 tile per CTA: 64 k-blocks of 4 MMAs
+    rows = np.array([0, 5, 777, 2047])
+    assert rel_fro(c.to_numpy()[rows], a[rows].astype(np.float64) @ b.astype(np.float64)) < TOL_TF32
+
+
 def _random_case(rng):
     """A random product: batch broadcasting, operand layouts (transposed / sliced views), ragged sizes."""
     nb = int(rng.integers(0, 4))
