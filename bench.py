@@ -43,9 +43,9 @@ def set_size(n):
     FLOP_PER_STEP = 3 * 2 * n ** 3
     WORKLOAD = WORKLOAD.replace("8192", str(n))
 
-# DRAM bytes moved by one launch of the dominant kernel (dA = dC.B^T at 8192^3, TF32 mode), from
-# an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/. None = not captured.
-NCU_TRAFFIC_BYTES = 1886157312  # dA launch at 8192^3: 1 652 729 088 read + 233 428 224 written (forward and dB within 0.5 %)
+# DRAM bytes moved by one launch of the dominant kernel (forward C = A.B at 8192^3, TF32 mode, 512 x 256 tiles on
+# CTA pairs), from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); see profiles/. None = not captured.
+NCU_TRAFFIC_BYTES = 1891505408  # forward launch at 8192^3: 1 654 704 384 read + 236 801 024 written (dA and dB within 0.3 %)
 
 
 
