@@ -2480,14 +2480,16 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
 // contraction is long enough to amortise the pair's hand-shakes: each CTA reads only half of B per MMA and converts
 // only its own share, which is what this shared-memory-bound mode needs (2560^3: 0.253 -> 0.183 ms, 4096 x 1024 x
 // 4096: 0.185 -> 0.147 ms, 64 x (512 x 512 x 2048): 0.369 -> 0.312 ms against one CTA per 128 x 256 tile). Short
-// contractions stay with the general kernel (K = 256 equal, K = 128 8 % slower on pairs). Debug bit 5 routes every
+// contractions stay with the general kernel (K = 128: equal or slower on pairs). Debug bit 5 routes every
 // eligible shape here.
 bool use_pairs(const GemmDesc& g) {
     if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     if (tiles * 4 < gemm_sm100_num_ctas()) return false;
     const long long iters = (long long)g.red * ((g.K + PAIR_BK - 1) / PAIR_BK);
-    return iters >= 20 || (g.debug & 32);
+    // Batches of single 256 x 256 tiles (8192 x 256^3: 0.75 -> 0.70 ms per product) already pay at 16 k-blocks; with
+    // several tiles per batch entry the one-CTA kernel is still ahead there (1024 x 512 x 512 x 256: dA 0.57 against 0.62 ms).
+    return iters >= 20 || (iters >= 16 && g.M <= PAIR_BM && g.N <= PAIR_BN) || (g.debug & 32);
 }
 
 // TF32 mode on CTA pairs: long contractions whose 256 x 256 tiles give most pairs one tile but do not
