@@ -1266,13 +1266,15 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
 //   when this CTA's low parts are written (the peer with an arrive on the leader's barrier whose release is
 //   CTA-scoped: its payload never crosses the cluster through memory - each CTA's tensor core reads its own
 //   tiles, made visible to it by the converter's fence.proxy.async).
-constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 16, PAIR_KC = 4;
+// 32-deep k-blocks (128-byte rows of the K-major tiles): with 16-deep ones the TMA unit moves twice as many rows per
+// byte and every stage hand-over crosses the cluster twice as often (8192^3: 275 -> 287 TFLOP/s, 2048^3: 234 -> 256).
+constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 32, PAIR_KC = 64 / PAIR_BK;
 constexpr int PAIR_A_BYTES = 128 * PAIR_BK * 4, PAIR_B_BYTES = 128 * PAIR_BK * 4;
 constexpr int PAIR_RAW_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
 // The tiles are laid out as PAIR_RAW_STAGES raw stages followed by PAIR_LO_SLOTS low-part slots (16 KB each): a
 // low-part tile only lives from its conversion to the end of its MMAs. Six slots, not fewer: a slot's round trip
 // crosses the cluster twice (the peer's "written" arrive, the leader's commit back) and takes several microseconds.
-constexpr int PAIR_RAW_STAGES = 6, PAIR_LO_SLOTS = 6;
+constexpr int PAIR_RAW_STAGES = 96 / PAIR_BK, PAIR_LO_SLOTS = 96 / PAIR_BK;
 constexpr int PAIR_BAR_BYTES = 512;  // 32 mbarriers + TMEM slot + flags
 constexpr int PAIR_THREADS = 64 + 256 + 64;
 constexpr int PAIR_EPI_WARPS = 8, PAIR_CONV_WARPS = 2;
@@ -1441,8 +1443,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             const uint32_t issuer = ptx::elect_one();
             constexpr uint32_t IDESC = ptx::idesc_tf32(PAIR_BM, PAIR_BN, MAJA, MAJB);
             constexpr uint32_t K_SBO = 8 * PAIR_BK * 4;
-            constexpr uint32_t a_lay = MAJA == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
-            constexpr uint32_t b_lay = MAJB == 0 ? ptx::LAYOUT_SW64 : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t PAIR_K_LAY = PAIR_BK == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
+            constexpr uint32_t a_lay = MAJA == 0 ? PAIR_K_LAY : ptx::LAYOUT_SW128_ATOM32B;
+            constexpr uint32_t b_lay = MAJB == 0 ? PAIR_K_LAY : ptx::LAYOUT_SW128_ATOM32B;
             constexpr uint32_t a_lbo = MAJA == 0 ? 16 : PAIR_BK * 128, b_lbo = MAJB == 0 ? 16 : PAIR_BK * 128;
             constexpr uint32_t a_sbo = MAJA == 0 ? K_SBO : 512, b_sbo = MAJB == 0 ? K_SBO : 512;
             int stage = 0, slot = 0;
@@ -2480,16 +2483,15 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
 // contraction is long enough to amortise the pair's hand-shakes: each CTA reads only half of B per MMA and converts
 // only its own share, which is what this shared-memory-bound mode needs (2560^3: 0.253 -> 0.183 ms, 4096 x 1024 x
 // 4096: 0.185 -> 0.147 ms, 64 x (512 x 512 x 2048): 0.369 -> 0.312 ms against one CTA per 128 x 256 tile). Short
-// contractions stay with the general kernel (K = 128: equal or slower on pairs). Debug bit 5 routes every
-// eligible shape here.
+// contractions (below 256) stay with the general kernel. Debug bit 5 routes every eligible shape here.
 bool use_pairs(const GemmDesc& g) {
     if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     if (tiles * 4 < gemm_sm100_num_ctas()) return false;
     const long long iters = (long long)g.red * ((g.K + PAIR_BK - 1) / PAIR_BK);
-    // Batches of single 256 x 256 tiles (8192 x 256^3: 0.75 -> 0.70 ms per product) already pay at 16 k-blocks; with
-    // several tiles per batch entry the one-CTA kernel is still ahead there (1024 x 512 x 512 x 256: dA 0.57 against 0.62 ms).
-    return iters >= 20 || (iters >= 16 && g.M <= PAIR_BM && g.N <= PAIR_BN) || (g.debug & 32);
+    // Contractions of 256 and more (8 k-blocks): 8192 x 256^3 4.5 against 5.1 ms per fwd + dA + dB step, 1024 x 512 x 512 x
+    // 256 2.0 against 2.1-2.4 ms; at 128 the two kernels are level.
+    return iters >= 8 || (g.debug & 32);
 }
 
 // TF32 mode on CTA pairs: long contractions whose 256 x 256 tiles give most pairs one tile but do not
@@ -2648,7 +2650,11 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     // 16-deep k-blocks: finer stages for the hi+lo mode. The large-tile TF32 kernels keep 32-deep ones: twice as
     // many stage hand-overs cost them 16 % at 8192^3 (debug bit 14 selects the finer ring in diagnostic builds).
     const bool fine = (big || quad) && AKR_DIAG(gd.debug, 16384);
-    const int bk = (g.terms == 3 || fine) ? 16 : BK;
+    // fp32-accurate tiles of 64 and 128 columns take 32-deep k-blocks (128-byte rows): with 16-deep ones the TMA unit
+    // moves twice as many rows per byte and the ring hands over twice as often (config 3's dA, N = 64: 0.216 -> 0.158
+    // ms; 65536 x 128 x 1024: 0.138 -> 0.112 ms). 256-wide tiles have no room for 32-deep raw stages plus low-part slots.
+    const bool fp32_wide_k = g.terms == 3 && !pairs && pick_bn(g) <= 128;
+    const int bk = (g.terms == 3 && pairs) ? PAIR_BK : (((g.terms == 3 && !fp32_wide_k) || fine) ? 16 : BK);
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
@@ -2799,14 +2805,15 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     // fp32-accurate mode: 16-deep k-blocks, chains of 4 of them (64 deep) inside the tensor core.
     int rc;
     if (g.terms == 3) {
-        // raw stages x 24 / 16 / 12 KB in flight from HBM + a short ring of low-part tiles
+        // raw stages (24 KB of 16-deep k-blocks for 256-wide tiles, 32 / 24 KB of 32-deep ones for 128- / 64-wide tiles)
+        // in flight from HBM + a short ring of low-part tiles
         // A low-part slot is busy from its conversion until its MMAs have finished and the commit has arrived:
         // the narrower the tile, the shorter that work and the more slots it takes to cover the hand-over latency.
         const bool short_k = (long long)kp.red * kp.nkb <= 8 && kp.splits == 1;
         rc = bn == 256 ? (short_k ? launch_major<256, 3, 4, 4, 16, 2>(g, kp, grid, stream, err, errlen)
                                   : launch_major<256, 3, 5, 4, 16, 3>(g, kp, grid, stream, err, errlen))
-             : bn == 128 ? launch_major<128, 3, 8, 4, 16, 4>(g, kp, grid, stream, err, errlen)
-                         : launch_major<64, 3, 12, 4, 16, 4>(g, kp, grid, stream, err, errlen);
+             : bn == 128 ? launch_major<128, 3, 4, 2, 32, 2>(g, kp, grid, stream, err, errlen)
+                         : launch_major<64, 3, 6, 2, 32, 2>(g, kp, grid, stream, err, errlen);
     } else if (bn == 64) {
         rc = launch_major<64, 1, 8, 0, 32>(g, kp, grid, stream, err, errlen);
     } else {
