@@ -1643,15 +1643,17 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
 //   (cp.async.bulk.tensor ... .cta_group::2, one destination CTA per copy, no multicast);
 //   leader: warp 1 issues the MMAs; tcgen05.commit signals "stage free" / "accumulator complete" to
 //   both CTAs; warps 2..9 of each CTA drain its 128 rows.
-constexpr int DUO_STAGES = 6;      // ring of load stages when a pair computes several tiles
-constexpr int DUO_STAGES_MAX = 7;  // one tile per pair: the epilogue staging area is a seventh stage until the
-                                   // main loop is over (nothing is loaded ahead for a next tile)
-constexpr int DUO_A_BYTES = 128 * BK * 4, DUO_B_BYTES = 128 * BK * 4;
-constexpr int DUO_STAGE_BYTES = DUO_A_BYTES + DUO_B_BYTES;
+// A stage holds a 64-deep k-block as two 32-deep sub-tiles per operand (a K-major row of the swizzled layout is 128
+// bytes), so that a stage carries eight MMAs like the stages of the large-tile kernels: with 32-deep stages of four
+// MMAs the main loop took 665 cycles per 512 of MMA work, and 601 with the loads switched off - the hand-over of a
+// stage, not its bytes, was what it waited for.
+constexpr int DUO_STAGES = 3, DUO_SUBS = 2;
+constexpr int DUO_SUB_BYTES = 128 * BK * 4;                  // one operand, one 32-deep sub-tile: 16 KB
+constexpr int DUO_A_BYTES = DUO_SUBS * DUO_SUB_BYTES, DUO_B_BYTES = DUO_SUBS * DUO_SUB_BYTES;
+constexpr int DUO_STAGE_BYTES = DUO_A_BYTES + DUO_B_BYTES;   // 64 KB per CTA
 constexpr int DUO_THREADS = 64 + 256;
 constexpr int DUO_EPI_WARPS = 8;
-static_assert(DUO_EPI_WARPS * EPI_STAGE_BYTES == DUO_STAGE_BYTES, "the staging area doubles as a load stage");
-constexpr int DUO_SMEM = DUO_STAGES_MAX * DUO_STAGE_BYTES + 256 + 1024;
+constexpr int DUO_SMEM = DUO_STAGES * DUO_STAGE_BYTES + DUO_EPI_WARPS * EPI_STAGE_BYTES + 256 + 1024;
 
 template <int MAJA, int MAJB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(DUO_THREADS, 1)
@@ -1661,11 +1663,12 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t* smem = smem_raw + pad;
     const uint32_t smem_base = raw_addr + pad;
-    constexpr int SM = DUO_STAGES_MAX;
-    // [6 stages][staging area = 7th stage][barriers]
+    constexpr int SM = DUO_STAGES;
+    constexpr int S = DUO_STAGES;
+    // [3 stages][staging area][barriers]
     uint8_t* epi_stage_base = smem + DUO_STAGES * DUO_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM * DUO_STAGE_BYTES);
-    const uint32_t bar_base = smem_base + SM * DUO_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM * DUO_STAGE_BYTES + DUO_EPI_WARPS * EPI_STAGE_BYTES);
+    const uint32_t bar_base = smem_base + SM * DUO_STAGE_BYTES + DUO_EPI_WARPS * EPI_STAGE_BYTES;
     auto ready_bar = [&](int s) { return bar_base + 8u * s; };             // leader: both CTAs' tiles landed
     auto empty_bar = [&](int s) { return bar_base + 8u * (SM + s); };      // local: stage may be refilled
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * SM + b); };    // local: accumulator complete
@@ -1679,7 +1682,6 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     const bool leader = rank == 0;
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
-    const int S = p.total_tiles <= num_pairs ? DUO_STAGES_MAX : DUO_STAGES;  // grid-uniform
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SM; ++s) {
@@ -1712,7 +1714,8 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     ptx::grid_dep_launch();
     ptx::grid_dep_wait();
     AKR_DIAG_CLK_BEGIN
-    const int total_iters = p.red * p.nkb;
+    const int nkb2 = (p.nkb + DUO_SUBS - 1) / DUO_SUBS;  // 64-deep steps; the last may hold one sub-tile of zeros
+    const int total_iters = p.red * nkb2;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (own tiles, leader's barrier)
@@ -1725,8 +1728,8 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                 const int m_row0 = c.m0 + 128 * (int)rank;  // this CTA's rows of A
                 const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
                 for (int it = 0; it < total_iters; ++it) {
-                    const int r = it / p.nkb;
-                    const int k0 = (it - r * p.nkb) * BK;
+                    const int r = it / nkb2;
+                    const int k00 = (it - r * nkb2) * (DUO_SUBS * BK);
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
@@ -1742,28 +1745,33 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         continue;
                     }
                     if (leader) ptx::mbar_arrive_expect_tx(ready_bar(stage), 2 * DUO_STAGE_BYTES);
-                    const uint32_t da = smem_base + stage * DUO_STAGE_BYTES;
-                    const uint32_t db = da + DUO_A_BYTES;
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
                     const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-                    if (MAJA == 0) {
-                        ptx::tma_load_5d_pair(da, &p.tmA, lb, k0, m_row0, a0, a1, a2);
-                    } else if (p.a_fold) {
-                        ptx::tma_load_5d_pair(da, &p.tmA, lb, 0, k0, m_row0 / CHUNK, a0, a1);
-                    } else {
 #pragma unroll
-                        for (int ch = 0; ch < 128 / CHUNK; ++ch)
-                            ptx::tma_load_5d_pair(da + ch * (BK * 128), &p.tmA, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
-                    }
-                    if (MAJB == 0) {
-                        ptx::tma_load_5d_pair(db, &p.tmB, lb, k0, n_col0, b0, b1, b2);
-                    } else if (p.b_fold) {
-                        ptx::tma_load_5d_pair(db, &p.tmB, lb, 0, k0, n_col0 / CHUNK, b0, b1);
-                    } else {
+                    for (int sub = 0; sub < DUO_SUBS; ++sub) {
+                        // a sub-tile that starts at or behind K is filled with zeros by the copy and still counts its bytes
+                        const int k0 = k00 + sub * BK;
+                        const uint32_t da = smem_base + stage * DUO_STAGE_BYTES + sub * DUO_SUB_BYTES;
+                        const uint32_t db = da + DUO_A_BYTES;
+                        if (MAJA == 0) {
+                            ptx::tma_load_5d_pair(da, &p.tmA, lb, k0, m_row0, a0, a1, a2);
+                        } else if (p.a_fold) {
+                            ptx::tma_load_5d_pair(da, &p.tmA, lb, 0, k0, m_row0 / CHUNK, a0, a1);
+                        } else {
 #pragma unroll
-                        for (int ch = 0; ch < 128 / CHUNK; ++ch)
-                            ptx::tma_load_5d_pair(db + ch * (BK * 128), &p.tmB, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                            for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                ptx::tma_load_5d_pair(da + ch * (BK * 128), &p.tmA, lb, m_row0 + ch * CHUNK, k0, a0, a1, a2);
+                        }
+                        if (MAJB == 0) {
+                            ptx::tma_load_5d_pair(db, &p.tmB, lb, k0, n_col0, b0, b1, b2);
+                        } else if (p.b_fold) {
+                            ptx::tma_load_5d_pair(db, &p.tmB, lb, 0, k0, n_col0 / CHUNK, b0, b1);
+                        } else {
+#pragma unroll
+                            for (int ch = 0; ch < 128 / CHUNK; ++ch)
+                                ptx::tma_load_5d_pair(db + ch * (BK * 128), &p.tmB, lb, n_col0 + ch * CHUNK, k0, b0, b1, b2);
+                        }
                     }
                     if (++stage == S) {
                         stage = 0;
@@ -1805,19 +1813,20 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sa = smem_base + stage * DUO_STAGE_BYTES;
-                    const uint32_t sb = sa + DUO_A_BYTES;
 #pragma unroll
-                    for (int k8 = 0; k8 < BK / UMMA_K; ++k8) {
+                    for (int k8s = 0; k8s < DUO_SUBS * (BK / UMMA_K); ++k8s) {
+                        const int sub = k8s / (BK / UMMA_K), k8 = k8s % (BK / UMMA_K);
+                        const uint32_t sa = smem_base + stage * DUO_STAGE_BYTES + sub * DUO_SUB_BYTES;
+                        const uint32_t sb = sa + DUO_A_BYTES;
                         const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
                         const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
                         const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                         const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                         if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                            if (it == 0 && k8 == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
+                            if (it == 0 && k8s == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
                             continue;
                         }
-                        ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8 == 0) ? 0u : 1u);
+                        ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8s == 0) ? 0u : 1u);
                     }
                     ptx::mma_commit_pair_elected(issuer, empty_bar(stage));  // both CTAs may refill this stage
                     if (++stage == S) {
@@ -2494,20 +2503,23 @@ bool use_pairs(const GemmDesc& g) {
     return iters >= 8 || (g.debug & 32);
 }
 
-// TF32 mode on CTA pairs: long contractions whose 256 x 256 tiles give most pairs one tile but do not
-// fill the machine with one tile per CTA (those go to the 256 x 256 single-CTA kernel, which is faster
-// over many waves: 1.36 ms against 1.58 ms at 8192^3; the pair's stage hand-over crosses the cluster
-// twice per k-block and its 192 KB of stages do not cover that round trip). In this band the pair kernel
-// is 3-6 % faster than 128 x 256 tiles on single CTAs. Debug bit 10 disables it, bit 11 prefers it
-// wherever it is applicable.
+// TF32 mode on CTA pairs (256 x 256 tiles, eight MMAs per 64-deep stage, the epilogue of a tile overlapping the next
+// one's MMAs). Over many waves of long contractions the kernels whose tiles fill the tensor memory move fewer bytes per
+// flop and win (8192^3: 1.35 against 1.48 ms, 4096^3: 0.186 against 0.197); everywhere else this one does:
+//   contractions of 1024 .. 2047 at any tile count, longer ones when the 256 x 256 tiles do not fill the SMs
+//   (2048^3: 0.0259 ms against 0.0315 on 128 x 256 tiles of single CTAs, 4096 x 1024 x 4096: 0.0514 against 0.0563);
+//   contractions of 256 .. 1023 when the tiles keep every pair busy (3072 x 3072 x 512: 0.0176 against 0.0206 ms,
+//   8192 x 8192 x 512: 0.113 against 0.133; with 64 tiles, 2048 x 2048 x 512, single CTAs stay 5 % ahead).
+// Debug bit 10 disables it (diagnostic builds), bit 11 prefers it wherever it is applicable.
 bool use_duo(const GemmDesc& g) {
     if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 1024)) return false;
     const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
-    if (tiles * 4 < gemm_sm100_num_ctas()) return false;
+    const int ctas = gemm_sm100_num_ctas();
+    if (tiles * 4 < ctas) return false;
     if (g.debug & 2048) return true;
-    // many waves of short contractions: the overlapped epilogue still wins (8192 x 4096 x 1024: 0.109 against 0.118 ms)
-    return iters >= 32 && (tiles < gemm_sm100_num_ctas() || iters < 64);
+    if (iters >= 32) return tiles < ctas || iters < 64;
+    return iters >= 8 && tiles * 2 >= ctas;
 }
 
 // 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
