@@ -1850,6 +1850,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
             const Epi epi = tile_epi(p, c);
+            const bool ring_free = t + num_pairs >= p.total_tiles;  // no later tile of this pair is being prefetched
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1u;
             bool got = __all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns));
@@ -1877,7 +1878,12 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                         if (AKR_DIAG(p.debug, 128)) continue;  // timing experiment: no stores
-                        if (use_tma)
+                        if (use_tma && ring_free) {
+                            // behind the pair's last tile the load stages are idle: a staging tile per block, no waits between
+                            const uint32_t off = (uint32_t)((slab * 4 + ch) * 4 * EPI_STAGE_BYTES);
+                            store_block_tma_once(f, reinterpret_cast<float4*>(smem + off + q * EPI_STAGE_BYTES), smem_base + off,
+                                                 &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias, lane, q == 0 && lane == 0, 2 + slab);
+                        } else if (use_tma)
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                             lane, q == 0 && lane == 0, 2 + slab);
                         else
