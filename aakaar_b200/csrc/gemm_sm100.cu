@@ -959,10 +959,11 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
         }
     }
 
-    // the threads that issued bulk stores wait for them before the CTA winds down
+    // the threads that issued bulk stores wait until the copies have read their shared-memory tiles before the CTA
+    // winds down (the writes themselves complete with the grid; waiting for them here cost about 2 kilocycles per CTA)
     if (p.c_tma != 0 && warp >= 2 && warp < 2 + EPI_WARPS && lane == 0 &&
         (WarpStore<BN, TERMS, STAGES, BKT, LO>::value || (hw_warp & 3) == 0))
-        ptx::bulk_wait_all();
+        ptx::bulk_wait_read_all();
 
     // ------------------------------------------------------------ teardown (all paths)
     ptx::tc_fence_before();
@@ -1241,7 +1242,7 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
         }
     }
 
-    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_read_all();
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -1898,7 +1899,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
     }
 
     // ------------------------------------------------------------ teardown (all paths)
-    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_read_all();
     ptx::tc_fence_before();
     __syncthreads();
     ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
@@ -2175,7 +2176,7 @@ gemm_tf32_quad_kernel(const __grid_constant__ KernelParams p) {
     }
 
     // ------------------------------------------------------------ teardown (all paths)
-    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_all();
+    if (p.c_tma != 0 && warp >= 2 && (warp & 3) == 0 && lane == 0) ptx::bulk_wait_read_all();
     ptx::tc_fence_before();
     __syncthreads();
     ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
