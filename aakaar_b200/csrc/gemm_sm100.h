@@ -48,12 +48,14 @@ struct GemmDesc {
     float* partials = nullptr;
     int* counters = nullptr;
     int debug = 0;  // hooks: bit 0 skips the TMA loads (MMA-only timing, results invalid), bit 4 makes the load
-                    // warp never signal (bounded-wait test), bit 5 routes fp32-accurate products with in-kernel low
-                    // parts through the CTA-pair kernel, bit 11 prefers the TF32 CTA-pair kernel wherever it applies.
+                    // warp never signal (bounded-wait test), bit 5 routes fp32-accurate products through the CTA-pair
+                    // kernel wherever its tiles apply, bit 11 prefers the TF32 256 x 256 CTA-pair kernel wherever it
+                    // applies, bit 15 is the clock probe (gemm_sm100_clock_read).
                     // Builds with -DAKR_B200_DIAG add timing experiments: bit 1 skips the MMAs, bit 2 disables the
                     // folded one-box-per-tile maps, bit 3 the 256 x 256 tile kernel, bit 6 one chain per tile in the
                     // fp32 pair kernel, bit 7 skips the output stores, bit 8 disables the TMA-store epilogue, bit 9
-                    // the fp32 CTA-pair kernel, bit 10 the TF32 CTA-pair kernel, bit 12 dependent launch.
+                    // the fp32 CTA-pair kernel, bit 10 the TF32 CTA-pair kernel, bit 12 dependent launch, bit 13 the
+                    // 512 x 256 pair tiles, bit 14 selects 16-deep k-blocks in the large-tile TF32 kernels.
 };
 
 // True when the operand can be read by TMA as it lies (16-byte aligned base, unit stride on one
