@@ -2524,8 +2524,9 @@ bool use_pairs(const GemmDesc& g) {
 // flop and win (8192^3: 1.35 against 1.48 ms, 4096^3: 0.186 against 0.197); everywhere else this one does:
 //   contractions of 1024 .. 2047 at any tile count, longer ones when the 256 x 256 tiles do not fill the SMs
 //   (2048^3: 0.0259 ms against 0.0315 on 128 x 256 tiles of single CTAs, 4096 x 1024 x 4096: 0.0514 against 0.0563);
-//   contractions of 256 .. 1023 when the tiles keep every pair busy (3072 x 3072 x 512: 0.0176 against 0.0206 ms,
-//   8192 x 8192 x 512: 0.113 against 0.133; with 64 tiles, 2048 x 2048 x 512, single CTAs stay 5 % ahead).
+//   contractions of 256 .. 1023 when the tiles keep every pair busy and the product is compute-bound
+//   (3072 x 3072 x 512: 0.0176 against 0.0206 ms, 8192 x 8192 x 512: 0.113 against 0.133, 2048 x 2048 x 512 with its
+//   64 tiles: 0.0130 against 0.0139).
 // Debug bit 10 disables it (diagnostic builds), bit 11 prefers it wherever it is applicable.
 bool use_duo(const GemmDesc& g) {
     if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 1024)) return false;
@@ -2535,7 +2536,11 @@ bool use_duo(const GemmDesc& g) {
     if (tiles * 16 < ctas) return false;  // from ten tiles on (1536^3, 36 tiles: 0.0240 -> 0.0202 ms; 1024^3, 16: 0.0162 -> 0.0157)
     if (g.debug & 2048) return true;
     if (iters >= 32) return tiles < ctas || iters < 64;
-    return iters >= 8 && tiles * 2 >= ctas;
+    // Short contractions only when the product is compute-bound: at 2 M N K / 4 (MK + KN + MN) below about 80 flop per
+    // byte (batches of 256^3: 43) the three-stage kernel with its per-warp store boxes is the faster streamer
+    // (8192 x 256^3: 0.93-0.98 ms per product against 1.01).
+    const double flop_per_byte = 2.0 * g.M * g.N * g.K / (4.0 * ((double)g.M * g.K + (double)g.K * g.N + (double)g.M * g.N));
+    return iters >= 8 && tiles * 4 >= ctas && flop_per_byte >= 80.0;
 }
 
 // 256 x 256 tiles pay off when they alone fill the machine and the contraction is long enough to
