@@ -466,6 +466,20 @@ def test_bounded_wait_abort_is_reported_and_recoverable():
             cabi.synchronize()
         assert e.value.code == cabi.ERR_ABORTED
         cabi.synchronize()
+        # the same product on the fp32-accurate CTA-pair kernel (its converter warps wait for tiles that never land)
+        cabi.matmul_fwd(A2, B2, mode=MODE_FP32)
+        with pytest.raises(cabi.AkrError) as e:
+            cabi.synchronize()
+        assert e.value.code == cabi.ERR_ABORTED
+        cabi.synchronize()
+        # 512 x 256 tiles on pairs (128 of them, 32 k-blocks)
+        A3, B3 = dev(uniform((4096, 1024), 5)), dev(uniform((1024, 4096), 6))
+        cabi.synchronize()
+        cabi.matmul_fwd(A3, B3, mode=MODE_TF32)
+        with pytest.raises(cabi.AkrError) as e:
+            cabi.synchronize()
+        assert e.value.code == cabi.ERR_ABORTED
+        cabi.synchronize()
     finally:
         cabi.check(lib.akr_debug_configure(0, 0))
     # the context is still usable and results are right again
