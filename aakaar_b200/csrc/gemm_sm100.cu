@@ -1740,7 +1740,10 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                 const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
                 const int m_row0 = c.m0 + 128 * (int)rank;  // this CTA's rows of A
                 const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
-                for (int it = 0; it < total_iters; ++it) {
+                // a split contraction: this tile's share of the (summed batch, k) steps
+                const int it0 = (int)((long long)total_iters * c.split / p.splits);
+                const int it1 = (int)((long long)total_iters * (c.split + 1) / p.splits);
+                for (int it = it0; it < it1; ++it) {
                     const int r = it / nkb2;
                     const int k00 = (it - r * nkb2) * (DUO_SUBS * BK);
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
@@ -1820,7 +1823,10 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                 }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * PAIR_BN;
-                for (int it = 0; it < total_iters; ++it) {
+                const int split = t % p.splits;
+                const int it0 = (int)((long long)total_iters * split / p.splits);
+                const int it1 = (int)((long long)total_iters * (split + 1) / p.splits);
+                for (int it = it0; it < it1; ++it) {
                     if (!ptx::mbar_wait(ready_bar(stage), phase, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
@@ -1836,10 +1842,10 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                         const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                         const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
                         if (AKR_DIAG(p.debug, 2)) {  // timing experiment: loads and hand-shakes only
-                            if (it == 0 && k8s == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
+                            if (it == it0 && k8s == 0) ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, 0u);
                             continue;
                         }
-                        ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == 0 && k8s == 0) ? 0u : 1u);
+                        ptx::mma_tf32_ss_pair_elected(issuer, d_tmem, da, db, IDESC, (it == it0 && k8s == 0) ? 0u : 1u);
                     }
                     ptx::mma_commit_pair_elected(issuer, empty_bar(stage));  // both CTAs may refill this stage
                     if (++stage == S) {
@@ -1854,7 +1860,8 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         // ------------------------------------------------------------ epilogue (warps 2..9): this CTA's 128 rows
         const int q = warp & 3;
         const int slab = (warp - 2) >> 2;
-        const bool vec = p.vec_ok != 0;
+        const bool split_mode = p.splits > 1;  // partial tiles to scratch, added up by the reduction kernel
+        const bool vec = split_mode ? (p.N & 3) == 0 : p.vec_ok != 0;
         const bool use_tma = p.c_tma != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (slab * 4 + q) * EPI_STAGE_BYTES);
         const uint32_t slab_tile_addr = smem_base + DUO_STAGES * DUO_STAGE_BYTES + slab * 4 * EPI_STAGE_BYTES;
@@ -1862,7 +1869,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs, ++local) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
-            const Epi epi = tile_epi(p, c);
+            const Epi epi = split_mode ? plain_epi() : tile_epi(p, c);
             const bool ring_free = t + num_pairs >= p.total_tiles;  // no later tile of this pair is being prefetched
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1u;
@@ -1876,7 +1883,9 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
             const int row_base = c.m0 + 128 * (int)rank;
             const int row0 = row_base + q * 32;
             const int slab_col0 = c.n0 + slab * 128;
-            float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            float* out_base = split_mode ? p.partials + ((size_t)c.split * (p.o0 * p.o1) + c.batch) * (size_t)p.M * (size_t)p.N
+                                         : p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            const long long out_ld = split_mode ? p.N : p.ldc;
             const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + buf * PAIR_BN + slab * 128;
             if (row_base < p.M) {  // CTA-uniform: the peer's half may lie below the matrix
 #pragma unroll 1
@@ -1900,7 +1909,7 @@ gemm_tf32_duo_kernel(const __grid_constant__ KernelParams p) {
                             store_block_tma(f, my_stage, slab_tile_addr, &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias,
                                             lane, q == 0 && lane == 0, 2 + slab);
                         else
-                            store_block_warp<true>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, epi, lane);
+                            store_block_warp<true>(f, my_stage, out_base, out_ld, row0, p.M, col0, p.N, vec, epi, lane);
                     }
                 }
             }
@@ -2534,8 +2543,12 @@ bool use_pairs(const GemmDesc& g) {
 //   64 tiles: 0.0130 against 0.0139).
 // Debug bit 10 disables it (diagnostic builds), bit 11 prefers it wherever it is applicable.
 bool use_duo(const GemmDesc& g) {
-    if (g.terms != 1 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 1024)) return false;
-    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+    if (g.terms != 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 1024)) return false;
+    // split contractions too (each pair takes a share of the k-steps of a tile), when a reduction kernel adds the
+    // partial tiles up; the single-launch form with tile counters stays with the one-CTA kernel
+    if (g.splits > 1 && (g.counters != nullptr || AKR_DIAG(g.debug, 524288))) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN) *
+                            (g.splits > 1 ? g.splits : 1);
     const long long iters = (long long)g.red * ((g.K + BK - 1) / BK);
     const int ctas = gemm_sm100_num_ctas();
     if (tiles * 16 < ctas) return false;  // from ten tiles on (1536^3, 36 tiles: 0.0240 -> 0.0202 ms; 1024^3, 16: 0.0162 -> 0.0157)
@@ -2656,6 +2669,71 @@ void gemm_sm100_split_scratch(const GemmDesc& g, size_t* partial_bytes, size_t* 
     const size_t tiles = (size_t)g.o0 * g.o1 * ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn);
     *partial_bytes = g.splits > 1 ? (size_t)g.splits * g.o0 * g.o1 * g.M * g.N * sizeof(float) : 0;
     *counter_count = g.splits > 1 ? tiles : 0;
+}
+
+// Split contraction without tile counters: the partial tiles are added up by a second, GPU-wide kernel.
+static int launch_split_reduce(const GemmDesc& g, const KernelParams& kp, cudaStream_t stream, char* err, int errlen) {
+    SplitReduceParams rp;
+    std::memset(&rp, 0, sizeof(rp));
+    rp.partials = g.partials;
+    rp.C = g.C;
+    rp.bias = g.bias;
+    rp.aux = g.aux_op ? g.aux : nullptr;
+    rp.ldc = g.ldc; rp.c_bs0 = g.c_bs0; rp.c_bs1 = g.c_bs1;
+    rp.aux_ld = g.aux_ld; rp.aux_cs = g.aux_cs; rp.aux_bs0 = g.aux_bs0; rp.aux_bs1 = g.aux_bs1;
+    rp.M = g.M; rp.N = g.N; rp.o1 = g.o1; rp.nbatch = g.o0 * g.o1; rp.splits = kp.splits;
+    rp.accumulate = g.accumulate; rp.aux_op = g.aux_op;
+    rp.alpha = g.alpha; rp.beta = g.beta;
+    const bool vec = kp.vec_ok && (g.N & 3) == 0;
+    const size_t work = (size_t)rp.nbatch * g.M * (size_t)(vec ? g.N / 4 : g.N);
+    size_t blocks = (work + 255) / 256;
+    const size_t cap = (size_t)gemm_sm100_num_ctas() * 8;
+    if (blocks > cap) blocks = cap;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (g_pdl_off || gemm_sm100_cta_limit_active()) ? 0 : 1;
+    if (vec) cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<true>, rp);
+    else cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<false>, rp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        seterr(err, errlen, cudaGetErrorString(e));
+        return -3;
+    }
+    return 0;
+}
+
+// What the clock probe recorded for the last GEMM launch of the current device: per-CTA cycles and nanoseconds.
+int gemm_sm100_clock_read(int ctas, double* mhz_mean, double* mhz_min, double* cycles_max, double* us_max) {
+    static unsigned long long h[2 * 256];
+    if (ctas < 1) ctas = 1;
+    if (ctas > 256) ctas = 256;
+    if (cudaMemcpyFromSymbol(h, g_clock_probe, sizeof(h)) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    double sum = 0, mn = 1e30, um = 0, cm = 0;
+    int n = 0;
+    for (int i = 0; i < ctas; ++i) {
+        if (h[2 * i + 1] == 0) continue;
+        const double mhz = 1e3 * (double)h[2 * i] / (double)h[2 * i + 1];
+        sum += mhz;
+        ++n;
+        if (mhz < mn) mn = mhz;
+        if ((double)h[2 * i + 1] * 1e-3 > um) um = (double)h[2 * i + 1] * 1e-3;
+        if ((double)h[2 * i] > cm) cm = (double)h[2 * i];
+    }
+    if (n == 0) return -2;
+    if (mhz_mean) *mhz_mean = sum / n;
+    if (mhz_min) *mhz_min = mn;
+    if (cycles_max) *cycles_max = cm;
+    if (us_max) *us_max = um;
+    return 0;
 }
 
 int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, char* err,
@@ -2811,12 +2889,15 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
             }
         }
         if (duo) {
+            int rcd;
             switch (sel) {
-                case 0: return launch_pair_variant<PAIR_DUO, 0, 0>(kp, 2 * npairs, stream, err, errlen);
-                case 1: return launch_pair_variant<PAIR_DUO, 0, 1>(kp, 2 * npairs, stream, err, errlen);
-                case 2: return launch_pair_variant<PAIR_DUO, 1, 0>(kp, 2 * npairs, stream, err, errlen);
-                default: return launch_pair_variant<PAIR_DUO, 1, 1>(kp, 2 * npairs, stream, err, errlen);
+                case 0: rcd = launch_pair_variant<PAIR_DUO, 0, 0>(kp, 2 * npairs, stream, err, errlen); break;
+                case 1: rcd = launch_pair_variant<PAIR_DUO, 0, 1>(kp, 2 * npairs, stream, err, errlen); break;
+                case 2: rcd = launch_pair_variant<PAIR_DUO, 1, 0>(kp, 2 * npairs, stream, err, errlen); break;
+                default: rcd = launch_pair_variant<PAIR_DUO, 1, 1>(kp, 2 * npairs, stream, err, errlen); break;
             }
+            if (rcd != 0 || kp.splits == 1) return rcd;
+            return launch_split_reduce(g, kp, stream, err, errlen);
         }
         switch (sel) {
             case 0: return launch_pair_variant<PAIR_FP32, 0, 0>(kp, 2 * npairs, stream, err, errlen);
@@ -2863,68 +2944,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     }
     if (rc != 0 || kp.splits == 1 || g.counters != nullptr) return rc;
 
-    // Split contraction without tile counters: the partial tiles are added up by a second, GPU-wide kernel.
-    SplitReduceParams rp;
-    std::memset(&rp, 0, sizeof(rp));
-    rp.partials = g.partials;
-    rp.C = g.C;
-    rp.bias = g.bias;
-    rp.aux = g.aux_op ? g.aux : nullptr;
-    rp.ldc = g.ldc; rp.c_bs0 = g.c_bs0; rp.c_bs1 = g.c_bs1;
-    rp.aux_ld = g.aux_ld; rp.aux_cs = g.aux_cs; rp.aux_bs0 = g.aux_bs0; rp.aux_bs1 = g.aux_bs1;
-    rp.M = g.M; rp.N = g.N; rp.o1 = g.o1; rp.nbatch = g.o0 * g.o1; rp.splits = kp.splits;
-    rp.accumulate = g.accumulate; rp.aux_op = g.aux_op;
-    rp.alpha = g.alpha; rp.beta = g.beta;
-    const bool vec = kp.vec_ok && (g.N & 3) == 0;
-    const size_t work = (size_t)rp.nbatch * g.M * (size_t)(vec ? g.N / 4 : g.N);
-    size_t blocks = (work + 255) / 256;
-    const size_t cap = (size_t)gemm_sm100_num_ctas() * 8;
-    if (blocks > cap) blocks = cap;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)blocks);
-    cfg.blockDim = dim3(256);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = (g_pdl_off || gemm_sm100_cta_limit_active()) ? 0 : 1;
-    if (vec) cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<true>, rp);
-    else cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<false>, rp);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        seterr(err, errlen, cudaGetErrorString(e));
-        return -3;
-    }
-    return 0;
-}
-
-// What the clock probe recorded for the last GEMM launch of the current device: per-CTA cycles and nanoseconds.
-int gemm_sm100_clock_read(int ctas, double* mhz_mean, double* mhz_min, double* cycles_max, double* us_max) {
-    static unsigned long long h[2 * 256];
-    if (ctas < 1) ctas = 1;
-    if (ctas > 256) ctas = 256;
-    if (cudaMemcpyFromSymbol(h, g_clock_probe, sizeof(h)) != cudaSuccess) {
-        cudaGetLastError();
-        return -1;
-    }
-    double sum = 0, mn = 1e30, um = 0, cm = 0;
-    int n = 0;
-    for (int i = 0; i < ctas; ++i) {
-        if (h[2 * i + 1] == 0) continue;
-        const double mhz = 1e3 * (double)h[2 * i] / (double)h[2 * i + 1];
-        sum += mhz;
-        ++n;
-        if (mhz < mn) mn = mhz;
-        if ((double)h[2 * i + 1] * 1e-3 > um) um = (double)h[2 * i + 1] * 1e-3;
-        if ((double)h[2 * i] > cm) cm = (double)h[2 * i];
-    }
-    if (n == 0) return -2;
-    if (mhz_mean) *mhz_mean = sum / n;
-    if (mhz_min) *mhz_min = mn;
-    if (cycles_max) *cycles_max = cm;
-    if (us_max) *us_max = um;
-    return 0;
+    return launch_split_reduce(g, kp, stream, err, errlen);
 }
 
 }  // namespace akr
