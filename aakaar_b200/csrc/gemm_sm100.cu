@@ -1361,6 +1361,11 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     ptx::grid_dep_wait();
     AKR_DIAG_CLK_BEGIN
     const int total_iters = p.red * p.nkb;
+    // A split contraction gives every tile-split its share [first, first + count) of the (summed batch, k) steps.
+    auto split_first = [&](int t) { return (int)((long long)total_iters * (t % p.splits) / p.splits); };
+    auto split_count = [&](int t) {
+        return (int)((long long)total_iters * (t % p.splits + 1) / p.splits) - (int)((long long)total_iters * (t % p.splits) / p.splits);
+    };
     const int kc = (AKR_DIAG(p.debug, 64)) ? 0x3fffffff : PAIR_KC;  // bit 6: one chain per tile (timing experiment)
 
     // 128 promotion accumulators per epilogue thread do not fit the uniform 168 registers of a 12-warp CTA (they
@@ -1379,9 +1384,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                 const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
                 const int m_row0 = c.m0 + 128 * (int)rank;  // this CTA's rows of A
                 const int n_col0 = c.n0 + 128 * (int)rank;  // this CTA's columns of B
-                for (int it = 0; it < total_iters; ++it) {
-                    const int r = it / p.nkb;
-                    const int k0 = (it - r * p.nkb) * PAIR_BK;
+                const int first = split_first(t), n_it = split_count(t);
+                for (int it = 0; it < n_it; ++it) {
+                    const int r = (first + it) / p.nkb;
+                    const int k0 = (first + it - r * p.nkb) * PAIR_BK;
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                         ok = false;
                         break;
@@ -1466,8 +1472,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             int handoff = 0;
             bool ok = true;
             for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
-                for (int cs = 0, ce = 0; cs < total_iters && ok; cs = ce) {
-                    ce = (total_iters - cs > kc) ? cs + kc : total_iters;
+                const int n_it = split_count(t);
+                for (int cs = 0, ce = 0; cs < n_it && ok; cs = ce) {
+                    ce = (n_it - cs > kc) ? cs + kc : n_it;
                     const int buf = handoff & 1;
                     const uint32_t acc_phase = (handoff >> 1) & 1u;
                     if (!ptx::mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) {
@@ -1530,7 +1537,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         bool ok = true;
         const uint32_t leader_ready0 = ptx::map_to_cta(ready_bar(0), 0);  // the leader's ready barriers, seen from here
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
-            for (int it = 0; it < total_iters; ++it) {
+            const int n_it = split_count(t);
+            for (int it = 0; it < n_it; ++it) {
                 // the raw tiles have landed, and the MMAs that read this low-part slot last have finished
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait_warp(landed_bar(stage), phase, abort_flag, p.wait_limit_ns)) ||
                     !__all_sync(0xffffffffu, ptx::mbar_wait_warp(lofree_bar(slot), slot_phase ^ 1u, abort_flag, p.wait_limit_ns))) {
@@ -1581,7 +1589,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         // ------------------------------------------------------------ epilogue (roles 2..9), fp32 promotion
         const int q = hw_warp & 3;  // TMEM lane quarter of this hardware warp
         const int slab = (warp - 2) >> 2;
-        const bool vec = p.vec_ok != 0;
+        const bool split_mode = p.splits > 1;  // partial tiles to scratch, added up by the reduction kernel
+        const bool vec = split_mode ? (p.N & 3) == 0 : p.vec_ok != 0;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
         int handoff = 0;
         bool ok = true;
@@ -1589,11 +1598,13 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
             const int row0 = c.m0 + 128 * (int)rank + q * 32;
             const int slab_col0 = c.n0 + slab * 128;
-            float* out_base = p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            float* out_base = split_mode ? p.partials + ((size_t)c.split * (p.o0 * p.o1) + c.batch) * (size_t)p.M * (size_t)p.N
+                                         : p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
+            const int n_it = split_count(t);
             float acc[128];
 #pragma unroll
             for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-            for (int cs = 0; cs < total_iters && ok; cs = (total_iters - cs > kc) ? cs + kc : total_iters) {
+            for (int cs = 0; cs < n_it && ok; cs = (n_it - cs > kc) ? cs + kc : n_it) {
                 const int buf = handoff & 1;
                 const uint32_t acc_phase = (handoff >> 1) & 1u;
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait_warp(tfull_bar(buf), acc_phase, abort_flag, p.wait_limit_ns))) {
@@ -1626,7 +1637,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
-                        store_block_warp<false>(f, my_stage, out_base, p.ldc, row0, p.M, col0, p.N, vec, lean_epi(p), lane);
+                        store_block_warp<false>(f, my_stage, out_base, split_mode ? (long long)p.N : p.ldc, row0, p.M, col0, p.N, vec,
+                                                split_mode ? plain_epi() : lean_epi(p), lane);
                     }
                 }
             }
@@ -2524,8 +2536,11 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
 // 4096: 0.185 -> 0.147 ms, 64 x (512 x 512 x 2048): 0.369 -> 0.312 ms against one CTA per 128 x 256 tile). Short
 // contractions (below 256) stay with the general kernel. Debug bit 5 routes every eligible shape here.
 bool use_pairs(const GemmDesc& g) {
-    if (g.terms != 3 || g.splits > 1 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
-    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN);
+    if (g.terms != 3 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
+    // split contractions too, when a reduction kernel adds the partial tiles up (no tile counters)
+    if (g.splits > 1 && (g.counters != nullptr || AKR_DIAG(g.debug, 524288))) return false;
+    const long long tiles = (long long)g.o0 * g.o1 * ((g.M + PAIR_BM - 1) / PAIR_BM) * ((g.N + PAIR_BN - 1) / PAIR_BN) *
+                            (g.splits > 1 ? g.splits : 1);
     if (tiles * 4 < gemm_sm100_num_ctas()) return false;
     const long long iters = (long long)g.red * ((g.K + PAIR_BK - 1) / PAIR_BK);
     // Contractions of 256 and more (8 k-blocks): 8192 x 256^3 4.5 against 5.1 ms per fwd + dA + dB step, 1024 x 512 x 512 x
@@ -2899,12 +2914,15 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
             if (rcd != 0 || kp.splits == 1) return rcd;
             return launch_split_reduce(g, kp, stream, err, errlen);
         }
+        int rcp;
         switch (sel) {
-            case 0: return launch_pair_variant<PAIR_FP32, 0, 0>(kp, 2 * npairs, stream, err, errlen);
-            case 1: return launch_pair_variant<PAIR_FP32, 0, 1>(kp, 2 * npairs, stream, err, errlen);
-            case 2: return launch_pair_variant<PAIR_FP32, 1, 0>(kp, 2 * npairs, stream, err, errlen);
-            default: return launch_pair_variant<PAIR_FP32, 1, 1>(kp, 2 * npairs, stream, err, errlen);
+            case 0: rcp = launch_pair_variant<PAIR_FP32, 0, 0>(kp, 2 * npairs, stream, err, errlen); break;
+            case 1: rcp = launch_pair_variant<PAIR_FP32, 0, 1>(kp, 2 * npairs, stream, err, errlen); break;
+            case 2: rcp = launch_pair_variant<PAIR_FP32, 1, 0>(kp, 2 * npairs, stream, err, errlen); break;
+            default: rcp = launch_pair_variant<PAIR_FP32, 1, 1>(kp, 2 * npairs, stream, err, errlen); break;
         }
+        if (rcp != 0 || kp.splits == 1) return rcp;
+        return launch_split_reduce(g, kp, stream, err, errlen);
     }
 #ifdef AKR_B200_DIAG
     if (big) {
