@@ -2662,8 +2662,12 @@ int gemm_sm100_pick_splits(const GemmDesc& g) {
     const int ctas = gemm_sm100_num_ctas();
     // The fp32-accurate mode spends three times as long per k-block, so splitting pays for shorter contractions
     // there (measured: 1024^3 36.6 -> 25.3 us, 768^3 28.8 -> 19.6 us; TF32 mode gains nothing below 64 k-blocks).
-    const int min_iters = g.terms == 3 ? 16 : 64;
-    const int min_per = g.terms == 3 ? 4 : 16;  // k-blocks (of 32) left to one split at least
+    // (TF32 with very few tiles - at most a quarter of the SMs busy - splits from 32 k-blocks on, 8 left per split:
+    // 768 x 768 x 1536 0.0217 -> 0.0159 ms, 512 x 512 x 1024 0.0161 -> 0.0128; with more tiles that costs: 1536 x 1536 x
+    // 1024 0.0160 -> 0.0210.)
+    const bool few = tiles * 4 <= ctas;
+    const int min_iters = g.terms == 3 ? 16 : (few ? 32 : 64);
+    const int min_per = g.terms == 3 ? 4 : (few ? 8 : 16);  // k-blocks (of 32) left to one split at least
     if (tiles * 2 > ctas || iters < min_iters) return 1;
     long long s = ctas / tiles;
     const long long max_by_work = iters / min_per;
