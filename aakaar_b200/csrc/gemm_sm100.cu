@@ -988,8 +988,9 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 }
 
 
-// ---------------------------------------------------------------------------------- 256 x 256 tiles
-// TF32 kernel for large products: one CTA computes a 256 x 256 tile as two 128 x 256 accumulators
+// ---------------------------------------------------------------------------------- 256 x 256 tiles (diagnostic builds)
+// The first TF32 kernel for large products, kept as the reference the 512 x 256 pair tiles are measured against:
+// one CTA computes a 256 x 256 tile as two 128 x 256 accumulators
 // that share the B tile in shared memory. Per flop it pulls one third fewer bytes from L2 than the
 // 128 x 256 kernel above, whose speed is set by the L2 -> SM load rate rather than by the MMA pipe.
 // Both accumulators fill all 512 TMEM columns, so a tile's MMAs may only start on an accumulator
@@ -997,12 +998,13 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
 // No split-K and no fp32 promotion here; those stay with the general kernel.
 // BKT = fp32 per k-block: 192 KB of load stages either way, as 3 x 64 KB (BKT = 32, the shipped form) or 6 x 32 KB
 // (BKT = 16, diagnostic builds: twice as many stage hand-overs made 8192^3 16 % slower, 1.60 against 1.38 ms).
-constexpr int BIG_BM = 256, BIG_BN = 256;
+constexpr int BIG_BM = 256, BIG_BN = 256;  // (also the tile count the routing of the pair tiles is stated in)
+
+#ifdef AKR_B200_DIAG
 constexpr int BIG_RING_BYTES = 192 * 1024;
 constexpr int BIG_THREADS = 64 + 256;
 constexpr int BIG_SMEM = BIG_RING_BYTES + 1024 + 256 + 8 * EPI_STAGE_BYTES;
 
-#ifdef AKR_B200_DIAG  // the single-CTA form is what the pair form is measured against: diagnostic builds only
 template <int MAJA, int MAJB, int BKT>
 __global__ void __launch_bounds__(BIG_THREADS, 1)
 gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
