@@ -468,12 +468,6 @@ int check_out(const akr_view* c, int nd, const int64_t* shape, const char* name)
     return AKR_OK;
 }
 
-size_t numel(const akr_view* v) {
-    size_t n = 1;
-    for (int i = 0; i < v->ndim; ++i) n *= (size_t)v->shape[i];
-    return n;
-}
-
 StridedView to_strided(const akr_view* v) {
     StridedView s;
     s.ptr = (const float*)v->data;
