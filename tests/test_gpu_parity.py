@@ -604,6 +604,31 @@ def test_clock_probe_reports_the_sm_clock_of_a_launch():
     assert rel_fro(c.to_numpy()[rows], a[rows].astype(np.float64) @ b.astype(np.float64)) < TOL_TF32
 
 
+@pytest.mark.parametrize("mode,tol", [(MODE_TF32, TOL_TF32), (MODE_FP32, TOL_FP32)])
+def test_split_contractions_on_cta_pairs(mode, tol):
+    # Weight-gradient shapes (few output tiles, long contraction): the contraction is split over CTA pairs, every pair
+    # writes a partial tile and the reduction kernel adds them. Ragged edges, the four layouts, a batch, a bias row
+    # (applied by the reduction), and C += (the reduction reads the old C).
+    rng = np.random.default_rng(97)
+    for (bt, M, N, K, ta, tb) in (((), 512, 512, 4096, 1, 0), ((), 1000, 700, 5000, 0, 0), ((), 768, 768, 3072, 0, 1),
+                                  ((2,), 300, 520, 2500, 1, 1), ((), 1536, 1536, 4096, 0, 0)):
+        a = uniform(bt + ((K, M) if ta else (M, K)), int(rng.integers(1 << 30)))
+        b = uniform(bt + ((N, K) if tb else (K, N)), int(rng.integers(1 << 30)))
+        A, B = dev(a), dev(b)
+        nd = len(bt) + 2
+        Av = A.transpose(nd - 2, nd - 1) if ta else A
+        Bv = B.transpose(nd - 2, nd - 1) if tb else B
+        ref = np.matmul((np.swapaxes(a, -1, -2) if ta else a).astype(np.float64), (np.swapaxes(b, -1, -2) if tb else b).astype(np.float64))
+        assert rel_fro(cabi.matmul_fwd(Av, Bv, mode=mode).to_numpy(), ref) < tol, (bt, M, N, K, ta, tb)
+        bias = normal((1, N), 98)
+        assert rel_fro(cabi.matmul_fwd(Av, Bv, bias=dev(bias), mode=mode).to_numpy(), ref + bias) < tol, (bt, M, N, K)
+    # the same through the backward entry point: dB = A^T dC with a long batch of rows
+    a, b, dc = uniform((6000, 520), 99), uniform((520, 700), 100), uniform((6000, 700), 101)
+    da, db = cabi.matmul_bwd(dev(a), dev(b), dev(dc), mode=mode)
+    assert rel_fro(db.to_numpy(), a.astype(np.float64).T @ dc.astype(np.float64)) < tol
+    assert rel_fro(da.to_numpy(), dc.astype(np.float64) @ b.astype(np.float64).T) < tol
+
+
 def _random_case(rng):
     """A random product: batch broadcasting, operand layouts (transposed / sliced views), ragged sizes."""
     nb = int(rng.integers(0, 4))
