@@ -441,6 +441,12 @@ template <int BN, int MAJA, int MAJB, int TERMS, int STAGES, int KC, int BKT, in
 __global__ void __launch_bounds__(num_threads<BN, TERMS>(), 1)
 gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     using L = SmemLayout<BN, TERMS, BKT>;
+    // A k-block deeper than 32 is held as sub-tiles of 32 (a K-major row of the swizzled layout is 128 bytes): BKT = 64
+    // gives the narrow TF32 tiles stages of eight MMAs (handing a stage over costs more than filling it).
+    constexpr int SUB = BKT > 32 ? 32 : BKT;
+    constexpr int SUBS = BKT / SUB;
+    static_assert(SUBS == 1 || TERMS == 1, "sub-tiles are a TF32-mode layout");
+    constexpr int A_SUB_BYTES = BM * SUB * 4, B_SUB_BYTES = BN * SUB * 4;
     constexpr int SLABS = slabs_of(BN);
     constexpr int SLAB_W = slab_cols(BN);
     constexpr int EPI_WARPS = SLABS * 4;
@@ -559,29 +565,32 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                     const int bcv[4] = {c.i1, c.i0, r, 0};
                     const int a0 = bcv[p.a_sel[0]], a1 = bcv[p.a_sel[1]], a2 = bcv[p.a_sel[2]];
                     const int b0 = bcv[p.b_sel[0]], b1 = bcv[p.b_sel[1]], b2 = bcv[p.b_sel[2]];
-                    {
+#pragma unroll
+                    for (int sub = 0; sub < SUBS; ++sub) {
+                        // (a sub-tile that starts at or behind K is filled with zeros by the copy and still counts its bytes)
                         const CUtensorMap* ma = &p.tmA;
                         const CUtensorMap* mb = &p.tmB;
-                        const uint32_t da = sa;
-                        const uint32_t db = sb;
+                        const uint32_t da = sa + sub * A_SUB_BYTES;
+                        const uint32_t db = sb + sub * B_SUB_BYTES;
+                        const int ks = k0 + sub * SUB;
                         if (MAJA == 0) {
-                            ptx::tma_load_5d(da, ma, fb, k0, c.m0, a0, a1, a2);
+                            ptx::tma_load_5d(da, ma, fb, ks, c.m0, a0, a1, a2);
                         } else if (p.a_fold) {
-                            ptx::tma_load_5d(da, ma, fb, 0, k0, c.m0 / CHUNK, a0, a1);
+                            ptx::tma_load_5d(da, ma, fb, 0, ks, c.m0 / CHUNK, a0, a1);
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BM / CHUNK; ++ch)
-                                ptx::tma_load_5d(da + ch * (BKT * 128), ma, fb, c.m0 + ch * CHUNK, k0,
+                                ptx::tma_load_5d(da + ch * (SUB * 128), ma, fb, c.m0 + ch * CHUNK, ks,
                                                  a0, a1, a2);
                         }
                         if (MAJB == 0) {
-                            ptx::tma_load_5d(db, mb, fb, k0, c.n0, b0, b1, b2);
+                            ptx::tma_load_5d(db, mb, fb, ks, c.n0, b0, b1, b2);
                         } else if (p.b_fold) {
-                            ptx::tma_load_5d(db, mb, fb, 0, k0, c.n0 / CHUNK, b0, b1);
+                            ptx::tma_load_5d(db, mb, fb, 0, ks, c.n0 / CHUNK, b0, b1);
                         } else {
 #pragma unroll
                             for (int ch = 0; ch < BN / CHUNK; ++ch)
-                                ptx::tma_load_5d(db + ch * (BKT * 128), mb, fb, c.n0 + ch * CHUNK, k0,
+                                ptx::tma_load_5d(db + ch * (SUB * 128), mb, fb, c.n0 + ch * CHUNK, ks,
                                                  b0, b1, b2);
                         }
                     }
@@ -651,25 +660,26 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
                         const uint32_t sa_lo = smem_base + LO_BASE + lo_slot * L::STAGE_BYTES;
                         const uint32_t sb_lo = sa_lo + L::A_BYTES;
 #pragma unroll
-                        for (int k8 = 0; k8 < BKT / UMMA_K; ++k8) {
+                        for (int k8s = 0; k8s < BKT / UMMA_K; ++k8s) {
+                            const int sub = k8s / (SUB / UMMA_K), k8 = k8s % (SUB / UMMA_K);
                             // K-major: step 32 bytes inside the 128-byte swizzle row.
                             // MN-major: step 8 k-rows (two 4-row swizzle groups, 8 * 128 bytes).
-                            const uint32_t a_off = MAJA == 0 ? k8 * 32 : k8 * 1024;
-                            const uint32_t b_off = MAJB == 0 ? k8 * 32 : k8 * 1024;
-                            // K-major rows are BKT * 4 bytes (128- or 64-byte swizzle), 8 rows per group.
-                            constexpr uint32_t K_LAY = BKT == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
-                            constexpr uint32_t K_SBO = 8 * BKT * 4;
-                            const uint32_t a_lbo = MAJA == 0 ? 16 : BKT * 128;
-                            const uint32_t b_lbo = MAJB == 0 ? 16 : BKT * 128;
+                            const uint32_t a_off = sub * A_SUB_BYTES + (MAJA == 0 ? k8 * 32 : k8 * 1024);
+                            const uint32_t b_off = sub * B_SUB_BYTES + (MAJB == 0 ? k8 * 32 : k8 * 1024);
+                            // K-major rows are SUB * 4 bytes (128- or 64-byte swizzle), 8 rows per group.
+                            constexpr uint32_t K_LAY = SUB == 32 ? ptx::LAYOUT_SW128 : ptx::LAYOUT_SW64;
+                            constexpr uint32_t K_SBO = 8 * SUB * 4;
+                            const uint32_t a_lbo = MAJA == 0 ? 16 : SUB * 128;
+                            const uint32_t b_lbo = MAJB == 0 ? 16 : SUB * 128;
                             const uint32_t a_sbo = MAJA == 0 ? K_SBO : 512;
                             const uint32_t b_sbo = MAJB == 0 ? K_SBO : 512;
                             constexpr uint32_t a_lay = MAJA == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
                             constexpr uint32_t b_lay = MAJB == 0 ? K_LAY : ptx::LAYOUT_SW128_ATOM32B;
                             const uint64_t da = ptx::smem_desc(sa + a_off, a_lbo, a_sbo, a_lay);
                             const uint64_t db = ptx::smem_desc(sb + b_off, b_lbo, b_sbo, b_lay);
-                            const uint32_t first = (it == cs && k8 == 0) ? 0u : 1u;
+                            const uint32_t first = (it == cs && k8s == 0) ? 0u : 1u;
                             if (AKR_DIAG(p.debug, 2)) {
-                                if (k8 == 0 && it == cs) ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, 0u);
+                                if (k8s == 0 && it == cs) ptx::mma_tf32_ss_elected(issuer, d_tmem, da, db, IDESC, 0u);
                             } else if (TERMS == 3) {
                                 const uint64_t da_lo = ptx::smem_desc(sa_lo + a_off, a_lbo, a_sbo, a_lay);
                                 const uint64_t db_lo = ptx::smem_desc(sb_lo + b_off, b_lbo, b_sbo, b_lay);
@@ -2792,17 +2802,23 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
     // moves twice as many rows per byte and the ring hands over twice as often (config 3's dA, N = 64: 0.216 -> 0.158
     // ms; 65536 x 128 x 1024: 0.138 -> 0.112 ms). 256-wide tiles have no room for 32-deep raw stages plus low-part slots.
     const bool fp32_wide_k = g.terms == 3 && !pairs && pick_bn(g) <= 128;
-    const int bk = (g.terms == 3 && pairs) ? PAIR_BK : (((g.terms == 3 && !fp32_wide_k) || fine) ? 16 : BK);
+    // TF32 tiles of 128 columns take 64-deep k-blocks (two 32-deep sub-tiles per operand) from a contraction of 512:
+    // their MMAs take 64 cycles, and a stage of four of them is over before it has been handed over (16384 x 128 x
+    // 4096: 0.0545 -> 0.0534 ms; 4096 x 128 x 16384: 0.0609 -> 0.0593 ms). Shorter contractions want the extra stages
+    // of the 32-deep ring, and 64-column tiles measured the same either way.
+    const bool tf32_deep_k = g.terms == 1 && !pairs && !big && pick_bn(g) == 128 && g.K >= 512 && !AKR_DIAG(gd.debug, 2097152);
+    const int bk = (g.terms == 3 && pairs) ? PAIR_BK : (tf32_deep_k ? 64 : (((g.terms == 3 && !fp32_wide_k) || fine) ? 16 : BK));
 
     KernelParams kp;
     std::memset(&kp, 0, sizeof(kp));
     MapPlan pa = plan_map(g.A, g.M, batch, !AKR_DIAG(g.debug, 4));
     MapPlan pb = plan_map(g.B, g.N, batch, !AKR_DIAG(g.debug, 4));
+    const int box_k = bk > 32 ? 32 : bk;  // a deeper k-block is fetched as 32-deep sub-tiles
     auto build = [&](CUtensorMap* map, const GemmOperand& op, MapPlan& mp, int mn, int tile) {
-        bool ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, bk);
+        bool ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, box_k);
         if (!ok && mp.fold) {  // the folded form is an optimisation: fall back to one box per chunk
             mp.fold = false;
-            ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, bk);
+            ok = make_map(map, op.ptr, op, mp, mn, g.K, tile, box_k);
         }
         return ok;
     };
@@ -2958,6 +2974,8 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
                          : launch_major<64, 3, 6, 2, 32, 2>(g, kp, grid, stream, err, errlen);
     } else if (bn == 64) {
         rc = launch_major<64, 1, 8, 0, 32>(g, kp, grid, stream, err, errlen);
+    } else if (bn == 128 && tf32_deep_k) {
+        rc = launch_major<128, 1, 3, 0, 64>(g, kp, grid, stream, err, errlen);
     } else {
         // Short contractions are write-heavy: three stages are plenty and leave room for a second set of
         // epilogue staging tiles.

@@ -585,6 +585,35 @@ def test_tf32_tall_pair_tile_kernel_parity():
     assert rel_fro(db.to_numpy()[krows], a[:, krows].astype(np.float64).T @ dc.astype(np.float64)) < TOL_TF32
 
 
+def test_tf32_128_column_tiles_with_64_deep_stages():
+    # TF32 products whose output is 65..128 columns wide and whose contraction is at least 512 run 128 x 128 tiles
+    # with 64-deep stages made of two 32-deep sub-tiles. Contraction tails that end in the first sub-tile (K % 64 in
+    # 1..32: the second one is all zero fill), in the second one, and none; the four operand layouts; a batch; bias.
+    rng = np.random.default_rng(191)
+    def check(bt, M, N, K, ta, tb, with_bias=False):
+        a = uniform(bt + ((K, M) if ta else (M, K)), int(rng.integers(1 << 30)))
+        b = uniform(bt + ((N, K) if tb else (K, N)), int(rng.integers(1 << 30)))
+        A, B = dev(a), dev(b)
+        nd = len(bt) + 2
+        Av = A.transpose(nd - 2, nd - 1) if ta else A
+        Bv = B.transpose(nd - 2, nd - 1) if tb else B
+        bias = normal((1, N), 192) if with_bias else None
+        c = cabi.matmul_fwd(Av, Bv, bias=dev(bias) if with_bias else None, mode=MODE_TF32).to_numpy()
+        an = np.swapaxes(a, -1, -2) if ta else a
+        bn = np.swapaxes(b, -1, -2) if tb else b
+        ref = np.matmul(an.astype(np.float64), bn.astype(np.float64))
+        if with_bias:
+            ref = ref + bias
+        assert rel_fro(c, ref) < TOL_TF32, (bt, M, N, K, ta, tb)
+    for ta in (0, 1):
+        for tb in (0, 1):
+            for K in (512, 516, 544, 548, 1000):          # K must be a multiple of 4 only for M-major operands
+                check((), 300, 128 if tb == 0 else 100, K, ta, tb)
+    check((), 1000, 100, 513, 0, 1)                       # a one-element tail (K-major operands have no stride rule)
+    check((5,), 260, 96, 800, 0, 0, with_bias=True)
+    check((), 40000, 128, 576, 0, 0)                      # more tiles than CTAs: the ring and TMEM halves wrap
+
+
 def test_clock_probe_reports_the_sm_clock_of_a_launch():
     # akr_debug_configure(32768): every CTA records cycles and nanoseconds; the ratio is the SM clock the kernel ran
     # at (B200: at most 1965 MHz), the cycle count is at least what the MMAs alone need; the product stays correct.
