@@ -1296,17 +1296,23 @@ gemm_tf32_big_kernel(const __grid_constant__ KernelParams p) {
 constexpr int PAIR_BM = 256, PAIR_BN = 256, PAIR_BK = 32, PAIR_KC = 64 / PAIR_BK;
 constexpr int PAIR_A_BYTES = 128 * PAIR_BK * 4, PAIR_B_BYTES = 128 * PAIR_BK * 4;
 constexpr int PAIR_RAW_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
-// The tiles are laid out as PAIR_RAW_STAGES raw stages followed by PAIR_LO_SLOTS low-part slots (16 KB each): a
-// low-part tile only lives from its conversion to the end of its MMAs. Six slots, not fewer: a slot's round trip
-// crosses the cluster twice (the peer's "written" arrive, the leader's commit back) and takes several microseconds.
-constexpr int PAIR_RAW_STAGES = 96 / PAIR_BK, PAIR_LO_SLOTS = 96 / PAIR_BK;
+// The tiles are laid out as PAIR_RAW_STAGES raw stages followed by LS low-part slots (32 KB each): a low-part tile
+// only lives from its conversion to the end of its MMAs, but a slot's round trip crosses the cluster twice (the peer's
+// "written" arrive, the leader's commit back). LS = 3 and one set of output staging tiles for long contractions;
+// LS = 2 and two sets (staging a box overlaps the TMA unit reading the one before) for short ones, where the output
+// is a large share of the bytes: 8192 products of 256^3 1.44 -> 1.37 ms, 8192^3 280 -> 275 TFLOP/s the other way.
+constexpr int PAIR_RAW_STAGES = 96 / PAIR_BK;
+constexpr int PAIR_SMEM_TILES = 7 * PAIR_RAW_BYTES;  // raw stages + low-part slots + staging sets, either way
 constexpr int PAIR_BAR_BYTES = 512;  // 32 mbarriers + TMEM slot + flags
 constexpr int PAIR_THREADS = 64 + 256 + 64;
 constexpr int PAIR_EPI_WARPS = 8, PAIR_CONV_WARPS = 2;
 
-template <int MAJA, int MAJB>
+template <int MAJA, int MAJB, int PAIR_LO_SLOTS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
+    constexpr int PAIR_EPI_SETS = PAIR_LO_SLOTS == 2 ? 2 : 1;
+    static_assert((PAIR_RAW_STAGES + PAIR_LO_SLOTS) * PAIR_RAW_BYTES + PAIR_EPI_SETS * PAIR_EPI_WARPS * EPI_STAGE_BYTES == PAIR_SMEM_TILES,
+                  "both layouts fill the same shared memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -1317,8 +1323,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     constexpr int TILE_BYTES = (S + LS) * PAIR_RAW_BYTES;
     constexpr int LO_BASE = S * PAIR_RAW_BYTES;
     constexpr int stage_bytes = PAIR_RAW_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TILE_BYTES);
-    const uint32_t bar_base = smem_base + TILE_BYTES;
+    // [raw stages][low-part slots][staging: two slabs of 128 rows x 128 bytes, 1024-byte aligned][barriers]
+    constexpr int STAGING_BYTES = PAIR_EPI_SETS * PAIR_EPI_WARPS * EPI_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TILE_BYTES + STAGING_BYTES);
+    const uint32_t bar_base = smem_base + TILE_BYTES + STAGING_BYTES;
     auto landed_bar = [&](int s) { return bar_base + 8u * s; };            // local: this CTA's TMA tiles arrived (0..7)
     auto empty_bar = [&](int s) { return bar_base + 8u * (8 + s); };       // local: stage may be refilled (8..15)
     // leader: the low parts of both CTAs are written, per low-part slot (16..21)
@@ -1328,7 +1336,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
     auto lofree_bar = [&](int l) { return bar_base + 8u * (26 + l); };     // local: low-part slot may be rewritten (26..31)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint8_t* epi_stage_base = smem + TILE_BYTES + PAIR_BAR_BYTES;
+    uint8_t* epi_stage_base = smem + TILE_BYTES;
 
     // Roles by hardware warp: 0..7 epilogue, 8 producer, 9 MMA, 10..11 converters, so that the two epilogue
     // warpgroups can take the registers the third one gives back. `warp` is the role index used below
@@ -1357,6 +1365,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&p.tmA);
         ptx::prefetch_tensormap(&p.tmB);
+        if (p.c_tma) ptx::prefetch_tensormap(&p.tmC);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair<512>(ptx::smem_u32(tmem_slot));
@@ -1557,7 +1566,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                     ok = false;
                     break;
                 }
-                {
+                if (!AKR_DIAG(p.debug, 4)) {  // bit 2: hand-shakes only, stale low parts (timing experiment)
                     const float4* src = reinterpret_cast<const float4*>(smem + stage * PAIR_RAW_BYTES);
                     float4* dst = reinterpret_cast<float4*>(smem + LO_BASE + slot * PAIR_RAW_BYTES);
                     constexpr int PER_THREAD = PAIR_RAW_BYTES / 16 / (PAIR_CONV_WARPS * 32);
@@ -1603,12 +1612,25 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
         const int slab = (warp - 2) >> 2;
         const bool split_mode = p.splits > 1;  // partial tiles to scratch, added up by the reduction kernel
         const bool vec = split_mode ? (p.N & 3) == 0 : p.vec_ok != 0;
+        // Aligned plain outputs leave through TMA: the four warps of a slab stage a 128-row box of 32 columns and are
+        // free again once the TMA unit has read it. With st.global the eight warps spent 9 of a tile's 22 kilocycles
+        // in the stores (8192 products of 256^3: every SM writes its 128 KB at the same moment), longer than the two
+        // chains the MMAs may run ahead of the promotion.
+        const bool use_tma = p.c_tma != 0 && !split_mode;
         float4* my_stage = reinterpret_cast<float4*>(epi_stage_base + (warp - 2) * EPI_STAGE_BYTES);
+        const uint32_t slab_tile_addr = smem_base + TILE_BYTES + slab * 4 * EPI_STAGE_BYTES;
+        constexpr int EPI_ALT = PAIR_EPI_WARPS * EPI_STAGE_BYTES;  // offset of the second set of staging tiles
+        int epi_buf = 0;
         int handoff = 0;
         bool ok = true;
+#ifdef AKR_B200_DIAG
+        long long diag_store = 0;
+        const long long diag_e0 = clock64();
+#endif
         for (int t = pair_id; t < p.total_tiles && ok; t += num_pairs) {
             const Tile c = decode_tile(t, p, PAIR_BN, PAIR_BM);
-            const int row0 = c.m0 + 128 * (int)rank + q * 32;
+            const int row_base = c.m0 + 128 * (int)rank;
+            const int row0 = row_base + q * 32;
             const int slab_col0 = c.n0 + slab * 128;
             float* out_base = split_mode ? p.partials + ((size_t)c.split * (p.o0 * p.o1) + c.batch) * (size_t)p.M * (size_t)p.N
                                          : p.C + c.i0 * p.c_bs0 + c.i1 * p.c_bs1;
@@ -1641,23 +1663,81 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(buf), 0));
                 ++handoff;
             }
-            if (ok) {
+#ifdef AKR_B200_DIAG
+            const long long diag_s0 = clock64();
+#endif
+            if (use_tma) ok = ptx::named_barrier_and(2 + slab, 128, ok);  // a slab's four warps store together or not at all
+            if (ok && use_tma) {
+                if (row_base < p.M) {  // CTA-uniform: the peer's half may lie below the matrix
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        const int col0 = slab_col0 + ch * 32;
+                        if (col0 < p.N) {  // slab-uniform
+                            float f[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
+                            store_block_tma<PAIR_EPI_SETS>(f, my_stage + epi_buf * (EPI_ALT / 16), slab_tile_addr + epi_buf * EPI_ALT,
+                                                           &p.tmC, col0, row_base, c.i1, c.i0, p.N, p.bias, lane,
+                                                           q == 0 && lane == 0, 2 + slab);
+                            if (PAIR_EPI_SETS == 2) epi_buf ^= 1;
+                        }
+                    }
+                }
+            } else if (ok) {
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     const int col0 = slab_col0 + ch * 32;
-                    if (col0 < p.N) {
+                    if (col0 < p.N && !(AKR_DIAG(p.debug, 128) && acc[ch * 32] != 12345.f)) {  // bit 7: no stores (timing experiment)
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
+#ifdef AKR_B200_DIAG
+                        if (AKR_DIAG(p.debug, 1024)) {  // timing experiment: the global stores alone (values in the wrong places)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int grow = row0 + 4 * i + (lane >> 3);
+                                if (grow < p.M)
+                                    *reinterpret_cast<float4*>(out_base + (long long)grow * p.ldc + col0 + 4 * (lane & 7)) =
+                                        make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                            }
+                            continue;
+                        }
+                        if (AKR_DIAG(p.debug, 2048)) {  // timing experiment: the staging round trip alone
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                my_stage[lane * 8 + (j ^ (lane & 7))] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+                            __syncwarp();
+                            float sum = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = 4 * i + (lane >> 3);
+                                const float4 x = my_stage[r * 8 + ((lane & 7) ^ (r & 7))];
+                                sum += x.x + x.y + x.z + x.w;
+                            }
+                            if (sum == 12345.678f) out_base[0] = sum;
+                            __syncwarp();
+                            continue;
+                        }
+#endif
                         store_block_warp<false>(f, my_stage, out_base, split_mode ? (long long)p.N : p.ldc, row0, p.M, col0, p.N, vec,
                                                 split_mode ? plain_epi() : lean_epi(p), lane);
                     }
                 }
             }
+#ifdef AKR_B200_DIAG
+            diag_store += clock64() - diag_s0;
+#endif
         }
+#ifdef AKR_B200_DIAG
+        if (AKR_DIAG(p.debug, 262144) && hw_warp == 0 && lane == 0 && blockIdx.x < 256) {  // bit 18: cycles in the stores
+            g_clock_probe[2 * blockIdx.x] = diag_store;
+            g_clock_probe[2 * blockIdx.x + 1] = clock64() - diag_e0;
+        }
+#endif
     }
 
     // ------------------------------------------------------------ teardown (all paths)
+    if (p.c_tma != 0 && hw_warp < 8 && (hw_warp & 3) == 0 && lane == 0) ptx::bulk_wait_read_all();
     ptx::tc_fence_before();
     __syncthreads();
     ptx::cluster_sync_all();  // no remote arrive or MMA of the pair is still in flight
@@ -2487,16 +2567,17 @@ int launch_big_variant(const KernelParams& kp, int grid, cudaStream_t stream, ch
 #endif
 
 // The three kernels on CTA pairs: the fp32-accurate one, TF32 with 256 x 256 tiles, TF32 with 512 x 256 tiles.
-enum PairKind { PAIR_FP32 = 0, PAIR_DUO = 1, PAIR_QUAD = 2 };
+enum PairKind { PAIR_FP32 = 0, PAIR_DUO = 1, PAIR_QUAD = 2, PAIR_FP32_SHORT = 3 };
 template <int KIND, int MAJA, int MAJB, int BKT = BK>
 int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, char* err, int errlen) {
     constexpr int smem = KIND == PAIR_QUAD ? QUAD_SMEM
                          : KIND == PAIR_DUO
                              ? DUO_SMEM
-                             : (PAIR_RAW_STAGES + PAIR_LO_SLOTS) * PAIR_RAW_BYTES + 1024 + PAIR_BAR_BYTES + PAIR_EPI_WARPS * EPI_STAGE_BYTES;
+                             : PAIR_SMEM_TILES + 1024 + PAIR_BAR_BYTES;
     constexpr int threads = KIND == PAIR_QUAD ? QUAD_THREADS : (KIND == PAIR_DUO ? DUO_THREADS : PAIR_THREADS);
     auto kern = KIND == PAIR_QUAD ? gemm_tf32_quad_kernel<MAJA, MAJB, BKT>
-                                  : (KIND == PAIR_DUO ? gemm_tf32_duo_kernel<MAJA, MAJB> : gemm_tf32_pair_kernel<MAJA, MAJB>);
+                                  : (KIND == PAIR_DUO ? gemm_tf32_duo_kernel<MAJA, MAJB>
+                                                      : gemm_tf32_pair_kernel<MAJA, MAJB, (KIND == PAIR_FP32_SHORT ? 2 : 3)>);
     static bool attr_done_dev[kMaxDev] = {};
     bool& attr_done = attr_done_dev[cur_dev()];
     if (!attr_done) {
@@ -2872,7 +2953,7 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
         seterr(err, errlen, "gemm_sm100: column sums of the output are produced by the TF32 kernels without a split contraction only");
         return -1;
     }
-    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && (!pairs || duo || quad) && g.colpart == nullptr &&
+    if (kp.vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && kp.splits == 1 && g.colpart == nullptr &&
         !AKR_DIAG(g.debug | g_debug_flags, 256)) {
         EncodeTiledFn enc = get_encode_fn();
         const uint64_t ldc_b = (uint64_t)(g.M > 1 ? g.ldc : ((g.N + 3) / 4) * 4) * 4;
@@ -2937,6 +3018,17 @@ int gemm_sm100_launch(const GemmDesc& g, cudaStream_t stream, int* status_dev, c
             return launch_split_reduce(g, kp, stream, err, errlen);
         }
         int rcp;
+        // contractions of at most 512 that store through TMA: two low-part slots, two sets of staging tiles
+        const bool short_pair = kp.c_tma != 0 && (long long)kp.red * kp.nkb <= 16 && !AKR_DIAG(gd.debug, 4194304);
+        if (short_pair) {
+            switch (sel) {
+                case 0: rcp = launch_pair_variant<PAIR_FP32_SHORT, 0, 0>(kp, 2 * npairs, stream, err, errlen); break;
+                case 1: rcp = launch_pair_variant<PAIR_FP32_SHORT, 0, 1>(kp, 2 * npairs, stream, err, errlen); break;
+                case 2: rcp = launch_pair_variant<PAIR_FP32_SHORT, 1, 0>(kp, 2 * npairs, stream, err, errlen); break;
+                default: rcp = launch_pair_variant<PAIR_FP32_SHORT, 1, 1>(kp, 2 * npairs, stream, err, errlen); break;
+            }
+            return rcp;
+        }
         switch (sel) {
             case 0: rcp = launch_pair_variant<PAIR_FP32, 0, 0>(kp, 2 * npairs, stream, err, errlen); break;
             case 1: rcp = launch_pair_variant<PAIR_FP32, 0, 1>(kp, 2 * npairs, stream, err, errlen); break;

@@ -512,6 +512,37 @@ def test_experimental_cta_pair_kernel_parity():
         cabi.check(lib.akr_debug_configure(0, 0))
 
 
+def test_fp32_pair_kernel_short_contractions_store_through_tma():
+    # fp32-accurate products on CTA pairs with a contraction of at most 512 run the layout with two low-part slots
+    # and two sets of output staging tiles, and aligned plain outputs leave through TMA boxes of 128 rows x 32
+    # columns: ragged edges in M and N (a last pair whose second CTA has no rows, a last box of 4 columns), the four
+    # operand layouts, batches, bias; an output whose row length is no multiple of 4 (plain stores instead).
+    rng = np.random.default_rng(291)
+    def check(bt, M, N, K, ta, tb, with_bias=False):
+        a = uniform(bt + ((K, M) if ta else (M, K)), int(rng.integers(1 << 30)))
+        b = uniform(bt + ((N, K) if tb else (K, N)), int(rng.integers(1 << 30)))
+        A, B = dev(a), dev(b)
+        nd = len(bt) + 2
+        Av = A.transpose(nd - 2, nd - 1) if ta else A
+        Bv = B.transpose(nd - 2, nd - 1) if tb else B
+        bias = normal((1, N), 292) if with_bias else None
+        c = cabi.matmul_fwd(Av, Bv, bias=dev(bias) if with_bias else None, mode=MODE_FP32).to_numpy()
+        an = np.swapaxes(a, -1, -2) if ta else a
+        bn = np.swapaxes(b, -1, -2) if tb else b
+        ref = np.matmul(an.astype(np.float64), bn.astype(np.float64))
+        if with_bias:
+            ref = ref + bias
+        assert rel_fro(c, ref) < TOL_FP32, (bt, M, N, K, ta, tb)
+    for ta in (0, 1):
+        for tb in (0, 1):
+            check((), 1400, 1796, 288, ta, tb)            # 6 x 8 tiles; 1400 = 5 x 256 + 120: the last pair's second CTA is empty
+    check((), 1536, 1800, 512, 0, 0, with_bias=True)      # 16 k-blocks: the longest contraction of this layout
+    check((), 1536, 1800, 544, 0, 0, with_bias=True)      # 17 k-blocks: three low-part slots, one set of staging tiles
+    check((48,), 256, 256, 256, 0, 0)                     # one tile per batch entry
+    check((3, 4), 300, 520, 256, 0, 1)
+    check((), 1400, 1798, 288, 0, 0)                      # rows of 1798 floats are not 16-byte aligned: plain stores
+
+
 def test_tf32_cta_pair_kernel_parity():
     # TF32 products on CTA pairs (cta_group::2, one 256 x 256 tile per pair): ragged edges, all four
     # operand layouts, bias, C +=, broadcast batches and a summed batch dim (weight gradient), with the
