@@ -1691,34 +1691,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ KernelParams p) {
                         float f[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) f[j] = acc[ch * 32 + j];
-#ifdef AKR_B200_DIAG
-                        if (AKR_DIAG(p.debug, 1024)) {  // timing experiment: the global stores alone (values in the wrong places)
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int grow = row0 + 4 * i + (lane >> 3);
-                                if (grow < p.M)
-                                    *reinterpret_cast<float4*>(out_base + (long long)grow * p.ldc + col0 + 4 * (lane & 7)) =
-                                        make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                            }
-                            continue;
-                        }
-                        if (AKR_DIAG(p.debug, 2048)) {  // timing experiment: the staging round trip alone
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                my_stage[lane * 8 + (j ^ (lane & 7))] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-                            __syncwarp();
-                            float sum = 0.f;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int r = 4 * i + (lane >> 3);
-                                const float4 x = my_stage[r * 8 + ((lane & 7) ^ (r & 7))];
-                                sum += x.x + x.y + x.z + x.w;
-                            }
-                            if (sum == 12345.678f) out_base[0] = sum;
-                            __syncwarp();
-                            continue;
-                        }
-#endif
                         store_block_warp<false>(f, my_stage, out_base, split_mode ? (long long)p.N : p.ldc, row0, p.M, col0, p.N, vec,
                                                 split_mode ? plain_epi() : lean_epi(p), lane);
                     }
