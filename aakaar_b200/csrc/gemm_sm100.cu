@@ -146,9 +146,19 @@ __host__ __device__ constexpr int slab_cols(int bn) { return bn >= 128 ? 128 : b
 
 // Threads of one CTA: producer warp, MMA warp and one epilogue warp per (TMEM lane quarter,
 // 128-column slab of the tile).
-// plus, in the fp32-accurate mode, two converter warps that derive the low parts in shared memory.
+// plus, in the fp32-accurate mode, the converter warps that derive the low parts in shared memory: two beside the
+// eight epilogue warps of a 256-column tile, six (four) beside the four epilogue warps of a 64- (128-) column one -
+// on an HBM-bound shape with a 64-column output two converter warps took 1190 cycles per 24 KB k-block with loads,
+// MMAs and stores all switched off, more than the 1040 cycles its bytes take from HBM (512 products of 512 x 64 x 512:
+// 0.158 ms with two, 0.146 with four, 0.137 with six, 0.143 with eight; 16384 x 128 x 4096: 0.110 ms with two, 0.098
+// with four. Eight beside a 128-column tile - fourteen warps - never finished and is not to be tried again: at launch
+// 448 threads x 144 registers leave the register file no room for the hand-over of setmaxnreg).
 template <int BN, int TERMS = 1>
-constexpr int num_threads() { return 64 + slabs_of(BN) * 128 + (TERMS == 3 ? 64 : 0); }
+__host__ __device__ constexpr int conv_warps() {
+    return TERMS == 3 ? (BN <= 64 ? 6 : (BN == 128 ? 4 : 2)) : 0;
+}
+template <int BN, int TERMS = 1>
+constexpr int num_threads() { return 64 + slabs_of(BN) * 128 + conv_warps<BN, TERMS>() * 32; }
 
 // Bytes of shared memory each epilogue warp uses to turn "one row per lane" into coalesced stores.
 constexpr int EPI_STAGE_BYTES = 32 * 128;
@@ -450,7 +460,7 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     constexpr int SLABS = slabs_of(BN);
     constexpr int SLAB_W = slab_cols(BN);
     constexpr int EPI_WARPS = SLABS * 4;
-    constexpr int CONV_WARPS = TERMS == 3 ? 2 : 0;
+    constexpr int CONV_WARPS = conv_warps<BN, TERMS>();
     constexpr int CHUNK_ITERS = KC > 0 ? KC : 0x7fffffff;
     constexpr int TMEM_COLS = 2 * BN;  // two accumulators
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM allocation must be a power of two");
@@ -484,13 +494,14 @@ gemm_tf32_kernel(const __grid_constant__ KernelParams p) {
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
     // `warp` is the role index: 0 producer, 1 MMA, 2 .. 2+EPI_WARPS-1 epilogue, then the converters. The
-    // fp32-accurate 256-wide instantiation has twelve warps, capped at 168 registers each unless the epilogue
-    // warps (128 promotion accumulators per thread) sit in warpgroups of their own and take registers the
-    // third warpgroup gives back: there hardware warps 0..7 are the epilogue, 8 the producer, 9 the MMA warp,
-    // 10..11 the converters.
-    constexpr bool REMAP = TERMS == 3 && BN == 256;
+    // fp32-accurate 256- and 128-wide instantiations have more than eight warps, capped at 168 registers each unless
+    // the epilogue warps (128 promotion accumulators per thread) sit in warpgroups of their own and take registers
+    // the other warpgroups give back: there the first EPI_WARPS hardware warps are the epilogue, the next two the
+    // producer and the MMA warp, the rest the converters.
+    constexpr bool REMAP = TERMS == 3 && BN >= 128;
     const int hw_warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // warp-uniform for the compiler too
-    const int warp = !REMAP ? hw_warp : (hw_warp < 8 ? hw_warp + 2 : (hw_warp < 10 ? hw_warp - 8 : hw_warp));
+    const int warp = !REMAP ? hw_warp
+                            : (hw_warp < EPI_WARPS ? hw_warp + 2 : (hw_warp < EPI_WARPS + 2 ? hw_warp - EPI_WARPS : hw_warp));
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
