@@ -2606,11 +2606,19 @@ int launch_pair_variant(const KernelParams& kp, int grid, cudaStream_t stream, c
     return 0;
 }
 
+// An output every kernel can store through TMA boxes: 16-byte aligned rows, nothing added to or applied on the product.
+bool plain_aligned_output(const GemmDesc& g) {
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(g.C) & 15u) == 0 && (g.ldc & 3) == 0 && (g.o0 == 1 || (g.c_bs0 & 3) == 0) &&
+                        (g.o1 == 1 || (g.c_bs1 & 3) == 0);
+    return vec_ok && !g.accumulate && g.aux_op == 0 && g.alpha == 1.f && g.splits <= 1 && g.colpart == nullptr;
+}
+
 // CTA pairs serve the fp32-accurate mode wherever 256 x 256 tiles fill a good part of the machine and the
 // contraction is long enough to amortise the pair's hand-shakes: each CTA reads only half of B per MMA and converts
 // only its own share, which is what this shared-memory-bound mode needs (2560^3: 0.253 -> 0.183 ms, 4096 x 1024 x
 // 4096: 0.185 -> 0.147 ms, 64 x (512 x 512 x 2048): 0.369 -> 0.312 ms against one CTA per 128 x 256 tile). Short
-// contractions (below 256) stay with the general kernel. Debug bit 5 routes every eligible shape here.
+// contractions (below 256; below 64 when the output can leave through TMA) stay with the general kernel. Debug bit 5
+// routes every eligible shape here.
 bool use_pairs(const GemmDesc& g) {
     if (g.terms != 3 || g.M <= 128 || g.N <= 128 || AKR_DIAG(g.debug, 512)) return false;
     // split contractions too, when a reduction kernel adds the partial tiles up (no tile counters)
@@ -2620,8 +2628,10 @@ bool use_pairs(const GemmDesc& g) {
     if (tiles * 4 < gemm_sm100_num_ctas()) return false;
     const long long iters = (long long)g.red * ((g.K + PAIR_BK - 1) / PAIR_BK);
     // Contractions of 256 and more (8 k-blocks): 8192 x 256^3 4.5 against 5.1 ms per fwd + dA + dB step, 1024 x 512 x 512 x
-    // 256 2.0 against 2.1-2.4 ms; at 128 the two kernels are level.
-    return iters >= 8 || (g.debug & 32);
+    // 256 2.0 against 2.1-2.4 ms; at 128 the two kernels were level while the pair kernel stored with st.global. With
+    // its output leaving through TMA boxes it wins from a contraction of 64 on (512 x (512 x 512 x K), K = 64 / 96 /
+    // 128 / 200: 0.135 -> 0.127, 0.184 -> 0.160, 0.222 -> 0.193, 0.318 -> 0.286 ms; 8192 x 8192 x 128: 0.108 -> 0.091).
+    return iters >= 8 || (iters >= 2 && plain_aligned_output(g)) || (g.debug & 32);
 }
 
 // TF32 mode on CTA pairs (256 x 256 tiles, eight MMAs per 64-deep stage, the epilogue of a tile overlapping the next

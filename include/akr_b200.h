@@ -243,7 +243,7 @@ AKR_API int akr_event_destroy(void* event);
  *       tcgen05.mma issue rate alone (the measured tensor-pipe ceiling a benchmark divides by); results invalid
  *   16  the load warp never signals its stages, so that every waiter gives up (failure-path test)
  *   32  fp32-accurate products run on the CTA-pair (cta_group::2) kernel wherever its tiles apply
- *       (by default contractions of at least 256 and enough 256 x 256 tiles to fill a quarter of the GPU)
+ *       (by default contractions of at least 256 - at least 64 for aligned plain outputs - and enough 256 x 256 tiles to fill a quarter of the GPU)
  * 2048  TF32 products run on the CTA-pair kernel wherever it applies (by default a band of shapes)
  * 32768 clock probe: every CTA of a GEMM launch records the SM cycles and the nanoseconds it ran for
  *       (read with akr_gemm_clock_read)

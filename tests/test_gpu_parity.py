@@ -536,6 +536,7 @@ def test_fp32_pair_kernel_short_contractions_store_through_tma():
     for ta in (0, 1):
         for tb in (0, 1):
             check((), 1400, 1796, 288, ta, tb)            # 6 x 8 tiles; 1400 = 5 x 256 + 120: the last pair's second CTA is empty
+            check((), 1400, 1796, 64 + 36 * ta + 8 * tb, ta, tb)  # the shortest contractions the pair kernel takes (two or three k-blocks)
     check((), 1536, 1800, 512, 0, 0, with_bias=True)      # 16 k-blocks: the longest contraction of this layout
     check((), 1536, 1800, 544, 0, 0, with_bias=True)      # 17 k-blocks: three low-part slots, one set of staging tiles
     check((48,), 256, 256, 256, 0, 0)                     # one tile per batch entry
